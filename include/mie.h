@@ -1,0 +1,205 @@
+/*
+ * libmie -- masked incremental inference kernels for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * This is the native boundary of the library.  It replaces the reference's pybind11 module
+ * `pointops_ext` (ext/pointops/_C_ext/pointops/ops.cpp:117-123) and the elementwise PyTorch code the
+ * reference runs around it (incr_modules/mask_incr_functional.py, incr_modules/mask_incr_modules.py).
+ *
+ * Conventions shared by every entry point
+ *  - every pointer is a DEVICE pointer unless its comment says "host"; the library allocates
+ *    nothing, owns nothing and keeps no state between calls (one exception is declared as such);
+ *  - tensors are fp32, NCHW-logical and channels-last in memory: element (n,y,x,c) of a field lives
+ *    at base[((n*H + y)*W + x)*ps + c]; `ps` (pixel stride, in floats) >= C lets a field be a channel
+ *    slice of a wider buffer;
+ *  - a *delta field* is such a tensor plus one 64-bit word per 8x8 tile (`bits`, N*TH*TW words,
+ *    TH=ceil(H/8), TW=ceil(W/8), tile index (n*TH+ty)*TW+tx): bit (py*8+px) is set when pixel
+ *    (ty*8+py, tx*8+px) is active.  Invariant kept by every kernel: the tensor is exactly 0 at
+ *    every pixel whose bit is clear;
+ *  - `stream` is a cudaStream_t passed as void*; kernels are enqueued, never synchronised;
+ *  - the return value is MIE_OK or a negative MIE_E* code; nothing ever calls exit() or traps
+ *    the device (the reference's CUDA_CHECK_ERRORS does, include/checks.h:12-21).
+ */
+#ifndef MIE_H
+#define MIE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MIE_OK = 0,
+  MIE_EINVAL = -1,      /* bad argument (null pointer, non-positive size, unsupported k/stride) */
+  MIE_EALIGN = -2,      /* pointer or stride not aligned as the entry point requires */
+  MIE_EUNSUPPORTED = -3,/* valid but not implemented combination */
+  MIE_ECUDA = -4,       /* a CUDA runtime call failed; see mie_last_cuda_error() */
+  MIE_ETOOBIG = -5      /* size beyond a fixed capacity */
+};
+
+enum { MIE_ACT_NONE = 0, MIE_ACT_RELU = 1, MIE_ACT_SIGMOID = 2, MIE_ACT_TANH = 3 };
+enum { MIE_UP_BILINEAR = 0, MIE_UP_NEAREST = 1 };
+
+int mie_version(void);
+const char *mie_status_string(int status);
+/* host: text of the last CUDA error seen by this thread inside the library */
+const char *mie_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Active-tile compaction.
+ * No counterpart runs in the reference: it returns None for every mask
+ * (incr_modules/mask_incr_modules.py:178) and discards the caller's (pointops_functional.py:22);
+ * the expression this follows is compute_mask (incr_modules/utils.py:22-25) with a 1x1 field.
+ * ------------------------------------------------------------------------------------------- */
+
+/* bits <- per-pixel any_c(|delta| > thr), strict.  Writes all N*TH*TW words. */
+int mie_mask_from_delta(const float *delta, int64_t ps, int N, int C, int H, int W, float thr,
+                        uint64_t *bits, void *stream);
+
+/* bits <- per-pixel any_c(mask != 0) from an explicit mask tensor with `cm` channels per pixel
+ * (1 for an [N,1,H,W] mask), channels-last, elements of `elem_size` bytes (1: bool/uint8, 4: int32 as
+ * the reference's kernels take, ext_conv.cu:238).  `mps` = pixel stride in elements. */
+int mie_mask_from_mask(const void *mask, int elem_size, int64_t mps, int cm, int N, int H, int W,
+                       uint64_t *bits, void *stream);
+
+/* list[0..count) <- ascending indices of tiles whose word is non-zero; counts[0] <- count. */
+int mie_tiles_compact(const uint64_t *bits, int ntiles, int32_t *list, int32_t *counts, void *stream);
+
+/* bytes[N*H*W] <- 0/1 per pixel, expanded from the tile words. */
+int mie_mask_expand(const uint64_t *bits, int N, int H, int W, uint8_t *bytes, void *stream);
+
+/* Output-tile set of a k x k / stride / pad convolution: an output tile is active when the
+ * receptive field of one of its pixels holds an active input pixel, or when its word in
+ * `union_bits` (output geometry, may be null) is non-zero.
+ *   list[0..counts[0])   ascending active output tiles
+ *   stale[0..counts[1])  tiles whose word in `out_bits` was non-zero (they hold data from the
+ *                        previous step) but are not active now: the consumer must zero them
+ *   out_bits             every word cleared to 0 (the convolution then sets the active ones)
+ * counts is int32[4]: {n_active, n_stale, ticket (must be 0 on entry, is 0 on exit), error flag}.
+ * flags is scratch of N*THo*TWo bytes. */
+int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout, int k,
+                     int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
+                     int32_t *list, int32_t *stale, int32_t *counts, uint8_t *flags, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Masked delta convolution with fused incremental activation.
+ * Replaces conv{1x1,3x3,5x5,7x7}_increment_ext (ops.cpp:51-114 -> ext_conv.cu:28-417) and, when
+ * act != NONE, the nnReservedActivation that follows every convolution in the networks
+ * (incr_modules/mask_incr_modules.py:101-103, 248-251).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct mie_conv_args {
+  /* input delta field */
+  const float *in; int64_t in_ps; int cin; int hin; int win;
+  /* weights packed by mie_pack_conv_weights: [k*k][cin_pad][cout_pad] */
+  const float *wpacked; int cin_pad; int cout; int cout_pad;
+  int n; int hout; int wout; int k; int stride; int pad;
+  /* work lists from mie_tiles_dilate */
+  const int32_t *list; const int32_t *stale; int32_t *counts; int max_tiles;
+  /* output delta field */
+  float *out; int64_t out_ps; uint64_t *out_bits;
+  /* fused epilogue: d = conv (+ addend); act==NONE: dy = d; else with x = *res:
+   *   dy = f(x + d) - (emitted ? *emitted : f(x));  *res = x + d;
+   * a pixel is sent when any channel has |dy| > thr; withheld pixels are written as 0;
+   * when `emitted` is given it accumulates what was sent. */
+  int act; float thr;
+  float *res; int64_t res_ps;
+  float *emitted; int64_t emitted_ps;
+  const float *addend; int64_t addend_ps;
+} mie_conv_args;
+
+int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);
+
+/* Host helper (no device work): floats needed for the packed copy of a [cout,cin,k,k] filter, and
+ * the padded extents the kernels assume. */
+int mie_conv_pack_dims(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats);
+
+/* wpacked[(ky*k+kx)][ci][co] <- w[co][ci][ky][kx] (PyTorch OIHW, contiguous), zero padded.
+ * The reference keeps a [Cin,kH,kW,Cout] copy for the same purpose
+ * (ext/pointops/pointops_functional.py:13-14). */
+int mie_pack_conv_weights(const float *w_oihw, int cout, int cin, int k, float *wpacked, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Reference-shaped entry points (same argument meaning as the pybind functions they replace).
+ * ------------------------------------------------------------------------------------------- */
+
+/* out = relu(X + in) - relu(X); X += in, over n contiguous floats.
+ * activation_increment(X, in_incr, out_incr), ops.cpp:8-23 -> pointop_cuda.cu:17-96 (ReLU only
+ * there; `op` selects MIE_ACT_* here). */
+int mie_activation_increment(float *X, const float *in_incr, float *out_incr, int64_t n, int op,
+                             void *stream);
+
+/* conv{k}x{k}_increment_ext(x_incr, mask, filter, out_incr, stride), ops.cpp:51-114.
+ * x_incr [N,Cin,H,W] channels-last; mask: same shape as x_incr, `mask_elem_size` bytes per element
+ * (0 = no mask given: derive it from x_incr != 0); filter [Cin,k,k,Cout] contiguous
+ * (pointops_functional.py:13-14); out_incr [N,Cout,Hout,Wout] channels-last, every element is
+ * written (the reference hands in torch.empty, pointops_functional.py:29).  pad = k/2.
+ * workspace: device scratch of mie_conv_increment_workspace_bytes(...) bytes, 256-byte aligned. */
+int64_t mie_conv_increment_workspace_bytes(int N, int cin, int H, int W, int cout, int k, int stride);
+int mie_conv_increment_ext(const float *x_incr, const void *mask, int mask_elem_size, const float *filter,
+                           float *out_incr, int N, int cin, int H, int W, int cout, int k, int stride,
+                           void *workspace, int64_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused incremental point operations over delta fields.  All of them walk every tile, skip tiles
+ * whose input words are all zero (clearing stale output there) and keep the zero invariant.
+ * ------------------------------------------------------------------------------------------- */
+
+/* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx; out mask = any_c |dy| > thr.
+ * nnReservedActivation.forward, incr_modules/mask_incr_modules.py:248-251.
+ * in/out may alias (in place) when in_ps == out_ps. */
+int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
+                 float *emitted, int64_t emitted_ps, float *out, int64_t out_ps, uint64_t *out_bits,
+                 int N, int C, int H, int W, int op, float thr, void *stream);
+
+/* out = (d2 + x2)*d1 + x1*d2; x1 += d1; x2 += d2.  Either delta may be null (all zero).
+ * IncrPointwiseMultiply + nnReservedMultiplication.forward,
+ * incr_modules/mask_incr_functional.py:52-54, incr_modules/mask_incr_modules.py:71-75. */
+int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x1, int64_t x1_ps,
+                 const float *d2, int64_t d2_ps, const uint64_t *bits2, float *x2, int64_t x2_ps,
+                 float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, float thr,
+                 void *stream);
+
+/* The point-wise part of ConvLSTMIncr.forward (incr_modules/e2depth_incr.py:103-120) in one pass:
+ * gate pre-activation deltas dg [N,4C,H,W] (order in, remember, out, cell) are folded into the
+ * pre-activation reservoir g; the three products and tanh of the cell follow.
+ *   g      [N,4C,H,W]  gate pre-activations (the four activation reservoirs side by side)
+ *   cprev  [N,C,H,W]   accumulated previous-cell input of product m2 (only touched if dc_prev given)
+ *   cell   [N,C,H,W]   accumulated cell (reservoir of the second tanh)
+ *   dc_prev/dcp_bits   incoming previous-cell delta, may be null
+ *   dh, dc             outgoing hidden and cell deltas with their masks
+ *   sum_m2             1: cell delta = m1 + m2 (dense-exact); 0: m1 only, as the reference computes
+ *                      (its `+` concatenates two lists, e2depth_incr.py:113) */
+int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, float *g, int64_t g_ps,
+                       const float *dc_prev, int64_t dcp_ps, const uint64_t *dcp_bits,
+                       float *cprev, int64_t cprev_ps, float *cell, int64_t cell_ps,
+                       float *dh, int64_t dh_ps, uint64_t *dh_bits, float *dc, int64_t dc_ps,
+                       uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2, float thr, void *stream);
+
+/* out[N,C,2H,2W] = up2(a (+ b)); bilinear (align_corners=False) or nearest.  b may be null.
+ * interpolate_from_module, incr_modules/mask_incr_functional.py:76-78; the sum is the skip
+ * connection the networks apply just before (incr_modules/e2depth_incr.py:430). */
+int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+                   const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C,
+                   int H, int W, int mode, void *stream);
+
+/* out = a + b, out mask = mask_a | mask_b.  Skip / residual sum of two delta fields. */
+int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+            const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
+            int W, void *stream);
+
+/* out[..., 0:ca] = a, out[..., ca:ca+cb] = b; out mask = mask_a | mask_b.  Channel concatenation
+ * (torch.cat in incr_modules/e2depth_incr.py:100 and skip_concat, incr_modules/evflownet_incr.py:9-14). */
+int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, int ca, const float *b, int64_t b_ps,
+             const uint64_t *b_bits, int cb, float *out, int64_t out_ps, uint64_t *out_bits, int N, int H,
+             int W, void *stream);
+
+/* y += d over the active tiles of d.  The caller-side accumulation of the driver loop
+ * (run_e2depth_continuous_dataset.py:74) and IncrementReserve.accumulate
+ * (incr_modules/mask_incr_functional.py:41-42). */
+int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const uint64_t *d_bits, int N,
+                   int C, int H, int W, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIE_H */

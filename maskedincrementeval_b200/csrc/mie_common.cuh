@@ -1,0 +1,88 @@
+// Shared helpers for the libmie kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "mie.h"
+
+#define MIE_TILE 8
+#define MIE_SM_COUNT 148  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+namespace mie {
+
+// Records the text of a failed CUDA runtime call for mie_last_cuda_error(); defined in mie_mask.cu.
+void set_cuda_error(cudaError_t e);
+
+static inline int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_cuda_error(e);
+    return MIE_ECUDA;
+  }
+  return MIE_OK;
+}
+
+static inline int divup(int a, int b) { return (a + b - 1) / b; }
+static inline int64_t divup64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+__device__ __forceinline__ float act_apply(int op, float x) {
+  // expf/tanhf are the accurate libm-class device functions (no fast-math): parity with
+  // torch.sigmoid / torch.tanh is required to 1e-4 of the output range.
+  switch (op) {
+    case MIE_ACT_RELU: return fmaxf(x, 0.0f);
+    case MIE_ACT_SIGMOID: return 1.0f / (1.0f + expf(-x));
+    case MIE_ACT_TANH: return tanhf(x);
+    default: return x;
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ float act_t(float x) {
+  if (OP == MIE_ACT_RELU) return fmaxf(x, 0.0f);
+  if (OP == MIE_ACT_SIGMOID) return 1.0f / (1.0f + expf(-x));
+  if (OP == MIE_ACT_TANH) return tanhf(x);
+  return x;
+}
+
+// Bit mask of the valid pixels of tile (ty, tx) in an H x W image (ragged right / bottom tiles).
+__device__ __forceinline__ unsigned long long tile_valid_mask(int ty, int tx, int H, int W) {
+  int rows = min(MIE_TILE, H - ty * MIE_TILE);
+  int cols = min(MIE_TILE, W - tx * MIE_TILE);
+  unsigned long long rowm = (1ull << cols) - 1ull;  // cols <= 8
+  unsigned long long m = 0;
+  for (int r = 0; r < rows; ++r) m |= rowm << (r * 8);
+  return m;
+}
+
+// Ordered compaction run by ONE thread block: list <- ascending i in [0,n) with pred(i) != 0.
+// Returns the count to every thread.  blockDim.x must be a multiple of 32, at most 1024.
+template <typename Pred>
+__device__ int block_ordered_compact(Pred pred, int n, int32_t *list) {
+  __shared__ int s_warp[32];
+  __shared__ int s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int start = 0; start < n; start += blockDim.x) {
+    int i = start + threadIdx.x;
+    bool p = (i < n) && pred(i);
+    unsigned ballot = __ballot_sync(0xffffffffu, p);
+    int within = __popc(ballot & ((1u << lane) - 1u));
+    if (lane == 0) s_warp[warp] = __popc(ballot);
+    __syncthreads();
+    int warp_off = 0, total = 0;
+    for (int w2 = 0; w2 < nwarps; ++w2) {
+      int c = s_warp[w2];
+      if (w2 < warp) warp_off += c;
+      total += c;
+    }
+    int base = s_base;
+    if (p) list[base + warp_off + within] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) s_base = base + total;
+    __syncthreads();
+  }
+  return s_base;
+}
+
+}  // namespace mie

@@ -1,0 +1,235 @@
+// Active-tile compaction: per-pixel masks as 64-bit tile words, ordered tile lists, and the
+// dilated output-tile set of a convolution.
+#include <stdio.h>
+#include <string.h>
+#include "mie_common.cuh"
+
+namespace mie {
+static thread_local char g_cuda_err[256] = "";
+void set_cuda_error(cudaError_t e) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+}
+}  // namespace mie
+
+using namespace mie;
+
+extern "C" int mie_version(void) { return 1; }
+
+extern "C" const char *mie_status_string(int s) {
+  switch (s) {
+    case MIE_OK: return "ok";
+    case MIE_EINVAL: return "invalid argument";
+    case MIE_EALIGN: return "misaligned pointer or stride";
+    case MIE_EUNSUPPORTED: return "unsupported combination";
+    case MIE_ECUDA: return "CUDA runtime error";
+    case MIE_ETOOBIG: return "size beyond capacity";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char *mie_last_cuda_error(void) { return g_cuda_err; }
+
+// ---------------------------------------------------------------------------------------------
+// mask words from a delta tensor or an explicit mask tensor: one warp per 8x8 tile
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool VEC4>
+__global__ void __launch_bounds__(256) mask_words_kernel(const T *__restrict__ src, int64_t ps, int C, int N,
+                                                         int H, int W, float thr, uint64_t *__restrict__ bits) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  const int ntiles = N * TH * TW;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < ntiles; t += warps_per_grid) {
+    const int tx = t % TW, ty = (t / TW) % TH, n = t / (TW * TH);
+    const int rows = min(8, H - ty * 8), cols = min(8, W - tx * 8);
+    unsigned lo = 0, hi = 0;
+    if (VEC4) {
+      // C % 4 == 0, ps % 4 == 0, base 16-byte aligned: each float4 lies inside one pixel
+      const int c4 = C >> 2;
+      const int per_row = cols * c4;
+      const int total = rows * per_row;
+      for (int i = lane; i < total; i += 32) {
+        const int r = i / per_row, rem = i - r * per_row;
+        const int px = rem / c4, q = rem - px * c4;
+        const float4 v = *reinterpret_cast<const float4 *>(
+            reinterpret_cast<const float *>(src) + ((int64_t)(n * H + ty * 8 + r) * W + tx * 8 + px) * ps + q * 4);
+        const bool a = fabsf(v.x) > thr || fabsf(v.y) > thr || fabsf(v.z) > thr || fabsf(v.w) > thr;
+        const int b = r * 8 + px;
+        if (a) { if (b < 32) lo |= 1u << b; else hi |= 1u << (b - 32); }
+      }
+    } else {
+      const int per_row = cols * C;
+      const int total = rows * per_row;
+      for (int i = lane; i < total; i += 32) {
+        const int r = i / per_row, rem = i - r * per_row;
+        const int px = rem / C, c = rem - px * C;
+        const T v = src[((int64_t)(n * H + ty * 8 + r) * W + tx * 8 + px) * ps + c];
+        bool a;
+        if (sizeof(T) == 4 && thr >= 0.0f) a = fabsf((float)v) > thr;  // float source
+        else a = v != (T)0;                                           // explicit mask source
+        const int b = r * 8 + px;
+        if (a) { if (b < 32) lo |= 1u << b; else hi |= 1u << (b - 32); }
+      }
+    }
+    lo = __reduce_or_sync(0xffffffffu, lo);
+    hi = __reduce_or_sync(0xffffffffu, hi);
+    if (lane == 0) bits[t] = ((uint64_t)hi << 32) | lo;
+  }
+}
+
+static int mask_grid(int ntiles) {
+  int blocks = divup(ntiles, 8);
+  int cap = MIE_SM_COUNT * 8;
+  return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
+}
+
+extern "C" int mie_mask_from_delta(const float *delta, int64_t ps, int N, int C, int H, int W, float thr,
+                                   uint64_t *bits, void *stream) {
+  if (!delta || !bits || N <= 0 || C <= 0 || H <= 0 || W <= 0 || ps < C || !(thr >= 0.0f)) return MIE_EINVAL;
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (C % 4 == 0) && (ps % 4 == 0) && aligned16(delta);
+  if (vec) mask_words_kernel<float, true><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
+  else mask_words_kernel<float, false><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
+  return check_launch();
+}
+
+extern "C" int mie_mask_from_mask(const void *mask, int elem_size, int64_t mps, int cm, int N, int H, int W,
+                                  uint64_t *bits, void *stream) {
+  if (!mask || !bits || N <= 0 || cm <= 0 || H <= 0 || W <= 0 || mps < cm) return MIE_EINVAL;
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (elem_size == 1)
+    mask_words_kernel<uint8_t, false><<<mask_grid(ntiles), 256, 0, st>>>((const uint8_t *)mask, mps, cm, N, H, W, -1.0f, bits);
+  else if (elem_size == 4)
+    mask_words_kernel<int32_t, false><<<mask_grid(ntiles), 256, 0, st>>>((const int32_t *)mask, mps, cm, N, H, W, -1.0f, bits);
+  else
+    return MIE_EUNSUPPORTED;
+  return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// ordered compaction of non-zero words (warp ballot + block prefix)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) tiles_compact_kernel(const uint64_t *__restrict__ bits, int ntiles,
+                                                             int32_t *__restrict__ list, int32_t *__restrict__ counts) {
+  int n = block_ordered_compact([&](int i) { return bits[i] != 0ull; }, ntiles, list);
+  if (threadIdx.x == 0) counts[0] = n;
+}
+
+extern "C" int mie_tiles_compact(const uint64_t *bits, int ntiles, int32_t *list, int32_t *counts, void *stream) {
+  if (!bits || !list || !counts || ntiles <= 0) return MIE_EINVAL;
+  tiles_compact_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(bits, ntiles, list, counts);
+  return check_launch();
+}
+
+__global__ void mask_expand_kernel(const uint64_t *__restrict__ bits, int N, int H, int W, uint8_t *__restrict__ out) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  const int64_t total = (int64_t)N * H * W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int x = (int)(i % W), y = (int)((i / W) % H), n = (int)(i / ((int64_t)W * H));
+    const uint64_t w = bits[((int64_t)n * TH + (y >> 3)) * TW + (x >> 3)];
+    out[i] = (uint8_t)((w >> ((y & 7) * 8 + (x & 7))) & 1ull);
+  }
+}
+
+extern "C" int mie_mask_expand(const uint64_t *bits, int N, int H, int W, uint8_t *bytes, void *stream) {
+  if (!bits || !bytes || N <= 0 || H <= 0 || W <= 0) return MIE_EINVAL;
+  const int64_t total = (int64_t)N * H * W;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > MIE_SM_COUNT * 16) blocks = MIE_SM_COUNT * 16;
+  mask_expand_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(bits, N, H, W, bytes);
+  return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// dilated output-tile set of a convolution, plus the stale list, in one launch
+// ---------------------------------------------------------------------------------------------
+// Bit j of the result is set when input row (base + j) feeds one of the valid output rows
+// [o0, o0 + cnt) of a tile: rows o*stride - pad + t for t in [0, k).
+__device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride, int pad, int base, int limit) {
+  unsigned set = 0;
+  for (int o = 0; o < cnt; ++o)
+    for (int t = 0; t < k; ++t) {
+      const int i = (o0 + o) * stride - pad + t;
+      if (i >= 0 && i < limit) set |= 1u << (i - base);
+    }
+  return set;
+}
+
+__global__ void __launch_bounds__(256) tiles_dilate_kernel(
+    const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
+    const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,
+    int32_t *__restrict__ stale, int32_t *__restrict__ counts, uint8_t *__restrict__ flags) {
+  const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
+  const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
+  const int ntiles = N * THo * TWo;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < ntiles) {
+    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+    const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
+    const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
+    const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
+    const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
+    bool active = false;
+    if (rset && cset) {
+      const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
+      const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
+      for (int ity = ylo >> 3; ity <= (yhi >> 3) && !active; ++ity) {
+        unsigned selr = 0;
+        for (int py = 0; py < 8; ++py) {
+          const int j = ity * 8 + py - ybase;
+          if (j >= 0 && j < 32 && ((rset >> j) & 1u)) selr |= 1u << py;
+        }
+        for (int itx = xlo >> 3; itx <= (xhi >> 3); ++itx) {
+          unsigned selc = 0;
+          for (int px = 0; px < 8; ++px) {
+            const int j = itx * 8 + px - xbase;
+            if (j >= 0 && j < 32 && ((cset >> j) & 1u)) selc |= 1u << px;
+          }
+          uint64_t m = 0;
+          for (int py = 0; py < 8; ++py)
+            if ((selr >> py) & 1u) m |= (uint64_t)selc << (py * 8);
+          if (in_bits[((int64_t)n * THi + ity) * TWi + itx] & m) { active = true; break; }
+        }
+      }
+    }
+    if (!active && union_bits && union_bits[t] != 0ull) active = true;
+    uint8_t f = active ? 1 : 0;
+    if (out_bits) {
+      if (!active && out_bits[t] != 0ull) f = 2;
+      out_bits[t] = 0ull;
+    }
+    flags[t] = f;
+  }
+  // the block that finishes last compacts both lists in ascending order
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&counts[2], 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int na = block_ordered_compact([&](int i) { return __ldcg(flags + i) == 1; }, ntiles, list);
+  __syncthreads();
+  int ns = 0;
+  if (stale) ns = block_ordered_compact([&](int i) { return __ldcg(flags + i) == 2; }, ntiles, stale);
+  if (threadIdx.x == 0) {
+    counts[0] = na;
+    counts[1] = ns;
+    counts[2] = 0;
+  }
+}
+
+extern "C" int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout, int k,
+                                int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
+                                int32_t *list, int32_t *stale, int32_t *counts, uint8_t *flags, void *stream) {
+  if (!in_bits || !list || !counts || !flags || N <= 0 || Hin <= 0 || Win <= 0 || Hout <= 0 || Wout <= 0)
+    return MIE_EINVAL;
+  if (k < 1 || k > 7 || stride < 1 || stride > 2 || pad < 0 || pad > k) return MIE_EUNSUPPORTED;
+  if (out_bits && !stale) return MIE_EINVAL;
+  const int ntiles = N * divup(Hout, 8) * divup(Wout, 8);
+  tiles_dilate_kernel<<<divup(ntiles, 256), 256, 0, (cudaStream_t)stream>>>(
+      in_bits, N, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits, list, stale, counts, flags);
+  return check_launch();
+}

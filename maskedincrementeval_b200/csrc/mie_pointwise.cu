@@ -1,0 +1,565 @@
+// Fused incremental point operations over delta fields.
+//
+// Every kernel walks all 8x8 tiles with a grid-stride loop, one thread block per tile at a time.
+// A tile whose input words are all zero costs one 8-byte read (plus clearing stale output if the
+// output tile held data from the previous step).  Inside an active tile only the active pixels touch
+// the persistent state, so reservoir traffic follows the pixel mask, not the tile mask.
+#include "mie_common.cuh"
+
+using namespace mie;
+
+namespace {
+
+constexpr int PW_THREADS = 128;
+
+static int tile_grid(int ntiles) {
+  const int cap = MIE_SM_COUNT * 8;
+  return ntiles < cap ? (ntiles > 0 ? ntiles : 1) : cap;
+}
+
+struct TileGeom {
+  int n, ty, tx, rows, cols;
+};
+
+__device__ __forceinline__ TileGeom tile_geom(int t, int H, int W) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  TileGeom g;
+  g.tx = t % TW;
+  g.ty = (t / TW) % TH;
+  g.n = t / (TW * TH);
+  g.rows = min(8, H - g.ty * 8);
+  g.cols = min(8, W - g.tx * 8);
+  return g;
+}
+
+__device__ __forceinline__ int64_t pix_index(const TileGeom &g, int p, int H, int W) {
+  return (int64_t)(g.n * H + g.ty * 8 + (p >> 3)) * W + g.tx * 8 + (p & 7);
+}
+
+__device__ __forceinline__ bool pix_valid(const TileGeom &g, int p) { return (p >> 3) < g.rows && (p & 7) < g.cols; }
+
+// zero every channel of every valid pixel of a tile
+__device__ __forceinline__ void zero_tile(float *out, int64_t ps, int C, const TileGeom &g, int H, int W) {
+  for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+    const int p = e / C, c = e - p * C;
+    if (pix_valid(g, p)) out[pix_index(g, p, H, W) * ps + c] = 0.0f;
+  }
+}
+
+__device__ __forceinline__ void or_word(unsigned *s_lo_hi, int p) {
+  atomicOr(&s_lo_hi[p >> 5], 1u << (p & 31));
+}
+
+// ---------------------------------------------------------------------------------------------
+// incremental activation
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(PW_THREADS) act_incr_kernel(
+    const float *in, int64_t in_ps, const uint64_t *__restrict__ in_bits, float *__restrict__ res,
+    int64_t res_ps, float *__restrict__ emitted, int64_t em_ps, float *out, int64_t out_ps, uint64_t *out_bits,
+    int N, int C, int H, int W, int op, float thr) {
+  __shared__ unsigned s_w[2];
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t win = in_bits[t];
+    const TileGeom g = tile_geom(t, H, W);
+    if (win == 0ull) {
+      if (out_bits[t] != 0ull) {  // uniform across the block
+        __syncthreads();
+        zero_tile(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float dy = 0.0f;
+      if ((win >> p) & 1ull) {
+        const float d = in[pix * in_ps + c];
+        const float x = res[pix * res_ps + c];
+        const float xn = x + d;
+        res[pix * res_ps + c] = xn;
+        const float base = emitted ? emitted[pix * em_ps + c] : act_apply(op, x);
+        dy = act_apply(op, xn) - base;
+        if (fabsf(dy) > thr) or_word(s_w, p);
+      }
+      out[pix * out_ps + c] = dy;
+    }
+    __syncthreads();
+    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (thr > 0.0f || emitted) {
+      // second pass: withheld pixels are written as zero; sent pixels are added to the carry
+      for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+        const int p = e / C, c = e - p * C;
+        if (!pix_valid(g, p) || !((win >> p) & 1ull)) continue;
+        const int64_t pix = pix_index(g, p, H, W);
+        if ((wout >> p) & 1ull) {
+          if (emitted) emitted[pix * em_ps + c] += out[pix * out_ps + c];
+        } else {
+          out[pix * out_ps + c] = 0.0f;
+        }
+      }
+    }
+    if (threadIdx.x == 0) out_bits[t] = wout;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// incremental product
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(PW_THREADS) mul_incr_kernel(
+    const float *__restrict__ d1, int64_t d1_ps, const uint64_t *__restrict__ bits1, float *__restrict__ x1, int64_t x1_ps,
+    const float *__restrict__ d2, int64_t d2_ps, const uint64_t *__restrict__ bits2, float *__restrict__ x2, int64_t x2_ps,
+    float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W, float thr) {
+  __shared__ unsigned s_w[2];
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t w1 = (d1 && bits1) ? bits1[t] : 0ull, w2 = (d2 && bits2) ? bits2[t] : 0ull;
+    const uint64_t win = w1 | w2;
+    const TileGeom g = tile_geom(t, H, W);
+    if (win == 0ull) {
+      if (out_bits[t] != 0ull) {
+        __syncthreads();
+        zero_tile(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float d = 0.0f;
+      if ((win >> p) & 1ull) {
+        const float a = ((w1 >> p) & 1ull) ? d1[pix * d1_ps + c] : 0.0f;
+        const float b = ((w2 >> p) & 1ull) ? d2[pix * d2_ps + c] : 0.0f;
+        const float v1 = x1[pix * x1_ps + c], v2 = x2[pix * x2_ps + c];
+        d = (b + v2) * a + v1 * b;
+        if (a != 0.0f) x1[pix * x1_ps + c] = v1 + a;
+        if (b != 0.0f) x2[pix * x2_ps + c] = v2 + b;
+        if (fabsf(d) > thr) or_word(s_w, p);
+      }
+      out[pix * out_ps + c] = d;
+    }
+    __syncthreads();
+    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (thr > 0.0f) {
+      for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+        const int p = e / C, c = e - p * C;
+        if (pix_valid(g, p) && ((win >> p) & 1ull) && !((wout >> p) & 1ull)) out[pix_index(g, p, H, W) * out_ps + c] = 0.0f;
+      }
+    }
+    if (threadIdx.x == 0) out_bits[t] = wout;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// ConvLSTM point-wise block
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_acc(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__global__ void __launch_bounds__(PW_THREADS) convlstm_point_kernel(
+    const float *__restrict__ dg, int64_t dg_ps, const uint64_t *__restrict__ dg_bits, float *__restrict__ gres, int64_t g_ps,
+    const float *__restrict__ dcp, int64_t dcp_ps, const uint64_t *__restrict__ dcp_bits, float *__restrict__ cprev,
+    int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
+    uint64_t *__restrict__ dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *__restrict__ dc_bits, int N, int C,
+    int H, int W, int sum_m2, float thr) {
+  __shared__ unsigned s_h[2], s_c[2];
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t wg = dg_bits[t];
+    const uint64_t wc = (dcp && dcp_bits) ? dcp_bits[t] : 0ull;
+    const uint64_t win = wg | wc;
+    const TileGeom g = tile_geom(t, H, W);
+    if (win == 0ull) {
+      const bool sh = dh_bits[t] != 0ull, sc = dc_bits[t] != 0ull;
+      if (sh || sc) {
+        __syncthreads();
+        if (sh) zero_tile(dh, dh_ps, C, g, H, W);
+        if (sc) zero_tile(dc, dc_ps, C, g, H, W);
+        if (threadIdx.x == 0) { dh_bits[t] = 0ull; dc_bits[t] = 0ull; }
+      }
+      continue;
+    }
+    if (threadIdx.x < 2) { s_h[threadIdx.x] = 0u; s_c[threadIdx.x] = 0u; }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float o_h = 0.0f, o_c = 0.0f;
+      if ((win >> p) & 1ull) {
+        const bool hg = (wg >> p) & 1ull;
+        float *gp = gres + pix * g_ps + c;
+        const float gi = gp[0], gf = gp[C], go = gp[2 * C], gc = gp[3 * C];
+        float di = 0.f, df = 0.f, dob = 0.f, dcg = 0.f;
+        if (hg) {
+          const float *dp = dg + pix * dg_ps + c;
+          di = dp[0]; df = dp[C]; dob = dp[2 * C]; dcg = dp[3 * C];
+          gp[0] = gi + di; gp[C] = gf + df; gp[2 * C] = go + dob; gp[3 * C] = gc + dcg;
+        }
+        const float i_o = sigmoidf_acc(gi), f_o = sigmoidf_acc(gf), o_o = sigmoidf_acc(go), g_o = tanhf(gc);
+        const float Di = sigmoidf_acc(gi + di) - i_o, Df = sigmoidf_acc(gf + df) - f_o;
+        const float Do = sigmoidf_acc(go + dob) - o_o, Dg = tanhf(gc + dcg) - g_o;
+        const float m1 = (Dg + g_o) * Di + i_o * Dg;
+        float m2 = 0.0f;
+        if (cprev) {
+          const float cp_o = cprev[pix * cprev_ps + c];
+          const float Dcp = ((wc >> p) & 1ull) ? dcp[pix * dcp_ps + c] : 0.0f;
+          m2 = (Dcp + cp_o) * Df + f_o * Dcp;
+          if (Dcp != 0.0f) cprev[pix * cprev_ps + c] = cp_o + Dcp;
+        }
+        const float Dc = sum_m2 ? (m1 + m2) : m1;
+        const float c_o = cell[pix * cell_ps + c];
+        const float tc_o = tanhf(c_o);
+        const float Dtc = tanhf(c_o + Dc) - tc_o;
+        if (Dc != 0.0f) cell[pix * cell_ps + c] = c_o + Dc;
+        o_h = (Dtc + tc_o) * Do + o_o * Dtc;
+        o_c = Dc;
+        if (fabsf(o_h) > thr) or_word(s_h, p);
+        if (fabsf(o_c) > thr) or_word(s_c, p);
+      }
+      dh[pix * dh_ps + c] = o_h;
+      dc[pix * dc_ps + c] = o_c;
+    }
+    __syncthreads();
+    const uint64_t wh = ((uint64_t)s_h[1] << 32) | s_h[0], wcc = ((uint64_t)s_c[1] << 32) | s_c[0];
+    if (thr > 0.0f) {
+      for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+        const int p = e / C, c = e - p * C;
+        if (!pix_valid(g, p) || !((win >> p) & 1ull)) continue;
+        const int64_t pix = pix_index(g, p, H, W);
+        if (!((wh >> p) & 1ull)) dh[pix * dh_ps + c] = 0.0f;
+        if (!((wcc >> p) & 1ull)) dc[pix * dc_ps + c] = 0.0f;
+      }
+    }
+    if (threadIdx.x == 0) { dh_bits[t] = wh; dc_bits[t] = wcc; }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// x2 upsample of (a + b)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool bit_at(const uint64_t *bits, int n, int y, int x, int TH, int TW) {
+  return (bits[((int64_t)n * TH + (y >> 3)) * TW + (x >> 3)] >> ((y & 7) * 8 + (x & 7))) & 1ull;
+}
+
+// source rows/cols and weights of output coordinate o for a x2 upsample of extent L
+__device__ __forceinline__ void up_src(int o, int L, int mode, int &i0, int &i1, float &w1) {
+  if (mode == MIE_UP_NEAREST) { i0 = i1 = o >> 1; w1 = 0.0f; return; }
+  float s = 0.5f * (o + 0.5f) - 0.5f;
+  if (s < 0.0f) s = 0.0f;
+  i0 = (int)s;
+  i1 = min(i0 + 1, L - 1);
+  w1 = s - (float)i0;
+  if (w1 == 0.0f) i1 = i0;
+}
+
+__global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps,
+    uint64_t *__restrict__ out_bits, int N, int C, int H, int W, int mode) {
+  const int Ho = 2 * H, Wo = 2 * W;
+  const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
+  const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
+  __shared__ unsigned s_w[2];
+  __shared__ unsigned char s_fa[64], s_fb[64];  // per output pixel: 4 source-activity bits for a and b
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const TileGeom g = tile_geom(t, Ho, Wo);
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const int p = threadIdx.x;
+      unsigned fa = 0, fb = 0;
+      if (pix_valid(g, p)) {
+        int y0, y1, x0, x1; float wy, wx;
+        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        fa = (bit_at(a_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(a_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
+             (bit_at(a_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(a_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
+        if (b)
+          fb = (bit_at(b_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(b_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
+               (bit_at(b_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(b_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
+      }
+      s_fa[p] = (unsigned char)fa;
+      s_fb[p] = (unsigned char)fb;
+      const unsigned bal = __ballot_sync(0xffffffffu, (fa | fb) != 0);
+      if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = bal;
+    }
+    __syncthreads();
+    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (wout == 0ull) {
+      if (out_bits[t] != 0ull) {
+        zero_tile(out, out_ps, C, g, Ho, Wo);
+        __syncthreads();
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      float v = 0.0f;
+      const unsigned fa = s_fa[p], fb = s_fb[p];
+      if (fa | fb) {
+        int y0, y1, x0, x1; float wy, wx;
+        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
+        float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
+        if (fa & 1u) v00 += a[(r0 + x0) * a_ps + c];
+        if (fa & 2u) v01 += a[(r0 + x1) * a_ps + c];
+        if (fa & 4u) v10 += a[(r1 + x0) * a_ps + c];
+        if (fa & 8u) v11 += a[(r1 + x1) * a_ps + c];
+        if (fb & 1u) v00 += b[(r0 + x0) * b_ps + c];
+        if (fb & 2u) v01 += b[(r0 + x1) * b_ps + c];
+        if (fb & 4u) v10 += b[(r1 + x0) * b_ps + c];
+        if (fb & 8u) v11 += b[(r1 + x1) * b_ps + c];
+        if (mode == MIE_UP_NEAREST) v = v00;
+        else v = (1.0f - wy) * ((1.0f - wx) * v00 + wx * v01) + wy * ((1.0f - wx) * v10 + wx * v11);
+      }
+      out[pix_index(g, p, Ho, Wo) * out_ps + c] = v;
+    }
+    if (threadIdx.x == 0) out_bits[t] = wout;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// add, concatenate, accumulate
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(PW_THREADS) add_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps,
+    uint64_t *__restrict__ out_bits, int N, int C, int H, int W) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (out_bits[t] != 0ull) {
+        __syncthreads();
+        zero_tile(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float v = 0.0f;
+      if ((wa >> p) & 1ull) v += a[pix * a_ps + c];
+      if ((wb >> p) & 1ull) v += b[pix * b_ps + c];
+      out[pix * out_ps + c] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
+__global__ void __launch_bounds__(PW_THREADS) cat2_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, int ca, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, int cb, float *__restrict__ out, int64_t out_ps,
+    uint64_t *__restrict__ out_bits, int N, int H, int W) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int C = ca + cb;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (out_bits[t] != 0ull) {
+        __syncthreads();
+        zero_tile(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float v = 0.0f;
+      if (c < ca) { if ((wa >> p) & 1ull) v = a[pix * a_ps + c]; }
+      else { if ((wb >> p) & 1ull) v = b[pix * b_ps + (c - ca)]; }
+      out[pix * out_ps + c] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
+__global__ void __launch_bounds__(PW_THREADS) accumulate_kernel(float *__restrict__ y, int64_t y_ps,
+                                                                const float *__restrict__ d, int64_t d_ps,
+                                                                const uint64_t *__restrict__ d_bits, int N, int C, int H,
+                                                                int W) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t w = d_bits[t];
+    if (w == 0ull) continue;
+    const TileGeom g = tile_geom(t, H, W);
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p) || !((w >> p) & 1ull)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      y[pix * y_ps + c] += d[pix * d_ps + c];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dense activation increment over n contiguous floats (the reference's native entry point)
+// ---------------------------------------------------------------------------------------------
+template <int OP, bool VEC>
+__global__ void __launch_bounds__(256) activation_increment_kernel(float *__restrict__ X, const float *__restrict__ in,
+                                                                   float *__restrict__ out, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    const int64_t n4 = n >> 2;
+    float4 *X4 = reinterpret_cast<float4 *>(X);
+    const float4 *I4 = reinterpret_cast<const float4 *>(in);
+    float4 *O4 = reinterpret_cast<float4 *>(out);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      const float4 x = X4[i], d = __ldcs(I4 + i);
+      const float4 xn = make_float4(x.x + d.x, x.y + d.y, x.z + d.z, x.w + d.w);
+      const float4 o = make_float4(act_t<OP>(xn.x) - act_t<OP>(x.x), act_t<OP>(xn.y) - act_t<OP>(x.y),
+                                   act_t<OP>(xn.z) - act_t<OP>(x.z), act_t<OP>(xn.w) - act_t<OP>(x.w));
+      X4[i] = xn;
+      __stcs(O4 + i, o);
+    }
+    for (int64_t i = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+      const float x = X[i], xn = x + in[i];
+      out[i] = act_t<OP>(xn) - act_t<OP>(x);
+      X[i] = xn;
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+      const float x = X[i], xn = x + in[i];
+      out[i] = act_t<OP>(xn) - act_t<OP>(x);
+      X[i] = xn;
+    }
+  }
+}
+
+template <int OP>
+int launch_act_dense(float *X, const float *in, float *out, int64_t n, cudaStream_t st) {
+  const bool vec = aligned16(X) && aligned16(in) && aligned16(out);
+  const int64_t work = vec ? (n >> 2) : n;
+  int64_t blocks = divup64(work > 0 ? work : 1, 256);
+  const int64_t cap = (int64_t)MIE_SM_COUNT * 8;  // 8 resident blocks of 256 threads per SM
+  if (blocks > cap) blocks = cap;
+  if (vec) activation_increment_kernel<OP, true><<<(int)blocks, 256, 0, st>>>(X, in, out, n);
+  else activation_increment_kernel<OP, false><<<(int)blocks, 256, 0, st>>>(X, in, out, n);
+  return check_launch();
+}
+
+}  // namespace
+
+extern "C" int mie_activation_increment(float *X, const float *in_incr, float *out_incr, int64_t n, int op, void *stream) {
+  if (!X || !in_incr || !out_incr || n < 0) return MIE_EINVAL;
+  if (n == 0) return MIE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (op) {
+    case MIE_ACT_RELU: return launch_act_dense<MIE_ACT_RELU>(X, in_incr, out_incr, n, st);
+    case MIE_ACT_SIGMOID: return launch_act_dense<MIE_ACT_SIGMOID>(X, in_incr, out_incr, n, st);
+    case MIE_ACT_TANH: return launch_act_dense<MIE_ACT_TANH>(X, in_incr, out_incr, n, st);
+    case MIE_ACT_NONE: return launch_act_dense<MIE_ACT_NONE>(X, in_incr, out_incr, n, st);
+    default: return MIE_EINVAL;
+  }
+}
+
+#define MIE_CHECK_FIELD(ptr, ps, C) if (!(ptr) || (ps) < (C)) return MIE_EINVAL
+
+extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
+                            float *emitted, int64_t emitted_ps, float *out, int64_t out_ps, uint64_t *out_bits, int N,
+                            int C, int H, int W, int op, float thr, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (op < MIE_ACT_NONE || op > MIE_ACT_TANH) return MIE_EINVAL;
+  MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(res, res_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
+  if (emitted && emitted_ps < C) return MIE_EINVAL;
+  if (in == out && in_ps != out_ps) return MIE_EINVAL;
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  act_incr_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+      in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr);
+  return check_launch();
+}
+
+extern "C" int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x1, int64_t x1_ps,
+                            const float *d2, int64_t d2_ps, const uint64_t *bits2, float *x2, int64_t x2_ps, float *out,
+                            int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, float thr, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  MIE_CHECK_FIELD(x1, x1_ps, C); MIE_CHECK_FIELD(x2, x2_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
+  if (d1 && (!bits1 || d1_ps < C)) return MIE_EINVAL;
+  if (d2 && (!bits2 || d2_ps < C)) return MIE_EINVAL;
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  mul_incr_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+      d1, d1_ps, bits1, x1, x1_ps, d2, d2_ps, bits2, x2, x2_ps, out, out_ps, out_bits, N, C, H, W, thr);
+  return check_launch();
+}
+
+extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, float *g, int64_t g_ps,
+                                  const float *dc_prev, int64_t dcp_ps, const uint64_t *dcp_bits, float *cprev,
+                                  int64_t cprev_ps, float *cell, int64_t cell_ps, float *dh, int64_t dh_ps,
+                                  uint64_t *dh_bits, float *dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H,
+                                  int W, int sum_m2, float thr, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  MIE_CHECK_FIELD(dg, dg_ps, 4 * C); MIE_CHECK_FIELD(g, g_ps, 4 * C); MIE_CHECK_FIELD(cell, cell_ps, C);
+  MIE_CHECK_FIELD(dh, dh_ps, C); MIE_CHECK_FIELD(dc, dc_ps, C);
+  if (dc_prev && (!dcp_bits || dcp_ps < C || !cprev)) return MIE_EINVAL;
+  if (cprev && cprev_ps < C) return MIE_EINVAL;
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  convlstm_point_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+      dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
+      dc_ps, dc_bits, N, C, H, W, sum_m2, thr);
+  return check_launch();
+}
+
+extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+                              const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
+                              int W, int mode, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !out_bits) return MIE_EINVAL;
+  if (mode != MIE_UP_BILINEAR && mode != MIE_UP_NEAREST) return MIE_EINVAL;
+  MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
+  if (b && (!b_bits || b_ps < C)) return MIE_EINVAL;
+  const int ntiles = N * divup(2 * H, 8) * divup(2 * W, 8);
+  upsample2x_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
+                                                                                out_ps, out_bits, N, C, H, W, mode);
+  return check_launch();
+}
+
+extern "C" int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+                       const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W,
+                       void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
+  MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(b, b_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  add_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps,
+                                                                         out_bits, N, C, H, W);
+  return check_launch();
+}
+
+extern "C" int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, int ca, const float *b, int64_t b_ps,
+                        const uint64_t *b_bits, int cb, float *out, int64_t out_ps, uint64_t *out_bits, int N, int H,
+                        int W, void *stream) {
+  if (N <= 0 || ca <= 0 || cb <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
+  MIE_CHECK_FIELD(a, a_ps, ca); MIE_CHECK_FIELD(b, b_ps, cb); MIE_CHECK_FIELD(out, out_ps, ca + cb);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  cat2_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
+                                                                          out_ps, out_bits, N, H, W);
+  return check_launch();
+}
+
+extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const uint64_t *d_bits, int N, int C,
+                              int H, int W, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !d_bits) return MIE_EINVAL;
+  MIE_CHECK_FIELD(y, y_ps, C); MIE_CHECK_FIELD(d, d_ps, C);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  accumulate_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(y, y_ps, d, d_ps, d_bits, N, C, H, W);
+  return check_launch();
+}

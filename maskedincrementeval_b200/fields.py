@@ -1,0 +1,257 @@
+"""Delta fields on the device: a channels-last fp32 tensor plus one 64-bit activity word per 8x8 tile.
+
+This is the host-side plumbing between the reference-shaped modules in ``incr_modules`` and the C ABI
+of libmie.  A ``Masked`` value in the reference is a 2-item list ``[delta, mask_or_None]``
+(``incr_modules/masked_types.py:14``); here the second item is ``None`` (unknown: the mask is derived
+from the delta on first use), a bool/uint8/int32 tensor, or a ``TileMask``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _native as nat
+
+TILE = 8
+
+
+def n_tiles(n: int, h: int, w: int) -> int:
+    return n * (-(-h // TILE)) * (-(-w // TILE))
+
+
+def conv_out_hw(h: int, w: int, k: int, stride: int, pad: int) -> Tuple[int, int]:
+    return (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+
+
+class IncrConfig:
+    """Library-wide defaults; a module reads them when it runs, so they can be changed between steps.
+
+    threshold        activation outputs with max_c |dy| <= threshold at a pixel are withheld (0 = lossless)
+    carry            keep what was withheld and send it once it grows past the threshold (bounded error)
+    input_threshold  threshold used when a mask has to be derived from a bare delta tensor
+    compat           "reference": networks wired as the reference is written; "exact": as intended, which
+                     makes the accumulated incremental output equal to a dense recompute
+    """
+    threshold: float = 0.0
+    carry: bool = True
+    input_threshold: float = 0.0
+    compat: str = "reference"
+
+
+config = IncrConfig()
+
+
+def pixel_stride(x: torch.Tensor) -> int:
+    """Pixel stride (floats) of a [N,C,H,W] tensor stored channels-last, possibly a channel slice."""
+    if x.dim() != 4:
+        raise RuntimeError("expected a 4-D NCHW tensor")
+    n, c, h, w = x.shape
+    ps = x.stride(3)
+    ok = (c == 1 or x.stride(1) == 1) and ps >= c and (h == 1 or x.stride(2) == w * ps) and \
+        (n == 1 or x.stride(0) == h * w * ps)
+    if w == 1:
+        ps = x.stride(2) if h > 1 else (x.stride(0) if n > 1 else c)
+        ok = (c == 1 or x.stride(1) == 1) and ps >= c
+    if not ok:
+        raise RuntimeError("tensor must be channels_last (NHWC in memory); got strides %s for shape %s"
+                           % (tuple(x.stride()), tuple(x.shape)))
+    return ps
+
+
+def as_channels_last(x: torch.Tensor) -> torch.Tensor:
+    nat.require_cuda(x, "tensor")
+    try:
+        pixel_stride(x)
+        return x
+    except RuntimeError:
+        return x.contiguous(memory_format=torch.channels_last)
+
+
+def new_field(n: int, c: int, h: int, w: int, device) -> torch.Tensor:
+    return torch.zeros((n, c, h, w), dtype=torch.float32, device=device).contiguous(memory_format=torch.channels_last)
+
+
+def new_bits(n: int, h: int, w: int, device) -> torch.Tensor:
+    return torch.zeros(n_tiles(n, h, w), dtype=torch.int64, device=device)
+
+
+class TileMask:
+    """Per-pixel activity of a delta field, stored as one int64 word per 8x8 tile (bit py*8+px)."""
+    __slots__ = ("bits", "n", "h", "w")
+
+    def __init__(self, bits: torch.Tensor, n: int, h: int, w: int):
+        self.bits, self.n, self.h, self.w = bits, n, h, w
+
+    @property
+    def shape(self):
+        return (self.n, 1, self.h, self.w)
+
+    def pixel_mask(self) -> torch.Tensor:
+        """[N,1,H,W] uint8, 1 where the pixel is active."""
+        out = torch.empty((self.n, 1, self.h, self.w), dtype=torch.uint8, device=self.bits.device)
+        nat.check(nat.lib.mie_mask_expand(self.bits.data_ptr(), self.n, self.h, self.w, out.data_ptr(),
+                                          nat.stream_ptr(self.bits.device)), "mask_expand")
+        return out
+
+    def tile_list(self) -> torch.Tensor:
+        """Ascending indices (n*TH+ty)*TW+tx of the active tiles (int32).  Synchronises."""
+        nt = self.bits.numel()
+        lst = torch.empty(nt, dtype=torch.int32, device=self.bits.device)
+        cnt = torch.zeros(4, dtype=torch.int32, device=self.bits.device)
+        nat.check(nat.lib.mie_tiles_compact(self.bits.data_ptr(), nt, lst.data_ptr(), cnt.data_ptr(),
+                                            nat.stream_ptr(self.bits.device)), "tiles_compact")
+        return lst[: int(cnt[0].item())]
+
+    def active_pixels(self) -> int:
+        return int(self.pixel_mask().sum().item())
+
+
+def mask_from_delta(x: torch.Tensor, thr: float = 0.0, bits: Optional[torch.Tensor] = None) -> TileMask:
+    n, c, h, w = x.shape
+    ps = pixel_stride(x)
+    if bits is None:
+        bits = torch.empty(n_tiles(n, h, w), dtype=torch.int64, device=x.device)
+    nat.check(nat.lib.mie_mask_from_delta(x.data_ptr(), ps, n, c, h, w, float(thr), bits.data_ptr(),
+                                          nat.stream_ptr(x.device)), "mask_from_delta")
+    return TileMask(bits, n, h, w)
+
+
+def mask_from_tensor(m: torch.Tensor, bits: Optional[torch.Tensor] = None) -> TileMask:
+    """Tile words from an explicit [N,1,H,W] or [N,C,H,W] mask tensor (bool, uint8 or int32)."""
+    if not m.is_cuda:
+        raise RuntimeError("mask must be a CUDA tensor")
+    if m.dtype == torch.bool:
+        m = m.view(torch.uint8) if m.is_contiguous() or m.is_contiguous(memory_format=torch.channels_last) else m.to(torch.uint8)
+    if m.dtype not in (torch.uint8, torch.int32):
+        m = (m != 0).to(torch.uint8)
+    n, c, h, w = m.shape
+    try:
+        ps = pixel_stride(m)
+    except RuntimeError:
+        m = m.contiguous(memory_format=torch.channels_last)
+        ps = pixel_stride(m)
+    if bits is None:
+        bits = torch.empty(n_tiles(n, h, w), dtype=torch.int64, device=m.device)
+    nat.check(nat.lib.mie_mask_from_mask(m.data_ptr(), m.element_size(), ps, c, n, h, w, bits.data_ptr(),
+                                         nat.stream_ptr(m.device)), "mask_from_mask")
+    return TileMask(bits, n, h, w)
+
+
+class Scratch:
+    """Named persistent device buffers owned by a module, so that steady-state steps allocate nothing
+    (a requirement for replaying a step as a CUDA graph)."""
+
+    def __init__(self):
+        self._b: Dict[Tuple, torch.Tensor] = {}
+
+    def get(self, key, shape, dtype, device, zero: bool = True, channels_last: bool = False) -> torch.Tensor:
+        k = (key, tuple(shape), dtype, str(device))
+        t = self._b.get(k)
+        if t is None:
+            t = torch.zeros(shape, dtype=dtype, device=device) if zero else torch.empty(shape, dtype=dtype, device=device)
+            if channels_last:
+                t = t.contiguous(memory_format=torch.channels_last)
+            self._b[k] = t
+        return t
+
+    def clear(self):
+        self._b.clear()
+
+
+def resolve(x_incr, scratch: Scratch, key: str = "in") -> Tuple[torch.Tensor, TileMask]:
+    """Return (delta as channels-last CUDA tensor, TileMask) for a reference-style ``Masked`` value."""
+    d, m = x_incr[0], x_incr[1]
+    d = as_channels_last(d)
+    n, c, h, w = d.shape
+    if isinstance(m, TileMask):
+        if (m.n, m.h, m.w) != (n, h, w):
+            raise RuntimeError("mask geometry does not match the delta tensor")
+        return d, m
+    bits = scratch.get(key + ".bits", (n_tiles(n, h, w),), torch.int64, d.device)
+    if m is None:
+        return d, mask_from_delta(d, config.input_threshold, bits)
+    return d, mask_from_tensor(m, bits)
+
+
+# ------------------------------------------------------------------------------------------------
+# thin wrappers over the point-wise entry points
+# ------------------------------------------------------------------------------------------------
+ACT_CODES = {"none": nat.ACT_NONE, "relu": nat.ACT_RELU, "sigmoid": nat.ACT_SIGMOID, "tanh": nat.ACT_TANH}
+
+
+def act_code(op) -> int:
+    """MIE_ACT_* for a torch unary function or a name."""
+    if isinstance(op, str):
+        name = op
+    else:
+        name = getattr(op, "__name__", str(op))
+    if name not in ACT_CODES:
+        raise NotImplementedError(f"incremental activation '{name}' has no kernel (relu, sigmoid, tanh do)")
+    return ACT_CODES[name]
+
+
+def act_incr(d, m: TileMask, res, emitted, out, out_bits, op_code: int, thr: float) -> TileMask:
+    n, c, h, w = d.shape
+    nat.check(nat.lib.mie_act_incr(d.data_ptr(), pixel_stride(d), m.bits.data_ptr(), res.data_ptr(), pixel_stride(res),
+                                   nat.ptr(emitted), pixel_stride(emitted) if emitted is not None else 0,
+                                   out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w, op_code,
+                                   float(thr), nat.stream_ptr(d.device)), "act_incr")
+    return TileMask(out_bits, n, h, w)
+
+
+def mul_incr(d1, m1, x1, d2, m2, x2, out, out_bits, thr: float = 0.0) -> TileMask:
+    n, c, h, w = x1.shape
+    nat.check(nat.lib.mie_mul_incr(
+        nat.ptr(d1), pixel_stride(d1) if d1 is not None else 0, m1.bits.data_ptr() if m1 is not None else None,
+        x1.data_ptr(), pixel_stride(x1),
+        nat.ptr(d2), pixel_stride(d2) if d2 is not None else 0, m2.bits.data_ptr() if m2 is not None else None,
+        x2.data_ptr(), pixel_stride(x2), out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w,
+        float(thr), nat.stream_ptr(x1.device)), "mul_incr")
+    return TileMask(out_bits, n, h, w)
+
+
+def upsample2x(a, ma: TileMask, b, mb: Optional[TileMask], out, out_bits, mode: int = nat.UP_BILINEAR) -> TileMask:
+    n, c, h, w = a.shape
+    nat.check(nat.lib.mie_upsample2x(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), nat.ptr(b),
+                                     pixel_stride(b) if b is not None else 0,
+                                     mb.bits.data_ptr() if mb is not None else None, out.data_ptr(), pixel_stride(out),
+                                     out_bits.data_ptr(), n, c, h, w, mode, nat.stream_ptr(a.device)), "upsample2x")
+    return TileMask(out_bits, n, 2 * h, 2 * w)
+
+
+def add(a, ma: TileMask, b, mb: TileMask, out, out_bits) -> TileMask:
+    n, c, h, w = a.shape
+    nat.check(nat.lib.mie_add(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), b.data_ptr(), pixel_stride(b),
+                              mb.bits.data_ptr(), out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w,
+                              nat.stream_ptr(a.device)), "add")
+    return TileMask(out_bits, n, h, w)
+
+
+def cat2(a, ma: TileMask, b, mb: TileMask, out, out_bits) -> TileMask:
+    n, ca, h, w = a.shape
+    cb = b.shape[1]
+    nat.check(nat.lib.mie_cat2(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), ca, b.data_ptr(), pixel_stride(b),
+                               mb.bits.data_ptr(), cb, out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, h, w,
+                               nat.stream_ptr(a.device)), "cat2")
+    return TileMask(out_bits, n, h, w)
+
+
+def accumulate(y, d, m: TileMask) -> None:
+    n, c, h, w = d.shape
+    nat.check(nat.lib.mie_accumulate(y.data_ptr(), pixel_stride(y), d.data_ptr(), pixel_stride(d), m.bits.data_ptr(),
+                                     n, c, h, w, nat.stream_ptr(d.device)), "accumulate")
+
+
+def pack_conv_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
+    """[Cout,Cin,k,k] -> device buffer laid out [k*k][cin_pad][cout_pad]; returns (buffer, cin_pad, cout_pad)."""
+    cout, cin, k, k2 = weight.shape
+    assert k == k2
+    cp, op, nf = C.c_int(), C.c_int(), C.c_int64()
+    nat.check(nat.lib.mie_conv_pack_dims(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims")
+    w = weight.detach().contiguous()
+    buf = torch.empty(nf.value, dtype=torch.float32, device=weight.device)
+    nat.check(nat.lib.mie_pack_conv_weights(w.data_ptr(), cout, cin, k, buf.data_ptr(), nat.stream_ptr(weight.device)),
+              "pack_conv_weights")
+    return buf, cp.value, op.value

@@ -1,0 +1,402 @@
+"""Module wrappers of the masked incremental path (reference: ``incr_modules/mask_incr_modules.py:1-271``).
+
+Every class keeps the reference's name, constructor and two entry points --
+``forward(Masked) -> Masked`` (incremental) and ``forward_refresh_reservoirs(DenseT) -> DenseT`` (dense
+pass that refills the persistent state) -- but the incremental entry points run libmie kernels over the
+active 8x8 tiles and return ``[delta, TileMask]`` instead of ``[delta, None]``.
+"""
+from typing import OrderedDict, Optional, Tuple
+
+import ctypes as C
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import _native as nat
+from .. import fields as fl
+from ..fields import Scratch, TileMask, config
+from .masked_types import DenseT, Masked
+from .mask_incr_functional import IncrementReserve, IncrPointwiseMultiply, bn2d_from_module, conv2d_from_module
+
+
+class IncrementMaskModule(nn.Module):
+    """Interface of an incremental module (reference ``:13-17``)."""
+
+    def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
+        return x
+
+
+class KFencedMaskModule(IncrementMaskModule):
+    """Sigma-delta quantiser with residual carry (reference ``:21-47``): T = carry + dx;
+    q = k*floor(0.5 + T/k); carry = T - q.  The reference builds one into every convolution and never
+    applies it in ``forward``; it is kept for the same reason and evaluated with tensor ops."""
+
+    def __init__(self, tp: float = .1):
+        super().__init__()
+        self.delta = IncrementReserve()
+        self.tp = tp
+        self.k = tp
+
+    def floor_by_k(self, T):
+        return self.k * torch.floor(0.5 + T / self.k)
+
+    def forward(self, incr: Masked) -> Masked:
+        T1 = self.delta.reservoir + incr[0]
+        f_delta = self.floor_by_k(T1)
+        self.delta.update_reservoir(T1 - f_delta)
+        return f_delta, None
+
+    def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
+        self.k = self.tp * torch.norm(x)
+        self.delta.update_reservoir(torch.zeros_like(x))
+        return x
+
+
+class PointwiseMultiplyIncr(IncrementMaskModule):
+    """Incremental product that leaves its reservoirs alone (reference ``:51-64``)."""
+
+    def __init__(self, x1res_module: IncrementReserve, x2res_module: IncrementReserve):
+        super().__init__()
+        self.x1_res: IncrementReserve = x1res_module
+        self.x2_res: IncrementReserve = x2res_module
+
+    def forward(self, x1_incr: Masked, x2_incr: Masked) -> Masked:
+        return IncrPointwiseMultiply(x1_incr, self.x1_res, x2_incr, self.x2_res)
+
+    def forward_refresh_reservoirs(self, x1: DenseT, x2: DenseT) -> DenseT:
+        return x1 * x2
+
+
+class nnReservedMultiplication(PointwiseMultiplyIncr):
+    """Incremental product that accumulates both operands (reference ``:67-81``), one fused kernel."""
+
+    def __init__(self):
+        super().__init__(IncrementReserve(), IncrementReserve())
+        self._scratch = Scratch()
+
+    def forward(self, x1_incr: Masked, x2_incr: Masked) -> Masked:
+        d1, m1 = fl.resolve(x1_incr, self._scratch, "in1")
+        d2, m2 = fl.resolve(x2_incr, self._scratch, "in2")
+        n, c, h, w = d1.shape
+        out = self._scratch.get("out", (n, c, h, w), torch.float32, d1.device, channels_last=True)
+        bits = self._scratch.get("out.bits", (fl.n_tiles(n, h, w),), torch.int64, d1.device)
+        m = fl.mul_incr(d1, m1, self.x1_res.reservoir, d2, m2, self.x2_res.reservoir, out, bits)
+        return [out, m]
+
+    def forward_refresh_reservoirs(self, x1: DenseT, x2: DenseT) -> DenseT:
+        out = x1 * x2
+        self.x1_res.update_reservoir(x1)
+        self.x2_res.update_reservoir(x2)
+        return out
+
+
+class NonlinearPointOpIncr(IncrementMaskModule):
+    """dy = op(res + dx) - op(res) against an external reservoir, which it does not update
+    (reference ``:86-103``)."""
+
+    def __init__(self, res_in: IncrementReserve, op=torch.tanh):
+        super().__init__()
+        self.reservoir_in = res_in
+        self.op = op
+
+    def forward(self, x_incr: Masked) -> Masked:
+        return self._nonlin(x_incr)
+
+    def forward_refresh_reservoirs(self, x: DenseT):
+        return self.op(x)
+
+    def _nonlin(self, x_incr: Masked):
+        keep = self.reservoir_in.reservoir.clone()
+        out = nnReservedActivation._run(self, x_incr, self.reservoir_in)
+        self.reservoir_in.reservoir.copy_(keep)
+        return out
+
+
+class nnReservedActivation(NonlinearPointOpIncr):
+    """Incremental activation with its own reservoir (reference ``:243-256``):
+    dy = op(res + dx) - op(res); res += dx -- one kernel, evaluated on active pixels only.
+
+    ``threshold`` (default: ``fields.config.threshold``) withholds pixels whose output change is at most
+    the threshold in every channel; with ``fields.config.carry`` what is withheld stays pending in a second
+    buffer and is sent once it grows, so the error downstream is bounded by the threshold."""
+
+    def __init__(self, op=torch.relu, threshold: Optional[float] = None):
+        self.in_res = IncrementReserve()
+        NonlinearPointOpIncr.__init__(self, self.in_res, op)
+        self.threshold = threshold
+        self.emitted: Optional[torch.Tensor] = None
+        self._scratch = Scratch()
+
+    # -- shared by the stand-alone path and NonlinearPointOpIncr ---------------------------------
+    def thr(self) -> float:
+        t = getattr(self, "threshold", None)
+        return float(config.threshold if t is None else t)
+
+    def carry_buffer(self, thr: float) -> Optional[torch.Tensor]:
+        """The buffer of what has been sent so far; created from the reservoir when first needed."""
+        if thr <= 0.0 or not config.carry:
+            return None
+        r = self.in_res.reservoir
+        if self.emitted is None or self.emitted.shape != r.shape or self.emitted.device != r.device:
+            self.emitted = self.op(r).contiguous(memory_format=torch.channels_last)
+        return self.emitted
+
+    @staticmethod
+    def _run(self, x_incr: Masked, reserve: IncrementReserve):
+        d = x_incr[0]
+        nat.require_cuda(d, "x_incr")
+        code = fl.act_code(self.op)
+        res = reserve.reservoir
+        if res is None:
+            raise RuntimeError("forward_refresh_reservoirs must run before the first incremental step")
+        if d.dim() != 4:
+            # any-shape dense form, as the reference's native entry point takes it (ops.cpp:8-23)
+            if not (d.is_contiguous() and res.is_contiguous()):
+                raise RuntimeError("x_incr must be contiguous")  # CHECK_CONTIGUOUS, include/checks.h:7
+            out = torch.empty_like(d)
+            nat.check(nat.lib.mie_activation_increment(res.data_ptr(), d.data_ptr(), out.data_ptr(), d.numel(), code,
+                                                       nat.stream_ptr(d.device)), "activation_increment")
+            return [out, x_incr[1]]
+        sc = getattr(self, "_scratch", None)
+        if sc is None:
+            sc = self._scratch = Scratch()
+        d, m = fl.resolve(x_incr, sc, "in")
+        n, c, h, w = d.shape
+        out = sc.get("out", (n, c, h, w), torch.float32, d.device, channels_last=True)
+        bits = sc.get("out.bits", (fl.n_tiles(n, h, w),), torch.int64, d.device)
+        thr = self.thr() if isinstance(self, nnReservedActivation) else 0.0
+        em = self.carry_buffer(thr) if isinstance(self, nnReservedActivation) else None
+        mo = fl.act_incr(d, m, res, em, out, bits, code, thr)
+        return [out, mo]
+
+    def forward(self, x_incr: Masked):
+        return nnReservedActivation._run(self, x_incr, self.in_res)
+
+    def forward_refresh_reservoirs(self, x: DenseT):
+        out = self.op(x)
+        self.in_res.update_reservoir(x)
+        if self.emitted is not None:
+            if self.emitted.shape == out.shape:
+                self.emitted.copy_(out)
+            else:
+                self.emitted = None
+        return out
+
+
+class nnReluIncr(nnReservedActivation):
+    def __init__(self):
+        nnReservedActivation.__init__(self, torch.relu)
+
+
+class nnSigmoidIncr(nnReservedActivation):
+    def __init__(self):
+        nnReservedActivation.__init__(self, torch.sigmoid)
+
+
+class nnTanhIncr(nnReservedActivation):
+    def __init__(self):
+        nnReservedActivation.__init__(self, torch.tanh)
+
+
+class nnLinearIncr(nn.Linear):
+    """Fully connected layer on a delta: no bias (reference ``:106-116``)."""
+
+    def forward(self, x_incr: Masked) -> Masked:
+        return F.linear(x_incr[0], self.weight, bias=None), None
+
+    def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
+        return super().forward(x)
+
+
+def _square(v) -> int:
+    if isinstance(v, (tuple, list)):
+        if len(v) != 2 or v[0] != v[1]:
+            raise NotImplementedError("only square kernels / equal strides and paddings have a kernel")
+        return int(v[0])
+    return int(v)
+
+
+class _ConvPlan:
+    """Device buffers and the argument block of one convolution at one input geometry."""
+
+    def __init__(self, conv: "nnConvIncr", n: int, hin: int, win: int, device):
+        k, s, p = conv._k, conv._s, conv._p
+        self.hout, self.wout = fl.conv_out_hw(hin, win, k, s, p)
+        if self.hout <= 0 or self.wout <= 0:
+            raise RuntimeError("convolution output would be empty")
+        nt = fl.n_tiles(n, self.hout, self.wout)
+        self.ntiles = nt
+        self.out = fl.new_field(n, conv.out_channels, self.hout, self.wout, device)
+        self.out_bits = torch.zeros(nt, dtype=torch.int64, device=device)
+        self.list = torch.zeros(nt, dtype=torch.int32, device=device)
+        self.stale = torch.zeros(nt, dtype=torch.int32, device=device)
+        self.counts = torch.zeros(4, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(nt, dtype=torch.uint8, device=device)
+        a = nat.ConvArgs()
+        a.hin, a.win, a.n, a.hout, a.wout = hin, win, n, self.hout, self.wout
+        a.k, a.stride, a.pad = k, s, p
+        a.list, a.stale, a.counts, a.max_tiles = self.list.data_ptr(), self.stale.data_ptr(), self.counts.data_ptr(), nt
+        a.out, a.out_ps, a.out_bits = self.out.data_ptr(), fl.pixel_stride(self.out), self.out_bits.data_ptr()
+        self.args = a
+        self.mask = TileMask(self.out_bits, n, self.hout, self.wout)
+
+
+class nnConvIncr(nn.Conv2d):
+    """Convolution of a masked delta (reference ``:146-196``).
+
+    incremental: out = conv(dx, W) without bias over the output tiles the active input pixels reach,
+                 optionally with the following incremental activation and a residual delta fused in;
+    refresh:     dense convolution with bias (a library call; it refills nothing by itself)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, bias=True):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, bias=bias)
+        self.kf = KFencedMaskModule(0.3)
+        self._k, self._s, self._p = _square(self.kernel_size), _square(self.stride), _square(self.padding)
+        self._packed = {}   # cin_limit -> (version, device, buffer, cin_pad, cout_pad)
+        self._plans = {}
+        self._cw = None
+        self._scratch = Scratch()
+
+    # The reference keeps a [Cin,kH,kW,Cout] copy of the filter in this attribute (``:156``).
+    @property
+    def conv2d_weights(self):
+        v = (self.weight._version, self.weight.device)
+        if self._cw is None or self._cw[0] != v:
+            self._cw = (v, torch.permute(self.weight.detach(), (1, 2, 3, 0)).contiguous())
+        return self._cw[1]
+
+    def load_state_dict(self, state_dict: 'OrderedDict[str, torch.Tensor]', strict: bool = True):
+        r = nn.Conv2d.load_state_dict(self, state_dict, strict=strict)
+        self._packed.clear()
+        self._cw = None
+        return r
+
+    def _weights(self, cin_limit: Optional[int] = None):
+        """Packed filter for the kernels, repacked whenever the parameter changed or moved."""
+        key = cin_limit or self.in_channels
+        ver = (self.weight._version, self.weight.device, self.weight.data_ptr())
+        hit = self._packed.get(key)
+        if hit is None or hit[0] != ver:
+            w = self.weight.detach()
+            if key != self.in_channels:
+                w = w[:, :key].contiguous()
+            buf, cp, op = fl.pack_conv_weights(w.float())
+            hit = (ver, buf, cp, op)
+            self._packed[key] = hit
+        return hit[1], hit[2], hit[3]
+
+    def _plan(self, n, hin, win, device) -> _ConvPlan:
+        if self.dilation != (1, 1) or self.groups != 1 or self.padding_mode != "zeros":
+            raise NotImplementedError("dilated / grouped / non-zero-padded convolutions have no kernel")
+        key = (n, hin, win, str(device))
+        p = self._plans.get(key)
+        if p is None:
+            p = self._plans[key] = _ConvPlan(self, n, hin, win, device)
+        return p
+
+    def forward_fused(self, x_incr: Masked, activation: "Optional[nnReservedActivation]" = None,
+                      addend: Optional[Masked] = None, cin_limit: Optional[int] = None) -> Masked:
+        """conv(dx) [+ addend] [-> incremental activation], one dilation launch and one convolution launch."""
+        sc = self._scratch
+        d, m = fl.resolve(x_incr, sc, "in")
+        n, cin, hin, win = d.shape
+        cin_eff = cin_limit or self.in_channels
+        if cin != cin_eff:
+            raise RuntimeError(f"expected {cin_eff} input channels, got {cin}")
+        plan = self._plan(n, hin, win, d.device)
+        wbuf, cp, op = self._weights(cin_limit)
+        a = plan.args
+        union = None
+        if addend is not None:
+            ad, am = fl.resolve(addend, sc, "addend")
+            if ad.shape != plan.out.shape:
+                raise RuntimeError("residual delta must have the convolution's output shape")
+            union = am.bits.data_ptr()
+            a.addend, a.addend_ps = ad.data_ptr(), fl.pixel_stride(ad)
+        else:
+            a.addend, a.addend_ps = None, 0
+        st = nat.stream_ptr(d.device)
+        nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), n, hin, win, plan.hout, plan.wout, self._k, self._s,
+                                           self._p, union, plan.out_bits.data_ptr(), plan.list.data_ptr(),
+                                           plan.stale.data_ptr(), plan.counts.data_ptr(), plan.flags.data_ptr(), st),
+                  "tiles_dilate")
+        a.in_, a.in_ps, a.cin = d.data_ptr(), fl.pixel_stride(d), cin
+        a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, self.out_channels, op
+        if activation is not None:
+            res = activation.in_res.reservoir
+            if res is None:
+                raise RuntimeError("forward_refresh_reservoirs must run before the first incremental step")
+            if res.shape != plan.out.shape:
+                raise RuntimeError("activation reservoir does not match the convolution output")
+            thr = activation.thr()
+            em = activation.carry_buffer(thr)
+            a.act, a.thr = fl.act_code(activation.op), thr
+            a.res, a.res_ps = res.data_ptr(), fl.pixel_stride(res)
+            a.emitted, a.emitted_ps = (em.data_ptr(), fl.pixel_stride(em)) if em is not None else (None, 0)
+        else:
+            a.act, a.thr, a.res, a.res_ps, a.emitted, a.emitted_ps = nat.ACT_NONE, 0.0, None, 0, None, 0
+        nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
+        return [plan.out, plan.mask]
+
+    def forward(self, x_incr):
+        return self.forward_fused(x_incr)
+
+    def forward_refresh_reservoirs(self, x):
+        # The reference also resets its (never applied) quantiser here, which costs a norm and a
+        # zero tensor of the input's size per convolution (``:193``); nothing reads either.
+        return nn.Conv2d.forward(self, x)
+
+
+class nnConvIncrBase(nnConvIncr):
+    """The reference's variant that always routes through ``conv2d_from_module`` (``:122-142``)."""
+
+    def forward(self, x_incr):
+        return conv2d_from_module(x_incr, self.conv2d_weights, stride=self.stride, padding=self.padding)
+
+
+class nnBatchNorm2dIncr(nn.BatchNorm2d):
+    """Eval batch-norm: a per-channel scale on a delta (reference ``:200-207``)."""
+
+    def forward(self, x_incr):
+        return bn2d_from_module(x_incr, self)
+
+    def forward_refresh_reservoirs(self, x):
+        return super().forward(x)
+
+
+class nnMaxPool2dIncr(nn.MaxPool2d):
+    """mp(res + dx) - mp(res); res += dx (reference ``:210-225``).  Tensor ops: no network in scope uses it."""
+
+    def __init__(self, kernel_size, stride=None, padding=0):
+        nn.MaxPool2d.__init__(self, kernel_size=kernel_size, stride=stride, padding=padding)
+        self.functional = lambda x: F.max_pool2d(x, kernel_size=self.kernel_size, stride=self.stride, padding=self.padding)
+        self.mp_res = IncrementReserve()
+
+    def forward(self, x_incr: Masked) -> Masked:
+        out = self.functional(self.mp_res.reservoir + x_incr[0]) - self.functional(self.mp_res.reservoir)
+        self.mp_res.accumulate(x_incr)
+        return out, None
+
+    def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
+        self.mp_res.update_reservoir(x)
+        return super().forward(x)
+
+
+class nnAdaptiveAvgPool2dIncr(nn.AdaptiveAvgPool2d):
+    """Linear, so applied to the delta as is (reference ``:228-233``)."""
+
+    def forward(self, x_incr):
+        return nn.AdaptiveAvgPool2d.forward(self, x_incr[0]), None
+
+    def forward_refresh_reservoirs(self, x):
+        return super().forward(x)
+
+
+class nnSequentialIncr(nn.Sequential):
+    """Chains ``forward_refresh_reservoirs`` (reference ``:236-240``)."""
+
+    def forward_refresh_reservoirs(self, x):
+        for module in self:
+            x = module.forward_refresh_reservoirs(x)
+        return x

@@ -1,0 +1,130 @@
+"""The reference's driver protocol as a small runtime.
+
+Every driver of the reference runs the same loop (``run_e2depth_continuous_dataset.py:55-74``,
+``run_fireflownet.py:85-109``, ``run_evflownet.py:91-115``):
+
+    frame 0, N, 2N, ...:  y = model.forward_refresh_reservoirs(x)            # dense pass, refills the state
+    other frames:         dy = model((x - x_prev, None)[, None]); y += dy[0]   # incremental pass
+
+``IncrementalRunner`` does exactly that with static device buffers, and replays the incremental step
+(input delta, every kernel of the network, output accumulation) as one CUDA graph: the kernels read their
+tile counts from device memory and run on fixed grids, so one captured graph serves every step whatever
+the activity is.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import fields as fl
+from .fields import TileMask
+
+
+def _deltas_of(out) -> List:
+    """The list of ``[delta, mask]`` outputs in whatever structure the network returns."""
+    if isinstance(out, dict):
+        return list(out["flow"])
+    if isinstance(out, tuple) and len(out) == 2 and isinstance(out[1], list) and not torch.is_tensor(out[0]):
+        # E2Depth: (pred_incr, states_incr)
+        return [out[0]]
+    if isinstance(out, (list, tuple)) and len(out) and isinstance(out[0], (list, tuple)):
+        return list(out)
+    raise TypeError("unrecognised network output")
+
+
+def _dense_of(out) -> List[torch.Tensor]:
+    if isinstance(out, dict):
+        return list(out["flow"])
+    if isinstance(out, tuple) and len(out) == 2 and isinstance(out[1], list):
+        return [out[0]]
+    if isinstance(out, (list, tuple)):
+        return list(out)
+    return [out]
+
+
+class IncrementalRunner:
+    """Runs one batch of independent event streams through a network with the refresh / delta protocol.
+
+    model          E2VIDRecurrentIncr, FireFlowNetIncr or MultiResUNetRecurrentIncr (takes ``prev_states`` iff
+                   it is the first)
+    use_graph      replay the incremental step as a CUDA graph (captured on the second incremental step)
+    refresh_every  dense refresh period in frames (None: only when ``refresh`` is called)
+    """
+
+    def __init__(self, model, use_graph: bool = True, refresh_every: Optional[int] = None):
+        self.model = model
+        self.use_graph = use_graph
+        self.refresh_every = refresh_every
+        self.takes_states = hasattr(model, "unetrecurrent") or hasattr(model, "encoders") and hasattr(model, "head")
+        self._x_prev = self._x_in = self._dx = None
+        self._y: List[torch.Tensor] = []
+        self._graph = None
+        self._eager_steps = 0
+        self._frame = 0
+        self.graph_replays = 0
+
+    # -- dense pass ------------------------------------------------------------------------------
+    def refresh(self, x: torch.Tensor):
+        x = fl.as_channels_last(x)
+        if hasattr(self.model, "reset_states"):
+            self.model.reset_states()
+        with torch.no_grad():
+            out = self.model.forward_refresh_reservoirs(x, None) if self.takes_states else \
+                self.model.forward_refresh_reservoirs(x)
+        ys = _dense_of(out)
+        if self._x_prev is None or self._x_prev.shape != x.shape:
+            self._x_prev = x.clone(memory_format=torch.channels_last)
+            self._x_in = torch.empty_like(self._x_prev)
+            self._dx = torch.zeros_like(self._x_prev)
+            self._y = [y.detach().clone().contiguous(memory_format=torch.channels_last) for y in ys]
+            self._graph = None
+            self._eager_steps = 0
+        else:
+            self._x_prev.copy_(x)
+            for dst, src in zip(self._y, ys):
+                dst.copy_(src)
+        self._frame = 1
+        return self._y[0] if len(self._y) == 1 else self._y
+
+    # -- incremental pass ------------------------------------------------------------------------
+    def _step_body(self):
+        torch.sub(self._x_in, self._x_prev, out=self._dx)
+        self._x_prev.copy_(self._x_in)
+        x_incr = (self._dx, None)
+        out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
+        for y, d in zip(self._y, _deltas_of(out)):
+            m = d[1]
+            if isinstance(m, TileMask):
+                fl.accumulate(y, d[0], m)
+            else:
+                y.add_(d[0])
+
+    def step(self, x: torch.Tensor):
+        if self._x_prev is None:
+            raise RuntimeError("call refresh() on the first frame")
+        if self.refresh_every and self._frame % self.refresh_every == 0:
+            return self.refresh(x)
+        self._x_in.copy_(x, non_blocking=True)
+        with torch.no_grad():
+            if self._graph is not None:
+                self._graph.replay()
+                self.graph_replays += 1
+            elif self.use_graph and self._eager_steps >= 1:
+                # every persistent buffer exists after one eager step; capture from now on
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._step_body()
+                self._graph = g
+                g.replay()
+                self.graph_replays += 1
+            else:
+                self._step_body()
+                self._eager_steps += 1
+        self._frame += 1
+        return self._y[0] if len(self._y) == 1 else self._y
+
+    @property
+    def output(self):
+        return self._y[0] if len(self._y) == 1 else self._y

@@ -1,0 +1,206 @@
+"""Network-level parity on the GPU: ConvLSTM cell and the three incremental networks against the golden
+vectors the reference produced (compat="reference") and against a dense recompute (compat="exact")."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from maskedincrementeval_b200.synthetic import seeded_state_dict  # noqa: E402
+from oracle import restatement as R  # noqa: E402
+from test_oracle import e2depth_shapes, flow_shapes_ev, flow_shapes_fire  # noqa: E402
+
+T = torch.from_numpy
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.backends.cudnn.allow_tf32 = False   # dense refresh in full fp32, as eval_e2depth_continuous_inputs.py:3-4
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return torch.device("cuda:0")
+
+
+def cl(t, dev):
+    return t.to(dev).contiguous(memory_format=torch.channels_last)
+
+
+def close(a, b, tol=1e-4, rng=None):
+    a, b = a.detach().float().cpu(), b.detach().float().cpu()
+    assert a.shape == b.shape, (a.shape, b.shape)
+    rng = rng or max(float(b.max() - b.min()), 1e-6)
+    err = float((a - b).abs().max())
+    assert err <= tol * rng, (err, rng)
+
+
+def sparse_delta(g, shape, frac, std=0.5):
+    n, c, h, w = shape
+    act = (torch.rand(n, 1, h, w, generator=g) < frac).float()
+    return torch.randn(shape, generator=g) * std * act
+
+
+def test_convlstm_golden(dev, golden):
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLSTMIncr
+    g = golden("convlstm")
+    cell = ConvLSTMIncr(6, 6, 3).to(dev).eval()
+    cell.load_state_dict(seeded_state_dict({k: tuple(v.shape) for k, v in cell.state_dict().items()}, int(g["seed"]),
+                                           "kaiming_normal"))
+    with torch.no_grad():
+        h0, c0 = cell.forward_refresh_reservoirs(cl(T(g["x"]), dev), None)
+        close(h0, T(g["h0"]), 1e-5)
+        close(c0, T(g["c0"]), 1e-5)
+        for s in (1, 2):
+            hid, cel = cell([cl(T(g[f"d{s}"]), dev), None], None)
+            close(hid[0], T(g[f"dh{s}"]), 1e-4, rng=float(T(g["h0"]).max() - T(g["h0"]).min()))
+            close(cel[0], T(g[f"dc{s}"]), 1e-4, rng=float(T(g["c0"]).max() - T(g["c0"]).min()))
+
+
+def test_convlstm_state_feedback_exact(dev):
+    """Feeding the returned state deltas back (no reference driver does) tracks the dense recurrence."""
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLSTMIncr
+    g = torch.Generator().manual_seed(2)
+    cell = ConvLSTMIncr(8, 8, 3).to(dev).eval()
+    cell.compat = "exact"
+    sd = seeded_state_dict({k: tuple(v.shape) for k, v in cell.state_dict().items()}, 5, "kaiming_normal")
+    cell.load_state_dict(sd)
+    orc = R.ConvLSTMOracle(sd["Gates.weight"], sd["Gates.bias"], "exact")
+    x = torch.randn(1, 8, 24, 32, generator=g)
+    with torch.no_grad():
+        h, c = cell.forward_refresh_reservoirs(cl(x, dev), None)
+        orc.refresh(x)
+        st = ([h.clone(), None], [c.clone(), None])      # first step: delta against the zero state
+        ost = (h.cpu().clone(), c.cpu().clone())
+        for step in range(4):
+            dx = sparse_delta(g, x.shape, 0.1)
+            hid, cel = cell([cl(dx, dev), None], st)
+            oh, oc = orc.step(dx, ost)
+            close(hid[0], oh, 1e-4, rng=2.0)
+            close(cel[0], oc, 1e-4, rng=2.0)
+            st = ([hid[0].clone(), hid[1]], [cel[0].clone(), cel[1]])
+            ost = (oh, oc)
+
+
+def _e2depth(dev, base, seed, compat):
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    net = E2VIDRecurrentIncr(dict(num_bins=5, num_encoders=3, base_num_channels=base, num_residual_blocks=2,
+                                  skip_type="sum", norm=None, use_upsample_conv=True, compat=compat)).to(dev).eval()
+    sd = seeded_state_dict(e2depth_shapes(base), seed, "kaiming_normal")
+    net.load_state_dict(sd)
+    return net, sd
+
+
+def test_e2depth_golden_reference_compat(dev, golden):
+    g = golden("e2depth_small")
+    net, _ = _e2depth(dev, int(g["base"]), int(g["seed"]), "reference")
+    with torch.no_grad():
+        y0, st = net.forward_refresh_reservoirs(cl(T(g["x"]), dev), None)
+        close(y0, T(g["y0"]), 1e-5)
+        close(st[0][0], T(g["h0_0"]), 1e-5)
+        rng = float(T(g["y0"]).max() - T(g["y0"]).min())
+        for s in (1, 2, 3):
+            dy, sti = net([cl(T(g[f"d{s}"]), dev), None], None)
+            close(dy[0], T(g[f"dy{s}"]), 1e-4, rng=rng)
+            close(sti[2][0][0], T(g[f"dh{s}_2"]), 1e-4, rng=1.0)
+
+
+def test_e2depth_exact_drift_vs_dense_64_steps(dev):
+    """compat="exact": accumulated incremental output vs dense recompute over 64 steps, 1e-4 of the range."""
+    net, sd = _e2depth(dev, 8, 77, "exact")
+    dense, _ = _e2depth(dev, 8, 77, "exact")
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, 5, 64, 96, generator=g)
+    with torch.no_grad():
+        y, _ = net.forward_refresh_reservoirs(cl(x, dev), None)
+        y = y.clone()
+        worst = 0.0
+        for step in range(64):
+            dx = sparse_delta(g, x.shape, 0.05)
+            x = x + dx
+            dy, _ = net([cl(dx, dev), None], None)
+            y += dy[0]
+            if step % 8 == 7 or step < 2:
+                yd, _ = dense.forward_refresh_reservoirs(cl(x, dev), None)
+                rng = float(yd.max() - yd.min())
+                worst = max(worst, float((y - yd).abs().max()) / rng)
+        assert worst <= 1e-4, worst
+
+
+def test_e2depth_batch_and_oracle_exact(dev):
+    """Batch of 2 streams, odd-ish size (48x72), against the CPU oracle in exact mode."""
+    net, sd = _e2depth(dev, 4, 13, "exact")
+    orc = R.E2DepthOracle(sd, compat="exact")
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 5, 48, 72, generator=g)
+    with torch.no_grad():
+        y, _ = net.forward_refresh_reservoirs(cl(x, dev), None)
+        yo, _ = orc.refresh(x)
+        close(y, yo, 1e-5)
+        rng = float(yo.max() - yo.min())
+        for step in range(3):
+            dx = sparse_delta(g, x.shape, 0.05)
+            dx[1] = 0  # one stream of the batch is idle
+            dy, _ = net([cl(dx, dev), None], None)
+            do, _ = orc.step(dx)
+            close(dy[0], do, 1e-4, rng=rng)
+            assert float(dy[0][1].abs().max()) == 0.0
+
+
+def test_fireflownet_golden_and_exact(dev, golden):
+    from maskedincrementeval_b200.incr_modules.fireflownet_incr import FireFlowNetIncr
+    g = golden("fireflownet_small")
+    kw = dict(base_num_channels=8, kernel_size=3, mask_output=False)
+    sd = seeded_state_dict(flow_shapes_fire(8), int(g["seed"]), "kaiming_normal")
+    net = FireFlowNetIncr(kw, 2, compat="reference").to(dev).eval()
+    net.load_state_dict(sd)
+    with torch.no_grad():
+        y0 = net.forward_refresh_reservoirs(cl(T(g["x"]), dev))["flow"][0]
+        close(y0, T(g["y0"]), 1e-5)
+        for s in (1, 2, 3):
+            dy = net([cl(T(g[f"d{s}"]), dev), None])["flow"][0]
+            close(dy[0], T(g[f"dy{s}"]), 1e-4, rng=2.0)
+        # exact wiring tracks a dense recompute
+        ex = FireFlowNetIncr(kw, 2, compat="exact").to(dev).eval()
+        de = FireFlowNetIncr(kw, 2, compat="exact").to(dev).eval()
+        ex.load_state_dict(sd), de.load_state_dict(sd)
+        x = T(g["x"])
+        y = ex.forward_refresh_reservoirs(cl(x, dev))["flow"][0].clone()
+        for s in (1, 2, 3):
+            x = x + T(g[f"d{s}"])
+            y += ex([cl(T(g[f"d{s}"]), dev), None])["flow"][0][0]
+            close(y, de.forward_refresh_reservoirs(cl(x, dev))["flow"][0], 1e-4, rng=2.0)
+
+
+def test_evflownet_golden(dev, golden):
+    from maskedincrementeval_b200.incr_modules.evflownet_incr import MultiResUNetRecurrentIncr
+    g = golden("evflownet_small")
+    net = MultiResUNetRecurrentIncr(compat="reference").to(dev).eval()
+    net.load_state_dict(seeded_state_dict(flow_shapes_ev(), int(g["seed"]), "kaiming_normal"))
+    with torch.no_grad():
+        for i, p in enumerate(net.forward_refresh_reservoirs(cl(T(g["x"]), dev))):
+            close(p, T(g[f"y0_{i}"]), 1e-5, rng=2.0)
+        for s in (1, 2):
+            for i, p in enumerate(net([cl(T(g[f"d{s}"]), dev), None])):
+                close(p[0], T(g[f"dy{s}_{i}"]), 1e-4, rng=2.0)
+
+
+def test_driver_protocol_with_graph_replay(dev):
+    """The reference's driver loop (run_e2depth_continuous_dataset.py:55-74): refresh, then delta steps
+    accumulated by the caller -- here with the step replayed as a CUDA graph."""
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    net, sd = _e2depth(dev, 8, 3, "exact")
+    eager, _ = _e2depth(dev, 8, 3, "exact")
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(1, 5, 64, 96, generator=g)
+    run = IncrementalRunner(net, use_graph=True)
+    with torch.no_grad():
+        y = run.refresh(cl(x, dev)).clone()
+        ye, _ = eager.forward_refresh_reservoirs(cl(x, dev), None)
+        ye = ye.clone()
+        for step in range(5):
+            x = x + sparse_delta(g, x.shape, 0.05)
+            y = run.step(cl(x, dev))
+            pass
+        yd, _ = eager.forward_refresh_reservoirs(cl(x, dev), None)
+        close(y, yd, 1e-4)
+    assert run.graph_replays >= 3
