@@ -1,0 +1,455 @@
+"""Benchmark of the masked incremental path: incremental E2Depth timesteps per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("e2depth_260x346_b1", BASELINE config 3): the E2Depth recurrent UNet (5-bin voxel input,
+head 32 ch, 3 ConvLSTM encoders 64/128/256, 2 residual blocks, 3 decoders, sigmoid head), random-init
+weights (PyTorch's default convolution init, what the reference's random-init network has), one event
+stream per GPU.  Every window draws 30k synthetic events from 10 drifting edge segments plus 5% uniform
+noise and bins them into a 5-bin voxel grid at 260x346, reflection-padded to 264x352 as the reference's
+driver does; a step feeds the network the delta against the previous grid and accumulates the output
+delta.  One dense refresh precedes the timed steps.  Synthetic events stand in for the DAVIS recordings
+the reference reads from disk, which are not available.
+
+One step = one incremental timestep of every stream of the rank.  The timed steps are replayed as a CUDA
+graph; L2 is flushed (256 MB write) before every timed step and each step is timed with its own pair of
+CUDA events on the launching stream, so the flush is outside the measured time.  With N GPUs every rank
+runs its own streams (no communication on the data path); the reported time per step is the maximum
+over ranks and the value is the sum of the streams' timesteps divided by it.
+
+The JSON line also carries
+  e2e          the same metric through IncrementalRunner.step with the voxel grid in pinned host memory
+               and the accumulated prediction read back to the host every step
+  roofline     the masked conv3x3 32->32 + incremental ReLU kernel of BASELINE config 1 (260x346, 5%
+               active pixels, drifting blobs), timed alone: algorithmic bytes touched / launch time
+  cpu_baseline the CPU restatement of the reference's incremental E2Depth step on this box's host cores
+  dense        the dense recompute (forward_refresh_reservoirs every step, cuDNN) for context
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "incremental timesteps/sec/GPU, E2Depth 260x346 @5% active; conv3x3 HBM GB/s"
+UNIT = "timesteps/s"
+WORKLOAD = "e2depth_260x346_b1"
+H, W, BINS, EVENTS, SEGMENTS = 260, 346, 5, 30000, 10
+E2DEPTH_CFG = dict(num_bins=BINS, skip_type="sum", recurrent_block_type="convlstm", num_encoders=3,
+                   base_num_channels=32, num_residual_blocks=2, norm=None, use_upsample_conv=True)
+
+
+def e2depth_shapes(base=32, bins=BINS, ne=3, nr=2):
+    s = {}
+    p = "unetrecurrent."
+
+    def conv(name, co, ci, k):
+        s[p + name + ".weight"] = (co, ci, k, k)
+        s[p + name + ".bias"] = (co,)
+
+    conv("head.conv2d", base, bins, 5)
+    for i in range(ne):
+        ci, co = base * 2 ** i, base * 2 ** (i + 1)
+        conv(f"encoders.{i}.conv.conv2d", co, ci, 5)
+        conv(f"encoders.{i}.recurrent_block.Gates", 4 * co, 2 * co, 3)
+    cm = base * 2 ** ne
+    for i in range(nr):
+        conv(f"resblocks.{i}.conv1", cm, cm, 3)
+        conv(f"resblocks.{i}.conv2", cm, cm, 3)
+    for i in range(ne):
+        ci = base * 2 ** (ne - i)
+        conv(f"decoders.{i}.conv2d", ci // 2, ci, 5)
+    conv("pred.conv2d", 1, base, 1)
+    return s
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])), mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's incremental step
+# --------------------------------------------------------------------------------------------------
+def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 25.0):
+    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+    from oracle.restatement import E2DepthOracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sd = seeded_state_dict(e2depth_shapes(), seed=0, init="default")
+    net = E2DepthOracle(sd, compat="reference")
+    frames = voxel_sequence(1, H, W, warmup + steps + 1, EVENTS, SEGMENTS, seed=0)
+    frames = [f.contiguous() for f in frames]
+    with torch.no_grad():
+        net.refresh(frames[0])
+        t_used, times = 0.0, []
+        for i in range(1, len(frames)):
+            dx = frames[i] - frames[i - 1]
+            t0 = time.perf_counter()
+            net.step(dx)
+            dt = time.perf_counter() - t0
+            if i > warmup:
+                times.append(dt)
+                t_used += dt
+            if t_used > budget_s:
+                break
+    ms = 1e3 * sum(times) / max(len(times), 1)
+    return {"value": 1e3 / ms, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{len(times)} incremental E2Depth steps at 264x352, batch 1, after a dense refresh; "
+                      f"torch {torch.__version__} CPU with {cores} threads", "ms_per_step": ms, "steps": len(times)}
+
+
+def run_reference_impl(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb = cpu_reference_arm(max(args.steps, 1), max(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": cb["steps"], "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "the reference's own (activity-independent) incremental step, "
+                       "restated on CPU; the reference checkout does not exist on this box"},
+            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def l2_flusher(dev):
+    buf = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+    return lambda: buf.fill_(1.0)
+
+
+def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3):
+    """BASELINE config 1: conv3x3 32->32 + incremental ReLU, 260x346, batch 1, 16 drifting-blob deltas at 5%."""
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    from maskedincrementeval_b200.synthetic import blob_delta_sequence, seeded_state_dict
+    layer = ConvLayerIncr(32, 32, 3, 1, 1, activation="relu").to(dev).eval()
+    sd = seeded_state_dict({"conv2d.weight": (32, 32, 3, 3), "conv2d.bias": (32,)}, 0, "kaiming_normal")
+    layer.load_state_dict(sd)
+    g = torch.Generator().manual_seed(0)
+    x0 = torch.randn(1, 32, H, W, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
+    deltas = [d.to(dev) for d in blob_delta_sequence(1, 32, H, W, 16, 0.05, seed=0)]
+    flush = l2_flusher(dev)
+    conv = layer.conv2d
+    times, tiles, stales, px = [], [], [], []
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(x0)
+        layer([deltas[0], None])  # allocate everything
+        st = torch.cuda.current_stream(dev)
+        for rep in range(repeats + 1):
+            layer.forward_refresh_reservoirs(x0)
+            for d in deltas:
+                m = fl.mask_from_delta(d, 1e-3, conv._scratch.get("in.bits", (fl.n_tiles(1, H, W),), torch.int64, dev))
+                plan = conv._plan(1, H, W, dev)
+                nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), 1, H, W, H, W, 3, 1, 1, None,
+                                                   plan.out_bits.data_ptr(), plan.list.data_ptr(),
+                                                   plan.stale.data_ptr(), plan.counts.data_ptr(),
+                                                   plan.flags.data_ptr(), st.cuda_stream), "dilate")
+                a = plan.args
+                a.in_, a.in_ps, a.cin = d.data_ptr(), 32, 32
+                wbuf, cp, op = conv._weights()
+                a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, 32, op
+                res = layer.activation.in_res.reservoir
+                a.act, a.thr, a.res, a.res_ps = nat.ACT_RELU, 0.0, res.data_ptr(), 32
+                a.emitted, a.emitted_ps, a.addend, a.addend_ps = None, 0, None, 0
+                flush()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                import ctypes as C
+                nat.check(nat.lib.mie_conv_tiles(C.byref(a), st.cuda_stream), "conv_tiles")
+                e1.record(st)
+                e1.synchronize()
+                if rep > 0:
+                    c = plan.counts.cpu().tolist()
+                    times.append(e0.elapsed_time(e1) * 1e-3)
+                    tiles.append(c[0]), stales.append(c[1])
+                    px.append(float(m.pixel_mask().float().mean()))
+    # algorithmic bytes of one launch: per active output tile 10*10*32*4 (input + halo) + 64*32*4*3
+    # (reservoir read, reservoir write, delta write) + 8 (tile word); weights once; stale tiles zeroed
+    per_tile = 10 * 10 * 32 * 4 + 64 * 32 * 4 * 3 + 8
+    byts = [t * per_tile + 9 * 32 * 32 * 4 + s * 64 * 32 * 4 for t, s in zip(tiles, stales)]
+    flops = [t * 64 * 32 * 9 * 32 * 2 for t in tiles]
+    tot_t = sum(times)
+    achieved = sum(byts) / tot_t / 1e9
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    if os.path.exists(tp):
+        try:
+            traffic = json.load(open(tp)).get("conv3x3_c1_dram_bytes_per_launch")
+        except Exception:
+            traffic = None
+    return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_tiles_kernel<3,1,4,1> (conv3x3 32->32 + ReLU, 260x346)",
+            "bytes_per_launch": sum(byts) / len(byts), "us_per_launch": 1e6 * tot_t / len(times),
+            "active_tiles_mean": sum(tiles) / len(tiles), "tiles_total": fl.n_tiles(1, H, W),
+            "active_pixel_frac": sum(px) / len(px), "fp32_tflops": sum(flops) / tot_t / 1e12, "launches": len(times)}
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+    import maskedincrementeval_b200 as mie
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+
+    mie.config.compat = "exact"
+    mie.config.threshold = args.threshold
+    streams = args.streams
+    K, Wm = args.steps, args.warmup
+    sd = seeded_state_dict(e2depth_shapes(), seed=0, init="default")
+
+    def make_net():
+        net = E2VIDRecurrentIncr(dict(E2DEPTH_CFG)).to(dev).eval()
+        net.load_state_dict(sd)
+        return net
+
+    net = make_net()
+    n_frames = Wm + K + 2
+    frames_host = voxel_sequence(streams, H, W, n_frames, EVENTS, SEGMENTS, seed=100 + rank)
+    frames_pinned = [f.pin_memory() for f in frames_host]
+    frames_dev = [f.to(dev) for f in frames_host]
+    in_bytes = frames_host[0].numel() * 4
+    run = IncrementalRunner(net, use_graph=True)
+    flush = l2_flusher(dev)
+    st = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm -----------------------------------------------------------------
+    run.refresh(frames_dev[0])
+    nat.reset_launch_count()
+    run.step(frames_dev[1])                      # eager step: allocates every persistent buffer
+    launches_per_step = nat.launch_count()
+    for i in range(2, 2 + Wm):                   # graph captured on the first of these
+        run.step(frames_dev[i])
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    t_wall0 = time.perf_counter()
+    ev = []
+    for i in range(K):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        run.step(frames_dev[2 + Wm + i])
+        e1.record(st)
+        ev.append((e0, e1))
+    barrier()
+    wall = time.perf_counter() - t_wall0
+    clocks = sampler.stop()
+    dev_s = sum(a.elapsed_time(b) for a, b in ev) * 1e-3
+    y_incr = run.output.clone()
+
+    # parity of what was just timed: accumulated incremental output vs a dense recompute of the last frame
+    dense = make_net()
+    with torch.no_grad():
+        yd, _ = dense.forward_refresh_reservoirs(frames_dev[2 + Wm + K - 1], None)
+    rng = float(yd.max() - yd.min())
+    parity = float((y_incr - yd).abs().max()) / max(rng, 1e-12)
+
+    # ---- end-to-end arm: pinned host input, prediction read back every step ---------------------
+    run.refresh(frames_dev[0])
+    out_host = torch.empty(run.output.shape, dtype=torch.float32).pin_memory()
+    for i in range(1, 2 + Wm):
+        run.step(frames_pinned[i].to(dev, non_blocking=True))
+    barrier()
+    e2e_ev = []
+    for i in range(K):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        y = run.step(frames_pinned[2 + Wm + i].to(dev, non_blocking=True))
+        out_host.copy_(y, non_blocking=True)
+        e1.record(st)
+        e1.synchronize()
+        e2e_ev.append((e0, e1))
+    barrier()
+    e2e_s = sum(a.elapsed_time(b) for a, b in e2e_ev) * 1e-3
+    out_bytes = out_host.numel() * 4
+
+    # ---- max over ranks ------------------------------------------------------------------------------
+    t = torch.tensor([dev_s, e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_s, e2e_s = float(t[0]), float(t[1])
+
+    if rank == 0:
+        total_steps = K * streams * world
+        line = {
+            "metric": METRIC, "value": total_steps / dev_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
+            "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": "260x346 padded to 264x352",
+                       "events_per_window": EVENTS, "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold,
+                       "weights": "random init (nn.Conv2d default), seed 0", "parallelism": f"{world} x independent streams",
+                       "l2": "flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
+                       "execution": "one CUDA graph replay per step"},
+            "clocks": clocks, "gpu_launches": launches_per_step * K,
+            "e2e": {"value": total_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": in_bytes,
+                    "d2h_bytes_per_step": out_bytes, "ms_per_step": 1e3 * e2e_s / K},
+            "parity": {"max_abs_err_over_range_vs_dense_recompute": parity, "after_steps": 1 + Wm + K, "tolerance": 1e-4},
+            "wall_s_timed_region": wall,
+        }
+        if world == 1:
+            peak, kind = load_peaks()
+            line["roofline"] = roofline_conv3x3(dev, peak, kind)
+            # dense recompute (the >=10x target's denominator), same frames
+            def time_dense(tf32):
+                torch.backends.cudnn.allow_tf32 = tf32
+                with torch.no_grad():
+                    for i in range(3):
+                        dense.forward_refresh_reservoirs(frames_dev[i], None)
+                    torch.cuda.synchronize()
+                    ts = []
+                    for i in range(min(K, 10)):
+                        flush()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(st)
+                        dense.forward_refresh_reservoirs(frames_dev[2 + i], None)
+                        e1.record(st)
+                        e1.synchronize()
+                        ts.append(e0.elapsed_time(e1))
+                torch.backends.cudnn.allow_tf32 = False
+                return sum(ts) / len(ts)
+            line["dense"] = {"ms_per_step_fp32": time_dense(False), "ms_per_step_tf32": time_dense(True),
+                             "note": "forward_refresh_reservoirs every step (cuDNN), same frames; context only"}
+            line["activity"] = activity_table(net, run, frames_dev[2 + Wm + K], dev)
+            line["cpu_baseline"] = {k: v for k, v in cpu_reference_arm(20, 2).items()
+                                    if k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def activity_table(net, run, frame, dev):
+    """Active pixel / tile fractions of each convolution's input on one more (eager) step."""
+    from maskedincrementeval_b200.fields import TileMask
+    rows = {}
+    hooks = []
+
+    def hook(name):
+        def f(mod, inp, out):
+            m = out[1] if isinstance(out, (list, tuple)) and isinstance(out[1], TileMask) else None
+            if m is not None:
+                rows[name] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4),
+                              "tiles": round(int((m.bits != 0).sum()) / m.bits.numel(), 4)}
+        return f
+    u = net.unetrecurrent
+    named = [("head", u.head)] + [(f"enc{i}", e) for i, e in enumerate(u.encoders)] + \
+            [(f"res{i}", r) for i, r in enumerate(u.resblocks)] + [(f"dec{i}", d) for i, d in enumerate(u.decoders)]
+    for n, mod in named:
+        hooks.append(mod.register_forward_hook(hook(n)))
+    with torch.no_grad():
+        dx = (frame - run._x_prev).contiguous(memory_format=torch.channels_last)
+        rows["input"] = {"px": round(float((dx != 0).any(1).float().mean()), 4)}
+        out = net((dx, None), None)
+        m = out[0][1]
+        rows["pred"] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4)}
+    for h in hooks:
+        h.remove()
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--streams", type=int, default=1, help="event streams per GPU (batch dimension)")
+    ap.add_argument("--threshold", type=float, default=0.0,
+                    help="activation threshold with residual carry; 0 = lossless (the headline)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_impl(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

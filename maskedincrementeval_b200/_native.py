@@ -83,11 +83,26 @@ class MieError(RuntimeError):
     pass
 
 
-def check(status: int, what: str = "") -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library enqueued through `check` since the last reset (host-side counter)."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def check(status: int, what: str = "", launches: int = 1) -> None:
     """Map a libmie status to the exception class the reference raises for the same condition:
     unsupported kernel size / stride -> NotImplementedError (ext/pointops/pointops_functional.py:41),
     everything else -> RuntimeError (TORCH_CHECK, include/checks.h:6-8)."""
     if status == OK:
+        global _launches
+        _launches += launches
         return
     msg = lib.mie_status_string(status).decode()
     if status == ECUDA:

@@ -249,7 +249,7 @@ def pack_conv_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
     cout, cin, k, k2 = weight.shape
     assert k == k2
     cp, op, nf = C.c_int(), C.c_int(), C.c_int64()
-    nat.check(nat.lib.mie_conv_pack_dims(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims")
+    nat.check(nat.lib.mie_conv_pack_dims(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims", 0)
     w = weight.detach().contiguous()
     buf = torch.empty(nf.value, dtype=torch.float32, device=weight.device)
     nat.check(nat.lib.mie_pack_conv_weights(w.data_ptr(), cout, cin, k, buf.data_ptr(), nat.stream_ptr(weight.device)),

@@ -16,6 +16,8 @@ T = torch.from_numpy
 def dev():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
+    torch.backends.cudnn.allow_tf32 = False   # dense refresh in full fp32 (eval_e2depth_continuous_inputs.py:3-4)
+    torch.backends.cuda.matmul.allow_tf32 = False
     return torch.device("cuda:0")
 
 
@@ -137,8 +139,8 @@ def test_activation_golden(dev, golden, op, tag):
     if op == "relu":
         assert torch.equal(o1.cpu(), k("o1").cpu()) and torch.equal(o2.cpu(), k("o2").cpu())
     else:
-        close(o1, k("o1"), 1e-6)
-        close(o2, k("o2"), 1e-6)
+        close(o1, k("o1"), 1e-5)   # a few ulp of sigmoid/tanh values against a delta of smaller range
+        close(o2, k("o2"), 1e-5)
 
 
 @pytest.mark.parametrize("tag", ["ref_test", "k5s2", "k1", "k3s2", "k5s1"])
