@@ -284,7 +284,7 @@ def run_ours(args):
         return net
 
     net = make_net()
-    n_frames = Wm + K + 2
+    n_frames = Wm + K + 3
     frames_host = voxel_sequence(streams, H, W, n_frames, EVENTS, SEGMENTS, seed=100 + rank)
     frames_pinned = [f.pin_memory() for f in frames_host]
     frames_dev = [f.to(dev) for f in frames_host]
@@ -358,6 +358,8 @@ def run_ours(args):
 
     if rank == 0:
         total_steps = K * streams * world
+        print(f"[bench] device {1e3 * dev_s / K:.3f} ms/step, e2e {1e3 * e2e_s / K:.3f} ms/step, "
+              f"{launches_per_step} launches/step, parity {parity:.2e}", file=sys.stderr)
         line = {
             "metric": METRIC, "value": total_steps / dev_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
