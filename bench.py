@@ -444,7 +444,16 @@ def main():
     ap.add_argument("--streams", type=int, default=1, help="event streams per GPU (batch dimension)")
     ap.add_argument("--threshold", type=float, default=0.0,
                     help="activation threshold with residual carry; 0 = lossless (the headline)")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
     args = ap.parse_args()
+    if args.roofline_only:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        torch.backends.cudnn.allow_tf32 = False
+        peak, kind = load_peaks()
+        print(json.dumps(roofline_conv3x3(dev, peak, kind, repeats=1)))
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
