@@ -184,7 +184,7 @@ def l2_flusher(dev):
     return lambda: buf.fill_(1.0)
 
 
-def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3):
+def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
     """BASELINE config 1: conv3x3 32->32 + incremental ReLU, 260x346, batch 1, 16 drifting-blob deltas at 5%."""
     from maskedincrementeval_b200 import _native as nat
     from maskedincrementeval_b200 import fields as fl
@@ -214,7 +214,8 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3):
                                                    plan.flags.data_ptr(), st.cuda_stream), "dilate")
                 a = plan.args
                 a.in_, a.in_ps, a.cin = d.data_ptr(), 32, 32
-                wbuf, cp, op = conv._weights()
+                wbuf, cp, op, wtc = conv._weights()
+                a.wpacked_tc = wtc.data_ptr() if (wtc is not None and args_tc) else None
                 a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, 32, op
                 res = layer.activation.in_res.reservoir
                 a.act, a.thr, a.res, a.res_ps = nat.ACT_RELU, 0.0, res.data_ptr(), 32

@@ -105,13 +105,24 @@ typedef struct mie_conv_args {
   float *res; int64_t res_ps;
   float *emitted; int64_t emitted_ps;
   const float *addend; int64_t addend_ps;
+  /* optional second copy of the filter packed by mie_pack_conv_weights_tc ([k*k][cout_pad][cin_pad32], TF32
+   * rounded).  When given, and the layer qualifies (Cin*k*k >= 256, 16-byte aligned channel strides, ...), the
+   * convolution runs on the tensor cores (tcgen05, TF32 inputs, FP32 accumulation); otherwise on the FP32 path. */
+  const float *wpacked_tc;
 } mie_conv_args;
 
 int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);
 
+/* Host only, no device work: 1 if mie_conv_tiles would run these arguments on the tensor cores, else 0. */
+int mie_conv_uses_tensor_cores(const mie_conv_args *args /* host */);
+
 /* Host helper (no device work): floats needed for the packed copy of a [cout,cin,k,k] filter, and
  * the padded extents the kernels assume. */
 int mie_conv_pack_dims(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats);
+
+/* Same for the tensor-core copy: cin padded to 32, layout [k*k][cout_pad][cin_pad]. */
+int mie_conv_pack_dims_tc(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats);
+int mie_pack_conv_weights_tc(const float *w_oihw, int cout, int cin, int k, float *wpacked, void *stream);
 
 /* wpacked[(ky*k+kx)][ci][co] <- w[co][ci][ky][kx] (PyTorch OIHW, contiguous), zero padded.
  * The reference keeps a [Cin,kH,kW,Cout] copy for the same purpose

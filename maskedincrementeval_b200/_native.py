@@ -33,6 +33,7 @@ class ConvArgs(C.Structure):
         ("res", _vp), ("res_ps", _i64),
         ("emitted", _vp), ("emitted_ps", _i64),
         ("addend", _vp), ("addend_ps", _i64),
+        ("wpacked_tc", _vp),
     ]
 
 
@@ -47,8 +48,11 @@ SIGNATURES = {
     "mie_mask_expand": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mie_tiles_dilate": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mie_conv_tiles": (_i, [C.POINTER(ConvArgs), _vp]),
+    "mie_conv_uses_tensor_cores": (_i, [C.POINTER(ConvArgs)]),
     "mie_conv_pack_dims": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "mie_pack_conv_weights": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "mie_conv_pack_dims_tc": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
+    "mie_pack_conv_weights_tc": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mie_activation_increment": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "mie_conv_increment_workspace_bytes": (_i64, [_i, _i, _i, _i, _i, _i, _i]),
     "mie_conv_increment_ext": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i64, _vp]),
@@ -66,7 +70,7 @@ SIGNATURES = {
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m maskedincrementeval_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python maskedincrementeval_b200/build.py` "
             "(nvcc, sm_100a).  This package has no fallback path.")
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

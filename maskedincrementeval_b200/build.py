@@ -1,6 +1,6 @@
 """Build libmie.so (hand-written CUDA for sm_100a, C ABI) next to this file.
 
-    python -m maskedincrementeval_b200.build [--force] [--verbose]
+    python maskedincrementeval_b200/build.py [--force] [--verbose]
 
 nvcc cross-compiles for sm_100a without a GPU.  The shared library is kept in the package directory
 so that it travels with the source tree; it is never installed into site-packages.
@@ -18,7 +18,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(HERE, "libmie.so")
-SOURCES = ["mie_mask.cu", "mie_conv.cu", "mie_pointwise.cu"]
+SOURCES = ["mie_mask.cu", "mie_conv.cu", "mie_conv_tc.cu", "mie_pointwise.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--extended-lambda", "-I", INCLUDE, "-I", CSRC]
 

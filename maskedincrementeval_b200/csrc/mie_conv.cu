@@ -15,6 +15,11 @@
 
 using namespace mie;
 
+namespace mie {
+bool tc_eligible(const mie_conv_args *a);
+int launch_conv_tc(const mie_conv_args *a, cudaStream_t st);
+}  // namespace mie
+
 namespace {
 
 struct ConvParams {
@@ -407,6 +412,8 @@ extern "C" int mie_pack_conv_weights(const float *w_oihw, int cout, int cin, int
   return check_launch();
 }
 
+extern "C" int mie_conv_uses_tensor_cores(const mie_conv_args *a) { return (a && tc_eligible(a)) ? 1 : 0; }
+
 extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (!a || !a->in || !a->wpacked || !a->list || !a->counts || !a->out || !a->out_bits) return MIE_EINVAL;
   if (a->cin <= 0 || a->cout <= 0 || a->n <= 0 || a->hin <= 0 || a->win <= 0 || a->hout <= 0 || a->wout <= 0) return MIE_EINVAL;
@@ -417,6 +424,8 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (a->act == MIE_ACT_NONE && a->emitted) return MIE_EINVAL;
   if (a->stride < 1 || a->stride > 2) return MIE_EUNSUPPORTED;
   if (!aligned16(a->wpacked)) return MIE_EALIGN;
+  if (a->wpacked_tc && !aligned16(a->wpacked_tc)) return MIE_EALIGN;
+  if (tc_eligible(a)) return launch_conv_tc(a, (cudaStream_t)stream);
 
   ConvParams p;
   p.in = a->in; p.in_ps = a->in_ps; p.cin = a->cin; p.hin = a->hin; p.win = a->win;

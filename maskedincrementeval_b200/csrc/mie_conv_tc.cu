@@ -1,0 +1,525 @@
+// Masked delta convolution on the 5th-generation tensor cores (tcgen05, TF32 inputs, FP32 accumulation in
+// tensor memory) for layers whose reduction depth Cin*k*k makes a dense contraction pay off.
+//
+// Implicit GEMM over the compact list of active 8x8 output tiles:
+//   M = 128 rows   = 2 active tiles x 64 pixels (one tensor-memory lane per pixel)
+//   N = NB columns = up to 256 output channels (one tensor-memory column per channel)
+//   K              = Cin * k * k, walked as (32-channel chunk, filter tap); one pipeline stage per (chunk, tap).
+// Stage contents, both moved by TMA (tiled mode, 128-byte swizzle, no cluster, no multicast):
+//   A: for each of the two tiles a box [1 image][8 rows][8 cols][32 channels] of the input field, shifted by
+//      the tap; out-of-image elements are zero-filled by the TMA unit, which is the convolution padding.
+//      The box lands as 64 rows of 128 bytes in pixel order = the K-major operand layout tcgen05.mma reads.
+//      Stride-2 layers read from four parity views of the input (one tensor map per row/column parity).
+//   B: box [1 tap][NB output channels][32 input channels] of the filter, stored [tap][cout][cin].
+// Roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and owner of the
+// tensor-memory allocation, warps 2..5 = epilogue (tcgen05.ld, fused incremental activation, tile words).
+// Every mbarrier wait is bounded; on expiry the block raises counts[3], leaves its loops, frees its tensor
+// memory and returns.
+#include <cuda.h>
+#include <string.h>
+#include "mie_common.cuh"
+
+using namespace mie;
+
+namespace mie {
+
+struct TcParams {
+  int cin, cout, cout_pad, cin_pad;   // cin_pad: multiple of 32 (filter K extent)
+  int n, hin, win, hout, wout, k, stride, pad;
+  const int32_t *list; const int32_t *stale; int32_t *counts; int max_tiles;
+  float *out; int64_t out_ps; unsigned int *out_bits32;
+  int act; float thr;
+  float *res; int64_t res_ps;
+  float *emitted; int64_t emitted_ps;
+  const float *addend; int64_t addend_ps;
+  int nb;        // output channels per block (multiple of 16, <= 256)
+  int stages;    // pipeline depth
+};
+
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr int A_STAGE_BYTES = 128 * 128;  // 128 pixels x 32 channels x 4 B
+constexpr unsigned SPIN_LIMIT = 1u << 20;
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait on a phase parity.  Returns false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, volatile int *abort_flag) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+      "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+      "r"(c2)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled
+// K-major), [32,46) stride offset>>4, [46,48) version = 1, [61,64) layout = 2 (128-byte swizzle).
+__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32, FP32 accumulator, both operands K-major, M = 128.
+__device__ __forceinline__ unsigned make_idesc_tf32(int n) {
+  unsigned d = 0;
+  d |= 1u << 4;                 // accumulator format F32
+  d |= 2u << 7;                 // A format TF32
+  d |= 2u << 10;                // B format TF32
+  d |= (unsigned)(n >> 3) << 17;
+  d |= (unsigned)(128 >> 4) << 24;
+  return d;
+}
+
+__device__ __forceinline__ void umma_tf32(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcMaps {
+  CUtensorMap in[4];  // stride 1: [0] only; stride 2: [row parity * 2 + column parity]
+  CUtensorMap w;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // 1024-byte alignment of every stage is what the 128-byte swizzle of TMA and of the MMA descriptors assume
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int NB = p.nb;
+  const int stage_bytes = A_STAGE_BYTES + NB * 128;
+  __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full, acc_empty;
+  __shared__ unsigned s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
+  const int ntiles_total = p.n * THo * TWo;
+  unsigned tmem_cols = 32;
+  while ((int)tmem_cols < NB) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_full, 1);
+    mbar_init(&acc_empty, 4);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = s_tmem_base;
+
+  // ---- zero stale tiles (all threads) ----------------------------------------------------------------
+  {
+    const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
+    for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
+      const int t = p.stale[s];
+      if (t < 0 || t >= ntiles_total) { if (tid == 0) p.counts[3] = 1; continue; }
+      const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+      for (int i = tid; i < 64 * p.cout; i += TC_THREADS) {
+        const int px = i / p.cout, c = i - px * p.cout;
+        const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
+        if (oy < p.hout && ox < p.wout) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
+      }
+    }
+  }
+
+  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_pairs = (n_active + 1) >> 1;
+  const int n_cblk = p.cout_pad / NB;
+  const int n_items = n_pairs * n_cblk;
+  const int n_chunks = p.cin_pad >> 5;
+  const int taps = p.k * p.k;
+  const int k_iters = n_chunks * taps;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      unsigned it_global = 0;
+      for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+        const int pair = item / n_cblk, cb = item - pair * n_cblk;
+        int t0 = p.list[2 * pair];
+        int t1 = (2 * pair + 1 < n_active) ? p.list[2 * pair + 1] : -1;
+        if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
+        const int tx0 = t0 % TWo, ty0 = (t0 / TWo) % THo, n0 = t0 / (TWo * THo);
+        const int tx1 = (t1 >= 0) ? t1 % TWo : 0, ty1 = (t1 >= 0) ? (t1 / TWo) % THo : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
+        const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + NB * 128;
+        for (int ki = 0; ki < k_iters; ++ki, ++it_global) {
+          const int s = it_global % p.stages;
+          const unsigned ph = (it_global / p.stages) & 1u;
+          if (it_global >= (unsigned)p.stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &s_abort)) break;
+          const int chunk = ki / taps, tap = ki - chunk * taps;
+          const int ky = tap / p.k, kx = tap - ky * p.k;
+          unsigned char *stage = smem + (size_t)s * stage_bytes;
+          mbar_expect_tx(&full_bar[s], tx_bytes);
+          int dy = ky - p.pad, dx = kx - p.pad, mi = 0;
+          if (p.stride == 2) {
+            const int py = dy & 1, pxp = dx & 1;
+            mi = py * 2 + pxp;
+            dy = (dy - py) >> 1;
+            dx = (dx - pxp) >> 1;
+          }
+          tma_load_4d(stage, &maps.in[mi], &full_bar[s], chunk * 32, tx0 * 8 + dx, ty0 * 8 + dy, n0);
+          if (t1 >= 0) tma_load_4d(stage + A_STAGE_BYTES / 2, &maps.in[mi], &full_bar[s], chunk * 32, tx1 * 8 + dx, ty1 * 8 + dy, n1);
+          tma_load_3d(stage + A_STAGE_BYTES, &maps.w, &full_bar[s], chunk * 32, cb * NB, tap);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const unsigned idesc = make_idesc_tf32(NB);
+      unsigned it_global = 0, item_idx = 0;
+      for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
+        // the epilogue must have drained the accumulator of the previous item
+        if (item_idx > 0 && !mbar_wait(&acc_empty, (item_idx - 1) & 1u, &s_abort)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int ki = 0; ki < k_iters; ++ki, ++it_global) {
+          const int s = it_global % p.stages;
+          const unsigned ph = (it_global / p.stages) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, &s_abort)) { ok = false; break; }
+          tc_fence_after();
+          const unsigned a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+          const unsigned b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // 4 x (K = 8 tf32 = 32 bytes) inside the 128-byte swizzled row
+            umma_tf32(tmem_base, make_smem_desc(a_addr + kk * 32), make_smem_desc(b_addr + kk * 32), idesc,
+                      (ki > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // arrives once the MMAs above have finished reading the stage
+        }
+        if (!ok) break;
+        umma_commit(&acc_full);
+      }
+    }
+  } else {
+    // =========================== epilogue (warps 2..5) ===========================
+    const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
+    const int m = q * 32 + lane;      // accumulator row = pixel of the pair
+    const int slot = m >> 6, pxi = m & 63;
+    unsigned item_idx = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
+      const int pair = item / n_cblk, cb = item - pair * n_cblk;
+      const int li = 2 * pair + slot;
+      int t = (li < n_active) ? p.list[li] : -1;
+      if (t >= ntiles_total) t = -1;
+      if (!mbar_wait(&acc_full, item_idx & 1u, &s_abort)) break;
+      tc_fence_after();
+      const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
+      const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
+      const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
+      const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      const int co0 = cb * NB;
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16);
+      bool flag = false;
+      // pass A: does this pixel carry any change (skips reservoir traffic for untouched pixels of the tile)
+      bool any_d = false;
+      if (p.act != MIE_ACT_NONE && !p.emitted) {
+        for (int c = 0; c < NB; c += 16) {
+          float v[16];
+          tmem_ld16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) any_d |= (v[j] != 0.0f);
+        }
+        if (valid && p.addend && !any_d)
+          for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
+      } else {
+        any_d = true;
+      }
+      for (int c = 0; c < NB; c += 16) {
+        float v[16];
+        tmem_ld16(taddr + c, v);  // every lane of the warp takes part (aligned), valid or not
+        if (!valid) continue;
+        const int co = co0 + c;
+        if (co >= p.cout) continue;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const int cc = co + h * 4;
+          if (cc >= p.cout) break;
+          float4 d = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
+          if (p.addend) {
+            const float4 a = *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + cc);
+            d.x += a.x; d.y += a.y; d.z += a.z; d.w += a.w;
+          }
+          if (p.act != MIE_ACT_NONE) {
+            if (any_d) {
+              float4 *rp = reinterpret_cast<float4 *>(p.res + pix * p.res_ps + cc);
+              const float4 x = *rp;
+              const float4 xn = make_float4(x.x + d.x, x.y + d.y, x.z + d.z, x.w + d.w);
+              *rp = xn;
+              float4 base;
+              if (p.emitted) base = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + cc);
+              else base = make_float4(act_apply(p.act, x.x), act_apply(p.act, x.y), act_apply(p.act, x.z), act_apply(p.act, x.w));
+              d = make_float4(act_apply(p.act, xn.x) - base.x, act_apply(p.act, xn.y) - base.y,
+                              act_apply(p.act, xn.z) - base.z, act_apply(p.act, xn.w) - base.w);
+            } else {
+              d = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          flag |= fabsf(d.x) > p.thr || fabsf(d.y) > p.thr || fabsf(d.z) > p.thr || fabsf(d.w) > p.thr;
+          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + cc) = d;
+        }
+      }
+      // the accumulator has been read: hand tensor memory back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty);
+      // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
+      // selects this kernel with thr > 0 when one block holds every channel of a pixel.
+      if (valid && (p.thr > 0.0f || p.emitted)) {
+        const int cend = min(NB, p.cout - co0);
+        if (!flag) {
+          for (int c = 0; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if (p.emitted) {
+          for (int c = 0; c < cend; c += 4) {
+            const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
+            float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
+            float4 e = *ep;
+            e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
+            *ep = e;
+          }
+        }
+      }
+      const unsigned half = __ballot_sync(0xffffffffu, valid && flag);
+      if (lane == 0 && t >= 0 && half) {
+        unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
+        if (n_cblk > 1) atomicOr(wp, half);
+        else *wp = half;
+      }
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
+    if (tid == 0) p.counts[3] = 2;
+    // give copies that may still be in flight time to land before shared memory is released
+    if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void *ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+    if (e != cudaSuccess) set_cuda_error(e);
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+bool encode(EncodeTiledFn fn, CUtensorMap *m, int rank, const void *base, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
+            const cuuint32_t *box) {
+  cuuint32_t es[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims, strides_bytes, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Whether the tensor-core path can take this convolution (host-side rules only).
+bool tc_eligible(const mie_conv_args *a) {
+  if (!a->wpacked_tc) return false;
+  if (!(a->stride == 1 || a->stride == 2)) return false;
+  if (a->k != 1 && a->k != 3 && a->k != 5 && a->k != 7) return false;
+  if (a->cin % 4 || a->in_ps % 4 || !aligned16(a->in)) return false;            // TMA: 16-byte strides and base
+  if (a->cout % 4 || a->out_ps % 4 || !aligned16(a->out)) return false;          // float4 epilogue
+  if (a->res && (a->res_ps % 4 || !aligned16(a->res))) return false;
+  if (a->emitted && (a->emitted_ps % 4 || !aligned16(a->emitted))) return false;
+  if (a->addend && (a->addend_ps % 4 || !aligned16(a->addend))) return false;
+  if (a->cout_pad % 16) return false;
+  if (a->thr > 0.0f && a->cout_pad > 256) return false;
+  if ((int64_t)a->cin * a->k * a->k < 256) return false;                         // too shallow to pay off
+  if (a->stride == 2 && ((a->hin & 1) || (a->win & 1))) return false;            // parity views need even extents
+  return true;
+}
+
+int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
+  EncodeTiledFn fn = get_encode();
+  if (!fn) return MIE_ECUDA;
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.cin = a->cin; p.cout = a->cout; p.cout_pad = a->cout_pad;
+  p.cin_pad = (a->cin + 31) / 32 * 32;
+  p.n = a->n; p.hin = a->hin; p.win = a->win; p.hout = a->hout; p.wout = a->wout;
+  p.k = a->k; p.stride = a->stride; p.pad = a->pad;
+  p.list = a->list; p.stale = a->stale; p.counts = a->counts; p.max_tiles = a->max_tiles;
+  p.out = a->out; p.out_ps = a->out_ps; p.out_bits32 = reinterpret_cast<unsigned int *>(a->out_bits);
+  p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
+  p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
+  // channels per block: everything when it fits 256 accumulator columns, else 256
+  int nb = a->cout_pad <= 256 ? a->cout_pad : 256;
+  if (a->cout_pad % nb) nb = 128;
+  if (a->cout_pad % nb) nb = 64;
+  if (a->cout_pad % nb) nb = 32;
+  if (a->cout_pad % nb) nb = 16;
+  p.nb = nb;
+  const int stage_bytes = A_STAGE_BYTES + nb * 128;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return MIE_EUNSUPPORTED;
+  p.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+
+  TcMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const cuuint32_t box_in[4] = {32, 8, 8, 1};
+  if (a->stride == 1) {
+    const cuuint64_t dims[4] = {(cuuint64_t)a->cin, (cuuint64_t)a->win, (cuuint64_t)a->hin, (cuuint64_t)a->n};
+    const cuuint64_t str[3] = {(cuuint64_t)a->in_ps * 4, (cuuint64_t)a->win * a->in_ps * 4, (cuuint64_t)a->hin * a->win * a->in_ps * 4};
+    if (!encode(fn, &maps.in[0], 4, a->in, dims, str, box_in)) return MIE_EINVAL;
+  } else {
+    for (int py = 0; py < 2; ++py)
+      for (int px = 0; px < 2; ++px) {
+        const cuuint64_t dims[4] = {(cuuint64_t)a->cin, (cuuint64_t)((a->win - px + 1) / 2), (cuuint64_t)((a->hin - py + 1) / 2), (cuuint64_t)a->n};
+        const cuuint64_t str[3] = {(cuuint64_t)a->in_ps * 8, (cuuint64_t)a->win * a->in_ps * 8, (cuuint64_t)a->hin * a->win * a->in_ps * 4};
+        const float *base = a->in + ((int64_t)py * a->win + px) * a->in_ps;
+        if (!encode(fn, &maps.in[py * 2 + px], 4, base, dims, str, box_in)) return MIE_EINVAL;
+      }
+  }
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)p.cin_pad, (cuuint64_t)a->cout_pad, (cuuint64_t)(a->k * a->k)};
+    const cuuint64_t str[2] = {(cuuint64_t)p.cin_pad * 4, (cuuint64_t)a->cout_pad * p.cin_pad * 4};
+    const cuuint32_t box_w[3] = {32, (cuuint32_t)nb, 1};
+    if (!encode(fn, &maps.w, 3, a->wpacked_tc, dims, str, box_w)) return MIE_EINVAL;
+  }
+  static int smem_set = 0;
+  if ((int)smem > smem_set) {
+    cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+    smem_set = (int)smem;
+  }
+  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
+  int grid = max_items < MIE_SM_COUNT ? (int)max_items : MIE_SM_COUNT;
+  if (grid < 1) grid = 1;
+  conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
+  return check_launch();
+}
+
+}  // namespace mie
+
+// [k*k][cout_pad][cin_pad32] <- w[cout][cin][ky][kx], rounded to TF32 (round to nearest, ties away), zero padded
+__global__ void pack_weights_tc_kernel(const float *__restrict__ w, int cout, int cin, int k, int cin_pad, int cout_pad,
+                                       float *__restrict__ wp, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int ci = (int)(i % cin_pad);
+    int64_t rest = i / cin_pad;
+    const int co = (int)(rest % cout_pad);
+    const int tap = (int)(rest / cout_pad);
+    float v = 0.0f;
+    if (co < cout && ci < cin) v = w[((int64_t)co * cin + ci) * k * k + tap];
+    unsigned u = __float_as_uint(v);
+    u = (u + 0x1000u) & 0xFFFFE000u;  // keep 10 mantissa bits
+    wp[i] = __uint_as_float(u);
+  }
+}
+
+extern "C" int mie_conv_pack_dims_tc(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats) {
+  if (cin <= 0 || cout <= 0 || k <= 0) return MIE_EINVAL;
+  const int cp = divup(cin, 32) * 32, op = divup(cout, 32) * 32;
+  if (cin_pad) *cin_pad = cp;
+  if (cout_pad) *cout_pad = op;
+  if (n_floats) *n_floats = (int64_t)k * k * cp * op;
+  return MIE_OK;
+}
+
+extern "C" int mie_pack_conv_weights_tc(const float *w_oihw, int cout, int cin, int k, float *wpacked, void *stream) {
+  if (!w_oihw || !wpacked) return MIE_EINVAL;
+  int cp, op;
+  int64_t total;
+  int s = mie_conv_pack_dims_tc(cin, cout, k, &cp, &op, &total);
+  if (s != MIE_OK) return s;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  pack_weights_tc_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w_oihw, cout, cin, k, cp, op, wpacked, total);
+  return check_launch();
+}

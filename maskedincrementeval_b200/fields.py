@@ -31,6 +31,9 @@ class IncrConfig:
     threshold        activation outputs with max_c |dy| <= threshold at a pixel are withheld (0 = lossless)
     carry            keep what was withheld and send it once it grows past the threshold (bounded error)
     input_threshold  threshold used when a mask has to be derived from a bare delta tensor
+    tensor_cores     "auto" runs convolutions whose reduction depth Cin*k*k is at least 256 on the tensor cores
+                     (TF32 inputs, FP32 accumulation; values then agree with FP32 to about 1e-3 of the range);
+                     "off" keeps every convolution on the FP32 path
     compat           "reference": networks wired as the reference is written; "exact": as intended, which
                      makes the accumulated incremental output equal to a dense recompute
     """
@@ -38,6 +41,7 @@ class IncrConfig:
     carry: bool = True
     input_threshold: float = 0.0
     compat: str = "reference"
+    tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
 
 
 config = IncrConfig()
@@ -255,3 +259,16 @@ def pack_conv_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
     nat.check(nat.lib.mie_pack_conv_weights(w.data_ptr(), cout, cin, k, buf.data_ptr(), nat.stream_ptr(weight.device)),
               "pack_conv_weights")
     return buf, cp.value, op.value
+
+
+def pack_conv_weights_tc(weight: torch.Tensor) -> torch.Tensor:
+    """[Cout,Cin,k,k] -> device buffer [k*k][cout_pad][cin_pad32], rounded to TF32, for the tensor-core path."""
+    cout, cin, k, k2 = weight.shape
+    assert k == k2
+    cp, op, nf = C.c_int(), C.c_int(), C.c_int64()
+    nat.check(nat.lib.mie_conv_pack_dims_tc(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims_tc", 0)
+    w = weight.detach().contiguous()
+    buf = torch.empty(nf.value, dtype=torch.float32, device=weight.device)
+    nat.check(nat.lib.mie_pack_conv_weights_tc(w.data_ptr(), cout, cin, k, buf.data_ptr(),
+                                               nat.stream_ptr(weight.device)), "pack_conv_weights_tc")
+    return buf

@@ -282,9 +282,12 @@ class nnConvIncr(nn.Conv2d):
             if key != self.in_channels:
                 w = w[:, :key].contiguous()
             buf, cp, op = fl.pack_conv_weights(w.float())
-            hit = (ver, buf, cp, op)
+            tc = None
+            if key * self._k * self._k >= 256 and key % 4 == 0 and self.out_channels % 4 == 0:
+                tc = fl.pack_conv_weights_tc(w.float())
+            hit = (ver, buf, cp, op, tc)
             self._packed[key] = hit
-        return hit[1], hit[2], hit[3]
+        return hit[1], hit[2], hit[3], hit[4]
 
     def _plan(self, n, hin, win, device) -> _ConvPlan:
         if self.dilation != (1, 1) or self.groups != 1 or self.padding_mode != "zeros":
@@ -305,7 +308,7 @@ class nnConvIncr(nn.Conv2d):
         if cin != cin_eff:
             raise RuntimeError(f"expected {cin_eff} input channels, got {cin}")
         plan = self._plan(n, hin, win, d.device)
-        wbuf, cp, op = self._weights(cin_limit)
+        wbuf, cp, op, wtc = self._weights(cin_limit)
         a = plan.args
         union = None
         if addend is not None:
@@ -323,6 +326,7 @@ class nnConvIncr(nn.Conv2d):
                   "tiles_dilate")
         a.in_, a.in_ps, a.cin = d.data_ptr(), fl.pixel_stride(d), cin
         a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, self.out_channels, op
+        a.wpacked_tc = wtc.data_ptr() if (wtc is not None and config.tensor_cores == "auto") else None
         if activation is not None:
             res = activation.in_res.reservoir
             if res is None:
@@ -337,6 +341,7 @@ class nnConvIncr(nn.Conv2d):
         else:
             a.act, a.thr, a.res, a.res_ps, a.emitted, a.emitted_ps = nat.ACT_NONE, 0.0, None, 0, None, 0
         nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
+        self.last_used_tensor_cores = bool(nat.lib.mie_conv_uses_tensor_cores(C.byref(a)))
         return [plan.out, plan.mask]
 
     def forward(self, x_incr):

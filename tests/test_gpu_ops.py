@@ -21,6 +21,16 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True)
+def fp32_path():
+    """The 1e-4 bars in this file are for the FP32 kernels; the tensor-core tests switch it on themselves."""
+    from maskedincrementeval_b200 import fields as fl
+    old = fl.config.tensor_cores
+    fl.config.tensor_cores = "off"
+    yield
+    fl.config.tensor_cores = old
+
+
 def cl(t, dev):
     return t.to(dev).contiguous(memory_format=torch.channels_last)
 
@@ -327,5 +337,84 @@ def test_thresholded_fused_conv_matches_standalone(dev):
                 dy2, m2 = ref_act(raw)
                 assert torch.equal(pm, m2.pixel_mask())
                 close(dy, dy2, 1e-6)
+    finally:
+        fl.config.threshold = old
+
+
+# ----------------------------------------------------------------------------------------------
+# tensor-core path (tcgen05, TF32 inputs): 2e-3 of the output range
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cfg", [
+    # cin, cout, k, s, n, h, w, act
+    (32, 32, 3, 1, 1, 260, 346, "relu"), (64, 64, 3, 1, 1, 33, 44, "relu"), (128, 256, 3, 1, 1, 24, 40, None),
+    (32, 64, 5, 2, 2, 64, 96, "relu"), (256, 128, 5, 1, 1, 16, 24, "relu"), (64, 512, 3, 1, 1, 16, 16, None),
+    (40, 48, 3, 1, 1, 20, 28, "tanh"), (16, 32, 5, 1, 1, 19, 21, "sigmoid"), (32, 32, 3, 2, 1, 32, 48, "relu"),
+    (512, 16, 1, 1, 1, 9, 11, None)])
+def test_conv_tensor_core_path_vs_oracle(dev, cfg):
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    cin, cout, k, s, n, h, w, act = cfg
+    fl.config.tensor_cores = "auto"
+    g = torch.Generator().manual_seed(cin + cout + k)
+    layer = ConvLayerIncr(cin, cout, k, s, k // 2, activation=act).to(dev).eval()
+    wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()
+    x0 = torch.randn(n, cin, h, w, generator=g)
+    op = act or "none"
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        res = R.conv_dense(x0, wt, b, s, k // 2)
+        sent_total = R._OPS[op](res) if act else None
+        for step, frac in enumerate([0.05, 0.3, 0.0, 1.0, 0.02]):
+            dx = sparse_delta(g, (n, cin, h, w), frac)
+            dy, m = layer([cl(dx, dev), None])
+            assert layer.conv2d.last_used_tensor_cores
+            d = R.conv_delta(dx, wt, s, k // 2)
+            if act:
+                want, res = R.act_incr(res, d, op)
+            else:
+                want = d
+            scale = max(float(want.abs().max()), float(d.abs().max()), 1e-3)
+            assert float((dy.cpu() - want).abs().max()) <= 2e-3 * max(scale, 1.0), (float((dy.cpu() - want).abs().max()), scale)
+            if act:
+                # keep the oracle's state on the GPU's trajectory so that errors do not compound through relu kinks
+                res = layer.activation.in_res.reservoir.cpu().contiguous()
+            pm = m.pixel_mask().cpu()
+            assert float((dy.cpu() * (1 - pm.float())).abs().max()) == 0.0
+            assert torch.equal(pm, (dy.cpu() != 0).any(1, keepdim=True).to(torch.uint8))
+            reach = R.conv_out_mask(R.pixel_mask(dx), k, s, k // 2)
+            assert int((pm & ~reach).sum()) == 0
+            if frac == 0.0:
+                assert int(pm.sum()) == 0
+
+
+def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
+    """Same thresholded layer on both paths: values within the TF32 bar, and the carry keeps the total sent
+    within the threshold of the true output on both."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    g = torch.Generator().manual_seed(21)
+    old = fl.config.threshold
+    try:
+        fl.config.threshold = 0.02
+        layers = []
+        for mode in ("auto", "off"):
+            torch.manual_seed(0)
+            layers.append((mode, ConvLayerIncr(32, 64, 3, 1, 1, activation="tanh").to(dev).eval()))
+        x0 = torch.randn(1, 32, 40, 48, generator=g)
+        with torch.no_grad():
+            ys = []
+            for mode, l in layers:
+                fl.config.tensor_cores = mode
+                ys.append(l.forward_refresh_reservoirs(cl(x0, dev)).clone())
+            for step in range(6):
+                dx = cl(sparse_delta(g, x0.shape, 0.1, std=0.05), dev)
+                for i, (mode, l) in enumerate(layers):
+                    fl.config.tensor_cores = mode
+                    dy, m = l([dx, None])
+                    assert l.conv2d.last_used_tensor_cores == (mode == "auto")
+                    ys[i] += dy
+            truth = torch.tanh(layers[1][1].activation.in_res.reservoir)
+            for y in ys:
+                assert float((y - truth).abs().max()) <= 0.02 + 2e-3
     finally:
         fl.config.threshold = old
