@@ -177,7 +177,8 @@ int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x
  *   cprev  [N,C,H,W]   accumulated previous-cell input of product m2 (only touched if dc_prev given)
  *   cell   [N,C,H,W]   accumulated cell (reservoir of the second tanh)
  *   dc_prev/dcp_bits   incoming previous-cell delta, may be null
- *   dh, dc             outgoing hidden and cell deltas with their masks
+ *   dh, dc             outgoing hidden and cell deltas; their masks are the union of the incoming masks
+ *                      (gate delta | previous-cell delta), pixel for pixel; thr is reserved and must be 0
  *   sum_m2             1: cell delta = m1 + m2 (dense-exact); 0: m1 only, as the reference computes
  *                      (its `+` concatenates two lists, e2depth_incr.py:113) */
 int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, float *g, int64_t g_ps,

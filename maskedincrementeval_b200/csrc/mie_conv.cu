@@ -342,6 +342,99 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// 1x1 convolution to a handful of output channels (prediction heads: 32 -> 1, 64 -> 2, ...).
+// One thread per pixel, one 64-thread group per active tile; the filter sits in shared memory.
+// ---------------------------------------------------------------------------------------------
+constexpr int SMALL_COUT = 4;
+
+__global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) {
+  extern __shared__ float s_w[];  // [cin][SMALL_COUT]
+  const int tid = threadIdx.x, grp = tid >> 6, px = tid & 63, lane = tid & 31;
+  for (int i = tid; i < p.cin * SMALL_COUT; i += blockDim.x) {
+    const int ci = i / SMALL_COUT, co = i - ci * SMALL_COUT;
+    s_w[i] = (co < p.cout) ? p.w[(int64_t)ci * p.cout_pad + co] : 0.0f;
+  }
+  __syncthreads();
+  const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
+  const int ntiles_total = p.n * THo * TWo;
+  unsigned *bits32 = reinterpret_cast<unsigned *>(p.out_bits);
+  const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
+  for (int s = blockIdx.x * 4 + grp; s < n_stale; s += gridDim.x * 4) {
+    const int t = p.stale[s];
+    if (t < 0 || t >= ntiles_total) continue;
+    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+    const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
+    if (oy < p.hout && ox < p.wout)
+      for (int c = 0; c < p.cout; ++c) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
+  }
+  const int n_active = min(p.counts[0], p.max_tiles);
+  for (int li = blockIdx.x * 4 + grp; li < n_active; li += gridDim.x * 4) {
+    const int t = p.list[li];
+    if (t < 0 || t >= ntiles_total) { if (px == 0) p.counts[3] = 1; continue; }
+    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+    const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
+    const bool valid = oy < p.hout && ox < p.wout;
+    bool flag = false;
+    if (valid) {
+      const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;  // 1x1, stride 1: input pixel == output pixel
+      const float *ip = p.in + pix * p.in_ps;
+      float acc[SMALL_COUT] = {0.f, 0.f, 0.f, 0.f};
+      if (p.in_vec) {
+        for (int c = 0; c + 3 < p.cin; c += 4) {
+          const float4 v = *reinterpret_cast<const float4 *>(ip + c);
+          const float *w = s_w + c * SMALL_COUT;
+#pragma unroll
+          for (int j = 0; j < SMALL_COUT; ++j)
+            acc[j] += v.x * w[j] + v.y * w[SMALL_COUT + j] + v.z * w[2 * SMALL_COUT + j] + v.w * w[3 * SMALL_COUT + j];
+        }
+        for (int c = p.cin & ~3; c < p.cin; ++c)
+#pragma unroll
+          for (int j = 0; j < SMALL_COUT; ++j) acc[j] += ip[c] * s_w[c * SMALL_COUT + j];
+      } else {
+        for (int c = 0; c < p.cin; ++c) {
+          const float v = ip[c];
+#pragma unroll
+          for (int j = 0; j < SMALL_COUT; ++j) acc[j] += v * s_w[c * SMALL_COUT + j];
+        }
+      }
+      bool any_d = false;
+#pragma unroll
+      for (int j = 0; j < SMALL_COUT; ++j) {
+        if (j < p.cout && p.addend) acc[j] += p.addend[pix * p.addend_ps + j];
+        any_d |= (j < p.cout) && (acc[j] != 0.0f);
+      }
+      float dy[SMALL_COUT];
+#pragma unroll
+      for (int j = 0; j < SMALL_COUT; ++j) {
+        dy[j] = acc[j];
+        if (j < p.cout && p.act != MIE_ACT_NONE) {
+          if (any_d || p.emitted) {
+            float *rp = p.res + pix * p.res_ps + j;
+            const float x = *rp, xn = x + acc[j];
+            if (any_d) *rp = xn;
+            const float base = p.emitted ? p.emitted[pix * p.emitted_ps + j] : act_apply(p.act, x);
+            dy[j] = act_apply(p.act, xn) - base;
+          } else {
+            dy[j] = 0.0f;
+          }
+        }
+        flag |= (j < p.cout) && fabsf(dy[j]) > p.thr;
+      }
+#pragma unroll
+      for (int j = 0; j < SMALL_COUT; ++j)
+        if (j < p.cout) {
+          const float v = flag ? dy[j] : 0.0f;
+          p.out[pix * p.out_ps + j] = v;
+          if (p.emitted && flag) p.emitted[pix * p.emitted_ps + j] += v;
+        }
+    }
+    const unsigned half = __ballot_sync(0xffffffffu, flag);
+    if (lane == 0 && half) bits32[2 * (size_t)t + ((px >> 5) & 1)] = half;
+  }
+}
+
 template <int K, int S, int WT, int WN>
 int launch_conv(const ConvParams &p, int max_items, cudaStream_t st) {
   using G = Geo<K, S>;
@@ -436,10 +529,20 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   p.act = a->act; p.thr = a->thr;
   p.res = a->res; p.res_ps = a->res_ps; p.emitted = a->emitted; p.emitted_ps = a->emitted_ps;
   p.addend = a->addend; p.addend_ps = a->addend_ps;
-  p.in_vec = (a->cin % 4 == 0) && (a->in_ps % 4 == 0) && aligned16(a->in);
+  // 16-byte staging reads whole channel quads: with cin % 4 != 0 the last quad reaches into the pixel's
+  // padding channels (in_ps >= cin rounded up to 4), which meet zero filter rows and must be finite
+  p.in_vec = (a->in_ps % 4 == 0) && aligned16(a->in) && (a->in_ps >= (a->cin + 3) / 4 * 4);
   p.io_vec = (a->cout % 4 == 0) && (a->out_ps % 4 == 0) && aligned16(a->out) &&
              (!a->res || ((a->res_ps % 4 == 0) && aligned16(a->res))) &&
              (!a->emitted || ((a->emitted_ps % 4 == 0) && aligned16(a->emitted)));
+
+  if (a->k == 1 && a->stride == 1 && a->pad == 0 && a->cout <= SMALL_COUT && a->cin <= 2048) {
+    int blocks = divup(a->max_tiles, 4);
+    if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+    p.in_vec = p.in_vec && (a->cin % 4 == 0 || a->in_ps >= (a->cin + 3) / 4 * 4);
+    conv1x1_small_kernel<<<blocks, 256, (size_t)a->cin * SMALL_COUT * sizeof(float), (cudaStream_t)stream>>>(p);
+    return check_launch();
+  }
 
   // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels, except that a
   // thresholded fused activation needs every channel of a pixel in one block

@@ -129,6 +129,8 @@ __device__ __forceinline__ void umma_commit(unsigned long long *bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+__device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
 __device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
   unsigned r[16];
   asm volatile(
@@ -153,20 +155,20 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int NB = p.nb;
   const int stage_bytes = A_STAGE_BYTES + NB * 128;
-  __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full, acc_empty;
+  __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
   const int ntiles_total = p.n * THo * TWo;
-  unsigned tmem_cols = 32;
-  while ((int)tmem_cols < NB) tmem_cols <<= 1;
+  unsigned acc_cols = 32;            // columns of one accumulator (power of two >= NB)
+  while ((int)acc_cols < NB) acc_cols <<= 1;
+  const unsigned tmem_cols = 2 * acc_cols;  // two accumulators: the epilogue of one item overlaps the MMAs of the next
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&acc_full, 1);
-    mbar_init(&acc_empty, 4);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -243,9 +245,11 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned idesc = make_idesc_tf32(NB);
       unsigned it_global = 0, item_idx = 0;
       for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
-        // the epilogue must have drained the accumulator of the previous item
-        if (item_idx > 0 && !mbar_wait(&acc_empty, (item_idx - 1) & 1u, &s_abort)) break;
+        // the epilogue must have drained this accumulator (used two items ago)
+        const unsigned buf = item_idx & 1u;
+        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort)) break;
         tc_fence_after();
+        const unsigned tmem_d = tmem_base + buf * acc_cols;
         bool ok = true;
         for (int ki = 0; ki < k_iters; ++ki, ++it_global) {
           const int s = it_global % p.stages;
@@ -256,13 +260,13 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
           const unsigned b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {  // 4 x (K = 8 tf32 = 32 bytes) inside the 128-byte swizzled row
-            umma_tf32(tmem_base, make_smem_desc(a_addr + kk * 32), make_smem_desc(b_addr + kk * 32), idesc,
+            umma_tf32(tmem_d, make_smem_desc(a_addr + kk * 32), make_smem_desc(b_addr + kk * 32), idesc,
                       (ki > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // arrives once the MMAs above have finished reading the stage
         }
         if (!ok) break;
-        umma_commit(&acc_full);
+        umma_commit(&acc_full[buf]);
       }
     }
   } else {
@@ -276,18 +280,21 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int li = 2 * pair + slot;
       int t = (li < n_active) ? p.list[li] : -1;
       if (t >= ntiles_total) t = -1;
-      if (!mbar_wait(&acc_full, item_idx & 1u, &s_abort)) break;
+      const unsigned buf = item_idx & 1u;
+      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
       tc_fence_after();
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
       const int co0 = cb * NB;
-      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16);
+      const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
       bool flag = false;
-      // pass A: does this pixel carry any change (skips reservoir traffic for untouched pixels of the tile)
-      bool any_d = false;
+      // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
+      // zero: they skip the reservoir read-modify-write)
+      bool any_d = true;
       if (p.act != MIE_ACT_NONE && !p.emitted) {
+        any_d = false;
         for (int c = 0; c < NB; c += 16) {
           float v[16];
           tmem_ld16(taddr + c, v);
@@ -296,47 +303,50 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         }
         if (valid && p.addend && !any_d)
           for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
-      } else {
-        any_d = true;
       }
       for (int c = 0; c < NB; c += 16) {
         float v[16];
         tmem_ld16(taddr + c, v);  // every lane of the warp takes part (aligned), valid or not
-        if (!valid) continue;
         const int co = co0 + c;
-        if (co >= p.cout) continue;
+        if (!valid || co >= p.cout) continue;
+        const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
+        float4 d[4], x[4], base[4];
+        // all loads of the group first, then the arithmetic, then the stores
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-          const int cc = co + h * 4;
-          if (cc >= p.cout) break;
-          float4 d = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
-          if (p.addend) {
-            const float4 a = *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + cc);
-            d.x += a.x; d.y += a.y; d.z += a.z; d.w += a.w;
-          }
-          if (p.act != MIE_ACT_NONE) {
-            if (any_d) {
-              float4 *rp = reinterpret_cast<float4 *>(p.res + pix * p.res_ps + cc);
-              const float4 x = *rp;
-              const float4 xn = make_float4(x.x + d.x, x.y + d.y, x.z + d.z, x.w + d.w);
-              *rp = xn;
-              float4 base;
-              if (p.emitted) base = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + cc);
-              else base = make_float4(act_apply(p.act, x.x), act_apply(p.act, x.y), act_apply(p.act, x.z), act_apply(p.act, x.w));
-              d = make_float4(act_apply(p.act, xn.x) - base.x, act_apply(p.act, xn.y) - base.y,
-                              act_apply(p.act, xn.z) - base.z, act_apply(p.act, xn.w) - base.w);
-            } else {
-              d = make_float4(0.f, 0.f, 0.f, 0.f);
+          d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
+          if (h < nq) {
+            if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
+            if (p.act != MIE_ACT_NONE && any_d) {
+              x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
+              if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
             }
           }
-          flag |= fabsf(d.x) > p.thr || fabsf(d.y) > p.thr || fabsf(d.z) > p.thr || fabsf(d.w) > p.thr;
-          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + cc) = d;
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (h >= nq) continue;
+          float4 o = d[h];
+          if (p.act != MIE_ACT_NONE) {
+            if (any_d) {
+              const float4 xn = f4add(x[h], d[h]);
+              *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
+              if (!p.emitted)
+                base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
+              o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
+                              act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
+            } else {
+              o = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
+          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
         }
       }
-      // the accumulator has been read: hand tensor memory back to the MMA warp
+      // the accumulator has been read: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty);
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
       // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
       // selects this kernel with thr > 0 when one block holds every channel of a pixel.
       if (valid && (p.thr > 0.0f || p.emitted)) {
@@ -436,12 +446,13 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.out = a->out; p.out_ps = a->out_ps; p.out_bits32 = reinterpret_cast<unsigned int *>(a->out_bits);
   p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
   p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
-  // channels per block: everything when it fits 256 accumulator columns, else 256
-  int nb = a->cout_pad <= 256 ? a->cout_pad : 256;
-  if (a->cout_pad % nb) nb = 128;
-  if (a->cout_pad % nb) nb = 64;
-  if (a->cout_pad % nb) nb = 32;
-  if (a->cout_pad % nb) nb = 16;
+  // channels per block: as wide as fits 256 accumulator columns, narrowed (down to 32) while the layer could
+  // not otherwise put two work items on every SM even at full activity -- the small-image layers of a UNet
+  // have a few dozen tiles but thousands of reduction steps
+  int nb = 256;
+  while (nb > 16 && a->cout_pad % nb) nb >>= 1;
+  const int64_t pairs = (a->max_tiles + 1) / 2;
+  while (nb > 32 && a->thr == 0.0f && a->cout_pad % (nb / 2) == 0 && pairs < MIE_SM_COUNT && pairs * (a->cout_pad / nb) < 2 * MIE_SM_COUNT) nb >>= 1;
   p.nb = nb;
   const int stage_bytes = A_STAGE_BYTES + nb * 128;
   int stages = (200 * 1024) / stage_bytes;

@@ -77,6 +77,31 @@ __global__ void __launch_bounds__(256) mask_words_kernel(const T *__restrict__ s
   }
 }
 
+// Few channels: one thread per pixel, one warp per half tile, the ballot is the half word.
+template <typename T>
+__global__ void __launch_bounds__(256) mask_words_px_kernel(const T *__restrict__ src, int64_t ps, int C, int N, int H,
+                                                            int W, float thr, unsigned *__restrict__ bits32) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  const int ntiles = N * TH * TW;
+  const int lane = threadIdx.x & 31;
+  for (int t = blockIdx.x * 4 + (threadIdx.x >> 6); t < ntiles; t += gridDim.x * 4) {
+    const int p = threadIdx.x & 63;
+    const int tx = t % TW, ty = (t / TW) % TH, n = t / (TW * TH);
+    const int y = ty * 8 + (p >> 3), x = tx * 8 + (p & 7);
+    bool a = false;
+    if (y < H && x < W) {
+      const T *px = src + ((int64_t)(n * H + y) * W + x) * ps;
+      for (int c = 0; c < C; ++c) {
+        const T v = px[c];
+        if (sizeof(T) == 4 && thr >= 0.0f) a |= fabsf((float)v) > thr;
+        else a |= (v != (T)0);
+      }
+    }
+    const unsigned half = __ballot_sync(0xffffffffu, a);
+    if (lane == 0) bits32[2 * (size_t)t + ((p >> 5) & 1)] = half;
+  }
+}
+
 static int mask_grid(int ntiles) {
   int blocks = divup(ntiles, 8);
   int cap = MIE_SM_COUNT * 8;
@@ -89,6 +114,12 @@ extern "C" int mie_mask_from_delta(const float *delta, int64_t ps, int N, int C,
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (C % 4 == 0) && (ps % 4 == 0) && aligned16(delta);
+  if (C <= 16) {
+    int blocks = divup(ntiles, 4);
+    if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+    mask_words_px_kernel<float><<<blocks, 256, 0, st>>>(delta, ps, C, N, H, W, thr, reinterpret_cast<unsigned *>(bits));
+    return check_launch();
+  }
   if (vec) mask_words_kernel<float, true><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
   else mask_words_kernel<float, false><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
   return check_launch();

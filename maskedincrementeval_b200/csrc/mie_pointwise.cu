@@ -171,7 +171,6 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_kernel(
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
     uint64_t *__restrict__ dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *__restrict__ dc_bits, int N, int C,
     int H, int W, int sum_m2, float thr) {
-  __shared__ unsigned s_h[2], s_c[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t wg = dg_bits[t];
@@ -188,8 +187,6 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_kernel(
       }
       continue;
     }
-    if (threadIdx.x < 2) { s_h[threadIdx.x] = 0u; s_c[threadIdx.x] = 0u; }
-    __syncthreads();
     for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
       const int p = e / C, c = e - p * C;
       if (!pix_valid(g, p)) continue;
@@ -223,24 +220,12 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_kernel(
         if (Dc != 0.0f) cell[pix * cell_ps + c] = c_o + Dc;
         o_h = (Dtc + tc_o) * Do + o_o * Dtc;
         o_c = Dc;
-        if (fabsf(o_h) > thr) or_word(s_h, p);
-        if (fabsf(o_c) > thr) or_word(s_c, p);
       }
       dh[pix * dh_ps + c] = o_h;
       dc[pix * dc_ps + c] = o_c;
     }
     __syncthreads();
-    const uint64_t wh = ((uint64_t)s_h[1] << 32) | s_h[0], wcc = ((uint64_t)s_c[1] << 32) | s_c[0];
-    if (thr > 0.0f) {
-      for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
-        const int p = e / C, c = e - p * C;
-        if (!pix_valid(g, p) || !((win >> p) & 1ull)) continue;
-        const int64_t pix = pix_index(g, p, H, W);
-        if (!((wh >> p) & 1ull)) dh[pix * dh_ps + c] = 0.0f;
-        if (!((wcc >> p) & 1ull)) dc[pix * dc_ps + c] = 0.0f;
-      }
-    }
-    if (threadIdx.x == 0) { dh_bits[t] = wh; dc_bits[t] = wcc; }
+    if (threadIdx.x == 0) { dh_bits[t] = win; dc_bits[t] = win; }
     __syncthreads();
   }
 }
@@ -329,6 +314,221 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
     }
     if (threadIdx.x == 0) out_bits[t] = wout;
   }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// vectorised variants: work item = (tile, block of CB channels), float4 over channels.
+// The output mask of these operators is a function of the input masks alone (no value test), so blocks
+// that share a tile need no reduction: block 0 of a tile owns the tile word and the stale clean-up.
+// ---------------------------------------------------------------------------------------------
+constexpr int CB = 32;  // channels per work item
+
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+__device__ __forceinline__ void zero_tile4(float *out, int64_t ps, int C, const TileGeom &g, int H, int W) {
+  const int q4 = C >> 2;
+  for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+    const int p = e / q4, q = e - p * q4;
+    if (pix_valid(g, p)) st4(out + pix_index(g, p, H, W) * ps + q * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+  }
+}
+
+__device__ __forceinline__ void lstm_elem(float gi, float gf, float go, float gc, float di, float df, float dob, float dcg,
+                                          float cp_o, float Dcp, bool use_cp, float c_o, int sum_m2, float &o_h, float &o_c) {
+  const float i_o = sigmoidf_acc(gi), f_o = sigmoidf_acc(gf), o_o = sigmoidf_acc(go), g_o = tanhf(gc);
+  const float Di = sigmoidf_acc(gi + di) - i_o, Df = sigmoidf_acc(gf + df) - f_o;
+  const float Do = sigmoidf_acc(go + dob) - o_o, Dg = tanhf(gc + dcg) - g_o;
+  const float m1 = (Dg + g_o) * Di + i_o * Dg;
+  const float m2 = use_cp ? ((Dcp + cp_o) * Df + f_o * Dcp) : 0.0f;
+  const float Dc = sum_m2 ? (m1 + m2) : m1;
+  const float tc_o = tanhf(c_o);
+  const float Dtc = tanhf(c_o + Dc) - tc_o;
+  o_h = (Dtc + tc_o) * Do + o_o * Dtc;
+  o_c = Dc;
+}
+
+__global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
+    const float *__restrict__ dg, int64_t dg_ps, const uint64_t *__restrict__ dg_bits, float *__restrict__ gres, int64_t g_ps,
+    const float *__restrict__ dcp, int64_t dcp_ps, const uint64_t *__restrict__ dcp_bits, float *__restrict__ cprev,
+    int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
+    uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int ncb = (C + CB - 1) / CB;
+  const int n_items = ntiles * ncb;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, cb = item - t * ncb;
+    const uint64_t wg = dg_bits[t];
+    const uint64_t wc = (dcp && dcp_bits) ? dcp_bits[t] : 0ull;
+    const uint64_t win = wg | wc;
+    const TileGeom g = tile_geom(t, H, W);
+    if (win == 0ull) {
+      if (cb == 0) {
+        const bool sh = dh_bits[t] != 0ull, sc = dc_bits[t] != 0ull;  // only this block reads or writes them
+        if (sh || sc) {
+          __syncthreads();
+          if (sh) zero_tile4(dh, dh_ps, C, g, H, W);
+          if (sc) zero_tile4(dc, dc_ps, C, g, H, W);
+          if (threadIdx.x == 0) { dh_bits[t] = 0ull; dc_bits[t] = 0ull; }
+        }
+      }
+      continue;
+    }
+    const int c_lo = cb * CB, q4 = (min(C, c_lo + CB) - c_lo) >> 2;
+    for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+      const int p = e / q4, c = c_lo + (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float4 oh = make_float4(0.f, 0.f, 0.f, 0.f), oc = oh;
+      if ((win >> p) & 1ull) {
+        const bool hg = (wg >> p) & 1ull;
+        float *gp = gres + pix * g_ps + c;
+        const float4 gi = ld4(gp), gf = ld4(gp + C), go = ld4(gp + 2 * C), gc = ld4(gp + 3 * C);
+        float4 di = oh, df = oh, dob = oh, dcg = oh;
+        if (hg) {
+          const float *dp = dg + pix * dg_ps + c;
+          di = ld4(dp); df = ld4(dp + C); dob = ld4(dp + 2 * C); dcg = ld4(dp + 3 * C);
+          st4(gp, f4add(gi, di)); st4(gp + C, f4add(gf, df)); st4(gp + 2 * C, f4add(go, dob)); st4(gp + 3 * C, f4add(gc, dcg));
+        }
+        float4 cpo = oh, Dcp = oh;
+        if (cprev) {
+          cpo = ld4(cprev + pix * cprev_ps + c);
+          if ((wc >> p) & 1ull) {
+            Dcp = ld4(dcp + pix * dcp_ps + c);
+            st4(cprev + pix * cprev_ps + c, f4add(cpo, Dcp));
+          }
+        }
+        const float4 co = ld4(cell + pix * cell_ps + c);
+        lstm_elem(gi.x, gf.x, go.x, gc.x, di.x, df.x, dob.x, dcg.x, cpo.x, Dcp.x, cprev != nullptr, co.x, sum_m2, oh.x, oc.x);
+        lstm_elem(gi.y, gf.y, go.y, gc.y, di.y, df.y, dob.y, dcg.y, cpo.y, Dcp.y, cprev != nullptr, co.y, sum_m2, oh.y, oc.y);
+        lstm_elem(gi.z, gf.z, go.z, gc.z, di.z, df.z, dob.z, dcg.z, cpo.z, Dcp.z, cprev != nullptr, co.z, sum_m2, oh.z, oc.z);
+        lstm_elem(gi.w, gf.w, go.w, gc.w, di.w, df.w, dob.w, dcg.w, cpo.w, Dcp.w, cprev != nullptr, co.w, sum_m2, oh.w, oc.w);
+        st4(cell + pix * cell_ps + c, f4add(co, oc));
+      }
+      st4(dh + pix * dh_ps + c, oh);
+      st4(dc + pix * dc_ps + c, oc);
+    }
+    if (cb == 0 && threadIdx.x == 0) { dh_bits[t] = win; dc_bits[t] = win; }
+  }
+}
+
+__global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
+    int C, int H, int W, int mode) {
+  const int Ho = 2 * H, Wo = 2 * W;
+  const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
+  const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
+  const int ncb = (C + CB - 1) / CB;
+  const int n_items = ntiles * ncb;
+  __shared__ unsigned s_w[2];
+  __shared__ unsigned char s_fa[64], s_fb[64];
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, cb = item - t * ncb;
+    const TileGeom g = tile_geom(t, Ho, Wo);
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const int p = threadIdx.x;
+      unsigned fa = 0, fb = 0;
+      if (pix_valid(g, p)) {
+        int y0, y1, x0, x1; float wy, wx;
+        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        fa = (bit_at(a_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(a_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
+             (bit_at(a_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(a_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
+        if (b)
+          fb = (bit_at(b_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(b_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
+               (bit_at(b_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(b_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
+      }
+      s_fa[p] = (unsigned char)fa;
+      s_fb[p] = (unsigned char)fb;
+      const unsigned bal = __ballot_sync(0xffffffffu, (fa | fb) != 0);
+      if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = bal;
+    }
+    __syncthreads();
+    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (wout == 0ull) {
+      if (cb == 0 && out_bits[t] != 0ull) {
+        zero_tile4(out, out_ps, C, g, Ho, Wo);
+        __syncthreads();
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    const int c_lo = cb * CB, q4 = (min(C, c_lo + CB) - c_lo) >> 2;
+    for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+      const int p = e / q4, c = c_lo + (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      const unsigned fa = s_fa[p], fb = s_fb[p];
+      if (fa | fb) {
+        int y0, y1, x0, x1; float wy, wx;
+        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
+        float4 v00 = v, v01 = v, v10 = v, v11 = v;
+        if (fa & 1u) v00 = ld4(a + (r0 + x0) * a_ps + c);
+        if (fa & 2u) v01 = ld4(a + (r0 + x1) * a_ps + c);
+        if (fa & 4u) v10 = ld4(a + (r1 + x0) * a_ps + c);
+        if (fa & 8u) v11 = ld4(a + (r1 + x1) * a_ps + c);
+        if (fb & 1u) v00 = f4add(v00, ld4(b + (r0 + x0) * b_ps + c));
+        if (fb & 2u) v01 = f4add(v01, ld4(b + (r0 + x1) * b_ps + c));
+        if (fb & 4u) v10 = f4add(v10, ld4(b + (r1 + x0) * b_ps + c));
+        if (fb & 8u) v11 = f4add(v11, ld4(b + (r1 + x1) * b_ps + c));
+        if (mode == MIE_UP_NEAREST) {
+          v = v00;
+        } else {
+          const float ax = 1.0f - wx, ay = 1.0f - wy;
+          v.x = ay * (ax * v00.x + wx * v01.x) + wy * (ax * v10.x + wx * v11.x);
+          v.y = ay * (ax * v00.y + wx * v01.y) + wy * (ax * v10.y + wx * v11.y);
+          v.z = ay * (ax * v00.z + wx * v01.z) + wy * (ax * v10.z + wx * v11.z);
+          v.w = ay * (ax * v00.w + wx * v01.w) + wy * (ax * v10.w + wx * v11.w);
+        }
+      }
+      st4(out + pix_index(g, p, Ho, Wo) * out_ps + c, v);
+    }
+    if (cb == 0 && threadIdx.x == 0) out_bits[t] = wout;
+  }
+}
+
+__global__ void __launch_bounds__(PW_THREADS) add_vec_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
+    int C, int H, int W) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int ncb = (C + CB - 1) / CB;
+  const int n_items = ntiles * ncb;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, cb = item - t * ncb;
+    const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (cb == 0 && out_bits[t] != 0ull) {
+        __syncthreads();
+        zero_tile4(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    const int c_lo = cb * CB, q4 = (min(C, c_lo + CB) - c_lo) >> 2;
+    for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+      const int p = e / q4, c = c_lo + (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if ((wa >> p) & 1ull) v = ld4(a + pix * a_ps + c);
+      if ((wb >> p) & 1ull) v = f4add(v, ld4(b + pix * b_ps + c));
+      st4(out + pix * out_ps + c, v);
+    }
+    if (cb == 0 && threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
+static int item_grid(int64_t items) {
+  const int64_t cap = (int64_t)MIE_SM_COUNT * 16;
+  return (int)(items < cap ? (items > 0 ? items : 1) : cap);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -508,12 +708,22 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
                                   int64_t cprev_ps, float *cell, int64_t cell_ps, float *dh, int64_t dh_ps,
                                   uint64_t *dh_bits, float *dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H,
                                   int W, int sum_m2, float thr, void *stream) {
-  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits) return MIE_EINVAL;
+  if (thr != 0.0f) return MIE_EUNSUPPORTED;  // the cell's outputs are not thresholded
   MIE_CHECK_FIELD(dg, dg_ps, 4 * C); MIE_CHECK_FIELD(g, g_ps, 4 * C); MIE_CHECK_FIELD(cell, cell_ps, C);
   MIE_CHECK_FIELD(dh, dh_ps, C); MIE_CHECK_FIELD(dc, dc_ps, C);
   if (dc_prev && (!dcp_bits || dcp_ps < C || !cprev)) return MIE_EINVAL;
   if (cprev && cprev_ps < C) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  const bool vec = C % 4 == 0 && dg_ps % 4 == 0 && g_ps % 4 == 0 && cell_ps % 4 == 0 && dh_ps % 4 == 0 &&
+                   dc_ps % 4 == 0 && aligned16(dg) && aligned16(g) && aligned16(cell) && aligned16(dh) && aligned16(dc) &&
+                   (!dc_prev || (dcp_ps % 4 == 0 && aligned16(dc_prev))) && (!cprev || (cprev_ps % 4 == 0 && aligned16(cprev)));
+  if (vec) {
+    convlstm_point_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+        dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
+        dc_ps, dc_bits, N, C, H, W, sum_m2);
+    return check_launch();
+  }
   convlstm_point_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
       dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
       dc_ps, dc_bits, N, C, H, W, sum_m2, thr);
@@ -528,6 +738,11 @@ extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bi
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (b && (!b_bits || b_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(2 * H, 8) * divup(2 * W, 8);
+  if (C % 4 == 0 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
+    upsample2x_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode);
+    return check_launch();
+  }
   upsample2x_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
                                                                                 out_ps, out_bits, N, C, H, W, mode);
   return check_launch();
@@ -539,6 +754,11 @@ extern "C" int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, con
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(b, b_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  if (C % 4 == 0 && a_ps % 4 == 0 && b_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
+    add_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W);
+    return check_launch();
+  }
   add_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps,
                                                                          out_bits, N, C, H, W);
   return check_launch();

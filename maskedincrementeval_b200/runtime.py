@@ -76,7 +76,12 @@ class IncrementalRunner:
         if self._x_prev is None or self._x_prev.shape != x.shape:
             self._x_prev = x.clone(memory_format=torch.channels_last)
             self._x_in = torch.empty_like(self._x_prev)
-            self._dx = torch.zeros_like(self._x_prev)
+            n, c, h, w = x.shape
+            cpad = (c + 3) // 4 * 4
+            # pixel stride padded to a multiple of 4 floats so that the first convolution can stage the input
+            # delta with 16-byte copies (5 voxel bins -> stride 8); the padding channels stay zero
+            full = torch.zeros((n, cpad, h, w), dtype=x.dtype, device=x.device).contiguous(memory_format=torch.channels_last)
+            self._dx = full[:, :c]
             self._y = [y.detach().clone().contiguous(memory_format=torch.channels_last) for y in ys]
             self._graph = None
             self._eager_steps = 0
