@@ -446,13 +446,14 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.out = a->out; p.out_ps = a->out_ps; p.out_bits32 = reinterpret_cast<unsigned int *>(a->out_bits);
   p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
   p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
-  // channels per block: as wide as fits 256 accumulator columns, narrowed (down to 32) while the layer could
-  // not otherwise put two work items on every SM even at full activity -- the small-image layers of a UNet
-  // have a few dozen tiles but thousands of reduction steps
+  // channels per block: as wide as fits 256 accumulator columns; narrowed (down to 32) only while the layer
+  // could not keep about half of the SMs busy even at full activity -- the small-image layers of a UNet have
+  // a few dozen tiles but thousands of reduction steps.  Measured on B200: a pipeline stage costs about
+  // 0.6 us whatever its width, so narrowing pays only until the work items cover the machine once.
   int nb = 256;
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
-  while (nb > 32 && a->thr == 0.0f && a->cout_pad % (nb / 2) == 0 && pairs < MIE_SM_COUNT && pairs * (a->cout_pad / nb) < 2 * MIE_SM_COUNT) nb >>= 1;
+  while (nb > 32 && a->thr == 0.0f && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
   p.nb = nb;
   const int stage_bytes = A_STAGE_BYTES + nb * 128;
   int stages = (200 * 1024) / stage_bytes;
