@@ -81,6 +81,24 @@ int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout,
                      int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
                      int32_t *list, int32_t *stale, int32_t *counts, uint8_t *flags, void *stream);
 
+/* Same result as mie_tiles_dilate, for hosts that are not allowed to allocate device memory.
+ * It has no counterpart in the reference.
+ * mie_tiles_dilate borrows a flag byte per output tile and a ticket word from its caller.  A program that
+ * embeds this library in a camera / inference pipeline whose device memory was partitioned at start-up
+ * (allocation afterwards is forbidden there: cudaMalloc synchronises the device, may fail under fragmentation
+ * late in a recording, and is not permitted while a stream is being captured) has nowhere to take them from.
+ * This variant keeps that scratch inside the library, in a fixed array of MIE_STATIC_MAX_TILES + 256 bytes of
+ * device memory that every GPU loading the library holds until the process ends, and calls no allocating
+ * routine.  Inputs and outputs are still the caller's; counts is int32[2] = {n_active, n_stale}.
+ *  - more than MIE_STATIC_MAX_TILES output tiles -> MIE_ETOOBIG;
+ *  - the array is shared by all calls on a device and keeps the last call's contents (the word that must be
+ *    zero is cleared on `stream` before the launch): calls that overlap on the GPU race -- serialise them;
+ *  - the first call on a device resolves the array's address; make it before any stream capture starts. */
+#define MIE_STATIC_MAX_TILES 262144
+int mie_tiles_dilate_static(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout, int k,
+                            int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
+                            int32_t *list, int32_t *stale, int32_t *counts, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Masked delta convolution with fused incremental activation.
  * Replaces conv{1x1,3x3,5x5,7x7}_increment_ext (ops.cpp:51-114 -> ext_conv.cu:28-417) and, when

@@ -47,6 +47,7 @@ SIGNATURES = {
     "mie_tiles_compact": (_i, [_vp, _i, _vp, _vp, _vp]),
     "mie_mask_expand": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mie_tiles_dilate": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mie_tiles_dilate_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mie_conv_tiles": (_i, [C.POINTER(ConvArgs), _vp]),
     "mie_conv_uses_tensor_cores": (_i, [C.POINTER(ConvArgs)]),
     "mie_conv_pack_dims": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),

@@ -18,7 +18,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(HERE, "libmie.so")
-SOURCES = ["mie_mask.cu", "mie_conv.cu", "mie_conv_tc.cu", "mie_pointwise.cu"]
+SOURCES = ["mie_mask.cu", "mie_conv.cu", "mie_conv_tc.cu", "mie_pointwise.cu", "mie_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--extended-lambda", "-I", INCLUDE, "-I", CSRC]
 
