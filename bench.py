@@ -239,15 +239,14 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
     flops = [t * 64 * 32 * 9 * 32 * 2 for t in tiles]
     tot_t = sum(times)
     achieved = sum(byts) / tot_t / 1e9
-    traffic = None
-    tp = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    traffic = None  # DRAM bytes per launch of this kernel from the committed ncu capture of this same command
+    tp = os.path.join(ROOT, "profiles", "conv_tc_c1_conv3x3_260x346.md")
     if os.path.exists(tp):
-        try:
-            traffic = json.load(open(tp)).get("conv3x3_c1_dram_bytes_per_launch")
-        except Exception:
-            traffic = None
+        for ln in open(tp):
+            if ln.startswith("dram_bytes_per_launch:"):
+                traffic = float(ln.split(":")[1])
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_tiles_kernel<3,1,4,1> (conv3x3 32->32 + ReLU, 260x346)",
+            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": ("conv_tc_kernel" if conv.last_used_tensor_cores else "conv_tiles_kernel<3,1,4,1>") + " (conv3x3 32->32 + ReLU, 260x346)",
             "bytes_per_launch": sum(byts) / len(byts), "us_per_launch": 1e6 * tot_t / len(times),
             "active_tiles_mean": sum(tiles) / len(tiles), "tiles_total": fl.n_tiles(1, H, W),
             "active_pixel_frac": sum(px) / len(px), "fp32_tflops": sum(flops) / tot_t / 1e12, "launches": len(times)}
