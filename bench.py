@@ -284,8 +284,10 @@ def run_ours(args):
         return net
 
     net = make_net()
+    from maskedincrementeval_b200.sharding import job_throughput, streams_of_rank
+    my_streams = streams_of_rank(streams * world, world, rank)   # global stream ids of this rank
     n_frames = Wm + K + 3
-    frames_host = voxel_sequence(streams, H, W, n_frames, EVENTS, SEGMENTS, seed=100 + rank)
+    frames_host = voxel_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
     frames_pinned = [f.pin_memory() for f in frames_host]
     frames_dev = [f.to(dev) for f in frames_host]
     in_bytes = frames_host[0].numel() * 4
@@ -351,18 +353,15 @@ def run_ours(args):
     e2e_s = sum(a.elapsed_time(b) for a, b in e2e_ev) * 1e-3
     out_bytes = out_host.numel() * 4
 
-    # ---- max over ranks ------------------------------------------------------------------------------
-    t = torch.tensor([dev_s, e2e_s], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_s, e2e_s = float(t[0]), float(t[1])
+    # ---- whole-job numbers: stream-timesteps of all ranks over the time of the slowest rank ----------------------
+    value, total_steps, dev_s = job_throughput(K * len(my_streams), dev_s, dev)
+    e2e_value, _, e2e_s = job_throughput(K * len(my_streams), e2e_s, dev)
 
     if rank == 0:
-        total_steps = K * streams * world
         print(f"[bench] device {1e3 * dev_s / K:.3f} ms/step, e2e {1e3 * e2e_s / K:.3f} ms/step, "
               f"{launches_per_step} launches/step, parity {parity:.2e}", file=sys.stderr)
         line = {
-            "metric": METRIC, "value": total_steps / dev_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": "260x346 padded to 264x352",
@@ -371,7 +370,7 @@ def run_ours(args):
                        "l2": "flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
                        "execution": "one CUDA graph replay per step"},
             "clocks": clocks, "gpu_launches": launches_per_step * K,
-            "e2e": {"value": total_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": in_bytes,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes,
                     "d2h_bytes_per_step": out_bytes, "ms_per_step": 1e3 * e2e_s / K},
             "parity": {"max_abs_err_over_range_vs_dense_recompute": parity, "after_steps": 1 + Wm + K, "tolerance": 1e-4},
             "wall_s_timed_region": wall,

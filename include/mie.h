@@ -123,7 +123,7 @@ typedef struct mie_conv_args {
   float *res; int64_t res_ps;
   float *emitted; int64_t emitted_ps;
   const float *addend; int64_t addend_ps;
-  /* optional second copy of the filter packed by mie_pack_conv_weights_tc ([k*k][cout_pad][cin_pad32], TF32
+  /* optional second copy of the filter packed by mie_pack_conv_weights_tc ([k*k][cin_pad/32][cout_pad][32], TF32
    * rounded).  When given, and the layer qualifies (Cin*k*k >= 256, 16-byte aligned channel strides, ...), the
    * convolution runs on the tensor cores (tcgen05, TF32 inputs, FP32 accumulation); otherwise on the FP32 path. */
   const float *wpacked_tc;
@@ -138,7 +138,7 @@ int mie_conv_uses_tensor_cores(const mie_conv_args *args /* host */);
  * the padded extents the kernels assume. */
 int mie_conv_pack_dims(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats);
 
-/* Same for the tensor-core copy: cin padded to 32, layout [k*k][cout_pad][cin_pad]. */
+/* Same for the tensor-core copy: cin padded to 32, layout [k*k][cin_pad/32][cout_pad][32]. */
 int mie_conv_pack_dims_tc(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats);
 int mie_pack_conv_weights_tc(const float *w_oihw, int cout, int cin, int k, float *wpacked, void *stream);
 

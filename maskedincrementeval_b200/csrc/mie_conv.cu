@@ -187,7 +187,9 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
         __syncthreads();
         const float *B = Bs + (ky & 1) * B_STAGE_F + wn * 32 + nq * 8;
         const float4 *A = As + (ts * (CC / 4)) * G::IN_T * G::PITCH + ky * G::PITCH;
-#pragma unroll
+        // the tap loop stays rolled: its body (2 channel quads x 272 instructions) fits the instruction
+        // cache, the fully unrolled form (26 KB for k = 3, 43 KB for k = 5) did not
+#pragma unroll 1
         for (int kx = 0; kx < K; ++kx) {
 #pragma unroll
           for (int cq = 0; cq < CC / 4; ++cq) {

@@ -80,23 +80,14 @@ __device__ __forceinline__ void tma_load_4d(void *smem, const CUtensorMap *map, 
       "r"(c2), "r"(c3)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1,
-                                            int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
-      "r"(c2)
-      : "memory");
-}
-
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
 // 8-row groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled
 // K-major), [32,46) stride offset>>4, [46,48) version = 1, [61,64) layout = 2 (128-byte swizzle).
-__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr) {
+__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr, unsigned sbo_bytes = 1024) {
   unsigned long long d = 0;
   d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
   d |= (unsigned long long)1 << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)(sbo_bytes >> 4) << 32;
   d |= (unsigned long long)1 << 46;
   d |= (unsigned long long)2 << 61;
   return d;
@@ -141,6 +132,88 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Epilogue of one accumulator row (= one output pixel, all NB channels of the block): optional residual add,
+// incremental activation against the reservoir, per-pixel send decision, store.  Called by all 32 lanes of an
+// epilogue warp (the tensor-memory loads are warp-collective); returns whether the pixel was sent.
+__device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, unsigned taddr, bool valid, int64_t pix,
+                                                  int co0, unsigned long long *acc_empty_bar, int lane) {
+      bool flag = false;
+      // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
+      // zero: they skip the reservoir read-modify-write)
+      bool any_d = true;
+      if (p.act != MIE_ACT_NONE && !p.emitted) {
+        any_d = false;
+        for (int c = 0; c < NB; c += 16) {
+          float v[16];
+          tmem_ld16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) any_d |= (v[j] != 0.0f);
+        }
+        if (valid && p.addend && !any_d)
+          for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
+      }
+      for (int c = 0; c < NB; c += 16) {
+        float v[16];
+        tmem_ld16(taddr + c, v);  // every lane of the warp takes part (aligned), valid or not
+        const int co = co0 + c;
+        if (!valid || co >= p.cout) continue;
+        const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
+        float4 d[4], x[4], base[4];
+        // all loads of the group first, then the arithmetic, then the stores
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
+          if (h < nq) {
+            if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
+            if (p.act != MIE_ACT_NONE && any_d) {
+              x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
+              if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (h >= nq) continue;
+          float4 o = d[h];
+          if (p.act != MIE_ACT_NONE) {
+            if (any_d) {
+              const float4 xn = f4add(x[h], d[h]);
+              *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
+              if (!p.emitted)
+                base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
+              o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
+                              act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
+            } else {
+              o = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
+          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
+        }
+      }
+      // the accumulator has been read: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar);
+      // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
+      // selects this kernel with thr > 0 when one block holds every channel of a pixel.
+      if (valid && (p.thr > 0.0f || p.emitted)) {
+        const int cend = min(NB, p.cout - co0);
+        if (!flag) {
+          for (int c = 0; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if (p.emitted) {
+          for (int c = 0; c < cend; c += 4) {
+            const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
+            float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
+            float4 e = *ep;
+            e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
+            *ep = e;
+          }
+        }
+      }
+      return valid && flag;
 }
 
 struct TcMaps {
@@ -235,7 +308,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
           }
           tma_load_4d(stage, &maps.in[mi], &full_bar[s], chunk * 32, tx0 * 8 + dx, ty0 * 8 + dy, n0);
           if (t1 >= 0) tma_load_4d(stage + A_STAGE_BYTES / 2, &maps.in[mi], &full_bar[s], chunk * 32, tx1 * 8 + dx, ty1 * 8 + dy, n1);
-          tma_load_3d(stage + A_STAGE_BYTES, &maps.w, &full_bar[s], chunk * 32, cb * NB, tap);
+          tma_load_4d(stage + A_STAGE_BYTES, &maps.w, &full_bar[s], 0, cb * NB, chunk, tap);
         }
       }
     }
@@ -287,83 +360,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
-      const int co0 = cb * NB;
-      const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
-      bool flag = false;
-      // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
-      // zero: they skip the reservoir read-modify-write)
-      bool any_d = true;
-      if (p.act != MIE_ACT_NONE && !p.emitted) {
-        any_d = false;
-        for (int c = 0; c < NB; c += 16) {
-          float v[16];
-          tmem_ld16(taddr + c, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) any_d |= (v[j] != 0.0f);
-        }
-        if (valid && p.addend && !any_d)
-          for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
-      }
-      for (int c = 0; c < NB; c += 16) {
-        float v[16];
-        tmem_ld16(taddr + c, v);  // every lane of the warp takes part (aligned), valid or not
-        const int co = co0 + c;
-        if (!valid || co >= p.cout) continue;
-        const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
-        float4 d[4], x[4], base[4];
-        // all loads of the group first, then the arithmetic, then the stores
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
-          if (h < nq) {
-            if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
-            if (p.act != MIE_ACT_NONE && any_d) {
-              x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
-              if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
-            }
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          if (h >= nq) continue;
-          float4 o = d[h];
-          if (p.act != MIE_ACT_NONE) {
-            if (any_d) {
-              const float4 xn = f4add(x[h], d[h]);
-              *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
-              if (!p.emitted)
-                base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
-              o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
-                              act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
-            } else {
-              o = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          }
-          flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
-          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
-        }
-      }
-      // the accumulator has been read: hand it back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
-      // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
-      // selects this kernel with thr > 0 when one block holds every channel of a pixel.
-      if (valid && (p.thr > 0.0f || p.emitted)) {
-        const int cend = min(NB, p.cout - co0);
-        if (!flag) {
-          for (int c = 0; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-        } else if (p.emitted) {
-          for (int c = 0; c < cend; c += 4) {
-            const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
-            float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
-            float4 e = *ep;
-            e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
-            *ep = e;
-          }
-        }
-      }
-      const unsigned half = __ballot_sync(0xffffffffu, valid && flag);
+      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
+                                          cb * NB, &acc_empty[buf], lane);
+      const unsigned half = __ballot_sync(0xffffffffu, sent);
       if (lane == 0 && t >= 0 && half) {
         unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
         if (n_cblk > 1) atomicOr(wp, half);
@@ -386,6 +385,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
+
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -479,34 +479,40 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
       }
   }
   {
-    const cuuint64_t dims[3] = {(cuuint64_t)p.cin_pad, (cuuint64_t)a->cout_pad, (cuuint64_t)(a->k * a->k)};
-    const cuuint64_t str[2] = {(cuuint64_t)p.cin_pad * 4, (cuuint64_t)a->cout_pad * p.cin_pad * 4};
-    const cuuint32_t box_w[3] = {32, (cuuint32_t)nb, 1};
-    if (!encode(fn, &maps.w, 3, a->wpacked_tc, dims, str, box_w)) return MIE_EINVAL;
+    // filter stored [tap][32-channel chunk][cout_pad][32]: the box of one (tap, chunk, channel block) is contiguous
+    const cuuint64_t nch = (cuuint64_t)(p.cin_pad / 32);
+    const cuuint64_t dims[4] = {32, (cuuint64_t)a->cout_pad, nch, (cuuint64_t)(a->k * a->k)};
+    const cuuint64_t str[3] = {128, (cuuint64_t)a->cout_pad * 128, nch * a->cout_pad * 128};
+    const cuuint32_t box_w[4] = {32, (cuuint32_t)nb, 1, 1};
+    if (!encode(fn, &maps.w, 4, a->wpacked_tc, dims, str, box_w)) return MIE_EINVAL;
   }
+  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
+  int grid = max_items < MIE_SM_COUNT ? (int)max_items : MIE_SM_COUNT;
+  if (grid < 1) grid = 1;
   static int smem_set = 0;
   if ((int)smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     smem_set = (int)smem;
   }
-  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
-  int grid = max_items < MIE_SM_COUNT ? (int)max_items : MIE_SM_COUNT;
-  if (grid < 1) grid = 1;
   conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
   return check_launch();
 }
 
 }  // namespace mie
 
-// [k*k][cout_pad][cin_pad32] <- w[cout][cin][ky][kx], rounded to TF32 (round to nearest, ties away), zero padded
+// [k*k][cin_pad/32][cout_pad][32] <- w[cout][cin][ky][kx], rounded to TF32 (round to nearest, ties away), zero padded
 __global__ void pack_weights_tc_kernel(const float *__restrict__ w, int cout, int cin, int k, int cin_pad, int cout_pad,
                                        float *__restrict__ wp, int64_t total) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int ci = (int)(i % cin_pad);
-    int64_t rest = i / cin_pad;
+    // i = ((tap * n_chunks + chunk) * cout_pad + co) * 32 + ci_in_chunk
+    const int cl = (int)(i % 32);
+    int64_t rest = i / 32;
     const int co = (int)(rest % cout_pad);
-    const int tap = (int)(rest / cout_pad);
+    rest /= cout_pad;
+    const int nch = cin_pad / 32;
+    const int ci = (int)(rest % nch) * 32 + cl;
+    const int tap = (int)(rest / nch);
     float v = 0.0f;
     if (co < cout && ci < cin) v = w[((int64_t)co * cin + ci) * k * k + tap];
     unsigned u = __float_as_uint(v);

@@ -188,51 +188,57 @@ __device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride,
   return set;
 }
 
+// 0: inactive, 1: active, 2: inactive now but the output tile holds data from the previous step (stale).
+// Also clears the output word.
+__device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *__restrict__ in_bits, int Hin, int Win, int Hout,
+                                               int Wout, int k, int stride, int pad,
+                                               const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits) {
+  const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
+  const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
+  const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+  const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
+  const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
+  const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
+  const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
+  bool active = false;
+  if (rset && cset) {
+    const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
+    const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
+    for (int ity = ylo >> 3; ity <= (yhi >> 3) && !active; ++ity) {
+      unsigned selr = 0;
+      for (int py = 0; py < 8; ++py) {
+        const int j = ity * 8 + py - ybase;
+        if (j >= 0 && j < 32 && ((rset >> j) & 1u)) selr |= 1u << py;
+      }
+      for (int itx = xlo >> 3; itx <= (xhi >> 3); ++itx) {
+        unsigned selc = 0;
+        for (int px = 0; px < 8; ++px) {
+          const int j = itx * 8 + px - xbase;
+          if (j >= 0 && j < 32 && ((cset >> j) & 1u)) selc |= 1u << px;
+        }
+        uint64_t m = 0;
+        for (int py = 0; py < 8; ++py)
+          if ((selr >> py) & 1u) m |= (uint64_t)selc << (py * 8);
+        if (in_bits[((int64_t)n * THi + ity) * TWi + itx] & m) { active = true; break; }
+      }
+    }
+  }
+  if (!active && union_bits && union_bits[t] != 0ull) active = true;
+  uint8_t f = active ? 1 : 0;
+  if (out_bits) {
+    if (!active && out_bits[t] != 0ull) f = 2;
+    out_bits[t] = 0ull;
+  }
+  return f;
+}
+
 __global__ void __launch_bounds__(256) tiles_dilate_kernel(
     const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
     const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,
     int32_t *__restrict__ stale, int32_t *__restrict__ counts, uint8_t *__restrict__ flags) {
-  const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
-  const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
-  const int ntiles = N * THo * TWo;
+  const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < ntiles) {
-    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
-    const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
-    const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
-    const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
-    const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
-    bool active = false;
-    if (rset && cset) {
-      const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
-      const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
-      for (int ity = ylo >> 3; ity <= (yhi >> 3) && !active; ++ity) {
-        unsigned selr = 0;
-        for (int py = 0; py < 8; ++py) {
-          const int j = ity * 8 + py - ybase;
-          if (j >= 0 && j < 32 && ((rset >> j) & 1u)) selr |= 1u << py;
-        }
-        for (int itx = xlo >> 3; itx <= (xhi >> 3); ++itx) {
-          unsigned selc = 0;
-          for (int px = 0; px < 8; ++px) {
-            const int j = itx * 8 + px - xbase;
-            if (j >= 0 && j < 32 && ((cset >> j) & 1u)) selc |= 1u << px;
-          }
-          uint64_t m = 0;
-          for (int py = 0; py < 8; ++py)
-            if ((selr >> py) & 1u) m |= (uint64_t)selc << (py * 8);
-          if (in_bits[((int64_t)n * THi + ity) * TWi + itx] & m) { active = true; break; }
-        }
-      }
-    }
-    if (!active && union_bits && union_bits[t] != 0ull) active = true;
-    uint8_t f = active ? 1 : 0;
-    if (out_bits) {
-      if (!active && out_bits[t] != 0ull) f = 2;
-      out_bits[t] = 0ull;
-    }
-    flags[t] = f;
-  }
+  if (t < ntiles) flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
   // the block that finishes last compacts both lists in ascending order
   __shared__ bool s_last;
   __threadfence();
@@ -252,6 +258,29 @@ __global__ void __launch_bounds__(256) tiles_dilate_kernel(
   }
 }
 
+// Up to DILATE_SMALL_MAX tiles: one block keeps the flags in shared memory and compacts them itself -- no
+// ticket, no fence, no round trip through global memory (most levels of a UNet at batch 1 are this small).
+constexpr int DILATE_SMALL_MAX = 4096;
+
+__global__ void __launch_bounds__(1024) tiles_dilate_small_kernel(
+    const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
+    const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,
+    int32_t *__restrict__ stale, int32_t *__restrict__ counts) {
+  __shared__ uint8_t s_flags[DILATE_SMALL_MAX];
+  const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
+  for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
+    s_flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
+  __syncthreads();
+  const int na = block_ordered_compact([&](int i) { return s_flags[i] == 1; }, ntiles, list);
+  __syncthreads();
+  int ns = 0;
+  if (stale) ns = block_ordered_compact([&](int i) { return s_flags[i] == 2; }, ntiles, stale);
+  if (threadIdx.x == 0) {
+    counts[0] = na;
+    counts[1] = ns;
+  }
+}
+
 extern "C" int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout, int k,
                                 int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
                                 int32_t *list, int32_t *stale, int32_t *counts, uint8_t *flags, void *stream) {
@@ -260,6 +289,12 @@ extern "C" int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win
   if (k < 1 || k > 7 || stride < 1 || stride > 2 || pad < 0 || pad > k) return MIE_EUNSUPPORTED;
   if (out_bits && !stale) return MIE_EINVAL;
   const int ntiles = N * divup(Hout, 8) * divup(Wout, 8);
+  if (ntiles <= DILATE_SMALL_MAX) {
+    const int threads = ntiles <= 256 ? 256 : (ntiles <= 512 ? 512 : 1024);
+    tiles_dilate_small_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(in_bits, N, Hin, Win, Hout, Wout, k, stride, pad,
+                                                                       union_bits, out_bits, list, stale, counts);
+    return check_launch();
+  }
   tiles_dilate_kernel<<<divup(ntiles, 256), 256, 0, (cudaStream_t)stream>>>(
       in_bits, N, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits, list, stale, counts, flags);
   return check_launch();

@@ -113,6 +113,30 @@ def conv_delta(dx: Tensor, weight: Tensor, stride: int, pad: int) -> Tensor:
     return F.conv2d(dx, weight, None, stride, pad)
 
 
+# -- what the tensor-core path computes (this library's definition; the reference has no such path) -----------
+def tf32_truncate(x: Tensor) -> Tensor:
+    """fp32 -> TF32 by dropping the 13 low mantissa bits: what tcgen05.mma kind::tf32 does to an fp32 operand."""
+    return (x.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)
+
+
+def tf32_round(x: Tensor) -> Tensor:
+    """fp32 -> TF32, round to nearest (ties away from zero): how the library pre-rounds the filter."""
+    return ((x.contiguous().view(torch.int32) + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+def tc_eligible(cin: int, cout: int, k: int, stride: int, h: int, w: int) -> bool:
+    """Host-side rule that sends a convolution to the tensor cores (given 16-byte aligned channel strides)."""
+    return (cin * k * k >= 256 and cin % 4 == 0 and cout % 4 == 0 and stride in (1, 2)
+            and (stride == 1 or (h % 2 == 0 and w % 2 == 0)))
+
+
+def conv_delta_tf32(dx: Tensor, weight: Tensor, stride: int, pad: int) -> Tensor:
+    """Tensor-core convolution of a delta: TF32-truncated inputs x TF32-rounded filter, fp32 accumulation.
+    Truncating the inputs is not linear (trunc(a) + trunc(b) != trunc(a + b)), so on this path the accumulated
+    incremental output of a network differs from a dense pass by the rounding of every step's deltas."""
+    return F.conv2d(tf32_truncate(dx), tf32_round(weight), None, stride, pad)
+
+
 def conv_dense(x: Tensor, weight: Tensor, bias: Optional[Tensor], stride: int, pad: int) -> Tensor:
     """Dense refresh convolution with bias.  ``nnConvIncr.forward_refresh_reservoirs`` (``:182-196``)."""
     return F.conv2d(x, weight, bias, stride, pad)
@@ -318,17 +342,21 @@ def skip_concat(x1: Tensor, x2: Tensor) -> Tensor:
 
 
 class _FlowBase:
-    def __init__(self, sd: Dict[str, Tensor], compat: str):
+    def __init__(self, sd: Dict[str, Tensor], compat: str, tensor_cores: bool = False):
         assert compat in ("reference", "exact")
         self.sd = {k: v.detach().float().cpu() for k, v in sd.items()}
         self.compat = compat
+        self.tensor_cores = tensor_cores   # emulate the TF32 path on the layers the library would send there
         self.res: Dict[str, Tensor] = {}
 
     def _conv_d(self, x, name, stride, pad):
         return conv_dense(x, self.sd[name + ".weight"], self.sd.get(name + ".bias"), stride, pad)
 
     def _conv_i(self, dx, name, stride, pad):
-        return conv_delta(dx, self.sd[name + ".weight"], stride, pad)
+        w = self.sd[name + ".weight"]
+        if self.tensor_cores and tc_eligible(dx.shape[1], w.shape[0], w.shape[2], stride, dx.shape[2], dx.shape[3]):
+            return conv_delta_tf32(dx, w, stride, pad)
+        return conv_delta(dx, w, stride, pad)
 
     def _act_d(self, x, key, op):
         self.res[key] = x.clone()
@@ -370,8 +398,8 @@ class _FlowBase:
 class FireFlowNetOracle(_FlowBase):
     """``FireFlowNetIncr`` (``incr_modules/fireflownet_incr.py:6-72``)."""
 
-    def __init__(self, sd, kernel_size: int = 3, compat: str = "reference"):
-        super().__init__(sd, compat)
+    def __init__(self, sd, kernel_size: int = 3, compat: str = "reference", tensor_cores: bool = False):
+        super().__init__(sd, compat, tensor_cores)
         self.k = kernel_size
 
     def refresh(self, x):

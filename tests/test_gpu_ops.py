@@ -369,12 +369,17 @@ def test_conv_tensor_core_path_vs_oracle(dev, cfg):
             dy, m = layer([cl(dx, dev), None])
             assert layer.conv2d.last_used_tensor_cores
             d = R.conv_delta(dx, wt, s, k // 2)
+            d_tc = R.conv_delta_tf32(dx, wt, s, k // 2)
             if act:
+                want_tc, _ = R.act_incr(res, d_tc, op)
                 want, res = R.act_incr(res, d, op)
             else:
-                want = d
-            scale = max(float(want.abs().max()), float(d.abs().max()), 1e-3)
-            assert float((dy.cpu() - want).abs().max()) <= 2e-3 * max(scale, 1.0), (float((dy.cpu() - want).abs().max()), scale)
+                want, want_tc = d, d_tc
+            scale = max(float(want.abs().max()), float(d.abs().max()), 1.0)
+            # (i) bit-level statement of the path: fp32 convolution of truncated inputs and rounded filter
+            #     (only the summation order differs), (ii) the 2e-3 bar against the fp32 result
+            assert float((dy.cpu() - want_tc).abs().max()) <= 2e-5 * scale, (float((dy.cpu() - want_tc).abs().max()), scale)
+            assert float((dy.cpu() - want).abs().max()) <= 2e-3 * scale, (float((dy.cpu() - want).abs().max()), scale)
             if act:
                 # keep the oracle's state on the GPU's trajectory so that errors do not compound through relu kinks
                 res = layer.activation.in_res.reservoir.cpu().contiguous()
