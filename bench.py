@@ -364,7 +364,7 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": "260x346 padded to 264x352",
+            "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": f"{H}x{W}, reflection-padded to a multiple of 8",
                        "events_per_window": EVENTS, "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold,
                        "weights": "random init (nn.Conv2d default), seed 0", "parallelism": f"{world} x independent streams",
                        "l2": "flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
@@ -436,6 +436,7 @@ def activity_table(net, run, frame, dev):
 
 
 def main():
+    global H, W, EVENTS, SEGMENTS, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -444,9 +445,16 @@ def main():
     ap.add_argument("--streams", type=int, default=1, help="event streams per GPU (batch dimension)")
     ap.add_argument("--threshold", type=float, default=0.0,
                     help="activation threshold with residual carry; 0 = lossless (the headline)")
+    ap.add_argument("--size", default="260x346", help="sensor resolution HxW (secondary measurements; the headline is 260x346)")
+    ap.add_argument("--events", type=int, default=EVENTS)
+    ap.add_argument("--segments", type=int, default=SEGMENTS)
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
     args = ap.parse_args()
+    H, W = (int(v) for v in args.size.split("x"))
+    EVENTS, SEGMENTS = args.events, args.segments
+    if (H, W) != (260, 346) or args.streams != 1:
+        WORKLOAD = f"e2depth_{H}x{W}_b{args.streams}"
     if args.roofline_only:
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(0)

@@ -229,6 +229,29 @@ int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, int ca, const
 int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const uint64_t *d_bits, int N,
                    int C, int H, int W, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * The steps either side of the network in the reference's driver loop.
+ * ------------------------------------------------------------------------------------------- */
+
+/* dx = x - x_prev; x_prev = x; bits = per-pixel any_c(|dx| > thr), one pass.  Withheld pixels (all |dx| <= thr)
+ * are written as 0 and keep their x_prev, so nothing is lost, only deferred.
+ * The driver's `x = event_tensor - event_tensor_prev` (run_e2depth_continuous_dataset.py:66) plus the mask. */
+int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
+                   uint64_t *bits, int N, int C, int H, int W, float thr, void *stream);
+
+/* Voxel grid of one window of events: temporal-bilinear, spatial-nearest accumulation, as
+ * events_to_voxel_grid_absT (data_fetchers/utils/util.py:78-110).  events: [n_events][4] floats
+ * (t in [0,1), x, y, polarity; polarity 0 counts as -1).  voxel: [1, num_bins, H, W] channels-last with pixel
+ * stride v_ps, zeroed by this call; (pad_left, pad_top) shift the sensor image inside a larger grid
+ * (reflection padding itself is left to the caller). */
+int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sensor_h, int sensor_w,
+                        float *voxel, int64_t v_ps, int H, int W, int pad_left, int pad_top, void *stream);
+
+/* Sigma-delta quantiser with carry: T = carry + dx; q = k * floor(0.5 + T / k); carry = T - q; bits = q != 0.
+ * KFencedMaskModule.forward, incr_modules/mask_incr_modules.py:31-41. */
+int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,
+                uint64_t *bits, int N, int C, int H, int W, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,9 +47,6 @@ __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)_
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -72,14 +69,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
   return false;
 }
 
-__device__ __forceinline__ void tma_load_4d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1,
-                                            int c2, int c3) {
+__device__ __forceinline__ void tma_load_4d_raw(unsigned smem_addr, const CUtensorMap *map, unsigned bar_addr, int c0, int c1,
+                                                int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
-      "r"(c2), "r"(c3)
+      ::"r"(smem_addr), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
 // 8-row groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled
 // K-major), [32,46) stride offset>>4, [46,48) version = 1, [61,64) layout = 2 (128-byte swizzle).
@@ -104,12 +101,19 @@ __device__ __forceinline__ unsigned make_idesc_tf32(int n) {
   return d;
 }
 
-__device__ __forceinline__ void umma_tf32(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                          unsigned idesc, unsigned accumulate) {
+// The four K-slices of one stage (descriptor low words advance by 2 = 32 bytes), one predicate set-up.
+__device__ __forceinline__ void umma_tf32_x4(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                             unsigned idesc, unsigned accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u64 a1, %1, 2;\n\tadd.u64 a2, %1, 4;\n\tadd.u64 a3, %1, 6;\n\t"
+      "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a1, b1, %3, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a2, b2, %3, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a3, b3, %3, q;\n\t}"
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -277,46 +281,61 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int n_items = n_pairs * n_cblk;
   const int n_chunks = p.cin_pad >> 5;
   const int taps = p.k * p.k;
-  const int k_iters = n_chunks * taps;
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
+    // One thread issues every copy, so its scalar instructions are on the critical path: stage index, phase,
+    // stage address and tap coordinates are running counters -- no division, no 64-bit multiply in the loop.
     if (lane == 0) {
-      unsigned it_global = 0;
+      unsigned s = 0, wait_parity = 0;     // parity of the "stage is free" phase this pass around the ring waits for
+      bool first_pass = true;
+      const unsigned smem_base = smem_u32(smem);
+      unsigned stage_addr = smem_base;
+      const unsigned b_bytes = (unsigned)NB * 128u;
       for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
         const int pair = item / n_cblk, cb = item - pair * n_cblk;
         int t0 = p.list[2 * pair];
         int t1 = (2 * pair + 1 < n_active) ? p.list[2 * pair + 1] : -1;
         if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
-        const int tx0 = t0 % TWo, ty0 = (t0 / TWo) % THo, n0 = t0 / (TWo * THo);
-        const int tx1 = (t1 >= 0) ? t1 % TWo : 0, ty1 = (t1 >= 0) ? (t1 / TWo) % THo : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
-        const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + NB * 128;
-        for (int ki = 0; ki < k_iters; ++ki, ++it_global) {
-          const int s = it_global % p.stages;
-          const unsigned ph = (it_global / p.stages) & 1u;
-          if (it_global >= (unsigned)p.stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &s_abort)) break;
-          const int chunk = ki / taps, tap = ki - chunk * taps;
-          const int ky = tap / p.k, kx = tap - ky * p.k;
-          unsigned char *stage = smem + (size_t)s * stage_bytes;
-          mbar_expect_tx(&full_bar[s], tx_bytes);
-          int dy = ky - p.pad, dx = kx - p.pad, mi = 0;
-          if (p.stride == 2) {
-            const int py = dy & 1, pxp = dx & 1;
-            mi = py * 2 + pxp;
-            dy = (dy - py) >> 1;
-            dx = (dx - pxp) >> 1;
+        const int x0 = (t0 % TWo) * 8, y0 = ((t0 / TWo) % THo) * 8, n0 = t0 / (TWo * THo);
+        const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
+        const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + b_bytes;
+        const int cbn = cb * NB;
+        bool ok = true;
+        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+          const int c0 = chunk * 32;
+          int tap = 0;
+          for (int ky = 0; ky < p.k && ok; ++ky) {
+            int dy = ky - p.pad, pyb = 0;
+            if (p.stride == 2) { pyb = (dy & 1) * 2; dy = (dy - (dy & 1)) >> 1; }
+            for (int kx = 0; kx < p.k; ++kx, ++tap) {
+              if (!first_pass && !mbar_wait(&empty_bar[s], wait_parity, &s_abort)) { ok = false; break; }
+              int dx = kx - p.pad, mi = 0;
+              if (p.stride == 2) { mi = pyb + (dx & 1); dx = (dx - (dx & 1)) >> 1; }
+              const unsigned bar = smem_u32(&full_bar[s]);
+              asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx_bytes) : "memory");
+              tma_load_4d_raw(stage_addr, &maps.in[mi], bar, c0, x0 + dx, y0 + dy, n0);
+              if (t1 >= 0) tma_load_4d_raw(stage_addr + A_STAGE_BYTES / 2, &maps.in[mi], bar, c0, x1 + dx, y1 + dy, n1);
+              tma_load_4d_raw(stage_addr + A_STAGE_BYTES, &maps.w, bar, 0, cbn, chunk, tap);
+              stage_addr += (unsigned)stage_bytes;
+              if (++s == (unsigned)p.stages) { s = 0; stage_addr = smem_base; if (!first_pass) wait_parity ^= 1u; first_pass = false; }
+            }
           }
-          tma_load_4d(stage, &maps.in[mi], &full_bar[s], chunk * 32, tx0 * 8 + dx, ty0 * 8 + dy, n0);
-          if (t1 >= 0) tma_load_4d(stage + A_STAGE_BYTES / 2, &maps.in[mi], &full_bar[s], chunk * 32, tx1 * 8 + dx, ty1 * 8 + dy, n1);
-          tma_load_4d(stage + A_STAGE_BYTES, &maps.w, &full_bar[s], 0, cb * NB, chunk, tap);
         }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
+    // Same care as the producer: a lean loop issues an MMA every ~70 cycles, one that rebuilds descriptors and
+    // divides by the stage count needs ~250.  Descriptors are pre-built; a stage only adds its address.
     if (lane == 0) {
       const unsigned idesc = make_idesc_tf32(NB);
-      unsigned it_global = 0, item_idx = 0;
+      const unsigned smem_base = smem_u32(smem);
+      const unsigned long long desc_hi = make_smem_desc(0) & 0xFFFFFFFF00000000ull;   // stride, version, swizzle
+      const unsigned desc_lo_flags = (unsigned)(make_smem_desc(0) & 0xFFFF0000ull);     // leading-offset field
+      unsigned s = 0, parity = 0, stage_addr = smem_base, item_idx = 0;
+      const int k_iters = n_chunks * taps;
       for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
         // the epilogue must have drained this accumulator (used two items ago)
         const unsigned buf = item_idx & 1u;
@@ -324,19 +343,18 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         tc_fence_after();
         const unsigned tmem_d = tmem_base + buf * acc_cols;
         bool ok = true;
-        for (int ki = 0; ki < k_iters; ++ki, ++it_global) {
-          const int s = it_global % p.stages;
-          const unsigned ph = (it_global / p.stages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, &s_abort)) { ok = false; break; }
+        unsigned accumulate = 0;
+        for (int ki = 0; ki < k_iters; ++ki) {
+          if (!mbar_wait(&full_bar[s], parity, &s_abort)) { ok = false; break; }
           tc_fence_after();
-          const unsigned a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-          const unsigned b_addr = a_addr + A_STAGE_BYTES;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {  // 4 x (K = 8 tf32 = 32 bytes) inside the 128-byte swizzled row
-            umma_tf32(tmem_d, make_smem_desc(a_addr + kk * 32), make_smem_desc(b_addr + kk * 32), idesc,
-                      (ki > 0 || kk > 0) ? 1u : 0u);
-          }
+          const unsigned a_lo = desc_lo_flags | ((stage_addr & 0x3FFFFu) >> 4);
+          const unsigned b_lo = desc_lo_flags | (((stage_addr + A_STAGE_BYTES) & 0x3FFFFu) >> 4);
+          // 4 x (K = 8 tf32 = 32 bytes = 2 descriptor units) inside the 128-byte swizzled row
+          umma_tf32_x4(tmem_d, desc_hi | a_lo, desc_hi | b_lo, idesc, accumulate);
+          accumulate = 1u;
           umma_commit(&empty_bar[s]);  // arrives once the MMAs above have finished reading the stage
+          stage_addr += (unsigned)stage_bytes;
+          if (++s == (unsigned)p.stages) { s = 0; stage_addr = smem_base; parity ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);
@@ -385,6 +403,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
+
 
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -486,15 +505,15 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     const cuuint32_t box_w[4] = {32, (cuuint32_t)nb, 1, 1};
     if (!encode(fn, &maps.w, 4, a->wpacked_tc, dims, str, box_w)) return MIE_EINVAL;
   }
-  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
-  int grid = max_items < MIE_SM_COUNT ? (int)max_items : MIE_SM_COUNT;
-  if (grid < 1) grid = 1;
   static int smem_set = 0;
   if ((int)smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     smem_set = (int)smem;
   }
+  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
+  int grid = max_items < MIE_SM_COUNT ? (int)max_items : MIE_SM_COUNT;
+  if (grid < 1) grid = 1;
   conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
   return check_launch();
 }

@@ -659,6 +659,80 @@ int launch_act_dense(float *X, const float *in, float *out, int64_t n, cudaStrea
   return check_launch();
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// input side: delta against the previous frame + mask, event binning, quantiser
+// ---------------------------------------------------------------------------------------------
+// one thread per pixel, 64 threads per tile, 4 tiles per block; the ballot of a warp is half a tile word
+__global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict__ x, int64_t x_ps, float *__restrict__ xp,
+                                                         int64_t xp_ps, float *__restrict__ dx, int64_t dx_ps,
+                                                         unsigned *__restrict__ bits32, int N, int C, int H, int W, float thr) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  const int ntiles = N * TH * TW;
+  const int lane = threadIdx.x & 31;
+  for (int t = blockIdx.x * 4 + (threadIdx.x >> 6); t < ntiles; t += gridDim.x * 4) {
+    const int p = threadIdx.x & 63;
+    const int tx = t % TW, ty = (t / TW) % TH, n = t / (TW * TH);
+    const int y = ty * 8 + (p >> 3), xx = tx * 8 + (p & 7);
+    bool a = false;
+    if (y < H && xx < W) {
+      const int64_t pix = (int64_t)(n * H + y) * W + xx;
+      for (int c = 0; c < C; ++c) a |= fabsf(x[pix * x_ps + c] - xp[pix * xp_ps + c]) > thr;
+      for (int c = 0; c < C; ++c) {
+        const float v = x[pix * x_ps + c];
+        const float d = a ? v - xp[pix * xp_ps + c] : 0.0f;
+        dx[pix * dx_ps + c] = d;
+        if (a) xp[pix * xp_ps + c] = v;
+      }
+    }
+    const unsigned half = __ballot_sync(0xffffffffu, a);
+    if (lane == 0) bits32[2 * (size_t)t + ((p >> 5) & 1)] = half;
+  }
+}
+
+__global__ void __launch_bounds__(256) events_to_voxel_kernel(const float *__restrict__ ev, int n_events, int bins, int sh,
+                                                              int sw, float *__restrict__ vox, int64_t ps, int H, int W,
+                                                              int pl, int pt) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_events; i += gridDim.x * blockDim.x) {
+    const float4 e = *reinterpret_cast<const float4 *>(ev + 4 * (size_t)i);
+    const float ts = (float)(bins - 1) * e.x;
+    const int xi = (int)e.y, yi = (int)e.z;
+    if (xi < 0 || xi >= sw || yi < 0 || yi >= sh) continue;
+    const float pol = (e.w == 0.0f) ? -1.0f : e.w;
+    const int ti = (int)ts;
+    const float dt = ts - (float)ti;
+    const int64_t pix = (int64_t)(yi + pt) * W + (xi + pl);
+    if (ti >= 0 && ti < bins) atomicAdd(vox + pix * ps + ti, pol * (1.0f - dt));
+    if (ti + 1 >= 0 && ti + 1 < bins) atomicAdd(vox + pix * ps + ti + 1, pol * dt);
+  }
+}
+
+__global__ void __launch_bounds__(256) kfenced_kernel(const float *__restrict__ dx, int64_t dx_ps, float *__restrict__ carry,
+                                                      int64_t c_ps, float k, float *__restrict__ q, int64_t q_ps,
+                                                      unsigned *__restrict__ bits32, int N, int C, int H, int W) {
+  const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
+  const int ntiles = N * TH * TW;
+  const int lane = threadIdx.x & 31;
+  for (int t = blockIdx.x * 4 + (threadIdx.x >> 6); t < ntiles; t += gridDim.x * 4) {
+    const int p = threadIdx.x & 63;
+    const int tx = t % TW, ty = (t / TW) % TH, n = t / (TW * TH);
+    const int y = ty * 8 + (p >> 3), xx = tx * 8 + (p & 7);
+    bool a = false;
+    if (y < H && xx < W) {
+      const int64_t pix = (int64_t)(n * H + y) * W + xx;
+      for (int c = 0; c < C; ++c) {
+        const float T = carry[pix * c_ps + c] + dx[pix * dx_ps + c];
+        const float f = k * floorf(0.5f + T / k);
+        carry[pix * c_ps + c] = T - f;
+        q[pix * q_ps + c] = f;
+        a |= (f != 0.0f);
+      }
+    }
+    const unsigned half = __ballot_sync(0xffffffffu, a);
+    if (lane == 0) bits32[2 * (size_t)t + ((p >> 5) & 1)] = half;
+  }
+}
+
 }  // namespace
 
 extern "C" int mie_activation_increment(float *X, const float *in_incr, float *out_incr, int64_t n, int op, void *stream) {
@@ -781,5 +855,46 @@ extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_
   MIE_CHECK_FIELD(y, y_ps, C); MIE_CHECK_FIELD(d, d_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   accumulate_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(y, y_ps, d, d_ps, d_bits, N, C, H, W);
+  return check_launch();
+}
+
+extern "C" int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
+                              uint64_t *bits, int N, int C, int H, int W, float thr, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  MIE_CHECK_FIELD(x, x_ps, C); MIE_CHECK_FIELD(x_prev, xp_ps, C); MIE_CHECK_FIELD(dx, dx_ps, C);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  int blocks = divup(ntiles, 4);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  delta_mask_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, x_ps, x_prev, xp_ps, dx, dx_ps,
+                                                              reinterpret_cast<unsigned *>(bits), N, C, H, W, thr);
+  return check_launch();
+}
+
+extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sensor_h, int sensor_w, float *voxel,
+                                   int64_t v_ps, int H, int W, int pad_left, int pad_top, void *stream) {
+  if (!voxel || n_events < 0 || num_bins <= 0 || sensor_h <= 0 || sensor_w <= 0 || H <= 0 || W <= 0 || v_ps < num_bins)
+    return MIE_EINVAL;
+  if (pad_left < 0 || pad_top < 0 || sensor_h + pad_top > H || sensor_w + pad_left > W) return MIE_EINVAL;
+  if (n_events > 0 && (!events || !aligned16(events))) return events ? MIE_EALIGN : MIE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(voxel, 0, (size_t)H * W * v_ps * sizeof(float), st);
+  if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+  if (n_events == 0) return MIE_OK;
+  int blocks = divup(n_events, 256);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  events_to_voxel_kernel<<<blocks, 256, 0, st>>>(events, n_events, num_bins, sensor_h, sensor_w, voxel, v_ps, H, W, pad_left,
+                                                 pad_top);
+  return check_launch();
+}
+
+extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,
+                           uint64_t *bits, int N, int C, int H, int W, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(k > 0.0f)) return MIE_EINVAL;
+  MIE_CHECK_FIELD(dx, dx_ps, C); MIE_CHECK_FIELD(carry, c_ps, C); MIE_CHECK_FIELD(q, q_ps, C);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  int blocks = divup(ntiles, 4);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  kfenced_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dx, dx_ps, carry, c_ps, k, q, q_ps,
+                                                           reinterpret_cast<unsigned *>(bits), N, C, H, W);
   return check_launch();
 }

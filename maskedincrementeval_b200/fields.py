@@ -272,3 +272,32 @@ def pack_conv_weights_tc(weight: torch.Tensor) -> torch.Tensor:
     nat.check(nat.lib.mie_pack_conv_weights_tc(w.data_ptr(), cout, cin, k, buf.data_ptr(),
                                                nat.stream_ptr(weight.device)), "pack_conv_weights_tc")
     return buf
+
+
+def delta_mask(x: torch.Tensor, x_prev: torch.Tensor, dx: torch.Tensor, bits: torch.Tensor, thr: float = 0.0) -> TileMask:
+    """dx = x - x_prev, x_prev = x and the mask of dx in one kernel (pixels with every |dx| <= thr are deferred)."""
+    n, c, h, w = x.shape
+    nat.check(nat.lib.mie_delta_mask(x.data_ptr(), pixel_stride(x), x_prev.data_ptr(), pixel_stride(x_prev), dx.data_ptr(),
+                                     pixel_stride(dx), bits.data_ptr(), n, c, h, w, float(thr), nat.stream_ptr(x.device)),
+              "delta_mask")
+    return TileMask(bits, n, h, w)
+
+
+def events_to_voxel(events: torch.Tensor, num_bins: int, sensor_hw, out: torch.Tensor, pad_left: int = 0, pad_top: int = 0):
+    """Bin one window of events ([n,4] float32 on the device: t in [0,1), x, y, polarity) into ``out``
+    ([1,num_bins,H,W] channels-last), as the reference's ``events_to_voxel_grid_absT`` does on the host."""
+    if events.dtype != torch.float32 or not events.is_cuda or not events.is_contiguous():
+        raise RuntimeError("events must be a contiguous float32 CUDA tensor [n, 4]")
+    _, c, h, w = out.shape
+    nat.check(nat.lib.mie_events_to_voxel(events.data_ptr(), events.shape[0], num_bins, sensor_hw[0], sensor_hw[1],
+                                          out.data_ptr(), pixel_stride(out), h, w, pad_left, pad_top,
+                                          nat.stream_ptr(out.device)), "events_to_voxel")
+    return out
+
+
+def kfenced(dx: torch.Tensor, carry: torch.Tensor, k: float, q: torch.Tensor, bits: torch.Tensor) -> TileMask:
+    n, c, h, w = dx.shape
+    nat.check(nat.lib.mie_kfenced(dx.data_ptr(), pixel_stride(dx), carry.data_ptr(), pixel_stride(carry), float(k),
+                                  q.data_ptr(), pixel_stride(q), bits.data_ptr(), n, c, h, w, nat.stream_ptr(dx.device)),
+              "kfenced")
+    return TileMask(bits, n, h, w)

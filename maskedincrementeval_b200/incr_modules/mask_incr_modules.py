@@ -42,6 +42,16 @@ class KFencedMaskModule(IncrementMaskModule):
         return self.k * torch.floor(0.5 + T / self.k)
 
     def forward(self, incr: Masked) -> Masked:
+        d = incr[0]
+        if d.is_cuda and d.dim() == 4 and d.dtype == torch.float32:
+            # one kernel: quantise, update the carry, emit the mask of the quantised delta
+            sc = self.__dict__.setdefault("_scratch", Scratch())
+            d = fl.as_channels_last(d)
+            n, c, h, w = d.shape
+            q = sc.get("q", (n, c, h, w), torch.float32, d.device, channels_last=True)
+            bits = sc.get("q.bits", (fl.n_tiles(n, h, w),), torch.int64, d.device)
+            k = self._k_host if getattr(self, "_k_host", None) is not None else float(self.k)
+            return q, fl.kfenced(d, self.delta.reservoir, k, q, bits)
         T1 = self.delta.reservoir + incr[0]
         f_delta = self.floor_by_k(T1)
         self.delta.update_reservoir(T1 - f_delta)
@@ -49,6 +59,7 @@ class KFencedMaskModule(IncrementMaskModule):
 
     def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
         self.k = self.tp * torch.norm(x)
+        self._k_host = float(self.k)   # one host read per refresh, none per step
         self.delta.update_reservoir(torch.zeros_like(x))
         return x
 

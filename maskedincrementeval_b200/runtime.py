@@ -82,6 +82,7 @@ class IncrementalRunner:
             # delta with 16-byte copies (5 voxel bins -> stride 8); the padding channels stay zero
             full = torch.zeros((n, cpad, h, w), dtype=x.dtype, device=x.device).contiguous(memory_format=torch.channels_last)
             self._dx = full[:, :c]
+            self._dx_bits = fl.new_bits(n, h, w, x.device)
             self._y = [y.detach().clone().contiguous(memory_format=torch.channels_last) for y in ys]
             self._graph = None
             self._eager_steps = 0
@@ -94,9 +95,9 @@ class IncrementalRunner:
 
     # -- incremental pass ------------------------------------------------------------------------
     def _step_body(self):
-        torch.sub(self._x_in, self._x_prev, out=self._dx)
-        self._x_prev.copy_(self._x_in)
-        x_incr = (self._dx, None)
+        # input delta, previous-frame update and input mask in one kernel
+        m_in = fl.delta_mask(self._x_in, self._x_prev, self._dx, self._dx_bits, fl.config.input_threshold)
+        x_incr = (self._dx, m_in)
         out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
         for y, d in zip(self._y, _deltas_of(out)):
             m = d[1]

@@ -423,3 +423,50 @@ def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
                 assert float((y - truth).abs().max()) <= 0.02 + 2e-3
     finally:
         fl.config.threshold = old
+
+
+# ----------------------------------------------------------------------------------------------
+# the steps either side of the network: input delta + mask, event binning, quantiser
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("thr", [0.0, 0.05])
+def test_delta_mask_fused_input(dev, thr):
+    from maskedincrementeval_b200 import fields as fl
+    g = torch.Generator().manual_seed(17)
+    xp = torch.randn(2, 5, 37, 50, generator=g)
+    x = xp + sparse_delta(g, xp.shape, 0.1, std=0.1)
+    full = torch.zeros(2, 8, 37, 50).to(dev).contiguous(memory_format=torch.channels_last)
+    dx = full[:, :5]                      # padded pixel stride, as the runner allocates it
+    XP, X = cl(xp, dev), cl(x, dev)
+    m = fl.delta_mask(X, XP, dx, fl.new_bits(2, 37, 50, dev), thr)
+    want_mask = ((x - xp).abs() > thr).any(1, keepdim=True)
+    assert torch.equal(m.pixel_mask().cpu(), want_mask.to(torch.uint8))
+    assert torch.equal(dx.cpu(), (x - xp) * want_mask)
+    assert torch.equal(XP.cpu(), torch.where(want_mask, x, xp))   # withheld pixels keep their old frame: deferred, not lost
+    assert float(full[:, 5:].abs().max()) == 0.0
+
+
+def test_events_to_voxel_matches_host_binning(dev):
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.synthetic import EdgeEventStream, events_to_voxel_grid, reflection_pad_hw
+    ev = EdgeEventStream(260, 346, 30000, 10, seed=3).window()
+    ev[:5, 3] = 0                                # polarity 0 counts as -1
+    want = torch.from_numpy(events_to_voxel_grid(ev.copy(), 5, 260, 346))
+    l, r, t, b = reflection_pad_hw(260, 346)
+    out = fl.new_field(1, 5, 264, 352, dev)
+    fl.events_to_voxel(torch.from_numpy(ev.astype("float32")).to(dev), 5, (260, 346), out, l, t)
+    got = out[0, :, t:t + 260, l:l + 346].cpu()
+    assert float((got - want).abs().max()) <= 2e-4      # fp32 time stamps and atomic summation order
+    assert float(out.abs().sum() - got.abs().sum()) == 0.0   # nothing outside the sensor area
+
+
+def test_kfenced_kernel_golden(dev, golden):
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import KFencedMaskModule
+    g = golden("misc_ops")
+    kf = KFencedMaskModule(0.3)
+    kf.forward_refresh_reservoirs(cl(T(g["kf_x"]), dev))
+    assert abs(kf._k_host - float(g["kf_k"])) < 1e-4
+    for s in (1, 2, 3):
+        q, m = kf([cl(T(g[f"kf_d{s}"]), dev), None])
+        close(q, T(g[f"kf_q{s}"]), 1e-5)
+        close(kf.delta.reservoir, T(g[f"kf_c{s}"]), 1e-4)
+        assert torch.equal(m.pixel_mask().cpu(), (q.cpu() != 0).any(1, keepdim=True).to(torch.uint8))
