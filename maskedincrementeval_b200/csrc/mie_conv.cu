@@ -55,11 +55,14 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <int K, int S, int WT, int WN>
+// CPT = output channels per thread (8 or 4): a warp covers 4*CPT channels.  CPT = 4 doubles the warps per tile for
+// 32-channel layers, which otherwise run one warp per scheduler.
+template <int K, int S, int WT, int WN, int CPT>
 __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles_kernel(const ConvParams p) {
   using G = Geo<K, S>;
   constexpr int NT = 32 * WT * WN;
-  constexpr int NB = 32 * WN;
+  constexpr int NBW = 4 * CPT;          // channels per warp
+  constexpr int NB = NBW * WN;
   constexpr int B_STAGE_F = K * CC * NB;  // floats per filter stage (one ky, one chunk)
 
   extern __shared__ float4 smem4[];
@@ -108,11 +111,11 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
     }
     __syncthreads();
 
-    float acc[8][8];
+    float acc[8][CPT];
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[r][j] = 0.0f;
+      for (int j = 0; j < CPT; ++j) acc[r][j] = 0.0f;
 
     for (int ch = 0; ch < n_chunks; ++ch) {
       const int c0 = ch * CC;
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
           cp_async_wait<0>();
         }
         __syncthreads();
-        const float *B = Bs + (ky & 1) * B_STAGE_F + wn * 32 + nq * 8;
+        const float *B = Bs + (ky & 1) * B_STAGE_F + wn * NBW + nq * CPT;
         const float4 *A = As + (ts * (CC / 4)) * G::IN_T * G::PITCH + ky * G::PITCH;
         // the tap loop stays rolled: its body (2 channel quads x 272 instructions) fits the instruction
         // cache, the fully unrolled form (26 KB for k = 3, 43 KB for k = 5) did not
@@ -200,7 +203,8 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               const float4 b0 = *reinterpret_cast<const float4 *>(B + (kx * CC + cq * 4 + c) * NB);
-              const float4 b1 = *reinterpret_cast<const float4 *>(B + (kx * CC + cq * 4 + c) * NB + 4);
+              float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (CPT == 8) b1 = *reinterpret_cast<const float4 *>(B + (kx * CC + cq * 4 + c) * NB + 4);
 #pragma unroll
               for (int r = 0; r < 8; ++r) {
                 const float av = (c == 0) ? a[r].x : (c == 1) ? a[r].y : (c == 2) ? a[r].z : a[r].w;
@@ -208,10 +212,12 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
                 acc[r][1] = fmaf(av, b0.y, acc[r][1]);
                 acc[r][2] = fmaf(av, b0.z, acc[r][2]);
                 acc[r][3] = fmaf(av, b0.w, acc[r][3]);
-                acc[r][4] = fmaf(av, b1.x, acc[r][4]);
-                acc[r][5] = fmaf(av, b1.y, acc[r][5]);
-                acc[r][6] = fmaf(av, b1.z, acc[r][6]);
-                acc[r][7] = fmaf(av, b1.w, acc[r][7]);
+                if (CPT == 8) {
+                  acc[r][CPT - 4] = fmaf(av, b1.x, acc[r][CPT - 4]);
+                  acc[r][CPT - 3] = fmaf(av, b1.y, acc[r][CPT - 3]);
+                  acc[r][CPT - 2] = fmaf(av, b1.z, acc[r][CPT - 2]);
+                  acc[r][CPT - 1] = fmaf(av, b1.w, acc[r][CPT - 1]);
+                }
               }
             }
           }
@@ -223,7 +229,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
     // ---- epilogue ---------------------------------------------------------------------------------
     const int t = s_tile[ts];
     const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
-    const int co = n0 + wn * 32 + nq * 8;
+    const int co = n0 + wn * NBW + nq * CPT;
     const int ox = tx * 8 + pc;
     unsigned rowflags = 0;  // bit r: pixel (r, pc) has a channel with |dy| > thr
     if (t >= 0 && ox < p.wout) {
@@ -234,10 +240,10 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
         const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
         bool any_d = false;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) any_d |= (acc[r][j] != 0.0f);
+        for (int j = 0; j < CPT; ++j) any_d |= (acc[r][j] != 0.0f);
         if (p.addend) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < CPT; ++j)
             if (co + j < p.cout) {
               const float a = p.addend[pix * p.addend_ps + co + j];
               acc[r][j] += a;
@@ -249,7 +255,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
           if (any_d || p.emitted) {
             if (p.io_vec) {
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
+              for (int h = 0; h < CPT / 4; ++h) {
                 if (co + h * 4 < p.cout) {
                   float4 *rp = reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4);
                   const float4 x = *rp;
@@ -266,7 +272,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < CPT; ++j)
                 if (co + j < p.cout) {
                   float *rp = p.res + pix * p.res_ps + co + j;
                   const float x = *rp, xn = x + acc[r][j];
@@ -279,7 +285,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
         }
         bool f = false;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f |= (co + j < p.cout) && (fabsf(acc[r][j]) > p.thr);
+        for (int j = 0; j < CPT; ++j) f |= (co + j < p.cout) && (fabsf(acc[r][j]) > p.thr);
         if (f) rowflags |= 1u << r;
       }
     }
@@ -317,7 +323,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
           const bool send = (word >> (r * 8 + pc)) & 1ull;
           if (p.io_vec) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < CPT / 4; ++h)
               if (co + h * 4 < p.cout) {
                 const float4 v = send ? make_float4(acc[r][h * 4], acc[r][h * 4 + 1], acc[r][h * 4 + 2], acc[r][h * 4 + 3])
                                       : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -331,7 +337,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
               }
           } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < CPT; ++j)
               if (co + j < p.cout) {
                 const float v = send ? acc[r][j] : 0.0f;
                 p.out[pix * p.out_ps + co + j] = v;
@@ -437,15 +443,15 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
   }
 }
 
-template <int K, int S, int WT, int WN>
+template <int K, int S, int WT, int WN, int CPT = 8>
 int launch_conv(const ConvParams &p, int max_items, cudaStream_t st) {
   using G = Geo<K, S>;
   constexpr int NT = 32 * WT * WN;
-  constexpr int NB = 32 * WN;
+  constexpr int NB = 4 * CPT * WN;
   const size_t smem = (size_t)WT * G::A_TILE_F4 * 16 + (size_t)2 * K * CC * NB * 4;
   static bool attr_set = false;  // per instantiation; benign if two threads race (same value)
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(conv_tiles_kernel<K, S, WT, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(conv_tiles_kernel<K, S, WT, WN, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     attr_set = true;
   }
@@ -458,13 +464,13 @@ int launch_conv(const ConvParams &p, int max_items, cudaStream_t st) {
   int grid = MIE_SM_COUNT * per_sm;
   if (grid > max_items) grid = max_items;
   if (grid < 1) grid = 1;
-  conv_tiles_kernel<K, S, WT, WN><<<grid, NT, smem, st>>>(p);
+  conv_tiles_kernel<K, S, WT, WN, CPT><<<grid, NT, smem, st>>>(p);
   return check_launch();
 }
 
 template <int K, int S>
 int dispatch_w(const ConvParams &p, int wt, int wn, int max_items, cudaStream_t st) {
-  if (wt == 4 && wn == 1) return launch_conv<K, S, 4, 1>(p, max_items, st);
+  if (wt == 4 && wn == 1) return launch_conv<K, S, 4, 2, 4>(p, max_items, st);  // 32 channels: 2 warps x 16 channels per tile
   if (wt == 4 && wn == 2) return launch_conv<K, S, 4, 2>(p, max_items, st);
   if (wt == 2 && wn == 4) return launch_conv<K, S, 2, 4>(p, max_items, st);
   if (wt == 1 && wn == 8) return launch_conv<K, S, 1, 8>(p, max_items, st);

@@ -259,8 +259,9 @@ __global__ void __launch_bounds__(256) tiles_dilate_kernel(
 }
 
 // Up to DILATE_SMALL_MAX tiles: one block keeps the flags in shared memory and compacts them itself -- no
-// ticket, no fence, no round trip through global memory (most levels of a UNet at batch 1 are this small).
-constexpr int DILATE_SMALL_MAX = 4096;
+// ticket, no fence, no round trip through global memory (the deeper levels of a UNet at batch 1 are this small;
+// at 1452 tiles one block measured slower than the multi-block kernel).
+constexpr int DILATE_SMALL_MAX = 512;
 
 __global__ void __launch_bounds__(1024) tiles_dilate_small_kernel(
     const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
