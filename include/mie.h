@@ -113,7 +113,8 @@ typedef struct mie_conv_args {
   int n; int hout; int wout; int k; int stride; int pad;
   /* work lists from mie_tiles_dilate */
   const int32_t *list; const int32_t *stale; int32_t *counts; int max_tiles;
-  /* output delta field */
+  /* output delta field; the tile words of the listed tiles must be 0 on entry (mie_tiles_dilate clears them):
+   * the kernels OR the sent pixels in */
   float *out; int64_t out_ps; uint64_t *out_bits;
   /* fused epilogue: d = conv (+ addend); act==NONE: dy = d; else with x = *res:
    *   dy = f(x + d) - (emitted ? *emitted : f(x));  *res = x + d;

@@ -47,6 +47,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        deps = [os.path.join(CSRC, src), os.path.join(INCLUDE, "mie.h"), __file__] + \
+               [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+        if not force and not verbose and os.path.exists(obj) and all(os.path.getmtime(d) < os.path.getmtime(obj) for d in deps):
+            return obj
         cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

@@ -4,18 +4,27 @@
 // Implicit GEMM over the compact list of active 8x8 output tiles:
 //   M = 128 rows   = 2 active tiles x 64 pixels (one tensor-memory lane per pixel)
 //   N = NB columns = up to 256 output channels (one tensor-memory column per channel)
-//   K              = Cin * k * k, walked as (32-channel chunk, filter tap); one pipeline stage per (chunk, tap).
-// Stage contents, both moved by TMA (tiled mode, 128-byte swizzle, no cluster, no multicast):
+//   K              = Cin * k * k, walked as (32-channel chunk, filter tap).
+// Two kernels share the epilogue (tcgen05.ld, fused incremental activation, tile words):
+//
+// conv_tc_kernel (per-tap): one pipeline stage per (chunk, tap), both operands moved by TMA (tiled mode,
+// 128-byte swizzle, no cluster, no multicast):
 //   A: for each of the two tiles a box [1 image][8 rows][8 cols][32 channels] of the input field, shifted by
 //      the tap; out-of-image elements are zero-filled by the TMA unit, which is the convolution padding.
 //      The box lands as 64 rows of 128 bytes in pixel order = the K-major operand layout tcgen05.mma reads.
 //      Stride-2 layers read from four parity views of the input (one tensor map per row/column parity).
 //   B: box [1 tap][NB output channels][32 input channels] of the filter, stored [tap][cout][cin].
-// Roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and owner of the
-// tensor-memory allocation, warps 2..5 = epilogue (tcgen05.ld, fused incremental activation, tile words).
+//   Roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and owner of the
+//   tensor-memory allocation, warps 2..5 = epilogue.  Takes stride 2, k = 1 and blocks of 256 channels.
+//
+// conv_tc_halo_kernel (halo-resident): stride 1, k in {3,5,7}.  The input halo of both tiles stays in shared
+// memory for a whole channel chunk, a filter tap is an address shift of the operand descriptor, and only filter
+// slices stream through the ring -- several taps per stage, two MMA-issuing warps.  See the comment at the kernel.
+//
 // Every mbarrier wait is bounded; on expiry the block raises counts[3], leaves its loops, frees its tensor
 // memory and returns.
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 #include "mie_common.cuh"
 
@@ -34,6 +43,8 @@ struct TcParams {
   const float *addend; int64_t addend_ps;
   int nb;        // output channels per block (multiple of 16, <= 256)
   int stages;    // pipeline depth
+  int tps;       // halo kernel: filter taps per pipeline stage (divides k*k)
+  int issuers;   // halo kernel: 1 or 2 MMA-issuing warps (2: stages alternate, one accumulator each)
 };
 
 namespace {
@@ -77,6 +88,14 @@ __device__ __forceinline__ void tma_load_4d_raw(unsigned smem_addr, const CUtens
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_5d_raw(unsigned smem_addr, const CUtensorMap *map, unsigned bar_addr, int c0, int c1,
+                                                int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_addr), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
 // 8-row groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled
 // K-major), [32,46) stride offset>>4, [46,48) version = 1, [61,64) layout = 2 (128-byte swizzle).
@@ -87,6 +106,19 @@ __device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr,
   d |= (unsigned long long)(sbo_bytes >> 4) << 32;
   d |= (unsigned long long)1 << 46;
   d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+// Descriptor of a K-major operand stored WITHOUT swizzle: 8 rows x 16 bytes form one contiguous 128-byte core
+// matrix; `lbo_bytes` is the distance between the two core matrices an MMA reads along K, `sbo_bytes` the distance
+// between consecutive 8-row groups.  The start address only needs 16-byte alignment, which is what lets a filter
+// tap be expressed as an address shift inside a resident halo tile.
+__device__ __forceinline__ unsigned long long make_smem_desc_plain(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(lbo_bytes >> 4) << 16;
+  d |= (unsigned long long)(sbo_bytes >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
   return d;
 }
 
@@ -117,6 +149,22 @@ __device__ __forceinline__ void umma_tf32_x4(unsigned tmem_d, unsigned long long
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with a caller-given advance of the A descriptor per K-slice (in 16-byte units).
+__device__ __forceinline__ void umma_tf32_x4_step(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                                  unsigned idesc, unsigned accumulate, unsigned long long a_step) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u64 a1, %1, %5;\n\tadd.u64 a2, a1, %5;\n\tadd.u64 a3, a2, %5;\n\t"
+      "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a1, b1, %3, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a2, b2, %3, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a3, b3, %3, q;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_step)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(unsigned long long *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -138,11 +186,60 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Epilogue of one accumulator row (= one output pixel, all NB channels of the block): optional residual add,
-// incremental activation against the reservoir, per-pixel send decision, store.  Called by all 32 lanes of an
+// One group of 16 accumulator columns of one pixel: optional residual add, incremental activation against the
+// reservoir, store.
+__device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float *v, int64_t pix, int co, bool any_d) {
+  bool flag = false;
+  const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
+  float4 d[4], x[4], base[4];
+  // all loads of the group first, then the arithmetic, then the stores
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
+    if (h < nq) {
+      if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
+      if (p.act != MIE_ACT_NONE && any_d) {
+        x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
+        if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    if (h >= nq) continue;
+    float4 o = d[h];
+    if (p.act != MIE_ACT_NONE) {
+      if (any_d) {
+        const float4 xn = f4add(x[h], d[h]);
+        *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
+        if (!p.emitted)
+          base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
+        o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
+                        act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
+      } else {
+        o = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
+    *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
+  }
+  return flag;
+}
+
+// Epilogue of one accumulator row (= one output pixel, all NB channels of the block).  Called by all 32 lanes of an
 // epilogue warp (the tensor-memory loads are warp-collective); returns whether the pixel was sent.
+__device__ __forceinline__ void tmem_ld16_sum(unsigned taddr, unsigned acc2, float *v) {
+  tmem_ld16(taddr, v);
+  if (acc2) {   // a second partial accumulator (two MMA issuers): the sum is the result
+    float w[16];
+    tmem_ld16(taddr + acc2, w);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] += w[i];
+  }
+}
+
 __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, unsigned taddr, bool valid, int64_t pix,
-                                                  int co0, unsigned long long *acc_empty_bar, int lane) {
+                                                  int co0, unsigned long long *acc_empty_bar, int lane, unsigned acc2 = 0) {
       bool flag = false;
       // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
       // zero: they skip the reservoir read-modify-write)
@@ -151,7 +248,7 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
         any_d = false;
         for (int c = 0; c < NB; c += 16) {
           float v[16];
-          tmem_ld16(taddr + c, v);
+          tmem_ld16_sum(taddr + c, acc2, v);
 #pragma unroll
           for (int j = 0; j < 16; ++j) any_d |= (v[j] != 0.0f);
         }
@@ -160,42 +257,8 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
       }
       for (int c = 0; c < NB; c += 16) {
         float v[16];
-        tmem_ld16(taddr + c, v);  // every lane of the warp takes part (aligned), valid or not
-        const int co = co0 + c;
-        if (!valid || co >= p.cout) continue;
-        const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
-        float4 d[4], x[4], base[4];
-        // all loads of the group first, then the arithmetic, then the stores
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
-          if (h < nq) {
-            if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
-            if (p.act != MIE_ACT_NONE && any_d) {
-              x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
-              if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
-            }
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          if (h >= nq) continue;
-          float4 o = d[h];
-          if (p.act != MIE_ACT_NONE) {
-            if (any_d) {
-              const float4 xn = f4add(x[h], d[h]);
-              *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
-              if (!p.emitted)
-                base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
-              o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
-                              act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
-            } else {
-              o = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          }
-          flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
-          *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
-        }
+        tmem_ld16_sum(taddr + c, acc2, v);  // every lane of the warp takes part (aligned), valid or not
+        if (valid && co0 + c < p.cout) flag |= tc_epilogue_group(p, v, pix, co0 + c, any_d);
       }
       // the accumulator has been read: hand it back to the MMA warp
       tc_fence_before();
@@ -224,6 +287,238 @@ struct TcMaps {
   CUtensorMap in[4];  // stride 1: [0] only; stride 2: [row parity * 2 + column parity]
   CUtensorMap w;
 };
+
+// Zeroes the stale tiles of the output field (all threads of the block take part).
+__device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_total, int THo, int TWo, int nthreads) {
+  const int tid = threadIdx.x;
+  const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
+  for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
+    const int t = p.stale[s];
+    if (t < 0 || t >= ntiles_total) { if (tid == 0) p.counts[3] = 1; continue; }
+    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+    for (int i = tid; i < 64 * p.cout; i += nthreads) {
+      const int px = i / p.cout, c = i - px * p.cout;
+      const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
+      if (oy < p.hout && ox < p.wout) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Halo-resident variant for stride-1 layers with k >= 3.
+//
+// The per-tap kernel below fetches the shifted 8x8x32 input box of every filter tap again (9 or 25 times the same
+// pixels), which makes the L2 -> shared-memory path its bound.  Here the (8+k-1)^2 halo of each of the two tiles
+// is fetched ONCE per 32-channel chunk and kept in shared memory in the un-swizzled operand layout
+//     [halo row y][tile 0|1][16-byte channel group c (8)][halo column x][4 channels],
+// in which the 8 pixels x..x+7 of one channel group are one contiguous 128-byte core matrix for ANY x.  A filter
+// tap (ky,kx) is then nothing but the descriptor start address  base + ky*2*ROW + kx*16  (ROW = 8*Wh*16 bytes),
+// with leading offset Wh*16 (next channel group) and stride offset ROW (next 8-pixel group).  Consecutive groups
+// alternate between the two tiles, so accumulator row m holds tile (m>>3)&1, pixel row m>>4, pixel column m&7.
+// Only the filter slices (NB x 32 floats per tap and chunk) stream through the stage ring.
+// Roles (256 threads): warp 0 = halo producer (one row per lane), warp 1 = filter producer, warps 2 and 3 = MMA
+// issuers (warp 2 owns the tensor memory), warps 4..7 = epilogue.  One thread issues a tcgen05.mma about every
+// 45 ns whatever its shape, which for blocks of <= 128 channels is several times the tensor core's own time: two
+// issuers take alternate pipeline stages and accumulate into separate accumulators that the epilogue adds.
+constexpr int HALO_THREADS = 256;
+constexpr int HALO_MAX_STAGES = 12;
+
+__global__ void __launch_bounds__(HALO_THREADS, 1)
+conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int NB = p.nb;
+  const unsigned b_bytes = (unsigned)NB * 128u;                 // one filter slice: NB rows of 32 floats, 128-byte swizzle
+  const unsigned st_bytes = b_bytes * (unsigned)p.tps;          // one stage: `tps` consecutive taps of one channel chunk
+  const int Wh = 8 + p.k - 1, Hh = 8 + p.k - 1;
+  const unsigned row_bytes = 8u * (unsigned)Wh * 16u;           // one halo row of one tile, all 8 channel groups
+  const unsigned a_buf_bytes = (unsigned)Hh * 2u * row_bytes;   // both tiles
+  __shared__ unsigned long long b_full[HALO_MAX_STAGES], b_empty[HALO_MAX_STAGES], a_full[2], a_empty[2], acc_full[2], acc_empty[2];
+  __shared__ unsigned s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
+  const int ntiles_total = p.n * THo * TWo;
+  unsigned acc_cols = 32;
+  while ((int)acc_cols < NB) acc_cols <<= 1;
+  const unsigned NI = (unsigned)p.issuers;
+  const unsigned tmem_cols = 2 * NI * acc_cols;   // per item buffer: one accumulator per issuer
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&a_full[b], 1); mbar_init(&a_empty[b], NI); mbar_init(&acc_full[b], NI); mbar_init(&acc_empty[b], 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = s_tmem_base;
+
+  tc_zero_stale(p, ntiles_total, THo, TWo, HALO_THREADS);
+
+  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_pairs = (n_active + 1) >> 1;
+  const int n_cblk = p.cout_pad / NB;
+  const int n_items = n_pairs * n_cblk;
+  const int n_chunks = p.cin_pad >> 5;
+  const int taps = p.k * p.k;
+  const unsigned b_base = smem_u32(smem);
+  const unsigned a_base = b_base + (unsigned)p.stages * st_bytes;
+
+  if (warp == 0) {
+    // =========================== halo producer: lane = 2 * halo row + tile ===========================
+    const int hy = lane >> 1, slot = lane & 1;
+    unsigned uses = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int pair = item / n_cblk;
+      int t0 = p.list[2 * pair];
+      int t1 = (2 * pair + 1 < n_active) ? p.list[2 * pair + 1] : -1;
+      if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { if (lane == 0) p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
+      const int t = slot ? t1 : t0;
+      const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
+      const unsigned tx_bytes = (t1 >= 0 ? 2u : 1u) * (unsigned)Hh * row_bytes;
+      bool ok = true;
+      for (int chunk = 0; chunk < n_chunks; ++chunk, ++uses) {
+        const unsigned buf = uses & 1u;
+        if (lane == 0) {
+          if (uses >= 2) ok = mbar_wait(&a_empty[buf], ((uses >> 1) - 1) & 1u, &s_abort);
+          if (ok) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&a_full[buf])), "r"(tx_bytes) : "memory");
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (hy < Hh && t >= 0)
+          tma_load_5d_raw(a_base + buf * a_buf_bytes + (unsigned)lane * row_bytes, &map_in, smem_u32(&a_full[buf]), 0, x0, chunk * 8, y0 + hy, n0);
+      }
+      if (!ok || s_abort) break;
+    }
+  } else if (warp == 1) {
+    // =========================== filter producer ===========================
+    if (lane == 0) {
+      unsigned s = 0, wait_parity = 0, stage_addr = b_base;
+      bool first_pass = true, ok = true;
+      for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x) {
+        const int cbn = (item % n_cblk) * NB;
+        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+          for (int tap = 0; tap < taps; tap += p.tps) {
+            if (!first_pass && !mbar_wait(&b_empty[s], wait_parity, &s_abort)) { ok = false; break; }
+            const unsigned bar = smem_u32(&b_full[s]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(st_bytes) : "memory");
+            tma_load_4d_raw(stage_addr, &map_w, bar, 0, cbn, chunk, tap);
+            stage_addr += st_bytes;
+            if (++s == (unsigned)p.stages) { s = 0; stage_addr = b_base; if (!first_pass) wait_parity ^= 1u; first_pass = false; }
+          }
+        }
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // =========================== MMA issuers ===========================
+    const unsigned me = (unsigned)warp - 2u;
+    if (lane == 0 && me < NI) {
+      const unsigned idesc = make_idesc_tf32(NB);
+      const unsigned long long b_hi = make_smem_desc(0) & 0xFFFFFFFF00000000ull;
+      const unsigned b_lo_flags = (unsigned)(make_smem_desc(0) & 0xFFFF0000ull);
+      const unsigned long long a_tmpl = make_smem_desc_plain(0, (unsigned)Wh * 16u, row_bytes);
+      const unsigned long long a_hi = a_tmpl & 0xFFFFFFFF00000000ull;
+      const unsigned a_lo_flags = (unsigned)(a_tmpl & 0xFFFF0000ull);
+      const unsigned long long a_step = 2ull * (unsigned)Wh;     // two channel groups (K = 8) in 16-byte units
+      const unsigned spc = (unsigned)(taps / p.tps);              // stages per channel chunk
+      const unsigned smask = (unsigned)p.stages - 1u;             // ring size is a power of two
+      unsigned g = 0;                                             // running stage number (all items of this block)
+      unsigned item_idx = 0, uses = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x, ++item_idx) {
+        const unsigned buf = item_idx & 1u;
+        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort)) break;
+        tc_fence_after();
+        const unsigned tmem_d = tmem_base + (buf * NI + me) * acc_cols;
+        unsigned accumulate = 0;
+        for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++uses, g += spc) {
+          const unsigned abuf = uses & 1u;
+          if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort)) { ok = false; break; }
+          const unsigned halo = a_base + abuf * a_buf_bytes;
+          bool issued = false;
+          for (unsigned st = (NI == 2u) ? ((me - g) & 1u) : 0u; st < spc; st += NI) {
+            const unsigned gs = g + st, slot = gs & smask;
+            if (!mbar_wait(&b_full[slot], (gs / (unsigned)p.stages) & 1u, &s_abort)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned t0 = st * (unsigned)p.tps;
+            unsigned ky = t0 / (unsigned)p.k, kx = t0 - ky * (unsigned)p.k;
+            unsigned row_addr = halo + ky * 2u * row_bytes, tap_addr = row_addr + kx * 16u;
+            unsigned b_addr = b_base + slot * st_bytes;
+            for (int j = 0; j < p.tps; ++j, b_addr += b_bytes) {
+              const unsigned a_lo = a_lo_flags | ((tap_addr & 0x3FFFFu) >> 4);
+              const unsigned b_lo = b_lo_flags | ((b_addr & 0x3FFFFu) >> 4);
+              umma_tf32_x4_step(tmem_d, a_hi | a_lo, b_hi | b_lo, idesc, accumulate, a_step);
+              accumulate = 1u;
+              tap_addr += 16u;
+              if (++kx == (unsigned)p.k) { kx = 0; row_addr += 2u * row_bytes; tap_addr = row_addr; }
+            }
+            umma_commit(&b_empty[slot]);
+            issued = true;
+          }
+          if (!ok) break;
+          // the halo buffer is free once the MMAs of both issuers have read it
+          if (issued) umma_commit(&a_empty[abuf]);
+          else mbar_arrive(&a_empty[abuf]);
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // =========================== epilogue (warps 4..7) ===========================
+    const int q = warp & 3;
+    const int m = q * 32 + lane;                       // accumulator row
+    const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
+    unsigned item_idx = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
+      const int pair = item / n_cblk, cb = item - pair * n_cblk;
+      const int li = 2 * pair + slot;
+      int t = (li < n_active) ? p.list[li] : -1;
+      if (t >= ntiles_total) t = -1;
+      const unsigned buf = item_idx & 1u;
+      const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
+      const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
+      const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
+      const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      tc_fence_after();
+      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
+                                              cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u);
+      // ballot bytes: [tile 0 row 2q][tile 1 row 2q][tile 0 row 2q+1][tile 1 row 2q+1]
+      const unsigned bal = __ballot_sync(0xffffffffu, sent);
+      if ((lane == 0 || lane == 8) && t >= 0) {
+        const unsigned sh = lane;                      // 0 for tile 0, 8 for tile 1
+        const unsigned rows = ((bal >> sh) & 0xFFu) | (((bal >> (16 + sh)) & 0xFFu) << 8);
+        if (rows) atomicOr(p.out_bits32 + 2 * (size_t)t + (q >> 1), rows << ((q & 1) * 16));
+      }
+    }
+  }
+
+  // ---- teardown ----
+  // the single-lane roles leave 31 lanes of their warp idle: reconverge before the block-wide barrier, which
+  // every warp must reach as a whole
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
+    if (tid == 0) p.counts[3] = 2;
+    if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
@@ -260,20 +555,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
 
-  // ---- zero stale tiles (all threads) ----------------------------------------------------------------
-  {
-    const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
-    for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
-      const int t = p.stale[s];
-      if (t < 0 || t >= ntiles_total) { if (tid == 0) p.counts[3] = 1; continue; }
-      const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
-      for (int i = tid; i < 64 * p.cout; i += TC_THREADS) {
-        const int px = i / p.cout, c = i - px * p.cout;
-        const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
-        if (oy < p.hout && ox < p.wout) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
-      }
-    }
-  }
+  tc_zero_stale(p, ntiles_total, THo, TWo, TC_THREADS);
 
   const int n_active = min(p.counts[0], p.max_tiles);
   const int n_pairs = (n_active + 1) >> 1;
@@ -372,12 +654,12 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       int t = (li < n_active) ? p.list[li] : -1;
       if (t >= ntiles_total) t = -1;
       const unsigned buf = item_idx & 1u;
-      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
-      tc_fence_after();
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      tc_fence_after();
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
                                           cb * NB, &acc_empty[buf], lane);
       const unsigned half = __ballot_sync(0xffffffffu, sent);
@@ -390,6 +672,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   }
 
   // ---- teardown ------------------------------------------------------------------------------------
+  __syncwarp();  // single-lane roles: the whole warp reaches the block-wide barrier together
   tc_fence_before();
   __syncthreads();
   if (s_abort) {
@@ -425,12 +708,18 @@ EncodeTiledFn get_encode() {
 }
 
 bool encode(EncodeTiledFn fn, CUtensorMap *m, int rank, const void *base, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
-            const cuuint32_t *box) {
+            const cuuint32_t *box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims, strides_bytes, box, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// MIE_TC_HALO=0 in the environment keeps every layer on the per-tap kernel (for A/B measurements).
+bool halo_enabled() {
+  static const bool on = []() { const char *e = getenv("MIE_TC_HALO"); return !(e && e[0] == '0'); }();
+  return on;
 }
 
 }  // namespace
@@ -474,6 +763,62 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t pairs = (a->max_tiles + 1) / 2;
   while (nb > 32 && a->thr == 0.0f && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
   p.nb = nb;
+  int acc_cols = 32;
+  while (acc_cols < nb) acc_cols <<= 1;
+  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
+
+  // ---- halo-resident kernel: stride 1, k in {3,5,7} ----
+  // (blocks of 256 channels are bound by the tensor core itself, not by instruction issue; with more work items
+  // than SMs the per-tap kernel measured 15 % faster there)
+  if (a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) && halo_enabled()) {
+    const int Wh = 8 + a->k - 1;
+    const int a_bytes = 2 * (Wh * 2 * 8 * Wh * 16);          // two buffers of [Hh][2 tiles][8 groups][Wh][16 B]
+    // A stage holds `tps` consecutive taps of one channel chunk (one TMA): the issuing thread pays its wait /
+    // fence / commit once per stage, so stages are made as fat as shared memory allows -- a whole filter (k*k
+    // taps), else one filter row (k taps), else a single tap -- even if only two ring slots remain (measured:
+    // 5-tap stages x 2 slots beat 1-tap stages x 4 slots by 25 % on a 5x5 256->128 layer).
+    const int budget = 200 * 1024 - a_bytes;
+    int tps = 0, stages = 0;
+    const int cand[3] = {a->k * a->k, a->k, 1};
+    for (int i = 0; i < 3 && !tps; ++i)
+      if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = 4 * cand[i] * nb * 128 <= budget ? 4 : 2; }
+    if (tps == a->k * a->k && p.cin_pad == 32) tps = a->k;   // at least two stages per work item, for the two issuers
+    p.tps = tps ? tps : 1;
+    const int b_bytes = p.tps * nb * 128;
+    p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;
+    if (stages >= 2) {
+      p.stages = stages;
+      const size_t smem = (size_t)stages * b_bytes + a_bytes + 1024;
+      int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
+      const int by_tmem = 512 / (2 * p.issuers * acc_cols);
+      if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem;
+      if (blocks_per_sm > 2) blocks_per_sm = 2;   // registers: 256 threads x ~106
+      if (blocks_per_sm < 1) blocks_per_sm = 1;
+      CUtensorMap map_in, map_w;
+      const cuuint64_t dims[5] = {4, (cuuint64_t)a->win, (cuuint64_t)(a->cin / 4), (cuuint64_t)a->hin, (cuuint64_t)a->n};
+      const cuuint64_t str[4] = {(cuuint64_t)a->in_ps * 4, 16, (cuuint64_t)a->win * a->in_ps * 4, (cuuint64_t)a->hin * a->win * a->in_ps * 4};
+      const cuuint32_t box[5] = {4, (cuuint32_t)Wh, 8, 1, 1};
+      const cuuint64_t nch = (cuuint64_t)(p.cin_pad / 32);
+      const cuuint64_t wdims[4] = {32, (cuuint64_t)a->cout_pad, nch, (cuuint64_t)(a->k * a->k)};
+      const cuuint64_t wstr[3] = {128, (cuuint64_t)a->cout_pad * 128, nch * a->cout_pad * 128};
+      const cuuint32_t box_w[4] = {32, (cuuint32_t)nb, 1, (cuuint32_t)p.tps};
+      if (encode(fn, &map_in, 5, a->in, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE) && encode(fn, &map_w, 4, a->wpacked_tc, wdims, wstr, box_w)) {
+        const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
+        int grid = max_items < cap ? (int)max_items : (int)cap;
+        if (grid < 1) grid = 1;
+        static int halo_smem_set = 0;
+        if ((int)smem > halo_smem_set) {
+          cudaError_t e = cudaFuncSetAttribute(conv_tc_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+          if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+          halo_smem_set = (int)smem;
+        }
+        conv_tc_halo_kernel<<<grid, HALO_THREADS, smem, st>>>(p, map_in, map_w);
+        return check_launch();
+      }
+      // a tensor map the driver refuses (unusual strides): the per-tap kernel below takes the layer
+    }
+  }
+
   const int stage_bytes = A_STAGE_BYTES + nb * 128;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 8) stages = 8;
@@ -485,7 +830,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
-  { int ac = 32; while (ac < nb) ac <<= 1; const int by_tmem = 512 / (2 * ac); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
+  { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
   if (blocks_per_sm > 4) blocks_per_sm = 4;
   if (blocks_per_sm < 1) blocks_per_sm = 1;
 
@@ -513,16 +858,15 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     const cuuint32_t box_w[4] = {32, (cuuint32_t)nb, 1, 1};
     if (!encode(fn, &maps.w, 4, a->wpacked_tc, dims, str, box_w)) return MIE_EINVAL;
   }
+  const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
+  int grid = max_items < cap ? (int)max_items : (int)cap;
+  if (grid < 1) grid = 1;
   static int smem_set = 0;
   if ((int)smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     smem_set = (int)smem;
   }
-  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
-  const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
-  int grid = max_items < cap ? (int)max_items : (int)cap;
-  if (grid < 1) grid = 1;
   conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
   return check_launch();
 }
@@ -569,3 +913,4 @@ extern "C" int mie_pack_conv_weights_tc(const float *w_oihw, int cout, int cin, 
   pack_weights_tc_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w_oihw, cout, cin, k, cp, op, wpacked, total);
   return check_launch();
 }
+
