@@ -149,20 +149,22 @@ __device__ __forceinline__ void umma_tf32_x4(unsigned tmem_d, unsigned long long
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Same with a caller-given advance of the A descriptor per K-slice (in 16-byte units).
-__device__ __forceinline__ void umma_tf32_x4_step(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                                  unsigned idesc, unsigned accumulate, unsigned long long a_step) {
+// Same with a caller-given advance of the A descriptor per K-slice (in 16-byte units) and only the first `nks`
+// (1..4) slices issued: a chunk that holds fewer than 32 real channels needs no MMA on its zero padding.
+__device__ __forceinline__ void umma_tf32_step(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                               unsigned idesc, unsigned accumulate, unsigned long long a_step, unsigned nks) {
   asm volatile(
-      "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "{\n\t.reg .pred p, q, r1, r2, r3;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "setp.eq.b32 q, 0, 0;\n\t"
+      "setp.gt.u32 r1, %6, 1;\n\tsetp.gt.u32 r2, %6, 2;\n\tsetp.gt.u32 r3, %6, 3;\n\t"
       "add.u64 a1, %1, %5;\n\tadd.u64 a2, a1, %5;\n\tadd.u64 a3, a2, %5;\n\t"
       "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a1, b1, %3, q;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a2, b2, %3, q;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], a3, b3, %3, q;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_step)
+      "@r1 tcgen05.mma.cta_group::1.kind::tf32 [%0], a1, b1, %3, q;\n\t"
+      "@r2 tcgen05.mma.cta_group::1.kind::tf32 [%0], a2, b2, %3, q;\n\t"
+      "@r3 tcgen05.mma.cta_group::1.kind::tf32 [%0], a3, b3, %3, q;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_step), "r"(nks)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long *bar) {
@@ -238,8 +240,11 @@ __device__ __forceinline__ void tmem_ld16_sum(unsigned taddr, unsigned acc2, flo
   }
 }
 
+// [c_lo, c_hi) is the column range this warp stores (two warps may share a pixel, each taking half the columns);
+// the "did anything change" scan always covers all NB columns.
 __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, unsigned taddr, bool valid, int64_t pix,
-                                                  int co0, unsigned long long *acc_empty_bar, int lane, unsigned acc2 = 0) {
+                                                  int co0, unsigned long long *acc_empty_bar, int lane, unsigned acc2 = 0,
+                                                  int c_lo = 0, int c_hi = 1 << 30) {
       bool flag = false;
       // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
       // zero: they skip the reservoir read-modify-write)
@@ -255,7 +260,8 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
         if (valid && p.addend && !any_d)
           for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
       }
-      for (int c = 0; c < NB; c += 16) {
+      c_hi = min(c_hi, NB);
+      for (int c = c_lo; c < c_hi; c += 16) {
         float v[16];
         tmem_ld16_sum(taddr + c, acc2, v);  // every lane of the warp takes part (aligned), valid or not
         if (valid && co0 + c < p.cout) flag |= tc_epilogue_group(p, v, pix, co0 + c, any_d);
@@ -266,7 +272,7 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
       if (lane == 0) mbar_arrive(acc_empty_bar);
       // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
       // selects this kernel with thr > 0 when one block holds every channel of a pixel.
-      if (valid && (p.thr > 0.0f || p.emitted)) {
+      if (valid && (p.thr > 0.0f || p.emitted) && c_lo == 0) {
         const int cend = min(NB, p.cout - co0);
         if (!flag) {
           for (int c = 0; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -316,11 +322,13 @@ __device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_tota
 // with leading offset Wh*16 (next channel group) and stride offset ROW (next 8-pixel group).  Consecutive groups
 // alternate between the two tiles, so accumulator row m holds tile (m>>3)&1, pixel row m>>4, pixel column m&7.
 // Only the filter slices (NB x 32 floats per tap and chunk) stream through the stage ring.
-// Roles (256 threads): warp 0 = halo producer (one row per lane), warp 1 = filter producer, warps 2 and 3 = MMA
-// issuers (warp 2 owns the tensor memory), warps 4..7 = epilogue.  One thread issues a tcgen05.mma about every
+// Roles (384 threads): warp 0 = halo producer (one row per lane), warp 1 = filter producer, warps 2 and 3 = MMA
+// issuers (warp 2 owns the tensor memory), warps 4..11 = epilogue: two warps per tensor-memory lane quarter, each
+// taking half of the block's channels (the epilogue is a chain of dependent global loads per 16 channels; with
+// four warps it, not the MMAs, set the pace of layers with many work items per block).  One thread issues a tcgen05.mma about every
 // 45 ns whatever its shape, which for blocks of <= 128 channels is several times the tensor core's own time: two
 // issuers take alternate pipeline stages and accumulate into separate accumulators that the epilogue adds.
-constexpr int HALO_THREADS = 256;
+constexpr int HALO_THREADS = 384;
 constexpr int HALO_MAX_STAGES = 12;
 
 __global__ void __launch_bounds__(HALO_THREADS, 1)
@@ -347,7 +355,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&a_full[b], 1); mbar_init(&a_empty[b], NI); mbar_init(&acc_full[b], NI); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&a_full[b], 1); mbar_init(&a_empty[b], NI); mbar_init(&acc_full[b], NI); mbar_init(&acc_empty[b], 8); }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -430,7 +438,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const unsigned a_lo_flags = (unsigned)(a_tmpl & 0xFFFF0000ull);
       const unsigned long long a_step = 2ull * (unsigned)Wh;     // two channel groups (K = 8) in 16-byte units
       const unsigned spc = (unsigned)(taps / p.tps);              // stages per channel chunk
-      const unsigned smask = (unsigned)p.stages - 1u;             // ring size is a power of two
+      const unsigned nst = (unsigned)p.stages;
       unsigned g = 0;                                             // running stage number (all items of this block)
       unsigned item_idx = 0, uses = 0;
       bool ok = true;
@@ -444,10 +452,11 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
           const unsigned abuf = uses & 1u;
           if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort)) { ok = false; break; }
           const unsigned halo = a_base + abuf * a_buf_bytes;
+          const unsigned nks = (unsigned)min(4, (p.cin - chunk * 32 + 7) >> 3);   // K-slices holding real channels
           bool issued = false;
           for (unsigned st = (NI == 2u) ? ((me - g) & 1u) : 0u; st < spc; st += NI) {
-            const unsigned gs = g + st, slot = gs & smask;
-            if (!mbar_wait(&b_full[slot], (gs / (unsigned)p.stages) & 1u, &s_abort)) { ok = false; break; }
+            const unsigned gs = g + st, lap = gs / nst, slot = gs - lap * nst;
+            if (!mbar_wait(&b_full[slot], lap & 1u, &s_abort)) { ok = false; break; }
             tc_fence_after();
             const unsigned t0 = st * (unsigned)p.tps;
             unsigned ky = t0 / (unsigned)p.k, kx = t0 - ky * (unsigned)p.k;
@@ -456,7 +465,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
             for (int j = 0; j < p.tps; ++j, b_addr += b_bytes) {
               const unsigned a_lo = a_lo_flags | ((tap_addr & 0x3FFFFu) >> 4);
               const unsigned b_lo = b_lo_flags | ((b_addr & 0x3FFFFu) >> 4);
-              umma_tf32_x4_step(tmem_d, a_hi | a_lo, b_hi | b_lo, idesc, accumulate, a_step);
+              umma_tf32_step(tmem_d, a_hi | a_lo, b_hi | b_lo, idesc, accumulate, a_step, nks);
               accumulate = 1u;
               tap_addr += 16u;
               if (++kx == (unsigned)p.k) { kx = 0; row_addr += 2u * row_bytes; tap_addr = row_addr; }
@@ -474,8 +483,14 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       }
     }
   } else {
-    // =========================== epilogue (warps 4..7) ===========================
+    // =========================== epilogue (warps 4..11) ===========================
     const int q = warp & 3;
+    const int half = (warp - 4) >> 2;                  // which half of the block's channels this warp stores
+    // one thread must see every channel of a pixel to decide whether it is sent: thresholded layers leave the
+    // whole pixel to the first warp of the pair
+    const bool whole = p.thr > 0.0f || p.emitted != nullptr || NB < 32;
+    const int c_lo = whole ? (half ? NB : 0) : half * (NB >> 1);
+    const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
     const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
     unsigned item_idx = 0;
@@ -492,7 +507,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
       tc_fence_after();
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
-                                              cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u);
+                                              cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u, c_lo, c_hi);
       // ballot bytes: [tile 0 row 2q][tile 1 row 2q][tile 0 row 2q+1][tile 1 row 2q+1]
       const unsigned bal = __ballot_sync(0xffffffffu, sent);
       if ((lane == 0 || lane == 8) && t >= 0) {
@@ -644,6 +659,8 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     }
   } else {
     // =========================== epilogue (warps 2..5) ===========================
+    // (a second set of four epilogue warps, as in the halo kernel, measured slower here: this kernel's small
+    // layers gain more from a third resident block per SM than from a shorter epilogue)
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
@@ -662,11 +679,10 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       tc_fence_after();
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
                                           cb * NB, &acc_empty[buf], lane);
-      const unsigned half = __ballot_sync(0xffffffffu, sent);
-      if (lane == 0 && t >= 0 && half) {
+      const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
+      if (lane == 0 && t >= 0 && sent_bits) {
         unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
-        if (n_cblk > 1) atomicOr(wp, half);
-        else *wp = half;
+        atomicOr(wp, sent_bits);
       }
     }
   }
@@ -729,14 +745,21 @@ bool tc_eligible(const mie_conv_args *a) {
   if (!a->wpacked_tc) return false;
   if (!(a->stride == 1 || a->stride == 2)) return false;
   if (a->k != 1 && a->k != 3 && a->k != 5 && a->k != 7) return false;
-  if (a->cin % 4 || a->in_ps % 4 || !aligned16(a->in)) return false;            // TMA: 16-byte strides and base
+  if (a->in_ps % 4 || !aligned16(a->in)) return false;                           // TMA: 16-byte strides and base
+  const bool halo_shape = a->stride == 1 && a->k >= 3 && a->k <= 7;
+  // a channel count that is no multiple of 4 is taken when the pixel stride covers the rounded-up count: the
+  // padding channels are read and meet zero filter entries (the same contract as the FP32 path's vector loads)
+  if (a->cin % 4 && !(halo_shape && a->in_ps >= (a->cin + 3) / 4 * 4)) return false;
   if (a->cout % 4 || a->out_ps % 4 || !aligned16(a->out)) return false;          // float4 epilogue
   if (a->res && (a->res_ps % 4 || !aligned16(a->res))) return false;
   if (a->emitted && (a->emitted_ps % 4 || !aligned16(a->emitted))) return false;
   if (a->addend && (a->addend_ps % 4 || !aligned16(a->addend))) return false;
   if (a->cout_pad % 16) return false;
   if (a->thr > 0.0f && a->cout_pad > 256) return false;
-  if ((int64_t)a->cin * a->k * a->k < 256) return false;                         // too shallow to pay off
+  // Too shallow to pay off.  (The 5x5 head of E2Depth, 5 -> 32 channels, would run 3x faster here than on the
+  // FP32 path, but it sees the raw input delta: truncating O(1) values to TF32 every step random-walks in the
+  // first reservoir and measured 1.1e-3 of the output range against 1.3e-5 with the head in FP32.)
+  if ((int64_t)a->cin * a->k * a->k < 256) return false;
   if (a->stride == 2 && ((a->hin & 1) || (a->win & 1))) return false;            // parity views need even extents
   return true;
 }
@@ -768,9 +791,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
 
   // ---- halo-resident kernel: stride 1, k in {3,5,7} ----
-  // (blocks of 256 channels are bound by the tensor core itself, not by instruction issue; with more work items
-  // than SMs the per-tap kernel measured 15 % faster there)
-  if (a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) && halo_enabled()) {
+  // Two shapes stay on the per-tap kernel: blocks of 256 channels with more work items than SMs (bound by the
+  // tensor core itself, not by instruction issue: per-tap measured 15 % faster), and layers of a single channel
+  // chunk (the halo is used for k*k taps only once: per-tap measured 8 % faster on 32 -> 32 channels, 3x3).
+  if (a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) && p.cin_pad > 32 && halo_enabled()) {
     const int Wh = 8 + a->k - 1;
     const int a_bytes = 2 * (Wh * 2 * 8 * Wh * 16);          // two buffers of [Hh][2 tiles][8 groups][Wh][16 B]
     // A stage holds `tps` consecutive taps of one channel chunk (one TMA): the issuing thread pays its wait /
@@ -781,8 +805,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     int tps = 0, stages = 0;
     const int cand[3] = {a->k * a->k, a->k, 1};
     for (int i = 0; i < 3 && !tps; ++i)
-      if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = 4 * cand[i] * nb * 128 <= budget ? 4 : 2; }
-    if (tps == a->k * a->k && p.cin_pad == 32) tps = a->k;   // at least two stages per work item, for the two issuers
+      if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = budget / (cand[i] * nb * 128); if (stages > 4) stages = 4; }
     p.tps = tps ? tps : 1;
     const int b_bytes = p.tps * nb * 128;
     p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;
@@ -792,10 +815,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
       int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
       const int by_tmem = 512 / (2 * p.issuers * acc_cols);
       if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem;
-      if (blocks_per_sm > 2) blocks_per_sm = 2;   // registers: 256 threads x ~106
+      if (blocks_per_sm > 1) blocks_per_sm = 1;   // registers: 384 threads x ~112
       if (blocks_per_sm < 1) blocks_per_sm = 1;
       CUtensorMap map_in, map_w;
-      const cuuint64_t dims[5] = {4, (cuuint64_t)a->win, (cuuint64_t)(a->cin / 4), (cuuint64_t)a->hin, (cuuint64_t)a->n};
+      const cuuint64_t dims[5] = {4, (cuuint64_t)a->win, (cuuint64_t)((a->cin + 3) / 4), (cuuint64_t)a->hin, (cuuint64_t)a->n};
       const cuuint64_t str[4] = {(cuuint64_t)a->in_ps * 4, 16, (cuuint64_t)a->win * a->in_ps * 4, (cuuint64_t)a->hin * a->win * a->in_ps * 4};
       const cuuint32_t box[5] = {4, (cuuint32_t)Wh, 8, 1, 1};
       const cuuint64_t nch = (cuuint64_t)(p.cin_pad / 32);
@@ -831,7 +854,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
   { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
-  if (blocks_per_sm > 4) blocks_per_sm = 4;
+  if (blocks_per_sm > 3) blocks_per_sm = 3;   // registers: 192 threads x ~100
   if (blocks_per_sm < 1) blocks_per_sm = 1;
 
   TcMaps maps;

@@ -294,7 +294,8 @@ class nnConvIncr(nn.Conv2d):
                 w = w[:, :key].contiguous()
             buf, cp, op = fl.pack_conv_weights(w.float())
             tc = None
-            if key * self._k * self._k >= 256 and key % 4 == 0 and self.out_channels % 4 == 0:
+            # the library decides per call whether the tensor-core copy is used; it never is below this depth
+            if key * self._k * self._k >= 256 and self.out_channels % 4 == 0:
                 tc = fl.pack_conv_weights_tc(w.float())
             hit = (ver, buf, cp, op, tc)
             self._packed[key] = hit

@@ -126,8 +126,9 @@ def tf32_round(x: Tensor) -> Tensor:
 
 def tc_eligible(cin: int, cout: int, k: int, stride: int, h: int, w: int) -> bool:
     """Host-side rule that sends a convolution to the tensor cores (given 16-byte aligned channel strides)."""
-    return (cin * k * k >= 256 and cin % 4 == 0 and cout % 4 == 0 and stride in (1, 2)
-            and (stride == 1 or (h % 2 == 0 and w % 2 == 0)))
+    halo_shape = stride == 1 and k in (3, 5, 7)     # the halo-resident kernel also takes channel counts off 4
+    return (cin * k * k >= 256 and (cin % 4 == 0 or halo_shape) and cout % 4 == 0
+            and stride in (1, 2) and (stride == 1 or (h % 2 == 0 and w % 2 == 0)))
 
 
 def conv_delta_tf32(dx: Tensor, weight: Tensor, stride: int, pad: int) -> Tensor:
