@@ -32,8 +32,8 @@ class IncrConfig:
     carry            keep what was withheld and send it once it grows past the threshold (bounded error)
     input_threshold  threshold used when a mask has to be derived from a bare delta tensor
     tensor_cores     "auto" runs convolutions whose reduction depth Cin*k*k is at least 256 on the tensor cores
-                     (TF32 inputs, FP32 accumulation; values then agree with FP32 to about 1e-3 of the range);
-                     "off" keeps every convolution on the FP32 path
+                     (TF32 inputs, FP32 accumulation; values then agree with FP32 to about 1e-3 of the range,
+                     E2Depth's accumulated output to about 1e-5); "off" keeps every convolution on the FP32 path
     compat           "reference": networks wired as the reference is written; "exact": as intended, which
                      makes the accumulated incremental output equal to a dense recompute
     """
