@@ -85,4 +85,38 @@ __device__ int block_ordered_compact(Pred pred, int n, int32_t *list) {
   return s_base;
 }
 
+// Two ordered compactions in one sweep (same barriers as one): listA <- i with flag(i) == 1, listB <- i with
+// flag(i) == 2 (listB may be null: then only counted as 0).  Returns the two counts through na / nb.
+template <typename Flag>
+__device__ void block_ordered_compact2(Flag flag, int n, int32_t *listA, int32_t *listB, int *na, int *nb) {
+  __shared__ int s_wa[32], s_wb[32];
+  __shared__ int s_ba, s_bb;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) { s_ba = 0; s_bb = 0; }
+  __syncthreads();
+  for (int start = 0; start < n; start += blockDim.x) {
+    const int i = start + threadIdx.x;
+    const int f = (i < n) ? flag(i) : 0;
+    const bool pa = f == 1, pb = (f == 2) && listB;
+    const unsigned ba = __ballot_sync(0xffffffffu, pa), bb = __ballot_sync(0xffffffffu, pb);
+    const unsigned below = (1u << lane) - 1u;
+    if (lane == 0) { s_wa[warp] = __popc(ba); s_wb[warp] = __popc(bb); }
+    __syncthreads();
+    int offa = 0, tota = 0, offb = 0, totb = 0;
+    for (int w2 = 0; w2 < nwarps; ++w2) {
+      const int ca = s_wa[w2], cb = s_wb[w2];
+      if (w2 < warp) { offa += ca; offb += cb; }
+      tota += ca; totb += cb;
+    }
+    const int basea = s_ba, baseb = s_bb;
+    if (pa) listA[basea + offa + __popc(ba & below)] = i;
+    if (pb) listB[baseb + offb + __popc(bb & below)] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) { s_ba = basea + tota; s_bb = baseb + totb; }
+    __syncthreads();
+  }
+  *na = s_ba;
+  *nb = s_bb;
+}
+
 }  // namespace mie

@@ -202,6 +202,8 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
               a[r] = A[(cq * G::IN_T + r * S) * G::PITCH + G::pos(pc * S + kx)];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+              // channels past Cin are zero padding (5 voxel bins in a chunk of 8): no FMAs for them
+              if (c0 + cq * 4 + c >= p.cin) break;
               const float4 b0 = *reinterpret_cast<const float4 *>(B + (kx * CC + cq * 4 + c) * NB);
               float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f);
               if (CPT == 8) b1 = *reinterpret_cast<const float4 *>(B + (kx * CC + cq * 4 + c) * NB + 4);

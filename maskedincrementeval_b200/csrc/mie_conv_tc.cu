@@ -346,6 +346,12 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // issued first so that their latency hides behind barrier set-up and the tensor-memory allocation
+  const int n_active = min(p.counts[0], p.max_tiles);
+  if (tid == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_in)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_w)) : "memory");
+  }
   const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
   const int ntiles_total = p.n * THo * TWo;
   unsigned acc_cols = 32;
@@ -372,7 +378,6 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
 
   tc_zero_stale(p, ntiles_total, THo, TWo, HALO_THREADS);
 
-  const int n_active = min(p.counts[0], p.max_tiles);
   const int n_pairs = (n_active + 1) >> 1;
   const int n_cblk = p.cout_pad / NB;
   const int n_items = n_pairs * n_cblk;
@@ -547,6 +552,12 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // issued first so that their latency hides behind barrier set-up and the tensor-memory allocation
+  const int n_active = min(p.counts[0], p.max_tiles);
+  if (tid == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&maps.in[0])) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&maps.w)) : "memory");
+  }
   const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
   const int ntiles_total = p.n * THo * TWo;
   unsigned acc_cols = 32;            // columns of one accumulator (power of two >= NB)
@@ -572,7 +583,6 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
 
   tc_zero_stale(p, ntiles_total, THo, TWo, TC_THREADS);
 
-  const int n_active = min(p.counts[0], p.max_tiles);
   const int n_pairs = (n_active + 1) >> 1;
   const int n_cblk = p.cout_pad / NB;
   const int n_items = n_pairs * n_cblk;

@@ -198,6 +198,9 @@ __device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *__restrict
   const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
   const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
   const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
+  // issued before the neighbourhood test so that the three latencies overlap
+  const uint64_t prev = out_bits ? out_bits[t] : 0ull;
+  const uint64_t uni = union_bits ? union_bits[t] : 0ull;
   const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
   const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
   bool active = false;
@@ -223,11 +226,11 @@ __device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *__restrict
       }
     }
   }
-  if (!active && union_bits && union_bits[t] != 0ull) active = true;
+  if (uni != 0ull) active = true;
   uint8_t f = active ? 1 : 0;
   if (out_bits) {
-    if (!active && out_bits[t] != 0ull) f = 2;
-    out_bits[t] = 0ull;
+    if (!active && prev != 0ull) f = 2;
+    if (prev != 0ull) out_bits[t] = 0ull;
   }
   return f;
 }
@@ -247,10 +250,8 @@ __global__ void __launch_bounds__(256) tiles_dilate_kernel(
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const int na = block_ordered_compact([&](int i) { return __ldcg(flags + i) == 1; }, ntiles, list);
-  __syncthreads();
-  int ns = 0;
-  if (stale) ns = block_ordered_compact([&](int i) { return __ldcg(flags + i) == 2; }, ntiles, stale);
+  int na, ns;
+  block_ordered_compact2([&](int i) { return (int)__ldcg(flags + i); }, ntiles, list, stale, &na, &ns);
   if (threadIdx.x == 0) {
     counts[0] = na;
     counts[1] = ns;
@@ -272,10 +273,8 @@ __global__ void __launch_bounds__(1024) tiles_dilate_small_kernel(
   for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
     s_flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
   __syncthreads();
-  const int na = block_ordered_compact([&](int i) { return s_flags[i] == 1; }, ntiles, list);
-  __syncthreads();
-  int ns = 0;
-  if (stale) ns = block_ordered_compact([&](int i) { return s_flags[i] == 2; }, ntiles, stale);
+  int na, ns;
+  block_ordered_compact2([&](int i) { return (int)s_flags[i]; }, ntiles, list, stale, &na, &ns);
   if (threadIdx.x == 0) {
     counts[0] = na;
     counts[1] = ns;

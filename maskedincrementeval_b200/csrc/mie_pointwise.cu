@@ -354,9 +354,10 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
     const float *__restrict__ dg, int64_t dg_ps, const uint64_t *__restrict__ dg_bits, float *__restrict__ gres, int64_t g_ps,
     const float *__restrict__ dcp, int64_t dcp_ps, const uint64_t *__restrict__ dcp_bits, float *__restrict__ cprev,
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
-    uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2) {
+    uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2,
+    int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */) {
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
-  const int ncb = (C + CB - 1) / CB;
+  const int ncb = (C + cbw - 1) / cbw;
   const int n_items = ntiles * ncb;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int t = item / ncb, cb = item - t * ncb;
@@ -376,7 +377,7 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
       }
       continue;
     }
-    const int c_lo = cb * CB, q4 = (min(C, c_lo + CB) - c_lo) >> 2;
+    const int c_lo = cb * cbw, q4 = (min(C, c_lo + cbw) - c_lo) >> 2;
     for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
       const int p = e / q4, c = c_lo + (e - p * q4) * 4;
       if (!pix_valid(g, p)) continue;
@@ -793,9 +794,13 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
                    dc_ps % 4 == 0 && aligned16(dg) && aligned16(g) && aligned16(cell) && aligned16(dh) && aligned16(dc) &&
                    (!dc_prev || (dcp_ps % 4 == 0 && aligned16(dc_prev))) && (!cprev || (cprev_ps % 4 == 0 && aligned16(cprev)));
   if (vec) {
-    convlstm_point_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+    // each element costs ~11 vector loads and 10 transcendentals: on the small fields of a UNet's deep levels a
+    // block of 64 px x 32 ch leaves most SMs with one block of four sequential rounds; narrower items fix that
+    int cbw = CB;
+    while (cbw > 8 && (int64_t)ntiles * divup(C, cbw) < (int64_t)MIE_SM_COUNT * 8) cbw >>= 1;
+    convlstm_point_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, cbw)), PW_THREADS, 0, (cudaStream_t)stream>>>(
         dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
-        dc_ps, dc_bits, N, C, H, W, sum_m2);
+        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw);
     return check_launch();
   }
   convlstm_point_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
