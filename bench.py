@@ -276,18 +276,48 @@ def run_ours(args):
     mie.config.threshold = args.threshold
     streams = args.streams
     K, Wm = args.steps, args.warmup
-    sd = seeded_state_dict(e2depth_shapes(), seed=0, init="default")
+    flow = args.net != "e2depth"
+    if flow:
+        from maskedincrementeval_b200.incr_modules.evflownet_incr import MultiResUNetRecurrentIncr
+        from maskedincrementeval_b200.incr_modules.fireflownet_incr import FireFlowNetIncr
+        from maskedincrementeval_b200.synthetic import count_image_sequence
+
+    def build_net():
+        if args.net == "fireflownet":
+            return FireFlowNetIncr(dict(base_num_channels=32, kernel_size=3, mask_output=False), 2, compat="exact")
+        if args.net == "evflownet":
+            return MultiResUNetRecurrentIncr(compat="exact")
+        return E2VIDRecurrentIncr(dict(E2DEPTH_CFG))
+
+    shapes = e2depth_shapes() if not flow else {k: tuple(v.shape) for k, v in build_net().state_dict().items()}
+    sd = seeded_state_dict(shapes, seed=0, init="default")
 
     def make_net():
-        net = E2VIDRecurrentIncr(dict(E2DEPTH_CFG)).to(dev).eval()
+        net = build_net().to(dev).eval()
         net.load_state_dict(sd)
         return net
+
+    def dense_out(model, x):
+        """Finest-scale dense output of one full pass (what the runner accumulates first)."""
+        with torch.no_grad():
+            if not flow:
+                return model.forward_refresh_reservoirs(x, None)[0]
+            if hasattr(model, "reset_states"):
+                model.reset_states()
+            out = model.forward_refresh_reservoirs(x)
+            return out["flow"][0] if isinstance(out, dict) else out[0]
+
+    def first(y):
+        return y[0] if isinstance(y, (list, tuple)) else y
 
     net = make_net()
     from maskedincrementeval_b200.sharding import job_throughput, streams_of_rank
     my_streams = streams_of_rank(streams * world, world, rank)   # global stream ids of this rank
     n_frames = Wm + K + 3
-    frames_host = voxel_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
+    if flow:
+        frames_host = count_image_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
+    else:
+        frames_host = voxel_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
     frames_pinned = [f.pin_memory() for f in frames_host]
     frames_dev = [f.to(dev) for f in frames_host]
     in_bytes = frames_host[0].numel() * 4
@@ -324,18 +354,17 @@ def run_ours(args):
     wall = time.perf_counter() - t_wall0
     clocks = sampler.stop()
     dev_s = sum(a.elapsed_time(b) for a, b in ev) * 1e-3
-    y_incr = run.output.clone()
+    y_incr = first(run.output).clone()
 
     # parity of what was just timed: accumulated incremental output vs a dense recompute of the last frame
     dense = make_net()
-    with torch.no_grad():
-        yd, _ = dense.forward_refresh_reservoirs(frames_dev[2 + Wm + K - 1], None)
+    yd = dense_out(dense, frames_dev[2 + Wm + K - 1])
     rng = float(yd.max() - yd.min())
     parity = float((y_incr - yd).abs().max()) / max(rng, 1e-12)
 
     # ---- end-to-end arm: pinned host input, prediction read back every step ---------------------
     run.refresh(frames_dev[0])
-    out_host = torch.empty(run.output.shape, dtype=torch.float32).pin_memory()
+    out_host = torch.empty(first(run.output).shape, dtype=torch.float32).pin_memory()
     for i in range(1, 2 + Wm):
         run.step(frames_pinned[i].to(dev, non_blocking=True))
     barrier()
@@ -345,7 +374,7 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(st)
         y = run.step(frames_pinned[2 + Wm + i].to(dev, non_blocking=True))
-        out_host.copy_(y, non_blocking=True)
+        out_host.copy_(first(y), non_blocking=True)
         e1.record(st)
         e1.synchronize()
         e2e_ev.append((e0, e1))
@@ -375,7 +404,11 @@ def run_ours(args):
             "parity": {"max_abs_err_over_range_vs_dense_recompute": parity, "after_steps": 1 + Wm + K, "tolerance": 1e-4},
             "wall_s_timed_region": wall,
         }
-        if world == 1:
+        if world == 1 and flow:
+            peak, kind = load_peaks()
+            line["roofline"] = roofline_conv3x3(dev, peak, kind)
+            line["metric"] = f"incremental timesteps/sec/GPU, {args.net} {H}x{W}; conv3x3 HBM GB/s"
+        if world == 1 and not flow:
             peak, kind = load_peaks()
             line["roofline"] = roofline_conv3x3(dev, peak, kind)
             # dense recompute (the >=10x target's denominator), same frames
@@ -383,14 +416,14 @@ def run_ours(args):
                 torch.backends.cudnn.allow_tf32 = tf32
                 with torch.no_grad():
                     for i in range(3):
-                        dense.forward_refresh_reservoirs(frames_dev[i], None)
+                        dense_out(dense, frames_dev[i])
                     torch.cuda.synchronize()
                     ts = []
                     for i in range(min(K, 10)):
                         flush()
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                         e0.record(st)
-                        dense.forward_refresh_reservoirs(frames_dev[2 + i], None)
+                        dense_out(dense, frames_dev[2 + i])
                         e1.record(st)
                         e1.synchronize()
                         ts.append(e0.elapsed_time(e1))
@@ -448,12 +481,21 @@ def main():
     ap.add_argument("--size", default="260x346", help="sensor resolution HxW (secondary measurements; the headline is 260x346)")
     ap.add_argument("--events", type=int, default=EVENTS)
     ap.add_argument("--segments", type=int, default=SEGMENTS)
+    ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet"],
+                    help="secondary measurements of the flow networks (BASELINE config 5: 256x336 two-channel event-count "
+                         "images, 20k events per window); the headline is e2depth")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
     args = ap.parse_args()
     H, W = (int(v) for v in args.size.split("x"))
     EVENTS, SEGMENTS = args.events, args.segments
-    if (H, W) != (260, 346) or args.streams != 1:
+    if args.net != "e2depth":
+        if args.size == "260x346":
+            H, W = 256, 336
+        if args.events == 30000:
+            EVENTS = 20000
+        WORKLOAD = f"{args.net}_{H}x{W}_b{args.streams}"
+    elif (H, W) != (260, 346) or args.streams != 1:
         WORKLOAD = f"e2depth_{H}x{W}_b{args.streams}"
     if args.roofline_only:
         dev = torch.device("cuda", 0)
