@@ -274,6 +274,7 @@ def run_ours(args):
 
     mie.config.compat = "exact"
     mie.config.threshold = args.threshold
+    mie.config.tensor_cores = args.tensor_cores
     streams = args.streams
     K, Wm = args.steps, args.warmup
     flow = args.net != "e2depth"
@@ -394,7 +395,7 @@ def run_ours(args):
             "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": f"{H}x{W}, reflection-padded to a multiple of 8",
-                       "events_per_window": EVENTS, "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold,
+                       "events_per_window": EVENTS, "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold, "tensor_cores": args.tensor_cores,
                        "weights": "random init (nn.Conv2d default), seed 0", "parallelism": f"{world} x independent streams",
                        "l2": "flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
                        "execution": "one CUDA graph replay per step"},
@@ -484,6 +485,8 @@ def main():
     ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet"],
                     help="secondary measurements of the flow networks (BASELINE config 5: 256x336 two-channel event-count "
                          "images, 20k events per window); the headline is e2depth")
+    ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
+                    help="off keeps every convolution on the FP32 path (secondary measurements)")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
     args = ap.parse_args()

@@ -53,7 +53,7 @@ __device__ __forceinline__ void or_word(unsigned *s_lo_hi, int p) {
 // ---------------------------------------------------------------------------------------------
 // incremental activation
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(PW_THREADS) act_incr_kernel(
+__global__ void __launch_bounds__(1024) act_incr_kernel(
     const float *in, int64_t in_ps, const uint64_t *__restrict__ in_bits, float *__restrict__ res,
     int64_t res_ps, float *__restrict__ emitted, int64_t em_ps, float *out, int64_t out_ps, uint64_t *out_bits,
     int N, int C, int H, int W, int op, float thr) {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(PW_THREADS) act_incr_kernel(
 // ---------------------------------------------------------------------------------------------
 // incremental product
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(PW_THREADS) mul_incr_kernel(
+__global__ void __launch_bounds__(1024) mul_incr_kernel(
     const float *__restrict__ d1, int64_t d1_ps, const uint64_t *__restrict__ bits1, float *__restrict__ x1, int64_t x1_ps,
     const float *__restrict__ d2, int64_t d2_ps, const uint64_t *__restrict__ bits2, float *__restrict__ x2, int64_t x2_ps,
     float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W, float thr) {
@@ -257,7 +257,10 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
   const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
   __shared__ unsigned s_w[2];
   __shared__ unsigned char s_fa[64], s_fb[64];  // per output pixel: 4 source-activity bits for a and b
-  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+  const int ncb = (C + 63) / 64;   // work item = (tile, block of 64 channels)
+  const int n_items = ntiles * ncb;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, blk = item - t * ncb;
     const TileGeom g = tile_geom(t, Ho, Wo);
     __syncthreads();
     if (threadIdx.x < 64) {
@@ -281,15 +284,16 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
     __syncthreads();
     const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
     if (wout == 0ull) {
-      if (out_bits[t] != 0ull) {
+      if (blk == 0 && out_bits[t] != 0ull) {   // only this block reads or writes the word
         zero_tile(out, out_ps, C, g, Ho, Wo);
         __syncthreads();
         if (threadIdx.x == 0) out_bits[t] = 0ull;
       }
       continue;
     }
-    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
-      const int p = e / C, c = e - p * C;
+    const int c_lo = blk * 64, cw = min(C, c_lo + 64) - c_lo;
+    for (int e = threadIdx.x; e < 64 * cw; e += blockDim.x) {
+      const int p = e / cw, c = c_lo + (e - p * cw);
       if (!pix_valid(g, p)) continue;
       float v = 0.0f;
       const unsigned fa = s_fa[p], fb = s_fb[p];
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
       }
       out[pix_index(g, p, Ho, Wo) * out_ps + c] = v;
     }
-    if (threadIdx.x == 0) out_bits[t] = wout;
+    if (blk == 0 && threadIdx.x == 0) out_bits[t] = wout;
   }
 }
 
@@ -527,6 +531,14 @@ __global__ void __launch_bounds__(PW_THREADS) add_vec_kernel(
   }
 }
 
+// Block size of the kernels that keep one block per tile (their output mask needs every channel of a pixel):
+// few tiles with many channels get wide blocks, so that a deep UNet level does not run on six small blocks.
+static int wide_threads(int ntiles, int C) {
+  int th = PW_THREADS;
+  while (th < 1024 && (int64_t)ntiles * th < (int64_t)MIE_SM_COUNT * 1024 && th * 8 <= 64 * C) th <<= 1;
+  return th;
+}
+
 static int item_grid(int64_t items) {
   const int64_t cap = (int64_t)MIE_SM_COUNT * 16;
   return (int)(items < cap ? (items > 0 ? items : 1) : cap);
@@ -565,25 +577,32 @@ __global__ void __launch_bounds__(PW_THREADS) add_kernel(
   }
 }
 
+constexpr int CBS = 64;  // channels per work item of the scalar channel-split kernels
+
+// work item = (tile, block of CBS channels): the deep levels of a UNet have a handful of tiles but a thousand channels
 __global__ void __launch_bounds__(PW_THREADS) cat2_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, int ca, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, int cb, float *__restrict__ out, int64_t out_ps,
     uint64_t *__restrict__ out_bits, int N, int H, int W) {
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int C = ca + cb;
-  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+  const int ncb = (C + CBS - 1) / CBS;
+  const int n_items = ntiles * ncb;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, blk = item - t * ncb;
     const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
     const TileGeom g = tile_geom(t, H, W);
     if (w == 0ull) {
-      if (out_bits[t] != 0ull) {
+      if (blk == 0 && out_bits[t] != 0ull) {   // only this block reads or writes the word
         __syncthreads();
         zero_tile(out, out_ps, C, g, H, W);
         if (threadIdx.x == 0) out_bits[t] = 0ull;
       }
       continue;
     }
-    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
-      const int p = e / C, c = e - p * C;
+    const int c_lo = blk * CBS, cw = min(C, c_lo + CBS) - c_lo;
+    for (int e = threadIdx.x; e < 64 * cw; e += blockDim.x) {
+      const int p = e / cw, c = c_lo + (e - p * cw);
       if (!pix_valid(g, p)) continue;
       const int64_t pix = pix_index(g, p, H, W);
       float v = 0.0f;
@@ -591,8 +610,7 @@ __global__ void __launch_bounds__(PW_THREADS) cat2_kernel(
       else { if ((wb >> p) & 1ull) v = b[pix * b_ps + (c - ca)]; }
       out[pix * out_ps + c] = v;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) out_bits[t] = w;
+    if (blk == 0 && threadIdx.x == 0) out_bits[t] = w;
   }
 }
 
@@ -760,7 +778,7 @@ extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_b
   if (emitted && emitted_ps < C) return MIE_EINVAL;
   if (in == out && in_ps != out_ps) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  act_incr_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+  act_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
       in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr);
   return check_launch();
 }
@@ -773,7 +791,7 @@ extern "C" int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits
   if (d1 && (!bits1 || d1_ps < C)) return MIE_EINVAL;
   if (d2 && (!bits2 || d2_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  mul_incr_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+  mul_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
       d1, d1_ps, bits1, x1, x1_ps, d2, d2_ps, bits2, x2, x2_ps, out, out_ps, out_bits, N, C, H, W, thr);
   return check_launch();
 }
@@ -822,7 +840,7 @@ extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bi
         a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode);
     return check_launch();
   }
-  upsample2x_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
+  upsample2x_kernel<<<item_grid((int64_t)ntiles * divup(C, 64)), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
                                                                                 out_ps, out_bits, N, C, H, W, mode);
   return check_launch();
 }
@@ -849,7 +867,7 @@ extern "C" int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, in
   if (N <= 0 || ca <= 0 || cb <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, ca); MIE_CHECK_FIELD(b, b_ps, cb); MIE_CHECK_FIELD(out, out_ps, ca + cb);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  cat2_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
+  cat2_kernel<<<item_grid((int64_t)ntiles * divup(ca + cb, CBS)), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
                                                                           out_ps, out_bits, N, H, W);
   return check_launch();
 }

@@ -42,7 +42,11 @@ def skip_concat_incr(x1_incr, x2_incr, scratch: Scratch, key: str):
     if a.shape[2:] != b.shape[2:]:
         raise NotImplementedError("incremental skip_concat needs equal spatial sizes (pad the input to a multiple of 16)")
     n, ca, h, w = a.shape
-    out = scratch.get(key, (n, ca + b.shape[1], h, w), torch.float32, a.device, channels_last=True)
+    c = ca + b.shape[1]
+    # pixel stride rounded up to 4 floats (the decoders see 2·C + 2 channels): 16-byte pixel addresses are what the
+    # convolution's vector loads and TMA need; the padding channels are never written and stay zero
+    full = scratch.get(key, (n, (c + 3) // 4 * 4, h, w), torch.float32, a.device, channels_last=True)
+    out = full[:, :c]
     bits = scratch.get(key + ".bits", (fl.n_tiles(n, h, w),), torch.int64, a.device)
     return [out, fl.cat2(a, ma, b, mb, out, bits)]
 
@@ -252,7 +256,8 @@ class UpsampleConvLayerIncr(nn.Module):
         sc = self._scratch
         d, m = fl.resolve(x, sc, "in")
         n, c, h, w = d.shape
-        up = sc.get("up", (n, c, 2 * h, 2 * w), torch.float32, d.device, channels_last=True)
+        # pixel stride rounded up to 4 floats (2·C + 2 input channels): see skip_concat_incr
+        up = sc.get("up", (n, (c + 3) // 4 * 4, 2 * h, 2 * w), torch.float32, d.device, channels_last=True)[:, :c]
         ub = sc.get("up.bits", (fl.n_tiles(n, 2 * h, 2 * w),), torch.int64, d.device)
         mu = fl.upsample2x(d, m, None, None, up, ub, nat.UP_BILINEAR)
         return self.conv2d.forward_fused([up, mu], self.activation)
