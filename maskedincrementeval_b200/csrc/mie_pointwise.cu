@@ -456,7 +456,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
     const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
     if (wout == 0ull) {
       if (cb == 0 && out_bits[t] != 0ull) {
-        zero_tile4(out, out_ps, C, g, Ho, Wo);
+        if (C & 3) zero_tile(out, out_ps, C, g, Ho, Wo);
+        else zero_tile4(out, out_ps, C, g, Ho, Wo);
         __syncthreads();
         if (threadIdx.x == 0) out_bits[t] = 0ull;
       }
@@ -493,6 +494,35 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
         }
       }
       st4(out + pix_index(g, p, Ho, Wo) * out_ps + c, v);
+    }
+    // channel counts off 4 (2·C + 2 in the flow decoders): the last block takes the 1..3 remaining channels one by one
+    const int ct = C & 3;
+    if (ct && cb == ncb - 1) {
+      const int c_tail = C - ct;
+      for (int e = threadIdx.x; e < 64 * ct; e += blockDim.x) {
+        const int p = e / ct, c = c_tail + (e - p * ct);
+        if (!pix_valid(g, p)) continue;
+        float v = 0.0f;
+        const unsigned fa = s_fa[p], fb = s_fb[p];
+        if (fa | fb) {
+          int y0, y1, x0, x1; float wy, wx;
+          up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
+          up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+          const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
+          float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
+          if (fa & 1u) v00 += a[(r0 + x0) * a_ps + c];
+          if (fa & 2u) v01 += a[(r0 + x1) * a_ps + c];
+          if (fa & 4u) v10 += a[(r1 + x0) * a_ps + c];
+          if (fa & 8u) v11 += a[(r1 + x1) * a_ps + c];
+          if (fb & 1u) v00 += b[(r0 + x0) * b_ps + c];
+          if (fb & 2u) v01 += b[(r0 + x1) * b_ps + c];
+          if (fb & 4u) v10 += b[(r1 + x0) * b_ps + c];
+          if (fb & 8u) v11 += b[(r1 + x1) * b_ps + c];
+          if (mode == MIE_UP_NEAREST) v = v00;
+          else v = (1.0f - wy) * ((1.0f - wx) * v00 + wx * v01) + wy * ((1.0f - wx) * v10 + wx * v11);
+        }
+        out[pix_index(g, p, Ho, Wo) * out_ps + c] = v;
+      }
     }
     if (cb == 0 && threadIdx.x == 0) out_bits[t] = wout;
   }
@@ -835,7 +865,7 @@ extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bi
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (b && (!b_bits || b_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(2 * H, 8) * divup(2 * W, 8);
-  if (C % 4 == 0 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
+  if (C >= 4 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
     upsample2x_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
         a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode);
     return check_launch();
