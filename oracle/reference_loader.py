@@ -33,7 +33,8 @@ import types
 import torch
 import torch.nn as nn
 
-DEFAULT_ROOT = "/root/reference"
+# where a checkout of the reference lives; MIE_REFERENCE_ROOT overrides the default location
+DEFAULT_ROOT = os.environ.get("MIE_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 
 
 def reference_available(root: str = DEFAULT_ROOT) -> bool:
