@@ -349,7 +349,9 @@ def test_thresholded_fused_conv_matches_standalone(dev):
     (32, 32, 3, 1, 1, 260, 346, "relu"), (64, 64, 3, 1, 1, 33, 44, "relu"), (128, 256, 3, 1, 1, 24, 40, None),
     (32, 64, 5, 2, 2, 64, 96, "relu"), (256, 128, 5, 1, 1, 16, 24, "relu"), (64, 512, 3, 1, 1, 16, 16, None),
     (40, 48, 3, 1, 1, 20, 28, "tanh"), (16, 32, 5, 1, 1, 19, 21, "sigmoid"), (32, 32, 3, 2, 1, 32, 48, "relu"),
-    (512, 16, 1, 1, 1, 9, 11, None)])
+    (512, 16, 1, 1, 1, 9, 11, None),
+    # long stride-2 reduction (two MMA issuers in the per-tap kernel), 7x7 halo, 3-slot filter ring (5x5, 64-channel blocks)
+    (64, 64, 5, 2, 1, 32, 48, "relu"), (64, 32, 7, 1, 1, 20, 28, "relu"), (128, 64, 5, 1, 1, 24, 24, "relu")])
 def test_conv_tensor_core_path_vs_oracle(dev, cfg):
     from maskedincrementeval_b200 import fields as fl
     from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
@@ -390,6 +392,37 @@ def test_conv_tensor_core_path_vs_oracle(dev, cfg):
             assert int((pm & ~reach).sum()) == 0
             if frac == 0.0:
                 assert int(pm.sum()) == 0
+
+
+def test_tensor_core_channel_count_off_four(dev):
+    """130 input channels (2·C + 2, the flow decoders) in a buffer whose pixel stride is rounded up to 132 floats:
+    the halo kernel takes the layer, reads the two zero padding channels and skips the K-slices that hold only padding."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    fl.config.tensor_cores = "auto"
+    cin, cout, k, n, h, w = 130, 32, 3, 1, 24, 40
+    g = torch.Generator().manual_seed(5)
+    layer = ConvLayerIncr(cin, cout, k, 1, 1, activation="relu").to(dev).eval()
+    wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()
+    x0 = torch.randn(n, cin, h, w, generator=g)
+    full = torch.zeros(n, 132, h, w, device=dev).contiguous(memory_format=torch.channels_last)
+    view = full[:, :cin]
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        res = R.conv_dense(x0, wt, b, 1, 1)
+        for frac in (0.2, 1.0, 0.03):
+            dx = sparse_delta(g, (n, cin, h, w), frac)
+            view.copy_(dx.to(dev))
+            dy, m = layer([view, None])
+            assert layer.conv2d.last_used_tensor_cores
+            want_tc, _ = R.act_incr(res, R.conv_delta_tf32(dx, wt, 1, 1), "relu")
+            want, _ = R.act_incr(res, R.conv_delta(dx, wt, 1, 1), "relu")
+            scale = max(float(want.abs().max()), 1.0)
+            assert float((dy.cpu() - want_tc).abs().max()) <= 2e-5 * scale
+            assert float((dy.cpu() - want).abs().max()) <= 2e-3 * scale
+            res = layer.activation.in_res.reservoir.cpu().contiguous()
+            pm = m.pixel_mask().cpu()
+            assert torch.equal(pm, (dy.cpu() != 0).any(1, keepdim=True).to(torch.uint8))
 
 
 def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
