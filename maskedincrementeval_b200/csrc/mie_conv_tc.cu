@@ -49,7 +49,7 @@ struct TcParams {
 
 namespace {
 
-constexpr int TC_MAX_THREADS = 352;   // producer + 2 issuers + 8 epilogue warps
+constexpr int TC_THREADS = 192;
 constexpr int A_STAGE_BYTES = 128 * 128;  // 128 pixels x 32 channels x 4 B
 constexpr unsigned SPIN_LIMIT = 1u << 20;
 
@@ -540,7 +540,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   }
 }
 
-__global__ void __launch_bounds__(TC_MAX_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment of every stage is what the 128-byte swizzle of TMA and of the MMA descriptors assume
@@ -562,17 +562,11 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int ntiles_total = p.n * THo * TWo;
   unsigned acc_cols = 32;            // columns of one accumulator (power of two >= NB)
   while ((int)acc_cols < NB) acc_cols <<= 1;
-  // Roles by warp: 0 = producer, 1..NI = MMA issuers (warp 1 owns the tensor memory), then 4 or 8 epilogue warps.
-  // Two issuers take alternate stages into separate accumulators (summed by the epilogue); a second set of epilogue
-  // warps takes half of the block's channels.  The host picks both per layer.
-  const unsigned NI = (unsigned)p.issuers;
-  const int ew0 = 1 + (int)NI;                               // first epilogue warp
-  const int n_epi = ((int)(blockDim.x >> 5) - ew0) >> 2;     // epilogue warp sets: 1 or 2
-  const unsigned tmem_cols = 2 * NI * acc_cols;  // two item buffers: the epilogue of one item overlaps the MMAs of the next
+  const unsigned tmem_cols = 2 * acc_cols;  // two accumulators: the epilogue of one item overlaps the MMAs of the next
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], NI); mbar_init(&acc_empty[b], 4 * n_epi); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -587,7 +581,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
 
-  tc_zero_stale(p, ntiles_total, THo, TWo, (int)blockDim.x);
+  tc_zero_stale(p, ntiles_total, THo, TWo, TC_THREADS);
 
   const int n_pairs = (n_active + 1) >> 1;
   const int n_cblk = p.cout_pad / NB;
@@ -638,51 +632,46 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         if (!ok) break;
       }
     }
-  } else if (warp <= (int)NI) {
-    // =========================== MMA issuers (warps 1..NI) ===========================
-    // Lean loop: descriptors are pre-built, a stage only adds its address.  Issuer `me` takes the stages whose
-    // running number is congruent to it modulo NI.
-    const unsigned me = (unsigned)warp - 1u;
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    // Same care as the producer: a lean loop issues an MMA every ~70 cycles, one that rebuilds descriptors and
+    // divides by the stage count needs ~250.  Descriptors are pre-built; a stage only adds its address.
     if (lane == 0) {
       const unsigned idesc = make_idesc_tf32(NB);
       const unsigned smem_base = smem_u32(smem);
       const unsigned long long desc_hi = make_smem_desc(0) & 0xFFFFFFFF00000000ull;   // stride, version, swizzle
       const unsigned desc_lo_flags = (unsigned)(make_smem_desc(0) & 0xFFFF0000ull);     // leading-offset field
-      const unsigned nst = (unsigned)p.stages;
-      const unsigned k_iters = (unsigned)(n_chunks * taps);
-      unsigned g = 0, item_idx = 0;      // g: running stage number over all items of this block
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x, ++item_idx, g += k_iters) {
-        // the epilogue must have drained this item buffer (used two items ago)
+      unsigned s = 0, parity = 0, stage_addr = smem_base, item_idx = 0;
+      const int k_iters = n_chunks * taps;
+      for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
+        // the epilogue must have drained this accumulator (used two items ago)
         const unsigned buf = item_idx & 1u;
         if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort)) break;
         tc_fence_after();
-        const unsigned tmem_d = tmem_base + (buf * NI + me) * acc_cols;
+        const unsigned tmem_d = tmem_base + buf * acc_cols;
+        bool ok = true;
         unsigned accumulate = 0;
-        for (unsigned ki = (NI == 2u) ? ((me - g) & 1u) : 0u; ki < k_iters; ki += NI) {
-          const unsigned gs = g + ki, lap = gs / nst, slot = gs - lap * nst;
-          if (!mbar_wait(&full_bar[slot], lap & 1u, &s_abort)) { ok = false; break; }
+        for (int ki = 0; ki < k_iters; ++ki) {
+          if (!mbar_wait(&full_bar[s], parity, &s_abort)) { ok = false; break; }
           tc_fence_after();
-          const unsigned stage_addr = smem_base + slot * (unsigned)stage_bytes;
           const unsigned a_lo = desc_lo_flags | ((stage_addr & 0x3FFFFu) >> 4);
           const unsigned b_lo = desc_lo_flags | (((stage_addr + A_STAGE_BYTES) & 0x3FFFFu) >> 4);
           // 4 x (K = 8 tf32 = 32 bytes = 2 descriptor units) inside the 128-byte swizzled row
           umma_tf32_x4(tmem_d, desc_hi | a_lo, desc_hi | b_lo, idesc, accumulate);
           accumulate = 1u;
-          umma_commit(&empty_bar[slot]);  // arrives once the MMAs above have finished reading the stage
+          umma_commit(&empty_bar[s]);  // arrives once the MMAs above have finished reading the stage
+          stage_addr += (unsigned)stage_bytes;
+          if (++s == (unsigned)p.stages) { s = 0; stage_addr = smem_base; parity ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);
       }
     }
   } else {
-    // =========================== epilogue ===========================
+    // =========================== epilogue (warps 2..5) ===========================
+    // (a second set of four epilogue warps, as in the halo kernel, measured slower here: this kernel's small
+    // layers gain more from a third resident block per SM than from a shorter epilogue)
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
-    const int half = (warp - ew0) >> 2;
-    // thresholded layers: one thread must see every channel of a pixel, so the first set takes them all
-    const bool whole = n_epi == 1 || p.thr > 0.0f || p.emitted != nullptr || NB < 32;
-    const int c_lo = whole ? (half ? NB : 0) : half * (NB >> 1);
-    const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
     unsigned item_idx = 0;
@@ -698,8 +687,8 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
       tc_fence_after();
-      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
-                                          cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u, c_lo, c_hi);
+      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
+                                          cb * NB, &acc_empty[buf], lane);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
       if (lane == 0 && t >= 0 && sent_bits) {
         unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
@@ -873,21 +862,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   if (stages < 2) return MIE_EUNSUPPORTED;
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
-  // Two MMA issuers (alternate stages, own accumulators) for blocks of <= 128 channels with long reductions: the
-  // issuing thread's wait / fence / commit per stage is what such a work item waits for.  Short reductions keep one
-  // issuer and the smaller block, of which a third fits an SM.
-  p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32) * a->k * a->k >= 32) ? 2 : 1;
-  { const char *e = getenv("MIE_TC_ISSUERS"); if (e && e[0] == '1') p.issuers = 1; }
-  int threads = 32 * (1 + p.issuers) + 128;
   int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
-  { const int by_tmem = 512 / (2 * p.issuers * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
-  { const int by_regs = 65536 / (threads * 112); if (blocks_per_sm > by_regs) blocks_per_sm = by_regs; }
+  { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
+  if (blocks_per_sm > 3) blocks_per_sm = 3;   // registers: 192 threads x ~100
   if (blocks_per_sm < 1) blocks_per_sm = 1;
-  // a second set of epilogue warps (half the channels each) where only one block runs per SM anyway
-  if (blocks_per_sm == 1 || max_items <= MIE_SM_COUNT) {
-    const char *e = getenv("MIE_TC_EPI");
-    if (!(e && e[0] == '1')) threads += 128;
-  }
 
   TcMaps maps;
   memset(&maps, 0, sizeof(maps));
@@ -922,7 +900,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     smem_set = (int)smem;
   }
-  conv_tc_kernel<<<grid, threads, smem, st>>>(p, maps);
+  conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
   return check_launch();
 }
 

@@ -60,6 +60,7 @@ class IncrementalRunner:
         self._x_prev = self._x_in = self._dx = None
         self._y: List[torch.Tensor] = []
         self._graph = None
+        self._pipe = None
         self._eager_steps = 0
         self._frame = 0
         self.graph_replays = 0
@@ -85,6 +86,7 @@ class IncrementalRunner:
             self._dx_bits = fl.new_bits(n, h, w, x.device)
             self._y = [y.detach().clone().contiguous(memory_format=torch.channels_last) for y in ys]
             self._graph = None
+            self._pipe = None
             self._eager_steps = 0
         else:
             self._x_prev.copy_(x)
@@ -130,6 +132,58 @@ class IncrementalRunner:
                 self._eager_steps += 1
         self._frame += 1
         return self._y[0] if len(self._y) == 1 else self._y
+
+    # -- pipelined host interface -----------------------------------------------------------------
+    def step_host(self, x_host: torch.Tensor, out_host: Optional[torch.Tensor] = None, timing: bool = False):
+        """``step()`` for a frame in pinned host memory, without a host wait.
+
+        The upload runs on a copy stream into one of two device staging buffers, the download of the (first)
+        accumulated output into ``out_host`` (pinned) on another stream from one of two staging copies.  A host loop
+        that calls this back to back runs ahead of the device, so the upload of frame t+1 and the download of result
+        t-1 overlap the kernels of frame t.  Returns the event that marks ``out_host`` valid (or the end of the step
+        when ``out_host`` is None); everything is ordered for the caller's current stream afterwards as with step().
+        """
+        if self._x_prev is None:
+            raise RuntimeError("call refresh() on the first frame")
+        if not x_host.is_pinned() or (out_host is not None and not out_host.is_pinned()):
+            raise RuntimeError("step_host needs pinned host tensors (torch.Tensor.pin_memory)")
+        dev = self._x_prev.device
+        cs = torch.cuda.current_stream(dev)
+        if self._pipe is None:
+            y0 = self._y[0]
+            self._pipe = dict(
+                s_in=torch.cuda.Stream(dev), s_out=torch.cuda.Stream(dev), n=0,
+                stage_in=[torch.empty_like(self._x_in) for _ in range(2)],
+                stage_out=[torch.empty_like(y0) for _ in range(2)],
+                in_ready=[torch.cuda.Event() for _ in range(2)], in_free=[None, None], out_done=[None, None])
+        P = self._pipe
+        b = P["n"] & 1
+        P["n"] += 1
+        with torch.cuda.stream(P["s_in"]):
+            if P["in_free"][b] is not None:
+                P["s_in"].wait_event(P["in_free"][b])      # the step that last read this staging buffer has consumed it
+            P["stage_in"][b].copy_(x_host, non_blocking=True)
+            P["in_ready"][b].record(P["s_in"])
+        cs.wait_event(P["in_ready"][b])
+        y = self.step(P["stage_in"][b])
+        free = torch.cuda.Event()
+        free.record(cs)
+        P["in_free"][b] = free
+        if out_host is None:
+            return free
+        y0 = y[0] if isinstance(y, (list, tuple)) else y
+        if P["out_done"][b] is not None:
+            cs.wait_event(P["out_done"][b])                # the previous download from this staging copy has finished
+        P["stage_out"][b].copy_(y0, non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record(cs)
+        done = torch.cuda.Event(enable_timing=timing)
+        with torch.cuda.stream(P["s_out"]):
+            P["s_out"].wait_event(ready)
+            out_host.copy_(P["stage_out"][b], non_blocking=True)
+            done.record(P["s_out"])
+        P["out_done"][b] = done
+        return done
 
     @property
     def output(self):

@@ -110,7 +110,8 @@ def _e2depth(dev, compat="exact"):
     return net
 
 
-@pytest.mark.parametrize("hw,streams,events,segs", [((260, 346), 1, 30000, 10), ((480, 640), 2, 80000, 15)])
+@pytest.mark.parametrize("hw,streams,events,segs", [((260, 346), 1, 30000, 10), ((480, 640), 2, 80000, 15),
+                                                     ((260, 346), 8, 30000, 10)])   # 8 streams: several work items per block
 def test_config3_config4_e2depth_tracks_dense(dev, hw, streams, events, segs):
     """E2Depth at 260x346 (padded to 264x352) and 480x640, synthetic event voxel grids, graph-replayed steps."""
     from maskedincrementeval_b200.runtime import IncrementalRunner

@@ -220,3 +220,28 @@ def test_driver_protocol_with_graph_replay(dev):
         yd, _ = eager.forward_refresh_reservoirs(cl(x, dev), None)
         close(y, yd, TOL())
     assert run.graph_replays >= 3
+
+
+def test_runner_step_host_matches_step(dev):
+    """The pipelined host interface (uploads and downloads on side streams, no host wait) produces the outputs of
+    the plain step() loop, and every step's prediction arrives in its pinned buffer."""
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import voxel_sequence
+    frames = voxel_sequence(1, 64, 96, 7, 4000, 6, seed=3)
+    net_a, net_b = _e2depth(dev, 8, 5, "exact")[0], _e2depth(dev, 8, 5, "exact")[0]
+    ra, rb = IncrementalRunner(net_a, use_graph=True), IncrementalRunner(net_b, use_graph=True)
+    pinned = [f.pin_memory() for f in frames]
+    outs = [torch.empty(1, 1, 64, 96).pin_memory() for _ in frames]
+    with torch.no_grad():
+        ra.refresh(frames[0].to(dev))
+        rb.refresh(frames[0].to(dev))
+        want = []
+        for f in frames[1:]:
+            want.append(ra.step(f.to(dev)).clone())
+        for i, f in enumerate(pinned[1:], 1):
+            rb.step_host(f, outs[i])
+        torch.cuda.synchronize()
+    for i, w in enumerate(want, 1):
+        assert torch.equal(outs[i], w.cpu())
+    with pytest.raises(RuntimeError):
+        rb.step_host(frames[1])   # not pinned
