@@ -248,6 +248,17 @@ int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, f
 int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sensor_h, int sensor_w,
                         float *voxel, int64_t v_ps, int H, int W, int pad_left, int pad_top, void *stream);
 
+/* Split-precision copy of a narrow delta field (C <= a few channels) for the tensor-core convolution, which
+ * truncates its inputs to TF32: with half = C rounded up to 8,
+ *   out[c] = d[c],  out[half + c] = d[c] - tf32_trunc(d[c]),  out[2*half + c] = d[c];
+ * the other channels of `out` (pixel stride out_ps >= 3*half, zero-initialised by the caller) are not written.
+ * Convolving `out` with the filter blocks [W, W, W - tf32(W)] at channel offsets 0, half, 2*half gives the fp32
+ * convolution of d with W (the dropped term is ~2^-21 relative).  out_bits (one word per tile, zero before the
+ * first call) remembers which tiles of `out` hold data so that they are zeroed again when their input tile goes
+ * inactive.  No counterpart in the reference. */
+int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int C, float *out, int64_t out_ps,
+                   uint64_t *out_bits, int N, int H, int W, void *stream);
+
 /* Sigma-delta quantiser with carry: T = carry + dx; q = k * floor(0.5 + T / k); carry = T - q; bits = q != 0.
  * KFencedMaskModule.forward, incr_modules/mask_incr_modules.py:31-41. */
 int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,

@@ -803,8 +803,8 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   // ---- halo-resident kernel: stride 1, k in {3,5,7} ----
   // Two shapes stay on the per-tap kernel: blocks of 256 channels with more work items than SMs (bound by the
   // tensor core itself, not by instruction issue: per-tap measured 15 % faster), and layers of a single channel
-  // chunk (the halo is used for k*k taps only once: per-tap measured 8 % faster on 32 -> 32 channels, 3x3).
-  if (a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) && p.cin_pad > 32 && halo_enabled()) {
+  // chunk with a 3x3 filter (the halo is used for 9 taps only once: per-tap measured 8 % faster on 32 -> 32 channels).
+  if (a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) && (p.cin_pad > 32 || a->k >= 5) && halo_enabled()) {
     const int Wh = 8 + a->k - 1;
     const int a_bytes = 2 * (Wh * 2 * 8 * Wh * 16);          // two buffers of [Hh][2 tiles][8 groups][Wh][16 B]
     // A stage holds `tps` consecutive taps of one channel chunk (one TMA): the issuing thread pays its wait /

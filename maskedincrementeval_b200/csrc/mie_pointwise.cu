@@ -797,6 +797,42 @@ extern "C" int mie_activation_increment(float *X, const float *in_incr, float *o
   }
 }
 
+// Split-precision copy of a narrow delta field for the tensor cores:
+//   out[c] = d, out[half + c] = d - tf32_trunc(d), out[2*half + c] = d.
+// The MMA truncates all three to TF32.  Against the filter blocks [W_hi, W_hi, W_lo] (W_hi = tf32(W), W_lo =
+// tf32(W - W_hi)) the convolution over the 3*half channels is d_hi*W_hi + d_lo*W_hi + d_hi*W_lo: the fp32
+// convolution of d with W up to the dropped d_lo*W_lo term (~2^-21 relative).
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict__ in, int64_t in_ps,
+                                                         const uint64_t *__restrict__ in_bits, int C, int half,
+                                                         float *__restrict__ out, int64_t out_ps,
+                                                         uint64_t *__restrict__ out_bits, int N, int H, int W) {
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t w = in_bits[t];
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (out_bits[t] != 0ull) {   // held data last step: back to zero
+        __syncthreads();
+        zero_tile(out, out_ps, 3 * half, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      const float v = ((w >> p) & 1ull) ? in[pix * in_ps + c] : 0.0f;
+      const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+      out[pix * out_ps + c] = v;
+      out[pix * out_ps + half + c] = v - hi;
+      out[pix * out_ps + 2 * half + c] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
 #define MIE_CHECK_FIELD(ptr, ps, C) if (!(ptr) || (ps) < (C)) return MIE_EINVAL
 
 extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
@@ -949,5 +985,16 @@ extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
   kfenced_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dx, dx_ps, carry, c_ps, k, q, q_ps,
                                                            reinterpret_cast<unsigned *>(bits), N, C, H, W);
+  return check_launch();
+}
+
+extern "C" int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int C, float *out, int64_t out_ps,
+                              uint64_t *out_bits, int N, int H, int W, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits) return MIE_EINVAL;
+  const int half = divup(C, 8) * 8;
+  MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(out, out_ps, 3 * half);
+  const int ntiles = N * divup(H, 8) * divup(W, 8);
+  split_tf32_kernel<<<tile_grid(ntiles), 256, 0, (cudaStream_t)stream>>>(in, in_ps, in_bits, C, half, out, out_ps, out_bits,
+                                                                        N, H, W);
   return check_launch();
 }

@@ -295,6 +295,15 @@ def events_to_voxel(events: torch.Tensor, num_bins: int, sensor_hw, out: torch.T
     return out
 
 
+def split_tf32(d: torch.Tensor, m: TileMask, out: torch.Tensor, out_bits: torch.Tensor) -> TileMask:
+    """out[:, :C] = d, out[:, half:half+C] = d - tf32_trunc(d), out[:, 2*half:2*half+C] = d (half = C rounded up to 8)
+    on the active tiles."""
+    n, c, h, w = d.shape
+    nat.check(nat.lib.mie_split_tf32(d.data_ptr(), pixel_stride(d), m.bits.data_ptr(), c, out.data_ptr(), pixel_stride(out),
+                                     out_bits.data_ptr(), n, h, w, nat.stream_ptr(d.device)), "split_tf32")
+    return TileMask(out_bits, n, h, w)
+
+
 def kfenced(dx: torch.Tensor, carry: torch.Tensor, k: float, q: torch.Tensor, bits: torch.Tensor) -> TileMask:
     n, c, h, w = dx.shape
     nat.check(nat.lib.mie_kfenced(dx.data_ptr(), pixel_stride(dx), carry.data_ptr(), pixel_stride(carry), float(k),

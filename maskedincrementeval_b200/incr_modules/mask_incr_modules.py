@@ -283,19 +283,41 @@ class nnConvIncr(nn.Conv2d):
         self._cw = None
         return r
 
-    def _weights(self, cin_limit: Optional[int] = None):
+    def _split_input(self, cin: int) -> bool:
+        """Narrow-input layers (the 5-bin voxel head) run on the tensor cores with a split-precision input: the raw
+        O(1) input delta must not be truncated to TF32 (it random-walks in the first reservoir) and neither may the
+        filter be rounded (the input changes by its full scale between frames); with [d, d - tf32(d), d] against
+        [W, W, W - tf32(W)] as 24 channels neither is."""
+        return (config.tensor_cores == "auto" and self._s == 1 and self._k in (3, 5, 7) and cin <= 8
+                and cin * self._k * self._k >= 100 and self.out_channels % 4 == 0)
+
+    def _weights(self, cin_limit: Optional[int] = None, split: bool = False):
         """Packed filter for the kernels, repacked whenever the parameter changed or moved."""
         key = cin_limit or self.in_channels
         ver = (self.weight._version, self.weight.device, self.weight.data_ptr())
+        if split:
+            key = ("split", key)
         hit = self._packed.get(key)
         if hit is None or hit[0] != ver:
             w = self.weight.detach()
-            if key != self.in_channels:
+            if not split and key != self.in_channels:
                 w = w[:, :key].contiguous()
+            if split:
+                c = key[1]
+                wf = w[:, :c].float()
+                w_hi = (wf.view(torch.int32) + 0x1000 & ~0x1FFF).view(torch.float32)   # TF32 rounding, as the packing does
+                w24 = torch.zeros((w.shape[0], 24, self._k, self._k), dtype=torch.float32, device=w.device)
+                w24[:, :c] = wf
+                w24[:, 8:8 + c] = wf
+                w24[:, 16:16 + c] = wf - w_hi
+                w = w24
+                key_depth = 24
+            else:
+                key_depth = key
             buf, cp, op = fl.pack_conv_weights(w.float())
             tc = None
             # the library decides per call whether the tensor-core copy is used; it never is below this depth
-            if key * self._k * self._k >= 256 and self.out_channels % 4 == 0:
+            if key_depth * self._k * self._k >= 256 and self.out_channels % 4 == 0:
                 tc = fl.pack_conv_weights_tc(w.float())
             hit = (ver, buf, cp, op, tc)
             self._packed[key] = hit
@@ -320,7 +342,13 @@ class nnConvIncr(nn.Conv2d):
         if cin != cin_eff:
             raise RuntimeError(f"expected {cin_eff} input channels, got {cin}")
         plan = self._plan(n, hin, win, d.device)
-        wbuf, cp, op, wtc = self._weights(cin_limit)
+        split = self._split_input(cin)
+        wbuf, cp, op, wtc = self._weights(cin_limit, split)
+        if split:
+            d24 = sc.get("split", (n, 24, hin, win), torch.float32, d.device, channels_last=True)
+            sb = sc.get("split.bits", (fl.n_tiles(n, hin, win),), torch.int64, d.device)
+            fl.split_tf32(d, m, d24, sb)
+            d, cin = d24, 24
         a = plan.args
         union = None
         if addend is not None:

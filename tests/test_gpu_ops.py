@@ -425,6 +425,34 @@ def test_tensor_core_channel_count_off_four(dev):
             assert torch.equal(pm, (dy.cpu() != 0).any(1, keepdim=True).to(torch.uint8))
 
 
+def test_tensor_core_split_precision_narrow_input(dev):
+    """The 5-channel 5x5 head runs on the tensor cores with input and filter split into TF32 hi/lo parts
+    ([d, d - tf32(d), d] against [W, W, W - tf32(W)]): the result is the fp32 convolution, not the TF32 one."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    fl.config.tensor_cores = "auto"
+    cin, cout, k, n, h, w = 5, 32, 5, 2, 40, 56
+    g = torch.Generator().manual_seed(9)
+    layer = ConvLayerIncr(cin, cout, k, 1, 2, activation="relu").to(dev).eval()
+    wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()
+    x0 = torch.randn(n, cin, h, w, generator=g)
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        res = R.conv_dense(x0, wt, b, 1, 2)
+        for frac in (0.1, 1.0, 0.0, 0.02):
+            dx = sparse_delta(g, (n, cin, h, w), frac) * 3.0      # O(1) deltas, as a raw input has
+            dy, m = layer([cl(dx, dev), None])
+            assert layer.conv2d.last_used_tensor_cores
+            want, _ = R.act_incr(res, R.conv_delta(dx, wt, 1, 2), "relu")
+            scale = max(float(want.abs().max()), 1.0)
+            assert float((dy.cpu() - want).abs().max()) <= 2e-5 * scale, float((dy.cpu() - want).abs().max())
+            res = layer.activation.in_res.reservoir.cpu().contiguous()
+            pm = m.pixel_mask().cpu()
+            assert float((dy.cpu() * (1 - pm.float())).abs().max()) == 0.0
+            if frac == 0.0:
+                assert int(pm.sum()) == 0
+
+
 def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
     """Same thresholded layer on both paths: values within the TF32 bar, and the carry keeps the total sent
     within the threshold of the true output on both."""
