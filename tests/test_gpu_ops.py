@@ -351,7 +351,9 @@ def test_thresholded_fused_conv_matches_standalone(dev):
     (40, 48, 3, 1, 1, 20, 28, "tanh"), (16, 32, 5, 1, 1, 19, 21, "sigmoid"), (32, 32, 3, 2, 1, 32, 48, "relu"),
     (512, 16, 1, 1, 1, 9, 11, None),
     # long stride-2 reduction in the per-tap kernel, 7x7 halo, 3-slot filter ring (5x5, 64-channel blocks)
-    (64, 64, 5, 2, 1, 32, 48, "relu"), (64, 32, 7, 1, 1, 20, 28, "relu"), (128, 64, 5, 1, 1, 24, 24, "relu")])
+    (64, 64, 5, 2, 1, 32, 48, "relu"), (64, 32, 7, 1, 1, 20, 28, "relu"), (128, 64, 5, 1, 1, 24, 24, "relu"),
+    # large fields: several work items per block
+    (64, 32, 5, 1, 2, 200, 228, "relu"), (64, 64, 3, 1, 1, 230, 250, "tanh")])
 def test_conv_tensor_core_path_vs_oracle(dev, cfg):
     from maskedincrementeval_b200 import fields as fl
     from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
