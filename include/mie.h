@@ -259,6 +259,12 @@ int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sen
 int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int C, float *out, int64_t out_ps,
                    uint64_t *out_bits, int N, int H, int W, void *stream);
 
+/* Fills the border of a [1,C,H,W] channels-last field by reflection of the sensor_h x sensor_w image that sits at
+ * (pad_top, pad_left) inside it -- the index arithmetic of torch.nn.ReflectionPad2d, which the reference's driver
+ * applies to the voxel grid before the network (run_e2depth_continuous_dataset.py:49). */
+int mie_reflect_border(float *field, int64_t ps, int C, int H, int W, int sensor_h, int sensor_w, int pad_left,
+                       int pad_top, void *stream);
+
 /* Sigma-delta quantiser with carry: T = carry + dx; q = k * floor(0.5 + T / k); carry = T - q; bits = q != 0.
  * KFencedMaskModule.forward, incr_modules/mask_incr_modules.py:31-41. */
 int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,

@@ -976,6 +976,36 @@ extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bi
   return check_launch();
 }
 
+// Border of a [1,C,H,W] field filled by reflection of its interior (sensor image of sh x sw placed at (pt, pl)),
+// index arithmetic of torch.nn.ReflectionPad2d: the edge pixel is not repeated.
+__global__ void __launch_bounds__(256) reflect_border_kernel(float *__restrict__ f, int64_t ps, int C, int H, int W, int sh,
+                                                             int sw, int pl, int pt) {
+  const int64_t total = (int64_t)H * W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int y = (int)(i / W), x = (int)(i - (int64_t)y * W);
+    int sy = y - pt, sx = x - pl;
+    if (sy >= 0 && sy < sh && sx >= 0 && sx < sw) continue;   // interior
+    if (sy < 0) sy = -sy; else if (sy >= sh) sy = 2 * (sh - 1) - sy;
+    if (sx < 0) sx = -sx; else if (sx >= sw) sx = 2 * (sw - 1) - sx;
+    const float *src = f + ((int64_t)(sy + pt) * W + (sx + pl)) * ps;
+    float *dst = f + i * ps;
+    for (int c = 0; c < C; ++c) dst[c] = src[c];
+  }
+}
+
+extern "C" int mie_reflect_border(float *field, int64_t ps, int C, int H, int W, int sensor_h, int sensor_w, int pad_left,
+                                  int pad_top, void *stream) {
+  if (!field || C <= 0 || ps < C || H <= 0 || W <= 0 || sensor_h <= 0 || sensor_w <= 0) return MIE_EINVAL;
+  if (pad_left < 0 || pad_top < 0 || sensor_h + pad_top > H || sensor_w + pad_left > W) return MIE_EINVAL;
+  // a reflected index must land inside the sensor image
+  if (pad_left >= sensor_w || W - sensor_w - pad_left >= sensor_w || pad_top >= sensor_h || H - sensor_h - pad_top >= sensor_h)
+    return MIE_EINVAL;
+  int blocks = divup(H * W, 256);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  reflect_border_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(field, ps, C, H, W, sensor_h, sensor_w, pad_left, pad_top);
+  return check_launch();
+}
+
 extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,
                            uint64_t *bits, int N, int C, int H, int W, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(k > 0.0f)) return MIE_EINVAL;

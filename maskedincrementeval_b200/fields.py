@@ -295,6 +295,15 @@ def events_to_voxel(events: torch.Tensor, num_bins: int, sensor_hw, out: torch.T
     return out
 
 
+def reflect_border(field: torch.Tensor, sensor_hw, pad_left: int, pad_top: int):
+    """Reflection-fill the border of a [1,C,H,W] field around the sensor image placed at (pad_top, pad_left)."""
+    n, c, h, w = field.shape
+    if n != 1:
+        raise RuntimeError("reflect_border takes one stream at a time")
+    nat.check(nat.lib.mie_reflect_border(field.data_ptr(), pixel_stride(field), c, h, w, sensor_hw[0], sensor_hw[1], pad_left,
+                                         pad_top, nat.stream_ptr(field.device)), "reflect_border")
+
+
 def split_tf32(d: torch.Tensor, m: TileMask, out: torch.Tensor, out_bits: torch.Tensor) -> TileMask:
     """out[:, :C] = d, out[:, half:half+C] = d - tf32_trunc(d), out[:, 2*half:2*half+C] = d (half = C rounded up to 8)
     on the active tiles."""

@@ -245,3 +245,36 @@ def test_runner_step_host_matches_step(dev):
         assert torch.equal(outs[i], w.cpu())
     with pytest.raises(RuntimeError):
         rb.step_host(frames[1])   # not pinned
+
+
+def test_runner_step_events_matches_host_binning(dev):
+    """Feeding raw events (binned and reflection-padded on the device) gives the steps that host-binned voxel
+    grids give; only the summation order of the binning differs."""
+    import numpy as np
+    import torch.nn.functional as F
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import EdgeEventStream, events_to_voxel_grid, reflection_pad_hw
+    sh, sw, n_streams = 60, 90, 2
+    l, r, t, b = reflection_pad_hw(sh, sw, 8)
+    streams = [EdgeEventStream(sh, sw, 3000, 6, 40 + s) for s in range(n_streams)]
+    net_a, net_b = _e2depth(dev, 8, 5, "exact")[0], _e2depth(dev, 8, 5, "exact")[0]
+    ra, rb = IncrementalRunner(net_a, use_graph=True), IncrementalRunner(net_b, use_graph=True)
+
+    def grid_of(evs):
+        g = torch.from_numpy(np.stack([events_to_voxel_grid(e.copy(), 5, sh, sw) for e in evs], 0))
+        return F.pad(g, (l, r, t, b), mode="reflect").contiguous(memory_format=torch.channels_last)
+
+    with torch.no_grad():
+        first = [s.window() for s in streams]
+        ra.refresh(grid_of(first).to(dev))
+        rb.refresh(grid_of(first).to(dev))
+        for _ in range(5):
+            evs = [s.window() for s in streams]
+            ya = ra.step(grid_of(evs).to(dev))
+            yb = rb.step_events([torch.from_numpy(e.astype("float32")).to(dev) for e in evs], (sh, sw))
+            rng = float(ya.max() - ya.min())
+            # FP32 path: only the order of the atomic adds differs; tensor-core path: those last-bit differences of
+            # the input pass through the TF32 truncation of the layers
+            bar = 1e-5 if TOL() <= 1e-4 else TOL()
+            assert float((ya - yb).abs().max()) <= bar * max(rng, 1e-6)
+    assert rb.graph_replays >= 3
