@@ -213,6 +213,13 @@ int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const f
                    const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C,
                    int H, int W, int mode, void *stream);
 
+/* The same for a scale of 1 (a masked copy), 2, 4, 8 or 16: out[N,C,scale*H,scale*W].  F.interpolate(delta, size=highest_resolution,
+ * mode="bilinear", align_corners=False) on the multi-resolution predictions and decoder outputs,
+ * incr_modules/delayedevflownet_incr.py:260-268. */
+int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+                 const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C,
+                 int H, int W, int scale, int mode, void *stream);
+
 /* out = a + b, out mask = mask_a | mask_b.  Skip / residual sum of two delta fields. */
 int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
             const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,

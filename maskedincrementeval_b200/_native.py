@@ -62,6 +62,7 @@ SIGNATURES = {
     "mie_convlstm_point": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp,
                                 _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp]),
     "mie_upsample2x": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mie_upsample": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mie_add": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
     "mie_cat2": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp]),
     "mie_accumulate": (_i, [_vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),

@@ -237,10 +237,11 @@ __device__ __forceinline__ bool bit_at(const uint64_t *bits, int n, int y, int x
   return (bits[((int64_t)n * TH + (y >> 3)) * TW + (x >> 3)] >> ((y & 7) * 8 + (x & 7))) & 1ull;
 }
 
-// source rows/cols and weights of output coordinate o for a x2 upsample of extent L
-__device__ __forceinline__ void up_src(int o, int L, int mode, int &i0, int &i1, float &w1) {
-  if (mode == MIE_UP_NEAREST) { i0 = i1 = o >> 1; w1 = 0.0f; return; }
-  float s = 0.5f * (o + 0.5f) - 0.5f;
+// source rows/cols and weights of output coordinate o for a x`scale` upsample of extent L (rs = 1 / scale):
+// the index arithmetic of torch's bilinear interpolation with align_corners=False
+__device__ __forceinline__ void up_src(int o, int L, int mode, int scale, float rs, int &i0, int &i1, float &w1) {
+  if (mode == MIE_UP_NEAREST) { i0 = i1 = o / scale; w1 = 0.0f; return; }
+  float s = rs * (o + 0.5f) - 0.5f;
   if (s < 0.0f) s = 0.0f;
   i0 = (int)s;
   i1 = min(i0 + 1, L - 1);
@@ -251,8 +252,9 @@ __device__ __forceinline__ void up_src(int o, int L, int mode, int &i0, int &i1,
 __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps,
-    uint64_t *__restrict__ out_bits, int N, int C, int H, int W, int mode) {
-  const int Ho = 2 * H, Wo = 2 * W;
+    uint64_t *__restrict__ out_bits, int N, int C, int H, int W, int mode, int scale) {
+  const int Ho = scale * H, Wo = scale * W;
+  const float rs = 1.0f / (float)scale;
   const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
   const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
   __shared__ unsigned s_w[2];
@@ -268,8 +270,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
       unsigned fa = 0, fb = 0;
       if (pix_valid(g, p)) {
         int y0, y1, x0, x1; float wy, wx;
-        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
-        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        up_src(g.ty * 8 + (p >> 3), H, mode, scale, rs, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, scale, rs, x0, x1, wx);
         fa = (bit_at(a_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(a_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
              (bit_at(a_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(a_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
         if (b)
@@ -299,8 +301,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
       const unsigned fa = s_fa[p], fb = s_fb[p];
       if (fa | fb) {
         int y0, y1, x0, x1; float wy, wx;
-        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
-        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        up_src(g.ty * 8 + (p >> 3), H, mode, scale, rs, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, scale, rs, x0, x1, wx);
         const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
         float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
         if (fa & 1u) v00 += a[(r0 + x0) * a_ps + c];
@@ -422,8 +424,9 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
 __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
-    int C, int H, int W, int mode) {
-  const int Ho = 2 * H, Wo = 2 * W;
+    int C, int H, int W, int mode, int scale) {
+  const int Ho = scale * H, Wo = scale * W;
+  const float rs = 1.0f / (float)scale;
   const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
   const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
   const int ncb = (C + CB - 1) / CB;
@@ -439,8 +442,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
       unsigned fa = 0, fb = 0;
       if (pix_valid(g, p)) {
         int y0, y1, x0, x1; float wy, wx;
-        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
-        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        up_src(g.ty * 8 + (p >> 3), H, mode, scale, rs, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, scale, rs, x0, x1, wx);
         fa = (bit_at(a_bits, g.n, y0, x0, THi, TWi) ? 1u : 0u) | (bit_at(a_bits, g.n, y0, x1, THi, TWi) ? 2u : 0u) |
              (bit_at(a_bits, g.n, y1, x0, THi, TWi) ? 4u : 0u) | (bit_at(a_bits, g.n, y1, x1, THi, TWi) ? 8u : 0u);
         if (b)
@@ -471,8 +474,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
       const unsigned fa = s_fa[p], fb = s_fb[p];
       if (fa | fb) {
         int y0, y1, x0, x1; float wy, wx;
-        up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
-        up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+        up_src(g.ty * 8 + (p >> 3), H, mode, scale, rs, y0, y1, wy);
+        up_src(g.tx * 8 + (p & 7), W, mode, scale, rs, x0, x1, wx);
         const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
         float4 v00 = v, v01 = v, v10 = v, v11 = v;
         if (fa & 1u) v00 = ld4(a + (r0 + x0) * a_ps + c);
@@ -506,8 +509,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
         const unsigned fa = s_fa[p], fb = s_fb[p];
         if (fa | fb) {
           int y0, y1, x0, x1; float wy, wx;
-          up_src(g.ty * 8 + (p >> 3), H, mode, y0, y1, wy);
-          up_src(g.tx * 8 + (p & 7), W, mode, x0, x1, wx);
+          up_src(g.ty * 8 + (p >> 3), H, mode, scale, rs, y0, y1, wy);
+          up_src(g.tx * 8 + (p & 7), W, mode, scale, rs, x0, x1, wx);
           const int64_t r0 = (int64_t)(g.n * H + y0) * W, r1 = (int64_t)(g.n * H + y1) * W;
           float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
           if (fa & 1u) v00 += a[(r0 + x0) * a_ps + c];
@@ -893,22 +896,29 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
   return check_launch();
 }
 
-extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+extern "C" int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                               const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
-                              int W, int mode, void *stream) {
+                              int W, int scale, int mode, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !out_bits) return MIE_EINVAL;
   if (mode != MIE_UP_BILINEAR && mode != MIE_UP_NEAREST) return MIE_EINVAL;
+  if (scale < 1 || scale > 16 || (scale & (scale - 1))) return MIE_EUNSUPPORTED;   // powers of two: 1/scale is exact (1 copies)
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (b && (!b_bits || b_ps < C)) return MIE_EINVAL;
-  const int ntiles = N * divup(2 * H, 8) * divup(2 * W, 8);
+  const int ntiles = N * divup(scale * H, 8) * divup(scale * W, 8);
   if (C >= 4 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
     upsample2x_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
-        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode);
+        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode, scale);
     return check_launch();
   }
   upsample2x_kernel<<<item_grid((int64_t)ntiles * divup(C, 64)), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
-                                                                                out_ps, out_bits, N, C, H, W, mode);
+                                                                                out_ps, out_bits, N, C, H, W, mode, scale);
   return check_launch();
+}
+
+extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
+                              const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
+                              int W, int mode, void *stream) {
+  return mie_upsample(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, 2, mode, stream);
 }
 
 extern "C" int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,

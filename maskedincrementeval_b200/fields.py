@@ -225,6 +225,15 @@ def upsample2x(a, ma: TileMask, b, mb: Optional[TileMask], out, out_bits, mode: 
     return TileMask(out_bits, n, 2 * h, 2 * w)
 
 
+def upsample(a, ma: TileMask, out, out_bits, scale: int, mode: int = nat.UP_BILINEAR) -> TileMask:
+    """out[N,C,scale*H,scale*W] = interpolate(a) for scale in {2,4,8,16}."""
+    n, c, h, w = a.shape
+    nat.check(nat.lib.mie_upsample(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), None, 0, None, out.data_ptr(),
+                                   pixel_stride(out), out_bits.data_ptr(), n, c, h, w, scale, mode,
+                                   nat.stream_ptr(a.device)), "upsample")
+    return TileMask(out_bits, n, scale * h, scale * w)
+
+
 def add(a, ma: TileMask, b, mb: TileMask, out, out_bits) -> TileMask:
     n, c, h, w = a.shape
     nat.check(nat.lib.mie_add(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), b.data_ptr(), pixel_stride(b),

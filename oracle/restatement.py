@@ -335,6 +335,11 @@ class E2DepthOracle:
 # ------------------------------------------------------------------------------------------
 # flow networks  (incr_modules/evflownet_incr.py, fireflownet_incr.py)
 # ------------------------------------------------------------------------------------------
+def interp_to(x: Tensor, size) -> Tensor:
+    """``F.interpolate(x, size=size, mode="bilinear", align_corners=False)``; linear, so exact on deltas."""
+    return F.interpolate(x, size=tuple(size), mode="bilinear", align_corners=False)
+
+
 def skip_concat(x1: Tensor, x2: Tensor) -> Tensor:
     """``skip_concat`` (``incr_modules/evflownet_incr.py:9-14``): zero-pad x1 to x2's size, concatenate."""
     dy, dxx = x2.shape[2] - x1.shape[2], x2.shape[3] - x1.shape[3]
@@ -493,3 +498,48 @@ class EVFlowNetOracle(_FlowBase):
             x = self._act_i(self._conv_i(up2(x), f"decoders.{i}.conv2d", 1, 1), f"decoders.{i}", "relu")
             preds.append(self._layer_i(x, f"preds.{i}", 1, 0, "tanh"))
         return preds
+
+
+class DelayedEVFlowNetOracle(_FlowBase):
+    """``DelayedMultiResUNetIncr`` (``incr_modules/delayedevflownet_incr.py:155-383``): feed-forward multi-resolution
+    UNet -- stride-2 encoders, residual blocks, one decoder per level fed by the encoder output of that level (the
+    lowest one by concat(resblock output, encoder output)), tanh predictions per level; decoder outputs (all but the
+    lowest) and predictions are interpolated to the input resolution, concatenated and reduced by two 1x1 layers
+    ("delayed" prediction).  Returns the interpolated predictions followed by the delayed prediction."""
+
+    def __init__(self, sd, compat: str = "reference", num_encoders: int = 4, num_residual_blocks: int = 2,
+                 kernel_size: int = 3):
+        super().__init__(sd, compat)
+        self.ne, self.nr, self.k = num_encoders, num_residual_blocks, kernel_size
+
+    def _run(self, x, dense: bool):
+        layer = self._layer_d if dense else self._layer_i
+        conv = self._conv_d if dense else self._conv_i
+        act = self._act_d if dense else self._act_i
+        res = self._resblock_d if dense else self._resblock_i
+        size = x.shape[-2:]
+        pad = self.k // 2
+        blocks = []
+        for i in range(self.ne):
+            x = layer(x, f"encoders.{i}", 2, pad, "relu")
+            blocks.append(x)
+        for i in range(self.nr):
+            x = res(x, f"resblocks.{i}")
+        outs, preds = [], []
+        for i in range(self.ne):
+            b = blocks[self.ne - i - 1]
+            d_in = skip_concat(x, b) if i == 0 else b
+            d = act(conv(up2(d_in), f"decoders.{i}.conv2d", 1, pad), f"decoders.{i}", "relu")
+            if i != 0:
+                outs.append(interp_to(d, size))
+            preds.append(interp_to(layer(d, f"preds.{i}", 1, 0, "tanh"), size))
+        din = torch.cat(outs + preds, 1)
+        mid = layer(din, "delayed_pred_layer_list.0", 1, 0, "relu")
+        last = layer(torch.cat([mid, din[:, -2 * self.ne:]], 1), "delayed_pred_layer_list.1", 1, 0, "tanh")
+        return preds + [last]
+
+    def refresh(self, x):
+        return self._run(x, True)
+
+    def step(self, dx):
+        return self._run(dx, False)

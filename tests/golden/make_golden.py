@@ -183,6 +183,22 @@ def main(ref_root: str = DEFAULT_ROOT):
         for i, p in enumerate(net([d, None])):
             out[f"dy{s}_{i}"] = _np(p[0])
     np.savez_compressed(os.path.join(OUT, "evflownet_small.npz"), **out)
+    # ---- delayed-prediction EVFlowNet (8 base channels, 32x48) ----
+    import importlib
+    delayed = importlib.import_module("incr_modules.delayedevflownet_incr")
+    out = {}
+    net = delayed.DelayedEVFlowNetIncr(dict(base_num_channels=8, kernel_size=3, mask_output=False), 2).eval()
+    net.load_state_dict(seeded_state_dict(_shapes(net), seed=51, init="kaiming_normal"))
+    x = torch.randn(1, 2, 32, 48, generator=g).contiguous(memory_format=torch.channels_last)
+    out["seed"], out["x"] = np.array(51), _np(x)
+    for i, p in enumerate(net.forward_refresh_reservoirs(x)["flow"]):
+        out[f"y0_{i}"] = _np(p)
+    for s in (1, 2, 3):
+        d = _sparse_delta(g, x.shape, frac=0.1)
+        out[f"d{s}"] = _np(d)
+        for i, p in enumerate(net([d, None])["flow"]):
+            out[f"dy{s}_{i}"] = _np(p if torch.is_tensor(p) else p[0])
+    np.savez_compressed(os.path.join(OUT, "delayedevflownet_small.npz"), **out)
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))
 
 

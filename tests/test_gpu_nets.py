@@ -278,3 +278,40 @@ def test_runner_step_events_matches_host_binning(dev):
             bar = 1e-5 if TOL() <= 1e-4 else TOL()
             assert float((ya - yb).abs().max()) <= bar * max(rng, 1e-6)
     assert rb.graph_replays >= 3
+
+
+def test_delayedevflownet_golden_and_dense(dev, golden):
+    """The delayed-prediction EV-FlowNet: reference wiring against the golden vectors of the real reference,
+    intended wiring against a dense recompute through the graph-replaying runner."""
+    from maskedincrementeval_b200.incr_modules.delayedevflownet_incr import DelayedEVFlowNetIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from test_oracle import flow_shapes_delayed
+    g = golden("delayedevflownet_small")
+    kw = dict(base_num_channels=8, kernel_size=3, mask_output=False)
+    sd = seeded_state_dict(flow_shapes_delayed(8), int(g["seed"]), "kaiming_normal")
+    net = DelayedEVFlowNetIncr(kw, 2, compat="reference").to(dev).eval()
+    net.load_state_dict(sd)
+    with torch.no_grad():
+        for i, p in enumerate(net.forward_refresh_reservoirs(cl(T(g["x"]), dev))["flow"]):
+            close(p, T(g[f"y0_{i}"]), 1e-5)
+        for s in (1, 2, 3):
+            flows = net([cl(T(g[f"d{s}"]), dev), None])["flow"]
+            for i, p in enumerate(flows):
+                close(p[0], T(g[f"dy{s}_{i}"]), TOL(), rng=2.0)
+                pm = p[1].pixel_mask().cpu()
+                assert float((p[0].cpu() * (1 - pm.float())).abs().max()) == 0.0
+
+    inc, dense = DelayedEVFlowNetIncr(kw, 2, compat="exact").to(dev).eval(), DelayedEVFlowNetIncr(kw, 2, compat="exact").to(dev).eval()
+    inc.load_state_dict(sd), dense.load_state_dict(sd)
+    run = IncrementalRunner(inc, use_graph=True)
+    x = T(g["x"]).clone()
+    gen = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        run.refresh(cl(x, dev))
+        for _ in range(6):
+            x = x + torch.randn(x.shape, generator=gen) * (torch.rand(1, 1, *x.shape[2:], generator=gen) < 0.1)
+            ys = run.step(cl(x, dev))
+        yds = dense.forward_refresh_reservoirs(cl(x, dev))["flow"]
+    for y, yd in zip(ys, yds):
+        close(y, yd, TOL(), rng=2.0)
+    assert run.graph_replays >= 4

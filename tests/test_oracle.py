@@ -182,6 +182,57 @@ def flow_shapes_ev():
     return s
 
 
+def flow_shapes_delayed(base=8, k=3, bins=2):
+    s = {}
+
+    def conv(name, co, ci, kk):
+        s["multires_unet." + name + ".weight"] = (co, ci, kk, kk)
+        s["multires_unet." + name + ".bias"] = (co,)
+
+    enc_in = [base * 2 ** i for i in range(4)]
+    enc_out = [base * 2 ** (i + 1) for i in range(4)]
+    for i in range(4):
+        conv(f"encoders.{i}.conv2d", enc_out[i], bins if i == 0 else enc_in[i], k)
+    for i in range(2):
+        conv(f"resblocks.{i}.conv1", enc_out[-1], enc_out[-1], 3)
+        conv(f"resblocks.{i}.conv2", enc_out[-1], enc_out[-1], 3)
+    for i, (ci, co) in enumerate(zip(reversed(enc_out), reversed(enc_in))):
+        conv(f"decoders.{i}.conv2d", co, (2 if i == 0 else 1) * ci, k)
+    for i, co in enumerate(reversed(enc_in)):
+        conv(f"preds.{i}.conv2d", 2, co, 1)
+    conv("delayed_pred_layer_list.0.conv2d", base, sum(enc_in[:-1]) + 8, 1)
+    conv("delayed_pred_layer_list.1.conv2d", 2, base + 8, 1)
+    return s
+
+
+def _delayed_oracle(sd, compat):
+    return R.DelayedEVFlowNetOracle({k.replace("multires_unet.", ""): v for k, v in sd.items()}, compat=compat)
+
+
+def test_delayedevflownet_golden(golden):
+    g = golden("delayedevflownet_small")
+    sd = seeded_state_dict(flow_shapes_delayed(8), seed=int(g["seed"]), init="kaiming_normal")
+    net = _delayed_oracle(sd, "reference")
+    for i, p in enumerate(net.refresh(T(g["x"]))):
+        close(p, g[f"y0_{i}"], 2e-6)
+    for s in (1, 2, 3):
+        for i, p in enumerate(net.step(T(g[f"d{s}"]))):
+            close(p, g[f"dy{s}_{i}"], 5e-6)
+
+
+def test_delayedevflownet_exact_tracks_dense(golden):
+    g = golden("delayedevflownet_small")
+    sd = seeded_state_dict(flow_shapes_delayed(8), seed=51, init="kaiming_normal")
+    net, dense = _delayed_oracle(sd, "exact"), _delayed_oracle(sd, "exact")
+    x = T(g["x"])
+    ys = net.refresh(x)
+    for s in (1, 2, 3):
+        x = x + T(g[f"d{s}"])
+        ys = [y + d for y, d in zip(ys, net.step(T(g[f"d{s}"])))]
+        for y, yd in zip(ys, dense.refresh(x)):
+            close(y, yd, 2e-5)
+
+
 def test_fireflownet_golden(golden):
     g = golden("fireflownet_small")
     sd = seeded_state_dict(flow_shapes_fire(8), seed=int(g["seed"]), init="kaiming_normal")
