@@ -23,7 +23,8 @@ def install_aliases() -> None:
                            ("ext.pointops", "maskedincrementeval_b200.ext.pointops")):
         sys.modules[ref_name] = importlib.import_module(ours)
     for sub in ("masked_types", "mask_incr_functional", "mask_incr_modules", "utils", "e2depth_incr",
-                "evflownet_incr", "fireflownet_incr", "delayedevflownet_incr"):
+                "evflownet_incr", "fireflownet_incr", "delayedevflownet_incr", "obj_detection_incr",
+                "event_representation_incr"):
         try:
             sys.modules["incr_modules." + sub] = importlib.import_module("maskedincrementeval_b200.incr_modules." + sub)
         except ModuleNotFoundError:

@@ -64,6 +64,24 @@ def seeded_state_dict(shapes: Dict[str, Tuple[int, ...]], seed: int, init: str =
     return out
 
 
+def seeded_bn_stats(sd: Dict[str, torch.Tensor], seed: int) -> Dict[str, torch.Tensor]:
+    """Gives every batch-norm layer of a state dict (found by its ``running_var`` entry) plausible eval statistics:
+    gamma and running_var in [0.5, 1.5), beta and running_mean ~ 0.1 * N(0,1).  In place; returns ``sd``."""
+    rng = _rng(seed)
+    for name in [k for k in sd if k.endswith("running_var")]:
+        pre = name[: -len("running_var")]
+        n = sd[name].numel()
+        sd[pre + "running_var"] = torch.from_numpy(rng.uniform(0.5, 1.5, size=n).astype(np.float32))
+        sd[pre + "running_mean"] = torch.from_numpy((0.1 * rng.standard_normal(n)).astype(np.float32))
+        if pre + "weight" in sd:
+            sd[pre + "weight"] = torch.from_numpy(rng.uniform(0.5, 1.5, size=n).astype(np.float32))
+        if pre + "bias" in sd:
+            sd[pre + "bias"] = torch.from_numpy((0.1 * rng.standard_normal(n)).astype(np.float32))
+        if pre + "num_batches_tracked" in sd:
+            sd[pre + "num_batches_tracked"] = torch.zeros((), dtype=torch.int64)
+    return sd
+
+
 # ----------------------------------------------------------------------------------------------
 # drifting-blob deltas (single-layer and layer-chain workloads)
 # ----------------------------------------------------------------------------------------------

@@ -84,6 +84,18 @@ def _install_stubs() -> None:
                 sys.modules[n] = mod
         sys.modules["ev_projs.rpg_e2depth.model.model"].BaseE2VID = BaseE2VID
 
+    # 2b. the learned quantisation layer of the un-vendored rpg_event_representation_learning project: two names
+    # imported by incr_modules/event_representation_incr.py:5 and only used by its ClassifierIncrEval wrapper.
+    if "ev_projs.rpg_event_representation_learning.utils.models" not in sys.modules:
+        for n in ["ev_projs.rpg_event_representation_learning", "ev_projs.rpg_event_representation_learning.utils",
+                  "ev_projs.rpg_event_representation_learning.utils.models"]:
+            mod = types.ModuleType(n)
+            mod.__path__ = []
+            sys.modules[n] = mod
+        models = sys.modules["ev_projs.rpg_event_representation_learning.utils.models"]
+        models.Classifier = type("Classifier", (nn.Module,), {})
+        models.QuantizationLayer = type("QuantizationLayer", (nn.Module,), {})
+
     # 3. CUDA-only calls, when there is no CUDA device.
     if not torch.cuda.is_available():
         torch.cuda.Stream = _NullStream  # type: ignore[assignment]
@@ -105,6 +117,9 @@ def load_reference(root: str = DEFAULT_ROOT):
     ns.e2depth = importlib.import_module("incr_modules.e2depth_incr")
     ns.evflownet = importlib.import_module("incr_modules.evflownet_incr")
     ns.fireflownet = importlib.import_module("incr_modules.fireflownet_incr")
+    ns.delayedevflownet = importlib.import_module("incr_modules.delayedevflownet_incr")
+    ns.obj_detection = importlib.import_module("incr_modules.obj_detection_incr")
+    ns.event_representation = importlib.import_module("incr_modules.event_representation_incr")
     # UNetRecurrentIncr.forward calls print_sparsity on a list and raises TypeError at HEAD
     # (incr_modules/e2depth_incr.py:404 -> incr_modules/utils.py:10); silence it.
     ns.e2depth.print_sparsity = lambda *a, **k: None

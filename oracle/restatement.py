@@ -543,3 +543,97 @@ class DelayedEVFlowNetOracle(_FlowBase):
 
     def step(self, dx):
         return self._run(dx, False)
+
+
+class _BNNet:
+    """Shared pieces of the two batch-normalised networks: bias-free convolutions, eval batch-norm (dense: the full
+    affine map; on a delta: the scale only, ``bn2d_from_module``), ReLU and max-pool reservoirs."""
+
+    def __init__(self, sd: Dict[str, Tensor]):
+        self.sd = {k: v.detach().cpu() for k, v in sd.items()}
+        self.res: Dict[str, Tensor] = {}
+
+    def _conv(self, x, name, stride, pad, dense):
+        w = self.sd[name + ".weight"].float()
+        return conv_dense(x, w, None, stride, pad) if dense else conv_delta(x, w, stride, pad)
+
+    def _bn(self, x, name, dense, eps=1e-5):
+        var, w = self.sd[name + ".running_var"].float(), self.sd[name + ".weight"].float()
+        if dense:
+            return F.batch_norm(x, self.sd[name + ".running_mean"].float(), var, w, self.sd[name + ".bias"].float(),
+                                False, 0.1, eps)
+        return bn_delta(x, var, w, eps)
+
+    def _relu(self, x, key, dense):
+        if dense:
+            self.res[key] = x.clone()
+            return torch.relu(x)
+        dy, self.res[key] = act_incr(self.res[key], x, "relu")
+        return dy
+
+    def _pool(self, x, key, k, stride, pad, dense):
+        if dense:
+            self.res[key] = x.clone()
+            return F.max_pool2d(x, k, stride, pad)
+        dy, self.res[key] = maxpool_incr(self.res[key], x, k, stride, pad)
+        return dy
+
+    def _fc(self, x, name, dense):
+        return F.linear(x, self.sd[name + ".weight"].float(), self.sd[name + ".bias"].float() if dense else None)
+
+
+class DenseObjectDetOracle(_BNNet):
+    """``DenseObjectDetIncr`` (``incr_modules/obj_detection_incr.py:5-77``)."""
+
+    def __init__(self, sd, nr_classes: int, nr_box: int = 2, small_out_map: bool = True):
+        super().__init__(sd)
+        self.grid = [5, 7] if small_out_map else [6, 8]
+        self.per_cell = nr_classes + 5 * nr_box
+
+    def _run(self, x, dense):
+        for b in range(5):
+            p = f"conv_layers.{b}"
+            for j in (0, 3):
+                x = self._conv(x, f"{p}.{j}", 1, 1, dense)
+                x = self._bn(x, f"{p}.{j + 1}", dense)
+                x = self._relu(x, f"{p}.{j + 2}", dense)
+            if b < 4:
+                x = self._pool(x, f"{p}.6", 3, 2, 0, dense)
+        x = self._relu(self._bn(self._conv(x, "conv_layers.5", 2, 0, dense), "conv_layers.6", dense), "conv_layers.7", dense)
+        x = self._relu(self._fc(torch.flatten(x, 1), "linear_1", dense), "relu1", dense)
+        return self._fc(x, "linear_2", dense).view([-1] + self.grid + [self.per_cell])
+
+    def refresh(self, x):
+        return self._run(x, True)
+
+    def step(self, dx):
+        return self._run(dx, False)
+
+
+class ResnetOracle(_BNNet):
+    """``ResnetIncr`` / ``BasicBlockIncr`` (``incr_modules/event_representation_incr.py:10-143``): ResNet-34 body."""
+
+    STAGES = ((64, 3, False), (128, 4, True), (256, 6, True), (512, 3, True))
+
+    def _block(self, x, p, down, dense):
+        stride = 2 if down else 1
+        out = self._relu(self._bn(self._conv(x, p + ".conv1", stride, 1, dense), p + ".bn1", dense), p + ".relu", dense)
+        out = self._bn(self._conv(out, p + ".conv2", 1, 1, dense), p + ".bn2", dense)
+        if down:
+            x = self._bn(self._conv(x, p + ".downsample.0", 2, 0, dense), p + ".downsample.1", dense)
+        return self._relu(out + x, p + ".relu2", dense)
+
+    def _run(self, x, dense):
+        x = self._relu(self._bn(self._conv(x, "conv1", 2, 3, dense), "bn1", dense), "relu", dense)
+        x = self._pool(x, "maxpool", 3, 2, 1, dense)
+        for si, (_, n_blocks, down) in enumerate(self.STAGES, 1):
+            for bi in range(n_blocks):
+                x = self._block(x, f"layer{si}.{bi}", down and bi == 0, dense)
+        x = torch.flatten(F.adaptive_avg_pool2d(x, (1, 1)), 1, -1)
+        return self._fc(x, "fc", dense)
+
+    def refresh(self, x):
+        return self._run(x, True)
+
+    def step(self, dx):
+        return self._run(dx, False)

@@ -199,6 +199,20 @@ def main(ref_root: str = DEFAULT_ROOT):
         for i, p in enumerate(net([d, None])["flow"]):
             out[f"dy{s}_{i}"] = _np(p if torch.is_tensor(p) else p[0])
     np.savez_compressed(os.path.join(OUT, "delayedevflownet_small.npz"), **out)
+    # ---- ResNet-34 body (64x64) and dense object detector (191x255 -> 5x7 grid), batch-norm statistics seeded ----
+    from maskedincrementeval_b200.synthetic import seeded_bn_stats
+    for tag, net, shape, frac in (("resnet_small", ref.event_representation.ResnetIncr().eval(), (1, 3, 64, 64), 0.1),
+                                  ("objdet_small", ref.obj_detection.DenseObjectDetIncr(2).eval(), (1, 2, 191, 255), 0.05)):
+        out = {}
+        net.load_state_dict(seeded_bn_stats(seeded_state_dict(_shapes(net), seed=61, init="kaiming_normal"), 62))
+        x = (torch.randn(*shape, generator=g) * 4).round() / 4      # quarter steps: the fixture compresses
+        x = x.contiguous(memory_format=torch.channels_last)
+        out["seed"], out["bn_seed"], out["x"] = np.array(61), np.array(62), _np(x)
+        out["y0"] = _np(net.forward_refresh_reservoirs(x))
+        for s in (1, 2):
+            d = _sparse_delta(g, x.shape, frac=frac)
+            out[f"d{s}"], out[f"dy{s}"] = _np(d), _np(net([d, None])[0])
+        np.savez_compressed(os.path.join(OUT, tag + ".npz"), **out)
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))
 
 

@@ -233,6 +233,79 @@ def test_delayedevflownet_exact_tracks_dense(golden):
             close(y, yd, 2e-5)
 
 
+def bn_net_state(net_cls_or_shapes, g):
+    """Seeded weights and batch-norm statistics of the ResNet / detector fixtures."""
+    from maskedincrementeval_b200.synthetic import seeded_bn_stats
+    return seeded_bn_stats(seeded_state_dict(net_cls_or_shapes, seed=int(g["seed"]), init="kaiming_normal"), int(g["bn_seed"]))
+
+
+def resnet_shapes():
+    s = {}
+
+    def bn(p, c):
+        s.update({p + ".weight": (c,), p + ".bias": (c,), p + ".running_mean": (c,), p + ".running_var": (c,),
+                  p + ".num_batches_tracked": ()})
+
+    s["conv1.weight"] = (64, 3, 7, 7)
+    bn("bn1", 64)
+    for si, (c, n, down) in enumerate(R.ResnetOracle.STAGES, 1):
+        for bi in range(n):
+            p = f"layer{si}.{bi}"
+            first = down and bi == 0
+            s[p + ".conv1.weight"] = (c, c // 2 if first else c, 3, 3)
+            bn(p + ".bn1", c)
+            s[p + ".conv2.weight"] = (c, c, 3, 3)
+            bn(p + ".bn2", c)
+            if first:
+                s[p + ".downsample.0.weight"] = (c, c // 2, 1, 1)
+                bn(p + ".downsample.1", c)
+    s["fc.weight"], s["fc.bias"] = (1000, 512), (1000,)
+    return s
+
+
+def objdet_shapes(nr_classes=2, in_c=2, nr_box=2):
+    s = {}
+
+    def bn(p, c):
+        s.update({p + ".weight": (c,), p + ".bias": (c,), p + ".running_mean": (c,), p + ".running_var": (c,),
+                  p + ".num_batches_tracked": ()})
+
+    ci = in_c
+    for b, co in enumerate((16, 32, 64, 128, 256)):
+        p = f"conv_layers.{b}"
+        s[p + ".0.weight"] = (co, ci, 3, 3)
+        bn(p + ".1", co)
+        s[p + ".3.weight"] = (co, co, 3, 3)
+        bn(p + ".4", co)
+        ci = co
+    s["conv_layers.5.weight"] = (512, 256, 3, 3)
+    bn("conv_layers.6", 512)
+    s["linear_1.weight"], s["linear_1.bias"] = (1024, 35 * 512), (1024,)
+    per = 35 * (nr_classes + 5 * nr_box)
+    s["linear_2.weight"], s["linear_2.bias"] = (per, 1024), (per,)
+    return s
+
+
+def rel_close(a, b, tol):
+    a, b = torch.as_tensor(a), torch.as_tensor(b)
+    scale = max(float(b.abs().max()), 1e-6)
+    assert float((a - b).abs().max()) <= tol * scale, (float((a - b).abs().max()), scale)
+
+
+@pytest.mark.parametrize("tag", ["resnet_small", "objdet_small"])
+def test_bn_networks_golden(golden, tag):
+    g = golden(tag)
+    if tag == "resnet_small":
+        net = R.ResnetOracle(bn_net_state(resnet_shapes(), g))
+    else:
+        net = R.DenseObjectDetOracle(bn_net_state(objdet_shapes(), g), nr_classes=2)
+    # the fixture was computed on channels-last tensors, this runs contiguous ones: a different convolution algorithm of
+    # the same CPU library, i.e. another summation order through up to 36 layers and a 17920-wide linear layer
+    rel_close(net.refresh(T(g["x"])), g["y0"], 2e-5)
+    for s in (1, 2):
+        rel_close(net.step(T(g[f"d{s}"])), g[f"dy{s}"], 1e-4)
+
+
 def test_fireflownet_golden(golden):
     g = golden("fireflownet_small")
     sd = seeded_state_dict(flow_shapes_fire(8), seed=int(g["seed"]), init="kaiming_normal")
