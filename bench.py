@@ -288,10 +288,19 @@ def run_ours(args):
             return FireFlowNetIncr(dict(base_num_channels=32, kernel_size=3, mask_output=False), 2, compat="exact")
         if args.net == "evflownet":
             return MultiResUNetRecurrentIncr(compat="exact")
+        if args.net == "delayedevflownet":
+            from maskedincrementeval_b200.incr_modules.delayedevflownet_incr import DelayedEVFlowNetIncr
+            return DelayedEVFlowNetIncr(dict(base_num_channels=32, kernel_size=3, mask_output=False), 2, compat="exact")
+        if args.net == "objdet":
+            from maskedincrementeval_b200.incr_modules.obj_detection_incr import DenseObjectDetIncr
+            return DenseObjectDetIncr(2)
         return E2VIDRecurrentIncr(dict(E2DEPTH_CFG))
 
     shapes = e2depth_shapes() if not flow else {k: tuple(v.shape) for k, v in build_net().state_dict().items()}
     sd = seeded_state_dict(shapes, seed=0, init="default")
+    if args.net == "objdet":
+        from maskedincrementeval_b200.synthetic import seeded_bn_stats
+        seeded_bn_stats(sd, 1)
 
     def make_net():
         net = build_net().to(dev).eval()
@@ -306,6 +315,8 @@ def run_ours(args):
             if hasattr(model, "reset_states"):
                 model.reset_states()
             out = model.forward_refresh_reservoirs(x)
+            if torch.is_tensor(out):
+                return out
             return out["flow"][0] if isinstance(out, dict) else out[0]
 
     def first(y):
@@ -494,7 +505,7 @@ def main():
     ap.add_argument("--size", default="260x346", help="sensor resolution HxW (secondary measurements; the headline is 260x346)")
     ap.add_argument("--events", type=int, default=EVENTS)
     ap.add_argument("--segments", type=int, default=SEGMENTS)
-    ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet"],
+    ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet", "delayedevflownet", "objdet"],
                     help="secondary measurements of the flow networks (BASELINE config 5: 256x336 two-channel event-count "
                          "images, 20k events per window); the headline is e2depth")
     ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
@@ -506,7 +517,7 @@ def main():
     EVENTS, SEGMENTS = args.events, args.segments
     if args.net != "e2depth":
         if args.size == "260x346":
-            H, W = 256, 336
+            H, W = (191, 255) if args.net == "objdet" else (256, 336)
         if args.events == 30000:
             EVENTS = 20000
         WORKLOAD = f"{args.net}_{H}x{W}_b{args.streams}"

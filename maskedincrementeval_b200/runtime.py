@@ -30,6 +30,8 @@ def _deltas_of(out) -> List:
         return [out[0]]
     if isinstance(out, (list, tuple)) and len(out) and isinstance(out[0], (list, tuple)):
         return list(out)
+    if isinstance(out, (list, tuple)) and len(out) == 2 and torch.is_tensor(out[0]) and not torch.is_tensor(out[1]):
+        return [out]                      # a single ``[delta, mask]`` pair (classifier / detector heads)
     raise TypeError("unrecognised network output")
 
 
