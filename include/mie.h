@@ -272,6 +272,13 @@ int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int 
 int mie_reflect_border(float *field, int64_t ps, int C, int H, int W, int sensor_h, int sensor_w, int pad_left,
                        int pad_top, void *stream);
 
+/* out = maxpool(res + d) - maxpool(res) for a k x k window (stride, pad as torch.nn.MaxPool2d, floor mode);
+ * out is [N,C,Ho,Wo] with Ho = (H + 2*pad - k)/stride + 1.  The reservoir is only read: advance it afterwards with
+ * mie_accumulate(res, d).  nnMaxPool2dIncr.forward, incr_modules/mask_incr_modules.py:217-220. */
+int mie_maxpool_incr(const float *d, int64_t d_ps, const uint64_t *d_bits, const float *res, int64_t res_ps,
+                     float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, int k, int stride,
+                     int pad, void *stream);
+
 /* Sigma-delta quantiser with carry: T = carry + dx; q = k * floor(0.5 + T / k); carry = T - q; bits = q != 0.
  * KFencedMaskModule.forward, incr_modules/mask_incr_modules.py:31-41. */
 int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t c_ps, float k, float *q, int64_t q_ps,

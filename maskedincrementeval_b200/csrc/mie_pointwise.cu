@@ -986,6 +986,75 @@ extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bi
   return check_launch();
 }
 
+// Max-pool of a delta field against its reservoir: out = maxpool(res + d) - maxpool(res) on the output tiles whose
+// windows touch an active input pixel; windows are clipped to the image (torch pads with -inf).  The reservoir is
+// only read here: neighbouring windows overlap, so it is advanced afterwards (mie_accumulate on the same delta).
+__global__ void __launch_bounds__(1024) maxpool_incr_kernel(
+    const float *__restrict__ d, int64_t d_ps, const uint64_t *__restrict__ d_bits, const float *__restrict__ res,
+    int64_t res_ps, float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W,
+    int Ho, int Wo, int k, int stride, int pad) {
+  __shared__ unsigned s_w[2], s_any[2];
+  const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
+  const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const TileGeom g = tile_geom(t, Ho, Wo);
+    __syncthreads();
+    if (threadIdx.x < 2) { s_w[threadIdx.x] = 0u; s_any[threadIdx.x] = 0u; }
+    __syncthreads();
+    // which output pixels of the tile have an active input pixel in their window
+    if (threadIdx.x < 64 && pix_valid(g, threadIdx.x)) {
+      const int oy = g.ty * 8 + (threadIdx.x >> 3), ox = g.tx * 8 + (threadIdx.x & 7);
+      bool a = false;
+      for (int ky = 0; ky < k && !a; ++ky) {
+        const int iy = oy * stride - pad + ky;
+        if (iy < 0 || iy >= H) continue;
+        for (int kx = 0; kx < k; ++kx) {
+          const int ix = ox * stride - pad + kx;
+          if (ix >= 0 && ix < W && bit_at(d_bits, g.n, iy, ix, THi, TWi)) { a = true; break; }
+        }
+      }
+      if (a) or_word(s_any, threadIdx.x);
+    }
+    __syncthreads();
+    const uint64_t touched = ((uint64_t)s_any[1] << 32) | s_any[0];
+    if (touched == 0ull) {
+      if (out_bits[t] != 0ull) {
+        zero_tile(out, out_ps, C, g, Ho, Wo);
+        __syncthreads();
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
+      const int p = e / C, c = e - p * C;
+      if (!pix_valid(g, p)) continue;
+      const int oy = g.ty * 8 + (p >> 3), ox = g.tx * 8 + (p & 7);
+      float v = 0.0f;
+      if ((touched >> p) & 1ull) {
+        float m_new = -INFINITY, m_old = -INFINITY;
+        for (int ky = 0; ky < k; ++ky) {
+          const int iy = oy * stride - pad + ky;
+          if (iy < 0 || iy >= H) continue;
+          for (int kx = 0; kx < k; ++kx) {
+            const int ix = ox * stride - pad + kx;
+            if (ix < 0 || ix >= W) continue;
+            const int64_t pix = (int64_t)(g.n * H + iy) * W + ix;
+            const float r = res[pix * res_ps + c];
+            const float dv = bit_at(d_bits, g.n, iy, ix, THi, TWi) ? d[pix * d_ps + c] : 0.0f;
+            m_old = fmaxf(m_old, r);
+            m_new = fmaxf(m_new, r + dv);
+          }
+        }
+        v = m_new - m_old;
+        if (v != 0.0f) or_word(s_w, p);
+      }
+      out[((int64_t)(g.n * Ho + oy) * Wo + ox) * out_ps + c] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0];
+  }
+}
+
 // Border of a [1,C,H,W] field filled by reflection of its interior (sensor image of sh x sw placed at (pt, pl)),
 // index arithmetic of torch.nn.ReflectionPad2d: the edge pixel is not repeated.
 __global__ void __launch_bounds__(256) reflect_border_kernel(float *__restrict__ f, int64_t ps, int C, int H, int W, int sh,
@@ -1036,5 +1105,20 @@ extern "C" int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   split_tf32_kernel<<<tile_grid(ntiles), 256, 0, (cudaStream_t)stream>>>(in, in_ps, in_bits, C, half, out, out_ps, out_bits,
                                                                         N, H, W);
+  return check_launch();
+}
+
+extern "C" int mie_maxpool_incr(const float *d, int64_t d_ps, const uint64_t *d_bits, const float *res, int64_t res_ps,
+                                float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, int k, int stride,
+                                int pad, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !d_bits || !out_bits) return MIE_EINVAL;
+  if (k < 1 || k > 7 || stride < 1 || stride > 4 || pad < 0 || 2 * pad > k) return MIE_EUNSUPPORTED;
+  MIE_CHECK_FIELD(d, d_ps, C); MIE_CHECK_FIELD(res, res_ps, C);
+  const int Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1;
+  if (Ho <= 0 || Wo <= 0) return MIE_EINVAL;
+  MIE_CHECK_FIELD(out, out_ps, C);
+  const int ntiles = N * divup(Ho, 8) * divup(Wo, 8);
+  maxpool_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
+      d, d_ps, d_bits, res, res_ps, out, out_ps, out_bits, N, C, H, W, Ho, Wo, k, stride, pad);
   return check_launch();
 }

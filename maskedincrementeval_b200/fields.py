@@ -304,6 +304,15 @@ def events_to_voxel(events: torch.Tensor, num_bins: int, sensor_hw, out: torch.T
     return out
 
 
+def maxpool_incr(d, m: TileMask, res, out, out_bits, k: int, stride: int, pad: int) -> TileMask:
+    """out = maxpool(res + d) - maxpool(res); the reservoir is left as it is (advance it with ``accumulate``)."""
+    n, c, h, w = d.shape
+    nat.check(nat.lib.mie_maxpool_incr(d.data_ptr(), pixel_stride(d), m.bits.data_ptr(), res.data_ptr(), pixel_stride(res),
+                                       out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w, k, stride, pad,
+                                       nat.stream_ptr(d.device)), "maxpool_incr")
+    return TileMask(out_bits, n, out.shape[2], out.shape[3])
+
+
 def reflect_border(field: torch.Tensor, sensor_hw, pad_left: int, pad_top: int):
     """Reflection-fill the border of a [1,C,H,W] field around the sensor image placed at (pad_top, pad_left)."""
     n, c, h, w = field.shape

@@ -411,17 +411,34 @@ class nnBatchNorm2dIncr(nn.BatchNorm2d):
 
 
 class nnMaxPool2dIncr(nn.MaxPool2d):
-    """mp(res + dx) - mp(res); res += dx (reference ``:210-225``).  Tensor ops: no network in scope uses it."""
+    """mp(res + dx) - mp(res); res += dx (reference ``:210-225``).  One kernel evaluates the windows that touch an
+    active input pixel against the reservoir, a second one advances the reservoir (windows overlap, so it may only
+    move once every window has been read)."""
 
     def __init__(self, kernel_size, stride=None, padding=0):
         nn.MaxPool2d.__init__(self, kernel_size=kernel_size, stride=stride, padding=padding)
         self.functional = lambda x: F.max_pool2d(x, kernel_size=self.kernel_size, stride=self.stride, padding=self.padding)
         self.mp_res = IncrementReserve()
+        self._scratch = Scratch()
 
     def forward(self, x_incr: Masked) -> Masked:
-        out = self.functional(self.mp_res.reservoir + x_incr[0]) - self.functional(self.mp_res.reservoir)
-        self.mp_res.accumulate(x_incr)
-        return out, None
+        res = self.mp_res.reservoir
+        if res is None:
+            raise RuntimeError("forward_refresh_reservoirs must run before the first incremental step")
+        k, s, p = _square(self.kernel_size), _square(self.stride), _square(self.padding)
+        if self.dilation != 1 or self.ceil_mode or self.return_indices or not (1 <= k <= 7 and 1 <= s <= 4 and 2 * p <= k):
+            out = self.functional(res + x_incr[0]) - self.functional(res)     # shapes the kernel does not take
+            self.mp_res.accumulate(x_incr)
+            return out, None
+        sc = self._scratch
+        d, m = fl.resolve(x_incr, sc, "in")
+        n, c, h, w = d.shape
+        ho, wo = fl.conv_out_hw(h, w, k, s, p)
+        out = sc.get("out", (n, c, ho, wo), torch.float32, d.device, channels_last=True)
+        bits = sc.get("out.bits", (fl.n_tiles(n, ho, wo),), torch.int64, d.device)
+        mo = fl.maxpool_incr(d, m, res, out, bits, k, s, p)
+        fl.accumulate(res, d, m)
+        return [out, mo]
 
     def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
         self.mp_res.update_reservoir(x)

@@ -533,3 +533,24 @@ def test_kfenced_kernel_golden(dev, golden):
         close(q, T(g[f"kf_q{s}"]), 1e-5)
         close(kf.delta.reservoir, T(g[f"kf_c{s}"]), 1e-4)
         assert torch.equal(m.pixel_mask().cpu(), (q.cpu() != 0).any(1, keepdim=True).to(torch.uint8))
+
+
+@pytest.mark.parametrize("k,s,p,shape", [(3, 2, 0, (2, 16, 37, 45)), (3, 2, 1, (1, 64, 32, 32)), (2, 2, 0, (1, 5, 20, 28)),
+                                         (3, 1, 1, (1, 8, 17, 9))])
+def test_maxpool_incr_matches_oracle(dev, k, s, p, shape):
+    """nnMaxPool2dIncr on the kernel: values and reservoir bit-exact (max and subtraction only), mask = out != 0."""
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import nnMaxPool2dIncr
+    g = torch.Generator().manual_seed(k * 100 + s * 10 + p)
+    mp = nnMaxPool2dIncr(kernel_size=k, stride=s, padding=p)
+    x0 = torch.randn(shape, generator=g)
+    with torch.no_grad():
+        mp.forward_refresh_reservoirs(cl(x0, dev))
+        res = x0.clone()
+        for frac in (0.1, 0.0, 1.0, 0.03, 0.0):
+            dx = sparse_delta(g, shape, frac)
+            out, m = mp([cl(dx, dev), None])
+            want, res = R.maxpool_incr(res, dx, k, s, p)
+            assert torch.equal(out.cpu(), want)
+            assert torch.equal(mp.mp_res.reservoir.cpu(), res)
+            pm = m.pixel_mask().cpu()
+            assert torch.equal(pm, (want != 0).any(1, keepdim=True).to(torch.uint8))
