@@ -291,19 +291,28 @@ class nnConvIncr(nn.Conv2d):
         return (config.tensor_cores == "auto" and self._s == 1 and self._k in (3, 5, 7) and cin <= 8
                 and cin * self._k * self._k >= 100 and self.out_channels % 4 == 0)
 
-    def _weights(self, cin_limit: Optional[int] = None, split: bool = False):
-        """Packed filter for the kernels, repacked whenever the parameter changed or moved."""
+    def _weights(self, cin_limit: Optional[int] = None, split: bool = False, bn: "Optional[nn.BatchNorm2d]" = None):
+        """Packed filter for the kernels, repacked whenever the parameter changed or moved.  ``bn``: an eval
+        batch-norm that follows the convolution; on a delta it is a per-channel scale (``bn2d_from_module``), which
+        is folded into the packed filter."""
         key = cin_limit or self.in_channels
         ver = (self.weight._version, self.weight.device, self.weight.data_ptr())
+        if bn is not None:
+            ver = ver + (id(bn), bn.running_var._version, bn.running_var.data_ptr(), bn.eps,
+                         None if bn.weight is None else (bn.weight._version, bn.weight.data_ptr()))
+            key = ("bn", id(bn), key)
         if split:
             key = ("split", key)
         hit = self._packed.get(key)
         if hit is None or hit[0] != ver:
             w = self.weight.detach()
-            if not split and key != self.in_channels:
-                w = w[:, :key].contiguous()
+            if bn is not None:
+                scale = (bn.weight.detach() if bn.weight is not None else 1.0) / torch.sqrt(bn.running_var + bn.eps)
+                w = w * scale.view(-1, 1, 1, 1)
+            if cin_limit and cin_limit != self.in_channels:
+                w = w[:, :cin_limit].contiguous()
             if split:
-                c = key[1]
+                c = cin_limit or self.in_channels
                 wf = w[:, :c].float()
                 w_hi = (wf.view(torch.int32) + 0x1000 & ~0x1FFF).view(torch.float32)   # TF32 rounding, as the packing does
                 w24 = torch.zeros((w.shape[0], 24, self._k, self._k), dtype=torch.float32, device=w.device)
@@ -313,7 +322,7 @@ class nnConvIncr(nn.Conv2d):
                 w = w24
                 key_depth = 24
             else:
-                key_depth = key
+                key_depth = cin_limit or self.in_channels
             buf, cp, op = fl.pack_conv_weights(w.float())
             tc = None
             # the library decides per call whether the tensor-core copy is used; it never is below this depth
@@ -333,8 +342,10 @@ class nnConvIncr(nn.Conv2d):
         return p
 
     def forward_fused(self, x_incr: Masked, activation: "Optional[nnReservedActivation]" = None,
-                      addend: Optional[Masked] = None, cin_limit: Optional[int] = None) -> Masked:
-        """conv(dx) [+ addend] [-> incremental activation], one dilation launch and one convolution launch."""
+                      addend: Optional[Masked] = None, cin_limit: Optional[int] = None,
+                      bn: "Optional[nn.BatchNorm2d]" = None) -> Masked:
+        """conv(dx) [* batch-norm scale] [+ addend] [-> incremental activation], one dilation launch and one
+        convolution launch."""
         sc = self._scratch
         d, m = fl.resolve(x_incr, sc, "in")
         n, cin, hin, win = d.shape
@@ -343,7 +354,7 @@ class nnConvIncr(nn.Conv2d):
             raise RuntimeError(f"expected {cin_eff} input channels, got {cin}")
         plan = self._plan(n, hin, win, d.device)
         split = self._split_input(cin)
-        wbuf, cp, op, wtc = self._weights(cin_limit, split)
+        wbuf, cp, op, wtc = self._weights(cin_limit, split, bn)
         if split:
             d24 = sc.get("split", (n, 24, hin, win), torch.float32, d.device, channels_last=True)
             sb = sc.get("split.bits", (fl.n_tiles(n, hin, win),), torch.int64, d.device)
@@ -456,7 +467,28 @@ class nnAdaptiveAvgPool2dIncr(nn.AdaptiveAvgPool2d):
 
 
 class nnSequentialIncr(nn.Sequential):
-    """Chains ``forward_refresh_reservoirs`` (reference ``:236-240``)."""
+    """Chains ``forward_refresh_reservoirs`` (reference ``:236-240``).  The incremental pass runs a convolution, the
+    eval batch-norm behind it (a per-channel scale on a delta) and the activation behind that as one fused launch."""
+
+    def forward(self, x_incr):
+        mods = list(self)
+        i = 0
+        while i < len(mods):
+            m = mods[i]
+            if type(m) is nnConvIncr:
+                j, bn, act = i + 1, None, None
+                if j < len(mods) and type(mods[j]) is nnBatchNorm2dIncr and not mods[j].training and mods[j].track_running_stats:
+                    bn, j = mods[j], j + 1
+                if j < len(mods) and isinstance(mods[j], nnReservedActivation) and mods[j].in_res.reservoir is not None \
+                        and mods[j].in_res.reservoir.dim() == 4:
+                    act, j = mods[j], j + 1
+                if bn is not None or act is not None:
+                    x_incr = m.forward_fused(x_incr, act, bn=bn)
+                    i = j
+                    continue
+            x_incr = m(x_incr)
+            i += 1
+        return x_incr
 
     def forward_refresh_reservoirs(self, x):
         for module in self:
