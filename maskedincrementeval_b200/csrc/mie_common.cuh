@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 #include "mie.h"
 
 #define MIE_TILE 8
@@ -19,6 +21,37 @@ static inline int check_launch() {
     return MIE_ECUDA;
   }
   return MIE_OK;
+}
+
+// Programmatic dependent launch.  The kernels of one timestep form a chain of short launches, each reading what the one
+// before wrote.  A kernel launched through launch_chained() may become resident while its predecessor in the stream is
+// still running: whatever it does before grid_dependency_wait() (barrier and tensor-memory set-up, nothing that
+// touches global memory) overlaps the predecessor's tail; the wait returns once the predecessor has finished and its
+// writes are visible.  grid_dependency_trigger() lets the next kernel of the chain start its own set-up.
+// Rule: every kernel launched through launch_chained() executes grid_dependency_wait() in every thread before its
+// first global-memory access.  MIE_PDL=0 in the environment launches without the attribute (plain stream order).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool chained_launch_enabled() {
+  static const bool on = []() { const char *e = getenv("MIE_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  (void)e;  // picked up by check_launch() through cudaGetLastError()
 }
 
 static inline int divup(int a, int b) { return (a + b - 1) / b; }

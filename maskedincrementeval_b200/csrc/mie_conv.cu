@@ -59,6 +59,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // 32-channel layers, which otherwise run one warp per scheduler.
 template <int K, int S, int WT, int WN, int CPT>
 __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles_kernel(const ConvParams p) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   using G = Geo<K, S>;
   constexpr int NT = 32 * WT * WN;
   constexpr int NBW = 4 * CPT;          // channels per warp
@@ -360,6 +362,8 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
 constexpr int SMALL_COUT = 4;
 
 __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   extern __shared__ float s_w[];  // [cin][SMALL_COUT]
   const int tid = threadIdx.x, grp = tid >> 6, px = tid & 63, lane = tid & 31;
   for (int i = tid; i < p.cin * SMALL_COUT; i += blockDim.x) {
@@ -466,7 +470,7 @@ int launch_conv(const ConvParams &p, int max_items, cudaStream_t st) {
   int grid = MIE_SM_COUNT * per_sm;
   if (grid > max_items) grid = max_items;
   if (grid < 1) grid = 1;
-  conv_tiles_kernel<K, S, WT, WN, CPT><<<grid, NT, smem, st>>>(p);
+  launch_chained(conv_tiles_kernel<K, S, WT, WN, CPT>, dim3(grid), dim3(NT), smem, st, p);
   return check_launch();
 }
 
@@ -550,7 +554,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
     int blocks = divup(a->max_tiles, 4);
     if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
     p.in_vec = p.in_vec && (a->cin % 4 == 0 || a->in_ps >= (a->cin + 3) / 4 * 4);
-    conv1x1_small_kernel<<<blocks, 256, (size_t)a->cin * SMALL_COUT * sizeof(float), (cudaStream_t)stream>>>(p);
+    launch_chained(conv1x1_small_kernel, dim3(blocks), dim3(256), (size_t)a->cin * SMALL_COUT * sizeof(float), (cudaStream_t)stream, p);
     return check_launch();
   }
 

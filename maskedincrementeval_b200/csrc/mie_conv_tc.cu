@@ -49,6 +49,20 @@ struct TcParams {
 
 namespace {
 
+// -DMIE_TC_TRACE (debug builds only): conv_tc_kernel records SM-clock timestamps of its phases per block, read back
+// through mie_debug_trace().  Compiled out of the product build.
+#ifdef MIE_TC_TRACE
+__device__ long long g_tc_trace[1024 * 16];
+__device__ __forceinline__ long long trace_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TC_TRACE(slot) do { if (blockIdx.x < 1024) g_tc_trace[blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#define TC_TRACE_G(slot) do { if (blockIdx.x < 1024) g_tc_trace[blockIdx.x * 16 + (slot)] = trace_gtime(); } while (0)
+#define TC_TRACE_V(slot, v) do { if (blockIdx.x < 1024) g_tc_trace[blockIdx.x * 16 + (slot)] = (v); } while (0)
+#else
+#define TC_TRACE(slot) do { } while (0)
+#define TC_TRACE_G(slot) do { } while (0)
+#define TC_TRACE_V(slot, v) do { } while (0)
+#endif
+
 constexpr int TC_THREADS = 192;
 constexpr int A_STAGE_BYTES = 128 * 128;  // 128 pixels x 32 channels x 4 B
 constexpr unsigned SPIN_LIMIT = 1u << 20;
@@ -189,8 +203,21 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
 }
 
 // One group of 16 accumulator columns of one pixel: optional residual add, incremental activation against the
-// reservoir, store.
-__device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float *v, int64_t pix, int co, bool any_d) {
+// reservoir, store.  The activation is a template argument: with a run-time switch every one of the 32 calls below
+// carried the code of all three functions, and the executed path hopped over ~50 KB of instructions -- after an L2
+// flush each hop is an instruction-cache miss served from DRAM (measured: 4 us of a 5.4 us epilogue).
+// ReLU and "none" are inlined; sigmoid and tanh go through one shared out-of-line copy (ACT = MIE_ACT_SIGMOID stands
+// for both): inlining 32 copies of expf / tanhf cost 180 registers and with them the third resident block.
+__device__ __noinline__ float tc_act_call(int op, float x) { return act_apply(op, x); }
+template <int ACT>
+__device__ __forceinline__ float tc_act(int op, float x) {
+  if (ACT == MIE_ACT_RELU) return fmaxf(x, 0.0f);
+  if (ACT == MIE_ACT_NONE) return x;
+  return tc_act_call(op, x);
+}
+
+template <int ACT>
+__device__ __forceinline__ bool tc_epilogue_group_t(const TcParams &p, const float *v, int64_t pix, int co, bool any_d) {
   bool flag = false;
   const int nq = min(4, (p.cout - co) >> 2);  // channel quads of this group that exist
   float4 d[4], x[4], base[4];
@@ -200,7 +227,7 @@ __device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float
     d[h] = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
     if (h < nq) {
       if (p.addend) d[h] = f4add(d[h], *reinterpret_cast<const float4 *>(p.addend + pix * p.addend_ps + co + h * 4));
-      if (p.act != MIE_ACT_NONE && any_d) {
+      if (ACT != MIE_ACT_NONE && any_d) {
         x[h] = *reinterpret_cast<const float4 *>(p.res + pix * p.res_ps + co + h * 4);
         if (p.emitted) base[h] = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
       }
@@ -210,14 +237,14 @@ __device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float
   for (int h = 0; h < 4; ++h) {
     if (h >= nq) continue;
     float4 o = d[h];
-    if (p.act != MIE_ACT_NONE) {
+    if (ACT != MIE_ACT_NONE) {
       if (any_d) {
         const float4 xn = f4add(x[h], d[h]);
         *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
         if (!p.emitted)
-          base[h] = make_float4(act_apply(p.act, x[h].x), act_apply(p.act, x[h].y), act_apply(p.act, x[h].z), act_apply(p.act, x[h].w));
-        o = make_float4(act_apply(p.act, xn.x) - base[h].x, act_apply(p.act, xn.y) - base[h].y,
-                        act_apply(p.act, xn.z) - base[h].z, act_apply(p.act, xn.w) - base[h].w);
+          base[h] = make_float4(tc_act<ACT>(p.act, x[h].x), tc_act<ACT>(p.act, x[h].y), tc_act<ACT>(p.act, x[h].z), tc_act<ACT>(p.act, x[h].w));
+        o = make_float4(tc_act<ACT>(p.act, xn.x) - base[h].x, tc_act<ACT>(p.act, xn.y) - base[h].y,
+                        tc_act<ACT>(p.act, xn.z) - base[h].z, tc_act<ACT>(p.act, xn.w) - base[h].w);
       } else {
         o = make_float4(0.f, 0.f, 0.f, 0.f);
       }
@@ -226,6 +253,15 @@ __device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float
     *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
   }
   return flag;
+}
+
+__device__ __forceinline__ bool tc_epilogue_group(const TcParams &p, const float *v, int64_t pix, int co, bool any_d) {
+  switch (p.act) {
+    case MIE_ACT_RELU: return tc_epilogue_group_t<MIE_ACT_RELU>(p, v, pix, co, any_d);
+    case MIE_ACT_SIGMOID:
+    case MIE_ACT_TANH: return tc_epilogue_group_t<MIE_ACT_SIGMOID>(p, v, pix, co, any_d);
+    default: return tc_epilogue_group_t<MIE_ACT_NONE>(p, v, pix, co, any_d);
+  }
 }
 
 // Epilogue of one accumulator row (= one output pixel, all NB channels of the block).  Called by all 32 lanes of an
@@ -289,6 +325,19 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
       return valid && flag;
 }
 
+// Asks for the lines the epilogue of one pixel will read (reservoir, residual addend, carry) while the MMAs of the item
+// are still running: the accumulator arrives to loads that hit the cache instead of starting a DRAM round trip each.
+__device__ __forceinline__ void tc_epilogue_prefetch(const TcParams &p, int64_t pix, int co0, int c_lo, int c_hi) {
+  c_hi = min(c_hi, p.cout - co0);
+  for (int c = c_lo; c < c_hi; c += 32) {
+    if (p.act != MIE_ACT_NONE) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.res + pix * p.res_ps + co0 + c));
+      if (p.emitted) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.emitted + pix * p.emitted_ps + co0 + c));
+    }
+    if (p.addend) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.addend + pix * p.addend_ps + co0 + c));
+  }
+}
+
 struct TcMaps {
   CUtensorMap in[4];  // stride 1: [0] only; stride 2: [row parity * 2 + column parity]
   CUtensorMap w;
@@ -346,8 +395,6 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // issued first so that their latency hides behind barrier set-up and the tensor-memory allocation
-  const int n_active = min(p.counts[0], p.max_tiles);
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_in)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_w)) : "memory");
@@ -375,6 +422,11 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
+
+  // everything above touched no global memory: it may overlap the tail of the previous kernel in the stream
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  const int n_active = min(p.counts[0], p.max_tiles);
 
   tc_zero_stale(p, ntiles_total, THo, TWo, HALO_THREADS);
 
@@ -509,6 +561,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      if (valid) tc_epilogue_prefetch(p, pix, cb * NB, c_lo, c_hi);
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
       tc_fence_after();
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
@@ -540,7 +593,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   }
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 3)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment of every stage is what the 128-byte swizzle of TMA and of the MMA descriptors assume
@@ -552,8 +605,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // issued first so that their latency hides behind barrier set-up and the tensor-memory allocation
-  const int n_active = min(p.counts[0], p.max_tiles);
+  if (tid == 0) { TC_TRACE(0); TC_TRACE_G(14); }
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&maps.in[0])) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&maps.w)) : "memory");
@@ -581,7 +633,15 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
 
+  // everything above touched no global memory: it may overlap the tail of the previous kernel in the stream
+  if (tid == 0) TC_TRACE(1);
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  const int n_active = min(p.counts[0], p.max_tiles);
+  if (tid == 0) TC_TRACE(2);
+
   tc_zero_stale(p, ntiles_total, THo, TWo, TC_THREADS);
+  if (tid == 0) TC_TRACE(3);
 
   const int n_pairs = (n_active + 1) >> 1;
   const int n_cblk = p.cout_pad / NB;
@@ -608,6 +668,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
         const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + b_bytes;
         const int cbn = cb * NB;
+        if (item == (int)blockIdx.x) { TC_TRACE_V(4, clock64() + (t0 & 0)); }
         bool ok = true;
         for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
           const int c0 = chunk * 32;
@@ -625,10 +686,11 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
               if (t1 >= 0) tma_load_4d_raw(stage_addr + A_STAGE_BYTES / 2, &maps.in[mi], bar, c0, x1 + dx, y1 + dy, n1);
               tma_load_4d_raw(stage_addr + A_STAGE_BYTES, &maps.w, bar, 0, cbn, chunk, tap);
               stage_addr += (unsigned)stage_bytes;
-              if (++s == (unsigned)p.stages) { s = 0; stage_addr = smem_base; if (!first_pass) wait_parity ^= 1u; first_pass = false; }
+              if (++s == (unsigned)p.stages) { s = 0; stage_addr = smem_base; if (!first_pass) wait_parity ^= 1u; if (first_pass) TC_TRACE(5); first_pass = false; }
             }
           }
         }
+        if (item == (int)blockIdx.x) TC_TRACE(6);
         if (!ok) break;
       }
     }
@@ -653,6 +715,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         unsigned accumulate = 0;
         for (int ki = 0; ki < k_iters; ++ki) {
           if (!mbar_wait(&full_bar[s], parity, &s_abort)) { ok = false; break; }
+          if (ki == 0 && item_idx == 0) TC_TRACE(7);
           tc_fence_after();
           const unsigned a_lo = desc_lo_flags | ((stage_addr & 0x3FFFFu) >> 4);
           const unsigned b_lo = desc_lo_flags | (((stage_addr + A_STAGE_BYTES) & 0x3FFFFu) >> 4);
@@ -665,6 +728,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);
+        if (item_idx == 0) TC_TRACE(8);
       }
     }
   } else {
@@ -685,10 +749,14 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      if (valid) tc_epilogue_prefetch(p, pix, cb * NB, 0, NB);
+      if (tid == 64 && item_idx == 0) TC_TRACE_V(9, clock64() + (t & 0));
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      if (tid == 64 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
                                           cb * NB, &acc_empty[buf], lane);
+      if (tid == 64 && item_idx == 0) TC_TRACE(11);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
       if (lane == 0 && t >= 0 && sent_bits) {
         unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
@@ -711,6 +779,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
+  if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
 }
 
 
@@ -845,7 +914,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
           if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
           halo_smem_set = (int)smem;
         }
-        conv_tc_halo_kernel<<<grid, HALO_THREADS, smem, st>>>(p, map_in, map_w);
+        launch_chained(conv_tc_halo_kernel, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
         return check_launch();
       }
       // a tensor map the driver refuses (unusual strides): the per-tap kernel below takes the layer
@@ -858,7 +927,12 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   // Pipeline depth beyond 3 measured no gain (2 measured worse), while blocks of up to 128 channels are bound by the
   // latency of each work item (load -> MMA -> reservoir read-modify-write): keep them shallow so that 2-3 blocks
   // share an SM.
-  if (nb <= 128 && stages > 3) stages = 3;
+  // Narrow blocks may go deeper while three blocks still share an SM: a block that holds a single work item of few
+  // stages (3x3, one channel chunk) then has all its loads in flight at once instead of waiting for freed slots.
+  if (nb <= 128 && stages > 3) {
+    const int deep = ((220 * 1024) / 3 - 3072) / stage_bytes;
+    stages = deep > 3 ? (deep < stages ? deep : stages) : 3;
+  }
   if (stages < 2) return MIE_EUNSUPPORTED;
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
@@ -900,7 +974,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
     smem_set = (int)smem;
   }
-  conv_tc_kernel<<<grid, TC_THREADS, smem, st>>>(p, maps);
+  launch_chained(conv_tc_kernel, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
   return check_launch();
 }
 
@@ -925,6 +999,12 @@ __global__ void pack_weights_tc_kernel(const float *__restrict__ w, int cout, in
     wp[i] = __uint_as_float(u);
   }
 }
+
+#ifdef MIE_TC_TRACE
+extern "C" int mie_debug_trace(long long *host, int n) {
+  return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * (size_t)(n < 1024 * 16 ? n : 1024 * 16)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int mie_conv_pack_dims_tc(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats) {
   if (cin <= 0 || cout <= 0 || k <= 0) return MIE_EINVAL;

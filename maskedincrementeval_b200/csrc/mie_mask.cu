@@ -35,6 +35,8 @@ extern "C" const char *mie_last_cuda_error(void) { return g_cuda_err; }
 template <typename T, bool VEC4>
 __global__ void __launch_bounds__(256) mask_words_kernel(const T *__restrict__ src, int64_t ps, int C, int N,
                                                          int H, int W, float thr, uint64_t *__restrict__ bits) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
   const int ntiles = N * TH * TW;
   const int lane = threadIdx.x & 31;
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(256) mask_words_kernel(const T *__restrict__ s
 template <typename T>
 __global__ void __launch_bounds__(256) mask_words_px_kernel(const T *__restrict__ src, int64_t ps, int C, int N, int H,
                                                             int W, float thr, unsigned *__restrict__ bits32) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
   const int ntiles = N * TH * TW;
   const int lane = threadIdx.x & 31;
@@ -117,11 +121,11 @@ extern "C" int mie_mask_from_delta(const float *delta, int64_t ps, int N, int C,
   if (C <= 16) {
     int blocks = divup(ntiles, 4);
     if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-    mask_words_px_kernel<float><<<blocks, 256, 0, st>>>(delta, ps, C, N, H, W, thr, reinterpret_cast<unsigned *>(bits));
+    launch_chained(mask_words_px_kernel<float>, dim3(blocks), dim3(256), 0, st, delta, ps, C, N, H, W, thr, reinterpret_cast<unsigned *>(bits));
     return check_launch();
   }
-  if (vec) mask_words_kernel<float, true><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
-  else mask_words_kernel<float, false><<<mask_grid(ntiles), 256, 0, st>>>(delta, ps, C, N, H, W, thr, bits);
+  if (vec) launch_chained(mask_words_kernel<float, true>, dim3(mask_grid(ntiles)), dim3(256), 0, st, delta, ps, C, N, H, W, thr, bits);
+  else launch_chained(mask_words_kernel<float, false>, dim3(mask_grid(ntiles)), dim3(256), 0, st, delta, ps, C, N, H, W, thr, bits);
   return check_launch();
 }
 
@@ -131,9 +135,9 @@ extern "C" int mie_mask_from_mask(const void *mask, int elem_size, int64_t mps, 
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   cudaStream_t st = (cudaStream_t)stream;
   if (elem_size == 1)
-    mask_words_kernel<uint8_t, false><<<mask_grid(ntiles), 256, 0, st>>>((const uint8_t *)mask, mps, cm, N, H, W, -1.0f, bits);
+    launch_chained(mask_words_kernel<uint8_t, false>, dim3(mask_grid(ntiles)), dim3(256), 0, st, (const uint8_t *)mask, mps, cm, N, H, W, -1.0f, bits);
   else if (elem_size == 4)
-    mask_words_kernel<int32_t, false><<<mask_grid(ntiles), 256, 0, st>>>((const int32_t *)mask, mps, cm, N, H, W, -1.0f, bits);
+    launch_chained(mask_words_kernel<int32_t, false>, dim3(mask_grid(ntiles)), dim3(256), 0, st, (const int32_t *)mask, mps, cm, N, H, W, -1.0f, bits);
   else
     return MIE_EUNSUPPORTED;
   return check_launch();
@@ -144,13 +148,15 @@ extern "C" int mie_mask_from_mask(const void *mask, int elem_size, int64_t mps, 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) tiles_compact_kernel(const uint64_t *__restrict__ bits, int ntiles,
                                                              int32_t *__restrict__ list, int32_t *__restrict__ counts) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   int n = block_ordered_compact([&](int i) { return bits[i] != 0ull; }, ntiles, list);
   if (threadIdx.x == 0) counts[0] = n;
 }
 
 extern "C" int mie_tiles_compact(const uint64_t *bits, int ntiles, int32_t *list, int32_t *counts, void *stream) {
   if (!bits || !list || !counts || ntiles <= 0) return MIE_EINVAL;
-  tiles_compact_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(bits, ntiles, list, counts);
+  launch_chained(tiles_compact_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, bits, ntiles, list, counts);
   return check_launch();
 }
 
@@ -239,6 +245,8 @@ __global__ void __launch_bounds__(256) tiles_dilate_kernel(
     const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
     const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,
     int32_t *__restrict__ stale, int32_t *__restrict__ counts, uint8_t *__restrict__ flags) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < ntiles) flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
@@ -268,6 +276,8 @@ __global__ void __launch_bounds__(1024) tiles_dilate_small_kernel(
     const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
     const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,
     int32_t *__restrict__ stale, int32_t *__restrict__ counts) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   __shared__ uint8_t s_flags[DILATE_SMALL_MAX];
   const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
   for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
@@ -291,11 +301,11 @@ extern "C" int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win
   const int ntiles = N * divup(Hout, 8) * divup(Wout, 8);
   if (ntiles <= DILATE_SMALL_MAX) {
     const int threads = ntiles <= 256 ? 256 : (ntiles <= 512 ? 512 : 1024);
-    tiles_dilate_small_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(in_bits, N, Hin, Win, Hout, Wout, k, stride, pad,
+    launch_chained(tiles_dilate_small_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream, in_bits, N, Hin, Win, Hout, Wout, k, stride, pad,
                                                                        union_bits, out_bits, list, stale, counts);
     return check_launch();
   }
-  tiles_dilate_kernel<<<divup(ntiles, 256), 256, 0, (cudaStream_t)stream>>>(
+  launch_chained(tiles_dilate_kernel, dim3(divup(ntiles, 256)), dim3(256), 0, (cudaStream_t)stream, 
       in_bits, N, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits, list, stale, counts, flags);
   return check_launch();
 }

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
     const float *in, int64_t in_ps, const uint64_t *__restrict__ in_bits, float *__restrict__ res,
     int64_t res_ps, float *__restrict__ emitted, int64_t em_ps, float *out, int64_t out_ps, uint64_t *out_bits,
     int N, int C, int H, int W, int op, float thr) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
@@ -115,6 +117,8 @@ __global__ void __launch_bounds__(1024) mul_incr_kernel(
     const float *__restrict__ d1, int64_t d1_ps, const uint64_t *__restrict__ bits1, float *__restrict__ x1, int64_t x1_ps,
     const float *__restrict__ d2, int64_t d2_ps, const uint64_t *__restrict__ bits2, float *__restrict__ x2, int64_t x2_ps,
     float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W, float thr) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
@@ -171,6 +175,8 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_kernel(
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
     uint64_t *__restrict__ dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *__restrict__ dc_bits, int N, int C,
     int H, int W, int sum_m2, float thr) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t wg = dg_bits[t];
@@ -253,6 +259,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps,
     uint64_t *__restrict__ out_bits, int N, int C, int H, int W, int mode, int scale) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int Ho = scale * H, Wo = scale * W;
   const float rs = 1.0f / (float)scale;
   const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
@@ -362,6 +370,8 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
     uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2,
     int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int ncb = (C + cbw - 1) / cbw;
   const int n_items = ntiles * ncb;
@@ -425,6 +435,8 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
     int C, int H, int W, int mode, int scale) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int Ho = scale * H, Wo = scale * W;
   const float rs = 1.0f / (float)scale;
   const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
@@ -535,6 +547,8 @@ __global__ void __launch_bounds__(PW_THREADS) add_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
     int C, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int ncb = (C + CB - 1) / CB;
   const int n_items = ntiles * ncb;
@@ -584,6 +598,8 @@ __global__ void __launch_bounds__(PW_THREADS) add_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps,
     uint64_t *__restrict__ out_bits, int N, int C, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
@@ -617,6 +633,8 @@ __global__ void __launch_bounds__(PW_THREADS) cat2_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, int ca, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, int cb, float *__restrict__ out, int64_t out_ps,
     uint64_t *__restrict__ out_bits, int N, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int C = ca + cb;
   const int ncb = (C + CBS - 1) / CBS;
@@ -651,6 +669,8 @@ __global__ void __launch_bounds__(PW_THREADS) accumulate_kernel(float *__restric
                                                                 const float *__restrict__ d, int64_t d_ps,
                                                                 const uint64_t *__restrict__ d_bits, int N, int C, int H,
                                                                 int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t w = d_bits[t];
@@ -719,6 +739,8 @@ int launch_act_dense(float *X, const float *in, float *out, int64_t n, cudaStrea
 __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict__ x, int64_t x_ps, float *__restrict__ xp,
                                                          int64_t xp_ps, float *__restrict__ dx, int64_t dx_ps,
                                                          unsigned *__restrict__ bits32, int N, int C, int H, int W, float thr) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
   const int ntiles = N * TH * TW;
   const int lane = threadIdx.x & 31;
@@ -745,6 +767,8 @@ __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict
 __global__ void __launch_bounds__(256) events_to_voxel_kernel(const float *__restrict__ ev, int n_events, int bins, int sh,
                                                               int sw, float *__restrict__ vox, int64_t ps, int H, int W,
                                                               int pl, int pt) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_events; i += gridDim.x * blockDim.x) {
     const float4 e = *reinterpret_cast<const float4 *>(ev + 4 * (size_t)i);
     const float ts = (float)(bins - 1) * e.x;
@@ -762,6 +786,8 @@ __global__ void __launch_bounds__(256) events_to_voxel_kernel(const float *__res
 __global__ void __launch_bounds__(256) kfenced_kernel(const float *__restrict__ dx, int64_t dx_ps, float *__restrict__ carry,
                                                       int64_t c_ps, float k, float *__restrict__ q, int64_t q_ps,
                                                       unsigned *__restrict__ bits32, int N, int C, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
   const int ntiles = N * TH * TW;
   const int lane = threadIdx.x & 31;
@@ -809,6 +835,8 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict
                                                          const uint64_t *__restrict__ in_bits, int C, int half,
                                                          float *__restrict__ out, int64_t out_ps,
                                                          uint64_t *__restrict__ out_bits, int N, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t w = in_bits[t];
@@ -847,7 +875,7 @@ extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_b
   if (emitted && emitted_ps < C) return MIE_EINVAL;
   if (in == out && in_ps != out_ps) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  act_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
+  launch_chained(act_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
       in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr);
   return check_launch();
 }
@@ -860,7 +888,7 @@ extern "C" int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits
   if (d1 && (!bits1 || d1_ps < C)) return MIE_EINVAL;
   if (d2 && (!bits2 || d2_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  mul_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
+  launch_chained(mul_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
       d1, d1_ps, bits1, x1, x1_ps, d2, d2_ps, bits2, x2, x2_ps, out, out_ps, out_bits, N, C, H, W, thr);
   return check_launch();
 }
@@ -885,12 +913,12 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
     // block of 64 px x 32 ch leaves most SMs with one block of four sequential rounds; narrower items fix that
     int cbw = CB;
     while (cbw > 8 && (int64_t)ntiles * divup(C, cbw) < (int64_t)MIE_SM_COUNT * 8) cbw >>= 1;
-    convlstm_point_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, cbw)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+    launch_chained(convlstm_point_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, cbw))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
         dc_ps, dc_bits, N, C, H, W, sum_m2, cbw);
     return check_launch();
   }
-  convlstm_point_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(
+  launch_chained(convlstm_point_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
       dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
       dc_ps, dc_bits, N, C, H, W, sum_m2, thr);
   return check_launch();
@@ -906,11 +934,11 @@ extern "C" int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits
   if (b && (!b_bits || b_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(scale * H, 8) * divup(scale * W, 8);
   if (C >= 4 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
-    upsample2x_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+    launch_chained(upsample2x_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, CB))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode, scale);
     return check_launch();
   }
-  upsample2x_kernel<<<item_grid((int64_t)ntiles * divup(C, 64)), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out,
+  launch_chained(upsample2x_kernel, dim3(item_grid((int64_t)ntiles * divup(C, 64))), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, b, b_ps, b_bits, out,
                                                                                 out_ps, out_bits, N, C, H, W, mode, scale);
   return check_launch();
 }
@@ -928,11 +956,11 @@ extern "C" int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, con
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(b, b_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   if (C % 4 == 0 && a_ps % 4 == 0 && b_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
-    add_vec_kernel<<<item_grid((int64_t)ntiles * divup(C, CB)), PW_THREADS, 0, (cudaStream_t)stream>>>(
+    launch_chained(add_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, CB))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W);
     return check_launch();
   }
-  add_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps,
+  launch_chained(add_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps,
                                                                          out_bits, N, C, H, W);
   return check_launch();
 }
@@ -943,7 +971,7 @@ extern "C" int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, in
   if (N <= 0 || ca <= 0 || cb <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, ca); MIE_CHECK_FIELD(b, b_ps, cb); MIE_CHECK_FIELD(out, out_ps, ca + cb);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  cat2_kernel<<<item_grid((int64_t)ntiles * divup(ca + cb, CBS)), PW_THREADS, 0, (cudaStream_t)stream>>>(a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
+  launch_chained(cat2_kernel, dim3(item_grid((int64_t)ntiles * divup(ca + cb, CBS))), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
                                                                           out_ps, out_bits, N, H, W);
   return check_launch();
 }
@@ -953,7 +981,7 @@ extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !d_bits) return MIE_EINVAL;
   MIE_CHECK_FIELD(y, y_ps, C); MIE_CHECK_FIELD(d, d_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  accumulate_kernel<<<tile_grid(ntiles), PW_THREADS, 0, (cudaStream_t)stream>>>(y, y_ps, d, d_ps, d_bits, N, C, H, W);
+  launch_chained(accumulate_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, y, y_ps, d, d_ps, d_bits, N, C, H, W);
   return check_launch();
 }
 
@@ -964,7 +992,7 @@ extern "C" int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   int blocks = divup(ntiles, 4);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-  delta_mask_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, x_ps, x_prev, xp_ps, dx, dx_ps,
+  launch_chained(delta_mask_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, x_ps, x_prev, xp_ps, dx, dx_ps,
                                                               reinterpret_cast<unsigned *>(bits), N, C, H, W, thr);
   return check_launch();
 }
@@ -981,7 +1009,7 @@ extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bi
   if (n_events == 0) return MIE_OK;
   int blocks = divup(n_events, 256);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-  events_to_voxel_kernel<<<blocks, 256, 0, st>>>(events, n_events, num_bins, sensor_h, sensor_w, voxel, v_ps, H, W, pad_left,
+  launch_chained(events_to_voxel_kernel, dim3(blocks), dim3(256), 0, st, events, n_events, num_bins, sensor_h, sensor_w, voxel, v_ps, H, W, pad_left,
                                                  pad_top);
   return check_launch();
 }
@@ -993,6 +1021,8 @@ __global__ void __launch_bounds__(1024) maxpool_incr_kernel(
     const float *__restrict__ d, int64_t d_ps, const uint64_t *__restrict__ d_bits, const float *__restrict__ res,
     int64_t res_ps, float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W,
     int Ho, int Wo, int k, int stride, int pad) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   __shared__ unsigned s_w[2], s_any[2];
   const int THi = (H + 7) >> 3, TWi = (W + 7) >> 3;
   const int ntiles = N * ((Ho + 7) >> 3) * ((Wo + 7) >> 3);
@@ -1059,6 +1089,8 @@ __global__ void __launch_bounds__(1024) maxpool_incr_kernel(
 // index arithmetic of torch.nn.ReflectionPad2d: the edge pixel is not repeated.
 __global__ void __launch_bounds__(256) reflect_border_kernel(float *__restrict__ f, int64_t ps, int C, int H, int W, int sh,
                                                              int sw, int pl, int pt) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int64_t total = (int64_t)H * W;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int y = (int)(i / W), x = (int)(i - (int64_t)y * W);
@@ -1081,7 +1113,7 @@ extern "C" int mie_reflect_border(float *field, int64_t ps, int C, int H, int W,
     return MIE_EINVAL;
   int blocks = divup(H * W, 256);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-  reflect_border_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(field, ps, C, H, W, sensor_h, sensor_w, pad_left, pad_top);
+  launch_chained(reflect_border_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, field, ps, C, H, W, sensor_h, sensor_w, pad_left, pad_top);
   return check_launch();
 }
 
@@ -1092,7 +1124,7 @@ extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   int blocks = divup(ntiles, 4);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-  kfenced_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dx, dx_ps, carry, c_ps, k, q, q_ps,
+  launch_chained(kfenced_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, dx, dx_ps, carry, c_ps, k, q, q_ps,
                                                            reinterpret_cast<unsigned *>(bits), N, C, H, W);
   return check_launch();
 }
@@ -1103,7 +1135,7 @@ extern "C" int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in
   const int half = divup(C, 8) * 8;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(out, out_ps, 3 * half);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
-  split_tf32_kernel<<<tile_grid(ntiles), 256, 0, (cudaStream_t)stream>>>(in, in_ps, in_bits, C, half, out, out_ps, out_bits,
+  launch_chained(split_tf32_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, in, in_ps, in_bits, C, half, out, out_ps, out_bits,
                                                                         N, H, W);
   return check_launch();
 }
@@ -1118,7 +1150,7 @@ extern "C" int mie_maxpool_incr(const float *d, int64_t d_ps, const uint64_t *d_
   if (Ho <= 0 || Wo <= 0) return MIE_EINVAL;
   MIE_CHECK_FIELD(out, out_ps, C);
   const int ntiles = N * divup(Ho, 8) * divup(Wo, 8);
-  maxpool_incr_kernel<<<tile_grid(ntiles), wide_threads(ntiles, C), 0, (cudaStream_t)stream>>>(
+  launch_chained(maxpool_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
       d, d_ps, d_bits, res, res_ps, out, out_ps, out_bits, N, C, H, W, Ho, Wo, k, stride, pad);
   return check_launch();
 }
