@@ -235,9 +235,67 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
     # algorithmic bytes of one launch: per active output tile 10*10*32*4 (input + halo) + 64*32*4*3
     # (reservoir read, reservoir write, delta write) + 8 (tile word); weights once; stale tiles zeroed
     per_tile = 10 * 10 * 32 * 4 + 64 * 32 * 4 * 3 + 8
+    cold_us = 1e6 * sum(times) / len(times)
+    cold_gbs = sum(t * per_tile + 9 * 32 * 32 * 4 + s * 64 * 32 * 4 for t, s in zip(tiles, stales)) / sum(times) / 1e9
+
+    # Steady state: the same kernel launched back to back over STREAMS independent layer states (own delta, reservoir,
+    # output, tile lists; 35 MB each), as a server stepping many event streams does.  The states together exceed L2
+    # several times over, so every launch finds its data cold in DRAM while kernel code, TLB entries and the launch
+    # pipeline stay warm -- the regime the roofline fraction is meant to describe.  A single launch after an L2 flush
+    # (above) is dominated by fixed cold-start latencies and is reported beside it.
+    import ctypes as C
+    STREAMS, PASSES = 32, 4
+    states = []
+    with torch.no_grad():
+        for i in range(STREAMS):
+            li = ConvLayerIncr(32, 32, 3, 1, 1, activation="relu").to(dev).eval()
+            li.load_state_dict(sd)
+            li.forward_refresh_reservoirs(x0)
+            d = deltas[i % len(deltas)].clone()
+            li([d, None])      # allocates plan, output and reservoir buffers of this state
+            ci = li.conv2d
+            m = fl.mask_from_delta(d, 1e-3, ci._scratch.get("in.bits", (fl.n_tiles(1, H, W),), torch.int64, dev))
+            plan = ci._plan(1, H, W, dev)
+            nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), 1, H, W, H, W, 3, 1, 1, None, plan.out_bits.data_ptr(),
+                                               plan.list.data_ptr(), plan.stale.data_ptr(), plan.counts.data_ptr(),
+                                               plan.flags.data_ptr(), st.cuda_stream), "dilate")
+            a = plan.args
+            a.in_, a.in_ps, a.cin = d.data_ptr(), 32, 32
+            wbuf, cp, op, wtc = ci._weights()
+            a.wpacked_tc = wtc.data_ptr() if (wtc is not None and args_tc) else None
+            a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, 32, op
+            res = li.activation.in_res.reservoir
+            a.act, a.thr, a.res, a.res_ps = nat.ACT_RELU, 0.0, res.data_ptr(), 32
+            a.emitted, a.emitted_ps, a.addend, a.addend_ps = None, 0, None, 0
+            states.append((li, d, m, plan, a, wbuf, wtc))
+        torch.cuda.synchronize(dev)
+        counts = [s_[3].counts.cpu().tolist() for s_ in states]
+        # one pass over all states as a CUDA graph (the way the runner replays a timestep): no host time in the figure
+        graph = torch.cuda.CUDAGraph()
+        cs = torch.cuda.Stream(dev)
+        cs.wait_stream(st)
+        with torch.cuda.stream(cs):
+            for s_ in states:   # warm-up pass on the capture stream
+                nat.check(nat.lib.mie_conv_tiles(C.byref(s_[4]), cs.cuda_stream), "conv_tiles")
+            cs.synchronize()
+            with torch.cuda.graph(graph, stream=cs):
+                for s_ in states:
+                    nat.check(nat.lib.mie_conv_tiles(C.byref(s_[4]), cs.cuda_stream), "conv_tiles")
+            graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cs)
+            for _ in range(PASSES):
+                graph.replay()
+            e1.record(cs)
+            e1.synchronize()
+        st.wait_stream(cs)
+    tot_t = e0.elapsed_time(e1) * 1e-3
+    n_launch = STREAMS * PASSES
+    tiles = [c[0] for c in counts] * PASSES
+    stales = [c[1] for c in counts] * PASSES
+    times = [tot_t / n_launch] * n_launch
     byts = [t * per_tile + 9 * 32 * 32 * 4 + s * 64 * 32 * 4 for t, s in zip(tiles, stales)]
     flops = [t * 64 * 32 * 9 * 32 * 2 for t in tiles]
-    tot_t = sum(times)
     achieved = sum(byts) / tot_t / 1e9
     traffic = None  # DRAM bytes per launch of this kernel from the committed ncu capture of this same command
     tp = os.path.join(ROOT, "profiles", "conv_tc_c1_conv3x3_260x346.md")
@@ -249,7 +307,11 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
             "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": ("conv_tc_kernel" if conv.last_used_tensor_cores else "conv_tiles_kernel<3,1,4,1>") + " (conv3x3 32->32 + ReLU, 260x346)",
             "bytes_per_launch": sum(byts) / len(byts), "us_per_launch": 1e6 * tot_t / len(times),
             "active_tiles_mean": sum(tiles) / len(tiles), "tiles_total": fl.n_tiles(1, H, W),
-            "active_pixel_frac": sum(px) / len(px), "fp32_tflops": sum(flops) / tot_t / 1e12, "launches": len(times)}
+            "active_pixel_frac": sum(px) / len(px), "fp32_tflops": sum(flops) / tot_t / 1e12, "launches": len(times),
+            "timing": f"{n_launch} back-to-back launches ({PASSES} replays of a CUDA graph of {STREAMS}) over {STREAMS} independent "
+                      "layer states (1.1 GB, several times L2), one CUDA-event pair around all of them",
+            "cold": {"us_per_launch": cold_us, "achieved": cold_gbs, "frac": cold_gbs / peak_gbs,
+                     "timing": "one launch per CUDA-event pair, L2 flushed before each"}}
 
 
 def run_ours(args):

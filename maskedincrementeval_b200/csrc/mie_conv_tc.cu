@@ -325,6 +325,90 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
       return valid && flag;
 }
 
+// ---- coalesced epilogue (lossless layers: no threshold, no carry) ----------------------------------------------
+// The accumulator arrives one pixel per lane, so a lane that stores its own pixel makes every warp-wide access touch
+// 32 different 128-byte lines for 16 bytes each.  Here a group of 16 channels goes through a 2 KB staging buffer per
+// warp instead ([32 pixels][4 x float4], the float4 slot XOR-swizzled by the pixel so that both the row-wise write
+// and the transposed read are free of bank conflicts), and is then handled with four lanes per pixel: one warp
+// access covers eight neighbouring pixels x 64 contiguous bytes, for the reservoir read-modify-write, the residual
+// addend and the output alike.  A float4 whose change is exactly zero leaves the reservoir untouched (x + 0 = x and
+// f(x) - f(x) = 0, so the result equals the full update).
+// Returns a mask with bit l set when pixel l of the warp (lane l's accumulator row) emitted a non-zero value.
+template <int ACT>
+__device__ __forceinline__ unsigned tc_epilogue_rows_t(const TcParams &p, float4 *stage, const float *v, int lane, int64_t pix,
+                                                       unsigned valid_mask, int co) {
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) stage[lane * 4 + (j ^ sw)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  unsigned sent = 0;
+  const int j = lane & 3, cj = co + 4 * j;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int pl = it * 8 + (lane >> 2);
+    float4 d = stage[pl * 4 + (j ^ ((pl >> 1) & 3))];
+    const int64_t px = __shfl_sync(0xffffffffu, pix, pl);
+    const bool ok = ((valid_mask >> pl) & 1u) && cj < p.cout;
+    bool flag = false;
+    if (ok) {
+      if (p.addend) d = f4add(d, *reinterpret_cast<const float4 *>(p.addend + px * p.addend_ps + cj));
+      float4 o = d;
+      if (ACT != MIE_ACT_NONE) {
+        if (d.x != 0.0f || d.y != 0.0f || d.z != 0.0f || d.w != 0.0f) {
+          float4 *rp = reinterpret_cast<float4 *>(p.res + px * p.res_ps + cj);
+          const float4 x = *rp;
+          const float4 xn = f4add(x, d);
+          *rp = xn;
+          o = make_float4(tc_act<ACT>(p.act, xn.x) - tc_act<ACT>(p.act, x.x), tc_act<ACT>(p.act, xn.y) - tc_act<ACT>(p.act, x.y),
+                          tc_act<ACT>(p.act, xn.z) - tc_act<ACT>(p.act, x.z), tc_act<ACT>(p.act, xn.w) - tc_act<ACT>(p.act, x.w));
+        }
+      }
+      flag = fabsf(o.x) > 0.0f || fabsf(o.y) > 0.0f || fabsf(o.z) > 0.0f || fabsf(o.w) > 0.0f;
+      *reinterpret_cast<float4 *>(p.out + px * p.out_ps + cj) = o;
+    }
+    unsigned bal = __ballot_sync(0xffffffffu, flag);
+    bal |= bal >> 1;
+    bal |= bal >> 2;   // bit 4k: any of the four lanes of pixel it * 8 + k
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sent |= ((bal >> (4 * k)) & 1u) << (it * 8 + k);
+  }
+  __syncwarp();   // the next group overwrites the buffer
+  return sent;
+}
+
+// One accumulator row per lane, columns [c_lo, c_hi) of the block's NB; same contract as tc_epilogue_pixel.
+__device__ __forceinline__ bool tc_epilogue_pixel_coalesced(const TcParams &p, int NB, unsigned taddr, bool valid, int64_t pix,
+                                                            int co0, unsigned long long *acc_empty_bar, int lane, float4 *stage,
+                                                            unsigned acc2, int c_lo, int c_hi) {
+  const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
+  c_hi = min(c_hi, NB);
+  unsigned sent = 0;
+  bool released = false;
+  for (int c = c_lo; c < c_hi; c += 16) {
+    float v[16];
+    tmem_ld16_sum(taddr + c, acc2, v);
+    if (c + 16 >= c_hi) {   // last read of this warp: hand the accumulator back before the global traffic
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar);
+      released = true;
+    }
+    if (co0 + c >= p.cout) continue;
+    switch (p.act) {
+      case MIE_ACT_RELU: sent |= tc_epilogue_rows_t<MIE_ACT_RELU>(p, stage, v, lane, pix, valid_mask, co0 + c); break;
+      case MIE_ACT_SIGMOID:
+      case MIE_ACT_TANH: sent |= tc_epilogue_rows_t<MIE_ACT_SIGMOID>(p, stage, v, lane, pix, valid_mask, co0 + c); break;
+      default: sent |= tc_epilogue_rows_t<MIE_ACT_NONE>(p, stage, v, lane, pix, valid_mask, co0 + c); break;
+    }
+  }
+  if (!released) {
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(acc_empty_bar);
+  }
+  return valid && ((sent >> lane) & 1u);
+}
+
 // Asks for the lines the epilogue of one pixel will read (reservoir, residual addend, carry) while the MMAs of the item
 // are still running: the accumulator arrives to loads that hit the cache instead of starting a DRAM round trip each.
 __device__ __forceinline__ void tc_epilogue_prefetch(const TcParams &p, int64_t pix, int co0, int c_lo, int c_hi) {
@@ -395,6 +479,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) { TC_TRACE(0); TC_TRACE_G(14); }
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_in)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_w)) : "memory");
@@ -424,11 +509,14 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const unsigned tmem_base = s_tmem_base;
 
   // everything above touched no global memory: it may overlap the tail of the previous kernel in the stream
+  if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
   const int n_active = min(p.counts[0], p.max_tiles);
+  if (tid == 0) TC_TRACE(2);
 
   tc_zero_stale(p, ntiles_total, THo, TWo, HALO_THREADS);
+  if (tid == 0) TC_TRACE(3);
 
   const int n_pairs = (n_active + 1) >> 1;
   const int n_cblk = p.cout_pad / NB;
@@ -451,6 +539,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
       const unsigned tx_bytes = (t1 >= 0 ? 2u : 1u) * (unsigned)Hh * row_bytes;
       bool ok = true;
+      if (lane == 0 && item == (int)blockIdx.x) TC_TRACE_V(4, clock64() + (t0 & 0));
       for (int chunk = 0; chunk < n_chunks; ++chunk, ++uses) {
         const unsigned buf = uses & 1u;
         if (lane == 0) {
@@ -461,6 +550,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
         if (!ok) break;
         if (hy < Hh && t >= 0)
           tma_load_5d_raw(a_base + buf * a_buf_bytes + (unsigned)lane * row_bytes, &map_in, smem_u32(&a_full[buf]), 0, x0, chunk * 8, y0 + hy, n0);
+        if (lane == 0 && uses == 0) TC_TRACE(5);
       }
       if (!ok || s_abort) break;
     }
@@ -477,6 +567,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
             const unsigned bar = smem_u32(&b_full[s]);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(st_bytes) : "memory");
             tma_load_4d_raw(stage_addr, &map_w, bar, 0, cbn, chunk, tap);
+            if (first_pass && s == 0) TC_TRACE(6);
             stage_addr += st_bytes;
             if (++s == (unsigned)p.stages) { s = 0; stage_addr = b_base; if (!first_pass) wait_parity ^= 1u; first_pass = false; }
           }
@@ -508,12 +599,14 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
         for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++uses, g += spc) {
           const unsigned abuf = uses & 1u;
           if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort)) { ok = false; break; }
+          if (me == 0 && uses == 0) TC_TRACE(7);
           const unsigned halo = a_base + abuf * a_buf_bytes;
           const unsigned nks = (unsigned)min(4, (p.cin - chunk * 32 + 7) >> 3);   // K-slices holding real channels
           bool issued = false;
           for (unsigned st = (NI == 2u) ? ((me - g) & 1u) : 0u; st < spc; st += NI) {
             const unsigned gs = g + st, lap = gs / nst, slot = gs - lap * nst;
             if (!mbar_wait(&b_full[slot], lap & 1u, &s_abort)) { ok = false; break; }
+            if (me == 0 && gs == 0) TC_TRACE(8);
             tc_fence_after();
             const unsigned t0 = st * (unsigned)p.tps;
             unsigned ky = t0 / (unsigned)p.k, kx = t0 - ky * (unsigned)p.k;
@@ -537,6 +630,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);
+        if (me == 0 && item_idx == 0) TC_TRACE(9);
       }
     }
   } else {
@@ -563,9 +657,13 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
       if (valid) tc_epilogue_prefetch(p, pix, cb * NB, c_lo, c_hi);
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      if (tid == 128 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
+      // (the coalesced epilogue of the per-tap kernel measured slower here: with eight epilogue warps and the MMAs of
+      // the next item running, the staging round trip costs more than the scattered accesses)
       const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
-                                              cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u, c_lo, c_hi);
+                                          cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u, c_lo, c_hi);
+      if (tid == 128 && item_idx == 0) TC_TRACE(11);
       // ballot bytes: [tile 0 row 2q][tile 1 row 2q][tile 0 row 2q+1][tile 1 row 2q+1]
       const unsigned bal = __ballot_sync(0xffffffffu, sent);
       if ((lane == 0 || lane == 8) && t >= 0) {
@@ -591,6 +689,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
+  if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 3)
@@ -601,6 +700,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int NB = p.nb;
   const int stage_bytes = A_STAGE_BYTES + NB * 128;
   __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+  __shared__ float4 s_epi[4][128];   // staging buffers of the coalesced epilogue, one per epilogue warp
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
@@ -736,6 +836,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     // (a second set of four epilogue warps, as in the halo kernel, measured slower here: this kernel's small
     // layers gain more from a third resident block per SM than from a shorter epilogue)
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
+    // narrow blocks (few MMAs per item: the epilogue is exposed) take the coalesced epilogue; wide blocks, whose
+    // epilogue hides behind the next item's MMAs, measured faster on the direct one
+    const bool coalesced = NB <= 32 && p.thr == 0.0f && !p.emitted && (p.cout & 3) == 0;
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
     unsigned item_idx = 0;
@@ -754,8 +857,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
       if (tid == 64 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
-      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
-                                          cb * NB, &acc_empty[buf], lane);
+      const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
+      const bool sent = coalesced ? tc_epilogue_pixel_coalesced(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, s_epi[warp - 2], 0u, 0, NB)
+                                  : tc_epilogue_pixel(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane);
       if (tid == 64 && item_idx == 0) TC_TRACE(11);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
       if (lane == 0 && t >= 0 && sent_bits) {
@@ -930,13 +1034,13 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   // Narrow blocks may go deeper while three blocks still share an SM: a block that holds a single work item of few
   // stages (3x3, one channel chunk) then has all its loads in flight at once instead of waiting for freed slots.
   if (nb <= 128 && stages > 3) {
-    const int deep = ((220 * 1024) / 3 - 3072) / stage_bytes;
+    const int deep = ((220 * 1024) / 3 - 3072 - 8192) / stage_bytes;   // 8 KB: the epilogue's staging buffers
     stages = deep > 3 ? (deep < stages ? deep : stages) : 3;
   }
   if (stages < 2) return MIE_EUNSUPPORTED;
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
-  int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
+  int blocks_per_sm = (int)((220 * 1024) / (smem + 2048 + 8192));
   { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
   if (blocks_per_sm > 3) blocks_per_sm = 3;   // registers: 192 threads x ~100
   if (blocks_per_sm < 1) blocks_per_sm = 1;
