@@ -692,6 +692,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
 }
 
+// COALESCED: the epilogue variant (and its 8 KB of staging buffers) is a compile-time choice, so that the wide-block
+// instantiation carries neither the code nor the shared memory of the other.
+template <bool COALESCED>
 __global__ void __launch_bounds__(TC_THREADS, 3)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -700,7 +703,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int NB = p.nb;
   const int stage_bytes = A_STAGE_BYTES + NB * 128;
   __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
-  __shared__ float4 s_epi[4][128];   // staging buffers of the coalesced epilogue, one per epilogue warp
+  __shared__ float4 s_epi[COALESCED ? 4 : 1][COALESCED ? 128 : 1];   // staging buffers of the coalesced epilogue, one per epilogue warp
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
@@ -836,9 +839,6 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     // (a second set of four epilogue warps, as in the halo kernel, measured slower here: this kernel's small
     // layers gain more from a third resident block per SM than from a shorter epilogue)
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
-    // narrow blocks (few MMAs per item: the epilogue is exposed) take the coalesced epilogue; wide blocks, whose
-    // epilogue hides behind the next item's MMAs, measured faster on the direct one
-    const bool coalesced = NB <= 32 && p.thr == 0.0f && !p.emitted && (p.cout & 3) == 0;
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
     unsigned item_idx = 0;
@@ -858,7 +858,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       if (tid == 64 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
-      const bool sent = coalesced ? tc_epilogue_pixel_coalesced(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, s_epi[warp - 2], 0u, 0, NB)
+      const bool sent = COALESCED ? tc_epilogue_pixel_coalesced(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, s_epi[COALESCED ? warp - 2 : 0], 0u, 0, NB)
                                   : tc_epilogue_pixel(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane);
       if (tid == 64 && item_idx == 0) TC_TRACE(11);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
@@ -1026,6 +1026,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   }
 
   const int stage_bytes = A_STAGE_BYTES + nb * 128;
+  // Narrow blocks (few MMAs per item: the epilogue is exposed) take the coalesced epilogue; wide blocks, whose epilogue
+  // hides behind the next item's MMAs, measured faster on the direct one.
+  const bool coalesced = nb <= 32 && a->thr == 0.0f && !a->emitted && (a->cout & 3) == 0;
+  const int epi_bytes = coalesced ? 8192 : 0;   // static staging buffers of the coalesced epilogue
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 8) stages = 8;
   // Pipeline depth beyond 3 measured no gain (2 measured worse), while blocks of up to 128 channels are bound by the
@@ -1034,13 +1038,13 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   // Narrow blocks may go deeper while three blocks still share an SM: a block that holds a single work item of few
   // stages (3x3, one channel chunk) then has all its loads in flight at once instead of waiting for freed slots.
   if (nb <= 128 && stages > 3) {
-    const int deep = ((220 * 1024) / 3 - 3072 - 8192) / stage_bytes;   // 8 KB: the epilogue's staging buffers
+    const int deep = ((220 * 1024) / 3 - 3072 - epi_bytes) / stage_bytes;
     stages = deep > 3 ? (deep < stages ? deep : stages) : 3;
   }
   if (stages < 2) return MIE_EUNSUPPORTED;
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
-  int blocks_per_sm = (int)((220 * 1024) / (smem + 2048 + 8192));
+  int blocks_per_sm = (int)((220 * 1024) / (smem + 2048 + epi_bytes));
   { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
   if (blocks_per_sm > 3) blocks_per_sm = 3;   // registers: 192 threads x ~100
   if (blocks_per_sm < 1) blocks_per_sm = 1;
@@ -1072,13 +1076,15 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
   int grid = max_items < cap ? (int)max_items : (int)cap;
   if (grid < 1) grid = 1;
-  static int smem_set = 0;
-  if ((int)smem > smem_set) {
-    cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static int smem_set[2] = {0, 0};
+  if ((int)smem > smem_set[coalesced]) {
+    cudaError_t e = coalesced ? cudaFuncSetAttribute(conv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                              : cudaFuncSetAttribute(conv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
-    smem_set = (int)smem;
+    smem_set[coalesced] = (int)smem;
   }
-  launch_chained(conv_tc_kernel, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  if (coalesced) launch_chained(conv_tc_kernel<true>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  else launch_chained(conv_tc_kernel<false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
   return check_launch();
 }
 
