@@ -494,6 +494,9 @@ def run_ours(args):
             peak, kind = load_peaks()
             line["roofline"] = roofline_conv3x3(dev, peak, kind)
             line["metric"] = f"incremental timesteps/sec/GPU, {args.net} {H}x{W}; conv3x3 HBM GB/s"
+        if world > 1:   # rank 0 alone, after the timed region: the kernel figure does not depend on N
+            peak, kind = load_peaks()
+            line["roofline"] = roofline_conv3x3(dev, peak, kind, repeats=1)
         if world == 1 and not flow:
             peak, kind = load_peaks()
             line["roofline"] = roofline_conv3x3(dev, peak, kind)

@@ -695,7 +695,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
 // COALESCED: the epilogue variant (and its 8 KB of staging buffers) is a compile-time choice, so that the wide-block
 // instantiation carries neither the code nor the shared memory of the other.
 template <bool COALESCED>
-__global__ void __launch_bounds__(TC_THREADS, 3)
+__global__ void __launch_bounds__(TC_THREADS, COALESCED ? 3 : 2)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment of every stage is what the 128-byte swizzle of TMA and of the MMA descriptors assume
@@ -1046,7 +1046,8 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   int blocks_per_sm = (int)((220 * 1024) / (smem + 2048 + epi_bytes));
   { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
-  if (blocks_per_sm > 3) blocks_per_sm = 3;   // registers: 192 threads x ~100
+  // registers: the coalesced instantiation (79) fits three blocks of 192 threads, the direct one (142) two
+  if (blocks_per_sm > (coalesced ? 3 : 2)) blocks_per_sm = coalesced ? 3 : 2;
   if (blocks_per_sm < 1) blocks_per_sm = 1;
 
   TcMaps maps;
