@@ -185,6 +185,12 @@ extern "C" int mie_mask_expand(const uint64_t *bits, int N, int H, int W, uint8_
 // Bit j of the result is set when input row (base + j) feeds one of the valid output rows
 // [o0, o0 + cnt) of a tile: rows o*stride - pad + t for t in [0, k).
 __device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride, int pad, int base, int limit) {
+  if (stride <= k) {
+    // consecutive outputs read adjacent or overlapping input ranges: their union is one interval [lo, hi)
+    const int lo = max(o0 * stride - pad, 0), hi = min((o0 + cnt - 1) * stride - pad + k, limit);
+    if (hi <= lo) return 0u;
+    return ((1u << (hi - base)) - 1u) & ~((1u << (lo - base)) - 1u);   // 0 <= lo - base < hi - base <= 21
+  }
   unsigned set = 0;
   for (int o = 0; o < cnt; ++o)
     for (int t = 0; t < k; ++t) {
@@ -213,24 +219,38 @@ __device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *__restrict
   if (rset && cset) {
     const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
     const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
-    for (int ity = ylo >> 3; ity <= (yhi >> 3) && !active; ++ity) {
-      unsigned selr = 0;
-      for (int py = 0; py < 8; ++py) {
-        const int j = ity * 8 + py - ybase;
-        if (j >= 0 && j < 32 && ((rset >> j) & 1u)) selr |= 1u << py;
+    // The receptive field spans at most 7 * stride + k <= 21 rows / columns = at most 4 x 4 input tiles.  All their
+    // words are loaded before any is tested: with an early exit each load waited for the test of the one before --
+    // a chain of up to nine round trips to L2 or DRAM per thread, which was this kernel's whole run time.
+    const int ity0 = ylo >> 3, ity1 = yhi >> 3, itx0 = xlo >> 3, itx1 = xhi >> 3;
+    uint64_t w[4][4];
+#pragma unroll
+    for (int dy = 0; dy < 4; ++dy)
+#pragma unroll
+      for (int dx = 0; dx < 4; ++dx) {
+        const int ity = ity0 + dy, itx = itx0 + dx;
+        w[dy][dx] = (ity <= ity1 && itx <= itx1) ? in_bits[((int64_t)n * THi + ity) * TWi + itx] : 0ull;
       }
-      for (int itx = xlo >> 3; itx <= (xhi >> 3); ++itx) {
-        unsigned selc = 0;
-        for (int px = 0; px < 8; ++px) {
-          const int j = itx * 8 + px - xbase;
-          if (j >= 0 && j < 32 && ((cset >> j) & 1u)) selc |= 1u << px;
-        }
-        uint64_t m = 0;
-        for (int py = 0; py < 8; ++py)
-          if ((selr >> py) & 1u) m |= (uint64_t)selc << (py * 8);
-        if (in_bits[((int64_t)n * THi + ity) * TWi + itx] & m) { active = true; break; }
-      }
+    unsigned selr[4], selc[4];
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      // bits of rset / cset that fall into input tile ity0 + d / itx0 + d, as an 8-bit row / column selection
+      const int jr = (ity0 + d) * 8 - ybase, jc = (itx0 + d) * 8 - xbase;   // in (-8, 32)
+      selr[d] = (jr >= 0 ? (jr < 32 ? rset >> jr : 0u) : rset << -jr) & 0xFFu;
+      selc[d] = (jc >= 0 ? (jc < 32 ? cset >> jc : 0u) : cset << -jc) & 0xFFu;
     }
+    uint64_t hit = 0ull;
+#pragma unroll
+    for (int dy = 0; dy < 4; ++dy) {
+      // row selection spread to bytes: byte py = 0xFF when row py is selected
+      uint64_t rowsel = 0ull;
+#pragma unroll
+      for (int py = 0; py < 8; ++py)
+        if ((selr[dy] >> py) & 1u) rowsel |= 0xFFull << (py * 8);
+#pragma unroll
+      for (int dx = 0; dx < 4; ++dx) hit |= w[dy][dx] & rowsel & (0x0101010101010101ull * (uint64_t)selc[dx]);
+    }
+    active = hit != 0ull;
   }
   if (uni != 0ull) active = true;
   uint8_t f = active ? 1 : 0;
