@@ -427,9 +427,9 @@ struct TcMaps {
   CUtensorMap w;
 };
 
-// Zeroes the stale tiles of the output field (all threads of the block take part).
-__device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_total, int THo, int TWo, int nthreads) {
-  const int tid = threadIdx.x;
+// Zeroes the stale tiles of the output field.  Run by the epilogue warps (`tid` = index within them, `nthreads` = how
+// many they are) before their first accumulator arrives: the producer and the MMA issuer do not wait for it.
+__device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_total, int THo, int TWo, int tid, int nthreads) {
   const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
     const int t = p.stale[s];
@@ -512,14 +512,20 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
+  // the halo producer asks for the tile-list entries of its first item together with the device-side count
+  const int n_cblk = p.cout_pad / NB;
+  int pre0 = -1, pre1 = -1;
+  if (warp == 0) {
+    const int e = 2 * ((int)blockIdx.x / n_cblk);
+    if (e < p.max_tiles) pre0 = p.list[e];
+    if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+  }
   const int n_active = min(p.counts[0], p.max_tiles);
   if (tid == 0) TC_TRACE(2);
 
-  tc_zero_stale(p, ntiles_total, THo, TWo, HALO_THREADS);
   if (tid == 0) TC_TRACE(3);
 
   const int n_pairs = (n_active + 1) >> 1;
-  const int n_cblk = p.cout_pad / NB;
   const int n_items = n_pairs * n_cblk;
   const int n_chunks = p.cin_pad >> 5;
   const int taps = p.k * p.k;
@@ -532,8 +538,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     unsigned uses = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
       const int pair = item / n_cblk;
-      int t0 = p.list[2 * pair];
-      int t1 = (2 * pair + 1 < n_active) ? p.list[2 * pair + 1] : -1;
+      const bool first = item == (int)blockIdx.x;
+      int t0 = first ? pre0 : p.list[2 * pair];
+      int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
       if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { if (lane == 0) p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
       const int t = slot ? t1 : t0;
       const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
@@ -644,6 +651,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
     const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
+    tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
     unsigned item_idx = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
@@ -740,14 +748,21 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
+  // The producer asks for the tile-list entries of its first item together with the device-side count, before the count
+  // is known: one round trip to memory instead of two on the path count -> list -> first operand load.
+  const int n_cblk = p.cout_pad / NB;
+  int pre0 = -1, pre1 = -1;
+  if (warp == 0) {
+    const int e = 2 * ((int)blockIdx.x / n_cblk);
+    if (e < p.max_tiles) pre0 = p.list[e];
+    if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+  }
   const int n_active = min(p.counts[0], p.max_tiles);
   if (tid == 0) TC_TRACE(2);
 
-  tc_zero_stale(p, ntiles_total, THo, TWo, TC_THREADS);
   if (tid == 0) TC_TRACE(3);
 
   const int n_pairs = (n_active + 1) >> 1;
-  const int n_cblk = p.cout_pad / NB;
   const int n_items = n_pairs * n_cblk;
   const int n_chunks = p.cin_pad >> 5;
   const int taps = p.k * p.k;
@@ -764,8 +779,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned b_bytes = (unsigned)NB * 128u;
       for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
         const int pair = item / n_cblk, cb = item - pair * n_cblk;
-        int t0 = p.list[2 * pair];
-        int t1 = (2 * pair + 1 < n_active) ? p.list[2 * pair + 1] : -1;
+        const bool first = item == (int)blockIdx.x;
+        int t0 = first ? pre0 : p.list[2 * pair];
+        int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
         if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
         const int x0 = (t0 % TWo) * 8, y0 = ((t0 / TWo) % THo) * 8, n0 = t0 / (TWo * THo);
         const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
@@ -841,6 +857,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
+    tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
     unsigned item_idx = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
