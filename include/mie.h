@@ -37,6 +37,29 @@ enum {
   MIE_ETOOBIG = -5      /* size beyond a fixed capacity */
 };
 
+/* Bits of the device-side error word counts[3] of a convolution's work lists (see mie_tiles_dilate).  The kernels
+ * never trap: a bad list entry is skipped, an expired wait makes the block leave its loops, free what it holds and
+ * return; the word tells the host afterwards.  The reference's answer to any CUDA error is exit(-1)
+ * (include/checks.h:12-21). */
+enum {
+  MIE_ERR_BAD_TILE = 1,     /* a tile-list entry was outside the field: skipped, its output left untouched */
+  MIE_ERR_WAIT_EXPIRED = 2  /* a bounded barrier wait ran out inside a tensor-core kernel: that launch's output is invalid */
+};
+
+/* Process-wide options (host).  No counterpart in the reference. */
+enum {
+  /* 1: thresholded convolutions (thr > 0 or a carry buffer) may run on the tensor cores when their channel count
+   *    is 32, 64, 128 or 256; 0 (default): they run on the FP32 kernel. */
+  MIE_OPT_TC_THRESHOLDED = 1,
+  /* iterations after which a barrier wait of the tensor-core kernels gives up; 0 restores the default (2^20) */
+  MIE_OPT_TC_SPIN_LIMIT = 2,
+  /* self-test of the expiry path: 1 makes the tensor-core kernels' producers issue no loads, so that the first wait
+   * of every block with work runs out and MIE_ERR_WAIT_EXPIRED is raised; the launch writes no output */
+  MIE_OPT_TC_WITHHOLD_LOADS = 3
+};
+int mie_set_option(int option, int value);
+int mie_get_option(int option, int *value /* host */);
+
 enum { MIE_ACT_NONE = 0, MIE_ACT_RELU = 1, MIE_ACT_SIGMOID = 2, MIE_ACT_TANH = 3 };
 enum { MIE_UP_BILINEAR = 0, MIE_UP_NEAREST = 1 };
 
@@ -75,7 +98,8 @@ int mie_mask_expand(const uint64_t *bits, int N, int H, int W, uint8_t *bytes, v
  *   stale[0..counts[1])  tiles whose word in `out_bits` was non-zero (they hold data from the
  *                        previous step) but are not active now: the consumer must zero them
  *   out_bits             every word cleared to 0 (the convolution then sets the active ones)
- * counts is int32[4]: {n_active, n_stale, ticket (must be 0 on entry, is 0 on exit), error flag}.
+ * counts is int32[4]: {n_active, n_stale, ticket (must be 0 on entry, is 0 on exit), error word (MIE_ERR_* bits,
+ * only ever OR-ed into by the convolution kernels; the host clears it)}.
  * flags is scratch of N*THo*TWo bytes. */
 int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout, int k,
                      int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
@@ -89,7 +113,8 @@ int mie_tiles_dilate(const uint64_t *in_bits, int N, int Hin, int Win, int Hout,
  * late in a recording, and is not permitted while a stream is being captured) has nowhere to take them from.
  * This variant keeps that scratch inside the library, in a fixed array of MIE_STATIC_MAX_TILES + 256 bytes of
  * device memory that every GPU loading the library holds until the process ends, and calls no allocating
- * routine.  Inputs and outputs are still the caller's; counts is int32[2] = {n_active, n_stale}.
+ * routine.  Inputs and outputs are still the caller's; counts is at least int32[2] =
+ * {n_active, n_stale}: only these two words are written, so the int32[4] block of mie_tiles_dilate can be passed as is.
  *  - more than MIE_STATIC_MAX_TILES output tiles -> MIE_ETOOBIG;
  *  - the array is shared by all calls on a device and keeps the last call's contents (the word that must be
  *    zero is cleared on `stream` before the launch): calls that overlap on the GPU race -- serialise them;

@@ -17,6 +17,8 @@ LIB_PATH = os.path.join(_HERE, "libmie.so")
 OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ETOOBIG = 0, -1, -2, -3, -4, -5
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 UP_BILINEAR, UP_NEAREST = 0, 1
+ERR_BAD_TILE, ERR_WAIT_EXPIRED = 1, 2
+OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS = 1, 2, 3
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -42,6 +44,8 @@ SIGNATURES = {
     "mie_version": (_i, []),
     "mie_status_string": (C.c_char_p, [_i]),
     "mie_last_cuda_error": (C.c_char_p, []),
+    "mie_set_option": (_i, [_i, _i]),
+    "mie_get_option": (_i, [_i, C.POINTER(_i)]),
     "mie_mask_from_delta": (_i, [_vp, _i64, _i, _i, _i, _i, _f, _vp, _vp]),
     "mie_mask_from_mask": (_i, [_vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "mie_tiles_compact": (_i, [_vp, _i, _vp, _vp, _vp]),
@@ -122,6 +126,28 @@ def check(status: int, what: str = "", launches: int = 1) -> None:
     if status == EUNSUPPORTED:
         raise NotImplementedError(f"libmie {what}: {msg}")
     raise MieError(f"libmie {what}: {msg}")
+
+
+def set_option(option: int, value: int) -> None:
+    check(lib.mie_set_option(option, int(value)), "set_option", 0)
+
+
+def get_option(option: int) -> int:
+    v = C.c_int()
+    check(lib.mie_get_option(option, C.byref(v)), "get_option", 0)
+    return v.value
+
+
+def describe_error_word(word: int) -> str:
+    """Text for the MIE_ERR_* bits a convolution kernel left in counts[3]."""
+    parts = []
+    if word & ERR_BAD_TILE:
+        parts.append("a tile-list entry was outside the field (skipped)")
+    if word & ERR_WAIT_EXPIRED:
+        parts.append("a bounded barrier wait ran out in a tensor-core kernel (that launch's output is invalid)")
+    if word & ~(ERR_BAD_TILE | ERR_WAIT_EXPIRED):
+        parts.append(f"unknown bits {word:#x}")
+    return "; ".join(parts)
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
     const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
     for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
       const int t = p.stale[s];
-      if (t < 0 || t >= ntiles_total) { if (tid == 0) p.counts[3] = 1; continue; }
+      if (t < 0 || t >= ntiles_total) { if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
       const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
       for (int i = tid; i < 64 * p.cout; i += NT) {
         const int px = i / p.cout, c = i - px * p.cout;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
     if (tid < WT) {
       const int li = grp * WT + tid;
       int t = (li < n_active) ? p.list[li] : -1;
-      if (t >= ntiles_total) { p.counts[3] = 1; t = -1; }
+      if (li < n_active && (t < 0 || t >= ntiles_total)) { atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); t = -1; }
       s_tile[tid] = t;
       s_bits[tid] = 0ull;
     }
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
   const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x * 4 + grp; s < n_stale; s += gridDim.x * 4) {
     const int t = p.stale[s];
-    if (t < 0 || t >= ntiles_total) continue;
+    if (t < 0 || t >= ntiles_total) { if (px == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
     const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
     const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
     if (oy < p.hout && ox < p.wout)
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
   const int n_active = min(p.counts[0], p.max_tiles);
   for (int li = blockIdx.x * 4 + grp; li < n_active; li += gridDim.x * 4) {
     const int t = p.list[li];
-    if (t < 0 || t >= ntiles_total) { if (px == 0) p.counts[3] = 1; continue; }
+    if (t < 0 || t >= ntiles_total) { if (px == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
     const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
     const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
     const bool valid = oy < p.hout && ox < p.wout;

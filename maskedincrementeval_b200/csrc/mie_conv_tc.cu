@@ -45,6 +45,8 @@ struct TcParams {
   int stages;    // pipeline depth
   int tps;       // halo kernel: filter taps per pipeline stage (divides k*k)
   int issuers;   // halo kernel: 1 or 2 MMA-issuing warps (2: stages alternate, one accumulator each)
+  unsigned spin_limit;   // iterations after which a barrier wait gives up (MIE_OPT_TC_SPIN_LIMIT)
+  int withhold_loads;    // self-test: the producers issue nothing, so the first wait runs out (MIE_OPT_TC_WITHHOLD_LOADS)
 };
 
 namespace {
@@ -65,7 +67,7 @@ __device__ __forceinline__ long long trace_gtime() { long long t; asm volatile("
 
 constexpr int TC_THREADS = 192;
 constexpr int A_STAGE_BYTES = 128 * 128;  // 128 pixels x 32 channels x 4 B
-constexpr unsigned SPIN_LIMIT = 1u << 20;
+constexpr unsigned SPIN_LIMIT = 1u << 20;   // default of TcParams::spin_limit
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -76,9 +78,9 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait on a phase parity.  Returns false when the limit ran out or another role gave up.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, volatile int *abort_flag, unsigned limit) {
   const unsigned addr = smem_u32(bar);
-  for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+  for (unsigned it = 0; it < limit; ++it) {
     unsigned done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -433,7 +435,7 @@ __device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_tota
   const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
     const int t = p.stale[s];
-    if (t < 0 || t >= ntiles_total) { if (tid == 0) p.counts[3] = 1; continue; }
+    if (t < 0 || t >= ntiles_total) { if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
     const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
     for (int i = tid; i < 64 * p.cout; i += nthreads) {
       const int px = i / p.cout, c = i - px * p.cout;
@@ -536,12 +538,17 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     // =========================== halo producer: lane = 2 * halo row + tile ===========================
     const int hy = lane >> 1, slot = lane & 1;
     unsigned uses = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items && !p.withhold_loads; item += gridDim.x) {
       const int pair = item / n_cblk;
       const bool first = item == (int)blockIdx.x;
       int t0 = first ? pre0 : p.list[2 * pair];
       int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
-      if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { if (lane == 0) p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
+      // An entry outside the field is reported and skipped: the epilogue ignores it too, its half of the operand is
+      // filled from tile 0 (any in-range load) or left out, and the partner tile of the pair is computed as usual.
+      const bool bad0 = t0 < 0 || t0 >= ntiles_total, bad1 = (2 * pair + 1 < n_active) && (t1 < 0 || t1 >= ntiles_total);
+      if ((bad0 || bad1) && lane == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE);
+      if (bad0) t0 = 0;
+      if (bad1) t1 = -1;
       const int t = slot ? t1 : t0;
       const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
       const unsigned tx_bytes = (t1 >= 0 ? 2u : 1u) * (unsigned)Hh * row_bytes;
@@ -550,7 +557,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       for (int chunk = 0; chunk < n_chunks; ++chunk, ++uses) {
         const unsigned buf = uses & 1u;
         if (lane == 0) {
-          if (uses >= 2) ok = mbar_wait(&a_empty[buf], ((uses >> 1) - 1) & 1u, &s_abort);
+          if (uses >= 2) ok = mbar_wait(&a_empty[buf], ((uses >> 1) - 1) & 1u, &s_abort, p.spin_limit);
           if (ok) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&a_full[buf])), "r"(tx_bytes) : "memory");
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -566,11 +573,11 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     if (lane == 0) {
       unsigned s = 0, wait_parity = 0, stage_addr = b_base;
       bool first_pass = true, ok = true;
-      for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok && !s_abort && !p.withhold_loads; item += gridDim.x) {
         const int cbn = (item % n_cblk) * NB;
         for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
           for (int tap = 0; tap < taps; tap += p.tps) {
-            if (!first_pass && !mbar_wait(&b_empty[s], wait_parity, &s_abort)) { ok = false; break; }
+            if (!first_pass && !mbar_wait(&b_empty[s], wait_parity, &s_abort, p.spin_limit)) { ok = false; break; }
             const unsigned bar = smem_u32(&b_full[s]);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(st_bytes) : "memory");
             tma_load_4d_raw(stage_addr, &map_w, bar, 0, cbn, chunk, tap);
@@ -599,20 +606,20 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x, ++item_idx) {
         const unsigned buf = item_idx & 1u;
-        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort)) break;
+        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
         tc_fence_after();
         const unsigned tmem_d = tmem_base + (buf * NI + me) * acc_cols;
         unsigned accumulate = 0;
         for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++uses, g += spc) {
           const unsigned abuf = uses & 1u;
-          if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort)) { ok = false; break; }
+          if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort, p.spin_limit)) { ok = false; break; }
           if (me == 0 && uses == 0) TC_TRACE(7);
           const unsigned halo = a_base + abuf * a_buf_bytes;
           const unsigned nks = (unsigned)min(4, (p.cin - chunk * 32 + 7) >> 3);   // K-slices holding real channels
           bool issued = false;
           for (unsigned st = (NI == 2u) ? ((me - g) & 1u) : 0u; st < spc; st += NI) {
             const unsigned gs = g + st, lap = gs / nst, slot = gs - lap * nst;
-            if (!mbar_wait(&b_full[slot], lap & 1u, &s_abort)) { ok = false; break; }
+            if (!mbar_wait(&b_full[slot], lap & 1u, &s_abort, p.spin_limit)) { ok = false; break; }
             if (me == 0 && gs == 0) TC_TRACE(8);
             tc_fence_after();
             const unsigned t0 = st * (unsigned)p.tps;
@@ -657,14 +664,14 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
       int t = (li < n_active) ? p.list[li] : -1;
-      if (t >= ntiles_total) t = -1;
+      if (t < 0 || t >= ntiles_total) t = -1;
       const unsigned buf = item_idx & 1u;
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
       if (valid) tc_epilogue_prefetch(p, pix, cb * NB, c_lo, c_hi);
-      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
       if (tid == 128 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       // (the coalesced epilogue of the per-tap kernel measured slower here: with eight epilogue warps and the MMAs of
@@ -689,7 +696,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   tc_fence_before();
   __syncthreads();
   if (s_abort) {
-    if (tid == 0) p.counts[3] = 2;
+    if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
     __syncthreads();
   }
@@ -777,12 +784,16 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned smem_base = smem_u32(smem);
       unsigned stage_addr = smem_base;
       const unsigned b_bytes = (unsigned)NB * 128u;
-      for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && !s_abort && !p.withhold_loads; item += gridDim.x) {
         const int pair = item / n_cblk, cb = item - pair * n_cblk;
         const bool first = item == (int)blockIdx.x;
         int t0 = first ? pre0 : p.list[2 * pair];
         int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
-        if (t0 < 0 || t0 >= ntiles_total || t1 >= ntiles_total) { p.counts[3] = 1; t0 = t0 < 0 || t0 >= ntiles_total ? 0 : t0; t1 = -1; }
+        // an entry outside the field is reported and skipped (see the halo kernel's producer)
+        const bool bad0 = t0 < 0 || t0 >= ntiles_total, bad1 = (2 * pair + 1 < n_active) && (t1 < 0 || t1 >= ntiles_total);
+        if (bad0 || bad1) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE);
+        if (bad0) t0 = 0;
+        if (bad1) t1 = -1;
         const int x0 = (t0 % TWo) * 8, y0 = ((t0 / TWo) % THo) * 8, n0 = t0 / (TWo * THo);
         const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
         const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + b_bytes;
@@ -796,7 +807,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
             int dy = ky - p.pad, pyb = 0;
             if (p.stride == 2) { pyb = (dy & 1) * 2; dy = (dy - (dy & 1)) >> 1; }
             for (int kx = 0; kx < p.k; ++kx, ++tap) {
-              if (!first_pass && !mbar_wait(&empty_bar[s], wait_parity, &s_abort)) { ok = false; break; }
+              if (!first_pass && !mbar_wait(&empty_bar[s], wait_parity, &s_abort, p.spin_limit)) { ok = false; break; }
               int dx = kx - p.pad, mi = 0;
               if (p.stride == 2) { mi = pyb + (dx & 1); dx = (dx - (dx & 1)) >> 1; }
               const unsigned bar = smem_u32(&full_bar[s]);
@@ -827,13 +838,13 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
         // the epilogue must have drained this accumulator (used two items ago)
         const unsigned buf = item_idx & 1u;
-        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort)) break;
+        if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
         tc_fence_after();
         const unsigned tmem_d = tmem_base + buf * acc_cols;
         bool ok = true;
         unsigned accumulate = 0;
         for (int ki = 0; ki < k_iters; ++ki) {
-          if (!mbar_wait(&full_bar[s], parity, &s_abort)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], parity, &s_abort, p.spin_limit)) { ok = false; break; }
           if (ki == 0 && item_idx == 0) TC_TRACE(7);
           tc_fence_after();
           const unsigned a_lo = desc_lo_flags | ((stage_addr & 0x3FFFFu) >> 4);
@@ -863,7 +874,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
       int t = (li < n_active) ? p.list[li] : -1;
-      if (t >= ntiles_total) t = -1;
+      if (t < 0 || t >= ntiles_total) t = -1;
       const unsigned buf = item_idx & 1u;
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
@@ -871,7 +882,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
       if (valid) tc_epilogue_prefetch(p, pix, cb * NB, 0, NB);
       if (tid == 64 && item_idx == 0) TC_TRACE_V(9, clock64() + (t & 0));
-      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort)) break;
+      if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
       if (tid == 64 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
@@ -891,7 +902,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   tc_fence_before();
   __syncthreads();
   if (s_abort) {
-    if (tid == 0) p.counts[3] = 2;
+    if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     // give copies that may still be in flight time to land before shared memory is released
     if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
     __syncthreads();
@@ -932,6 +943,28 @@ bool encode(EncodeTiledFn fn, CUtensorMap *m, int rank, const void *base, const 
   return r == CUDA_SUCCESS;
 }
 
+// Process-wide options of the tensor-core path (mie_set_option / mie_get_option).
+int g_opt_tc_thresholded = 0;               // MIE_OPT_TC_THRESHOLDED
+unsigned g_opt_spin_limit = SPIN_LIMIT;     // MIE_OPT_TC_SPIN_LIMIT
+int g_opt_withhold_loads = 0;               // MIE_OPT_TC_WITHHOLD_LOADS
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: the largest value set so far is
+// remembered per device, so a process that drives several GPUs raises the limit on each of them.
+constexpr int MAX_DEVICES = 64;
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, int *set_per_device, size_t smem) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+  if (dev < 0 || dev >= MAX_DEVICES) return MIE_EUNSUPPORTED;
+  if ((int)smem > set_per_device[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+    set_per_device[dev] = (int)smem;
+  }
+  return MIE_OK;
+}
+
 // MIE_TC_HALO=0 in the environment keeps every layer on the per-tap kernel (for A/B measurements).
 bool halo_enabled() {
   static const bool on = []() { const char *e = getenv("MIE_TC_HALO"); return !(e && e[0] == '0'); }();
@@ -955,7 +988,16 @@ bool tc_eligible(const mie_conv_args *a) {
   if (a->emitted && (a->emitted_ps % 4 || !aligned16(a->emitted))) return false;
   if (a->addend && (a->addend_ps % 4 || !aligned16(a->addend))) return false;
   if (a->cout_pad % 16) return false;
-  if (a->thr > 0.0f && a->cout_pad > 256) return false;
+  if (a->thr > 0.0f || a->emitted) {
+    // Thresholded layers (a pixel is sent or withheld as a whole, optionally with a carry buffer) run on the FP32
+    // kernel unless MIE_OPT_TC_THRESHOLDED is set: a full-network run of that mode on these kernels once ended in a
+    // device fault whose cause was not found.  When enabled, one block must hold every channel of a pixel
+    // (nb == cout_pad), which the block-width choice below only guarantees for these widths -- the same ones the FP32
+    // kernel accepts.
+    if (!g_opt_tc_thresholded) return false;
+    const int cp = a->cout_pad;
+    if (!(cp == 32 || cp == 64 || cp == 128 || cp == 256)) return false;
+  }
   // Too shallow to pay off.  (The 5x5 head of E2Depth, 5 -> 32 channels, would run 3x faster here than on the
   // FP32 path, but it sees the raw input delta: truncating O(1) values to TF32 every step random-walks in the
   // first reservoir and measured 1.1e-3 of the output range against 1.3e-5 with the head in FP32.)
@@ -969,6 +1011,8 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   if (!fn) return MIE_ECUDA;
   TcParams p;
   memset(&p, 0, sizeof(p));
+  p.spin_limit = g_opt_spin_limit;
+  p.withhold_loads = g_opt_withhold_loads;
   p.cin = a->cin; p.cout = a->cout; p.cout_pad = a->cout_pad;
   p.cin_pad = (a->cin + 31) / 32 * 32;
   p.n = a->n; p.hin = a->hin; p.win = a->win; p.hout = a->hout; p.wout = a->wout;
@@ -984,7 +1028,9 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   int nb = 256;
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
-  while (nb > 32 && a->thr == 0.0f && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
+  const bool whole_pixel = a->thr > 0.0f || a->emitted;   // tc_eligible admitted it: cout_pad is a power of two <= 256
+  while (nb > 32 && !whole_pixel && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
+  if (whole_pixel && nb != a->cout_pad) return MIE_EUNSUPPORTED;
   p.nb = nb;
   int acc_cols = 32;
   while (acc_cols < nb) acc_cols <<= 1;
@@ -1009,6 +1055,12 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     p.tps = tps ? tps : 1;
     const int b_bytes = p.tps * nb * 128;
     p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;
+    // Two issuers take alternate stages.  With an even ring every slot belongs to one issuer, which therefore sees
+    // each of its phases in turn.  With an odd ring a slot changes hands every lap: an issuer would wait for lap L of
+    // a slot whose lap L-1 it never observed, and if that earlier fill had not landed yet the parity wait would pass at
+    // once on the phase before (bulk copies may complete out of order) -- MMAs on a half-written slot and a second
+    // arrival on its "empty" barrier.  So the ring is made even.
+    if (p.issuers == 2 && (stages & 1)) stages -= 1;
     if (stages >= 2) {
       p.stages = stages;
       const size_t smem = (size_t)stages * b_bytes + a_bytes + 1024;
@@ -1029,12 +1081,8 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
         const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
         int grid = max_items < cap ? (int)max_items : (int)cap;
         if (grid < 1) grid = 1;
-        static int halo_smem_set = 0;
-        if ((int)smem > halo_smem_set) {
-          cudaError_t e = cudaFuncSetAttribute(conv_tc_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-          if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
-          halo_smem_set = (int)smem;
-        }
+        static int halo_smem_set[MAX_DEVICES] = {0};
+        { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel, halo_smem_set, smem); if (s_ != MIE_OK) return s_; }
         launch_chained(conv_tc_halo_kernel, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
         return check_launch();
       }
@@ -1094,12 +1142,11 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
   int grid = max_items < cap ? (int)max_items : (int)cap;
   if (grid < 1) grid = 1;
-  static int smem_set[2] = {0, 0};
-  if ((int)smem > smem_set[coalesced]) {
-    cudaError_t e = coalesced ? cudaFuncSetAttribute(conv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                              : cudaFuncSetAttribute(conv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
-    smem_set[coalesced] = (int)smem;
+  static int smem_set[2][MAX_DEVICES] = {{0}};
+  {
+    const int s_ = coalesced ? ensure_dynamic_smem(conv_tc_kernel<true>, smem_set[1], smem)
+                             : ensure_dynamic_smem(conv_tc_kernel<false>, smem_set[0], smem);
+    if (s_ != MIE_OK) return s_;
   }
   if (coalesced) launch_chained(conv_tc_kernel<true>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
   else launch_chained(conv_tc_kernel<false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
@@ -1133,6 +1180,28 @@ extern "C" int mie_debug_trace(long long *host, int n) {
   return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * (size_t)(n < 1024 * 16 ? n : 1024 * 16)) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+extern "C" int mie_set_option(int option, int value) {
+  switch (option) {
+    case MIE_OPT_TC_THRESHOLDED: g_opt_tc_thresholded = value ? 1 : 0; return MIE_OK;
+    case MIE_OPT_TC_SPIN_LIMIT:
+      if (value < 0) return MIE_EINVAL;
+      g_opt_spin_limit = value == 0 ? SPIN_LIMIT : (unsigned)value;
+      return MIE_OK;
+    case MIE_OPT_TC_WITHHOLD_LOADS: g_opt_withhold_loads = value ? 1 : 0; return MIE_OK;
+    default: return MIE_EINVAL;
+  }
+}
+
+extern "C" int mie_get_option(int option, int *value) {
+  if (!value) return MIE_EINVAL;
+  switch (option) {
+    case MIE_OPT_TC_THRESHOLDED: *value = g_opt_tc_thresholded; return MIE_OK;
+    case MIE_OPT_TC_SPIN_LIMIT: *value = (int)g_opt_spin_limit; return MIE_OK;
+    case MIE_OPT_TC_WITHHOLD_LOADS: *value = g_opt_withhold_loads; return MIE_OK;
+    default: return MIE_EINVAL;
+  }
+}
 
 extern "C" int mie_conv_pack_dims_tc(int cin, int cout, int k, int *cin_pad, int *cout_pad, int64_t *n_floats) {
   if (cin <= 0 || cout <= 0 || k <= 0) return MIE_EINVAL;

@@ -36,12 +36,15 @@ class IncrConfig:
                      E2Depth's accumulated output to about 1e-5); "off" keeps every convolution on the FP32 path
     compat           "reference": networks wired as the reference is written; "exact": as intended, which
                      makes the accumulated incremental output equal to a dense recompute
+    tc_thresholded   False (default): thresholded convolutions (threshold > 0, with or without carry) run on the FP32
+                     kernel; True lets layers of 32/64/128/256 output channels use the tensor cores in that mode too
     """
     threshold: float = 0.0
     carry: bool = True
     input_threshold: float = 0.0
     compat: str = "reference"
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
+    tc_thresholded: bool = False
 
 
 config = IncrConfig()

@@ -16,6 +16,7 @@ import torch.nn.functional as F
 from .. import _native as nat
 from .. import fields as fl
 from ..fields import Scratch, TileMask
+from .mask_incr_modules import set_precision
 from .evflownet_incr import ConvLayerIncr, ResidualBlockIncr, UpsampleConvLayerIncr, skip_concat, skip_concat_incr
 
 
@@ -141,7 +142,7 @@ class DelayedMultiResUNetIncr(nn.Module):
 class DelayedEVFlowNetIncr(nn.Module):
     """Reference ``DelayedEVFlowNetIncr`` (``:387-476``): fixed hyper-parameters around the UNet above."""
 
-    def __init__(self, unet_kwargs, num_bins, compat: Optional[str] = None):
+    def __init__(self, unet_kwargs, num_bins, compat: Optional[str] = None, precision: Optional[str] = "split"):
         super().__init__()
         self.crop = None
         kw = dict(unet_kwargs)
@@ -154,6 +155,9 @@ class DelayedEVFlowNetIncr(nn.Module):
         for k in ("name", "eval", "encoding", "mask_output", "mask_smoothing", "flow_scaling"):
             kw.pop(k, None)
         self.multires_unet = DelayedMultiResUNetIncr(kw, compat=compat)
+        # An un-normalised ReLU stack fed by raw event counts: a TF32 input's 2^-11 relative error is about 2e-3 of the
+        # flow range after a few dozen steps, so the tensor-core layers run in split precision by default.
+        set_precision(self, precision)
 
     def reset_states(self):
         pass

@@ -30,7 +30,7 @@ class IncrementMaskModule(nn.Module):
 class KFencedMaskModule(IncrementMaskModule):
     """Sigma-delta quantiser with residual carry (reference ``:21-47``): T = carry + dx;
     q = k*floor(0.5 + T/k); carry = T - q.  The reference builds one into every convolution and never
-    applies it in ``forward``; it is kept for the same reason and evaluated with tensor ops."""
+    applies it in ``forward``; it is kept for the same reason and runs on one kernel (``mie_kfenced``)."""
 
     def __init__(self, tp: float = .1):
         super().__init__()
@@ -43,19 +43,19 @@ class KFencedMaskModule(IncrementMaskModule):
 
     def forward(self, incr: Masked) -> Masked:
         d = incr[0]
-        if d.is_cuda and d.dim() == 4 and d.dtype == torch.float32:
-            # one kernel: quantise, update the carry, emit the mask of the quantised delta
-            sc = self.__dict__.setdefault("_scratch", Scratch())
-            d = fl.as_channels_last(d)
-            n, c, h, w = d.shape
-            q = sc.get("q", (n, c, h, w), torch.float32, d.device, channels_last=True)
-            bits = sc.get("q.bits", (fl.n_tiles(n, h, w),), torch.int64, d.device)
-            k = self._k_host if getattr(self, "_k_host", None) is not None else float(self.k)
-            return q, fl.kfenced(d, self.delta.reservoir, k, q, bits)
-        T1 = self.delta.reservoir + incr[0]
-        f_delta = self.floor_by_k(T1)
-        self.delta.update_reservoir(T1 - f_delta)
-        return f_delta, None
+        nat.require_cuda(d, "incr")
+        if d.dim() != 4:
+            raise RuntimeError("KFencedMaskModule takes a [N,C,H,W] delta")
+        if self.delta.reservoir is None:
+            raise RuntimeError("forward_refresh_reservoirs must run before the first incremental step")
+        # one kernel: quantise, update the carry, emit the mask of the quantised delta
+        sc = self.__dict__.setdefault("_scratch", Scratch())
+        d = fl.as_channels_last(d)
+        n, c, h, w = d.shape
+        q = sc.get("q", (n, c, h, w), torch.float32, d.device, channels_last=True)
+        bits = sc.get("q.bits", (fl.n_tiles(n, h, w),), torch.int64, d.device)
+        k = self._k_host if getattr(self, "_k_host", None) is not None else float(self.k)
+        return q, fl.kfenced(d, self.delta.reservoir, k, q, bits)
 
     def forward_refresh_reservoirs(self, x: DenseT) -> DenseT:
         self.k = self.tp * torch.norm(x)
@@ -147,6 +147,10 @@ class nnReservedActivation(NonlinearPointOpIncr):
     def carry_buffer(self, thr: float) -> Optional[torch.Tensor]:
         """The buffer of what has been sent so far; created from the reservoir when first needed."""
         if thr <= 0.0 or not config.carry:
+            # A step without the carry does not advance this buffer, so it must not survive into a later thresholded
+            # step (it would inject everything that happened in between as one spurious delta): drop it, and let the
+            # next thresholded step rebuild it from the reservoir.
+            self.emitted = None
             return None
         r = self.in_res.reservoir
         if self.emitted is None or self.emitted.shape != r.shape or self.emitted.device != r.device:
@@ -244,6 +248,7 @@ class _ConvPlan:
         self.stale = torch.zeros(nt, dtype=torch.int32, device=device)
         self.counts = torch.zeros(4, dtype=torch.int32, device=device)
         self.flags = torch.zeros(nt, dtype=torch.uint8, device=device)
+        self.geometry = (n, hin, win)
         a = nat.ConvArgs()
         a.hin, a.win, a.n, a.hout, a.wout = hin, win, n, self.hout, self.wout
         a.k, a.stride, a.pad = k, s, p
@@ -264,6 +269,7 @@ class nnConvIncr(nn.Conv2d):
         nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, bias=bias)
         self.kf = KFencedMaskModule(0.3)
         self._k, self._s, self._p = _square(self.kernel_size), _square(self.stride), _square(self.padding)
+        self.precision = None   # None: TF32 on the tensor cores; "split": split precision there (see _split_input)
         self._packed = {}   # cin_limit -> (version, device, buffer, cin_pad, cout_pad)
         self._plans = {}
         self._cw = None
@@ -284,12 +290,21 @@ class nnConvIncr(nn.Conv2d):
         return r
 
     def _split_input(self, cin: int) -> bool:
-        """Narrow-input layers (the 5-bin voxel head) run on the tensor cores with a split-precision input: the raw
-        O(1) input delta must not be truncated to TF32 (it random-walks in the first reservoir) and neither may the
-        filter be rounded (the input changes by its full scale between frames); with [d, d - tf32(d), d] against
-        [W, W, W - tf32(W)] as 24 channels neither is."""
-        return (config.tensor_cores == "auto" and self._s == 1 and self._k in (3, 5, 7) and cin <= 8
-                and cin * self._k * self._k >= 100 and self.out_channels % 4 == 0)
+        """Whether this layer runs on the tensor cores in split precision: input [d, d - tf32(d), d] against the
+        filter blocks [W, W, W - tf32(W)] (three times the channels), which is the fp32 convolution up to the dropped
+        lo*lo term.  Taken by
+          * narrow-input layers (the 5-bin voxel head): the raw O(1) input delta must not be truncated to TF32 (it
+            random-walks in the first reservoir) and neither may the filter be rounded (the input changes by its full
+            scale between frames);
+          * every tensor-core layer of a network built with ``precision = "split"`` (the un-normalised ReLU stacks
+            fed by raw event counts, FireFlowNet and the delayed EV-FlowNet): there the 2^-11 relative error of a
+            TF32 input is already 2e-3 of the output range after one step, whatever the rounding mode."""
+        if config.tensor_cores != "auto" or self.out_channels % 4:
+            return False
+        if self._s == 1 and self._k in (3, 5, 7) and cin <= 8 and cin * self._k * self._k >= 100:
+            return True
+        return (getattr(self, "precision", None) == "split" and cin * self._k * self._k >= 256
+                and self._k in (1, 3, 5, 7) and self._s in (1, 2))
 
     def _weights(self, cin_limit: Optional[int] = None, split: bool = False, bn: "Optional[nn.BatchNorm2d]" = None):
         """Packed filter for the kernels, repacked whenever the parameter changed or moved.  ``bn``: an eval
@@ -315,12 +330,13 @@ class nnConvIncr(nn.Conv2d):
                 c = cin_limit or self.in_channels
                 wf = w[:, :c].float()
                 w_hi = (wf.view(torch.int32) + 0x1000 & ~0x1FFF).view(torch.float32)   # TF32 rounding, as the packing does
-                w24 = torch.zeros((w.shape[0], 24, self._k, self._k), dtype=torch.float32, device=w.device)
-                w24[:, :c] = wf
-                w24[:, 8:8 + c] = wf
-                w24[:, 16:16 + c] = wf - w_hi
-                w = w24
-                key_depth = 24
+                half = (c + 7) // 8 * 8
+                w3 = torch.zeros((w.shape[0], 3 * half, self._k, self._k), dtype=torch.float32, device=w.device)
+                w3[:, :c] = wf
+                w3[:, half:half + c] = wf
+                w3[:, 2 * half:2 * half + c] = wf - w_hi
+                w = w3
+                key_depth = 3 * half
             else:
                 key_depth = cin_limit or self.in_channels
             buf, cp, op = fl.pack_conv_weights(w.float())
@@ -356,10 +372,11 @@ class nnConvIncr(nn.Conv2d):
         split = self._split_input(cin)
         wbuf, cp, op, wtc = self._weights(cin_limit, split, bn)
         if split:
-            d24 = sc.get("split", (n, 24, hin, win), torch.float32, d.device, channels_last=True)
+            c3 = 3 * ((cin + 7) // 8 * 8)
+            d3 = sc.get("split", (n, c3, hin, win), torch.float32, d.device, channels_last=True)
             sb = sc.get("split.bits", (fl.n_tiles(n, hin, win),), torch.int64, d.device)
-            fl.split_tf32(d, m, d24, sb)
-            d, cin = d24, 24
+            fl.split_tf32(d, m, d3, sb)
+            d, cin = d3, c3
         a = plan.args
         union = None
         if addend is not None:
@@ -391,6 +408,8 @@ class nnConvIncr(nn.Conv2d):
             a.emitted, a.emitted_ps = (em.data_ptr(), fl.pixel_stride(em)) if em is not None else (None, 0)
         else:
             a.act, a.thr, a.res, a.res_ps, a.emitted, a.emitted_ps = nat.ACT_NONE, 0.0, None, 0, None, 0
+        if a.thr > 0.0 or a.emitted:
+            nat.set_option(nat.OPT_TC_THRESHOLDED, 1 if config.tc_thresholded else 0)
         nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
         self.last_used_tensor_cores = bool(nat.lib.mie_conv_uses_tensor_cores(C.byref(a)))
         return [plan.out, plan.mask]
@@ -398,10 +417,44 @@ class nnConvIncr(nn.Conv2d):
     def forward(self, x_incr):
         return self.forward_fused(x_incr)
 
+    def error_words(self):
+        """``[(geometry, counts tensor)]`` of every plan: word 3 of ``counts`` holds the MIE_ERR_* bits the kernels
+        raised since it was last cleared (see ``check_device_errors``)."""
+        return [(p.geometry, p.counts) for p in self._plans.values()]
+
     def forward_refresh_reservoirs(self, x):
         # The reference also resets its (never applied) quantiser here, which costs a norm and a
         # zero tensor of the input's size per convolution (``:193``); nothing reads either.
         return nn.Conv2d.forward(self, x)
+
+
+def check_device_errors(model: nn.Module, clear: bool = True) -> None:
+    """Read the device-side error word of every convolution of ``model`` (one small copy to the host, which
+    synchronises) and raise ``MieError`` naming the layers whose kernels reported a skipped tile-list entry or an
+    expired wait.  The kernels themselves never stop the device; without this call such a step would return wrong data
+    silently.  The reference exits the process on any CUDA error instead (``include/checks.h:12-21``)."""
+    named = [(name, geo, cnt) for name, m in model.named_modules() if isinstance(m, nnConvIncr)
+             for geo, cnt in m.error_words()]
+    if not named:
+        return
+    words = torch.stack([cnt[3] for _, _, cnt in named]).cpu().tolist()
+    bad = [(name, geo, w) for (name, geo, _), w in zip(named, words) if w]
+    if not bad:
+        return
+    if clear:
+        for _, _, cnt in named:
+            cnt[3] = 0
+    raise nat.MieError("; ".join(f"{name or '<conv>'} (batch {g[0]}, input {g[1]}x{g[2]}): {nat.describe_error_word(w)}"
+                                 for name, g, w in bad))
+
+
+def set_precision(model: nn.Module, precision: Optional[str]) -> None:
+    """Set ``precision`` (None or "split") on every convolution of ``model``."""
+    if precision not in (None, "split"):
+        raise ValueError("precision must be None or 'split'")
+    for m in model.modules():
+        if isinstance(m, nnConvIncr):
+            m.precision = precision
 
 
 class nnConvIncrBase(nnConvIncr):

@@ -67,8 +67,17 @@ class IncrementalRunner:
         self._frame = 0
         self.graph_replays = 0
 
+    # -- device-side error status ----------------------------------------------------------------
+    def check(self) -> None:
+        """Raise ``MieError`` if a kernel of an earlier step skipped a bad tile-list entry or gave up a bounded wait
+        (the kernels record that in device memory and carry on).  Synchronises; ``refresh`` calls it, a caller
+        that wants the status per step calls it after ``step``."""
+        from .incr_modules.mask_incr_modules import check_device_errors
+        check_device_errors(self.model)
+
     # -- dense pass ------------------------------------------------------------------------------
     def refresh(self, x: torch.Tensor):
+        self.check()
         x = fl.as_channels_last(x)
         if hasattr(self.model, "reset_states"):
             self.model.reset_states()

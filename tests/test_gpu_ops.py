@@ -461,9 +461,10 @@ def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
     from maskedincrementeval_b200 import fields as fl
     from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
     g = torch.Generator().manual_seed(21)
-    old = fl.config.threshold
+    old, old_flag = fl.config.threshold, fl.config.tc_thresholded
     try:
         fl.config.threshold = 0.02
+        fl.config.tc_thresholded = True      # thresholded layers take the FP32 kernel unless this is set
         layers = []
         for mode in ("auto", "off"):
             torch.manual_seed(0)
@@ -485,7 +486,9 @@ def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
             for y in ys:
                 assert float((y - truth).abs().max()) <= 0.02 + 2e-3
     finally:
-        fl.config.threshold = old
+        fl.config.threshold, fl.config.tc_thresholded = old, old_flag
+        from maskedincrementeval_b200 import _native as nat
+        nat.set_option(nat.OPT_TC_THRESHOLDED, 0)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -1,0 +1,279 @@
+"""Device-side error status, thresholded layers and split precision of the convolution kernels.
+
+None of these tests faults, traps or hangs the device: a bad tile-list entry is written from the host and must be
+skipped; the bounded barrier wait is made to run out by a launch option that withholds the loads it waits for, with a
+limit of a few hundred polls, after which the kernel returns by itself and the next launch must work.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import restatement as R  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def restore_config():
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200 import fields as fl
+    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tc_thresholded", "compat")}
+    yield
+    for k, v in saved.items():
+        setattr(fl.config, k, v)
+    nat.set_option(nat.OPT_TC_SPIN_LIMIT, 0)
+    nat.set_option(nat.OPT_TC_WITHHOLD_LOADS, 0)
+    nat.set_option(nat.OPT_TC_THRESHOLDED, 0)
+
+
+def cl(t, dev):
+    return t.to(dev).contiguous(memory_format=torch.channels_last)
+
+
+def sparse_delta(g, shape, frac, std=0.5):
+    n, c, h, w = shape
+    act = (torch.rand(n, 1, h, w, generator=g) < frac).float()
+    return torch.randn(shape, generator=g) * std * act
+
+
+def _layer(dev, cin, cout, k, s, act, seed=0):
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    torch.manual_seed(seed)
+    return ConvLayerIncr(cin, cout, k, s, k // 2, activation=act).to(dev).eval()
+
+
+# ------------------------------------------------------------------------------------------------
+# counts[3]: a bad tile-list entry is skipped and reported; an expired wait is reported; the host raises
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cfg", [("off", 16, 32, 3, 1), ("auto", 32, 32, 3, 1), ("auto", 64, 64, 3, 1), ("auto", 32, 64, 5, 2)])
+def test_bad_tile_entry_is_skipped_and_reported(dev, cfg):
+    """The second entry of a hand-made tile list is out of range: its slot is skipped (nothing is written for it), the
+    tiles either side of it are computed as usual, counts[3] carries MIE_ERR_BAD_TILE, and check_device_errors raises."""
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import check_device_errors
+    mode, cin, cout, k, s = cfg
+    fl.config.tensor_cores = mode
+    n, h, w = 1, 48, 64
+    layer = _layer(dev, cin, cout, k, s, "relu")
+    conv = layer.conv2d
+    g = torch.Generator().manual_seed(11)
+    x0 = torch.randn(n, cin, h, w, generator=g)
+    dx = sparse_delta(g, (n, cin, h, w), 1.0)
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        dxd = cl(dx, dev)                                  # kept alive: the raw call below reads it again
+        dy, m = layer([dxd, None])                         # a regular step: builds the plan, full activity
+        assert conv.last_used_tensor_cores == (mode == "auto")
+        want = dy.clone()
+        plan = conv._plan(n, h, w, dev)
+        ho, wo = plan.hout, plan.wout
+        tw = -(-wo // 8)
+        # same step again from the same state, through the C ABI, with a corrupted list
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        good = [0, 1, 2, tw + 1, 3]
+        lst = torch.tensor([good[0], 10 ** 6, good[1], -7, good[2], good[3], 10 ** 6 + 1, good[4]], dtype=torch.int32, device=dev)
+        plan.list[: lst.numel()] = lst
+        plan.counts.copy_(torch.tensor([lst.numel(), 0, 0, 0], dtype=torch.int32))
+        plan.out.zero_()
+        plan.out_bits.zero_()
+        a = plan.args
+        nat.check(nat.lib.mie_conv_tiles(C.byref(a), nat.stream_ptr(dev)), "conv_tiles")
+        torch.cuda.synchronize()
+        assert int(plan.counts[3]) & nat.ERR_BAD_TILE
+        assert not int(plan.counts[3]) & nat.ERR_WAIT_EXPIRED
+        got = plan.out
+        tol = 2e-3 if mode == "auto" else 1e-5
+        covered = torch.zeros(1, 1, ho, wo, dtype=torch.bool)
+        for t in good:
+            ty, tx = divmod(t, tw)
+            covered[:, :, ty * 8:ty * 8 + 8, tx * 8:tx * 8 + 8] = True
+            a_, b_ = got[:, :, ty * 8:ty * 8 + 8, tx * 8:tx * 8 + 8], want[:, :, ty * 8:ty * 8 + 8, tx * 8:tx * 8 + 8]
+            assert float((a_ - b_).abs().max()) <= tol * max(float(want.abs().max()), 1.0)
+        assert float((got.cpu() * (~covered).float()).abs().max()) == 0.0      # nothing outside the five good tiles
+        with pytest.raises(nat.MieError, match="outside the field"):
+            check_device_errors(layer)
+        assert int(plan.counts[3]) == 0                                         # cleared by the check
+        check_device_errors(layer)                                              # and quiet afterwards
+
+
+@pytest.mark.parametrize("cfg", [(32, 32, 3, 1), (64, 64, 3, 1), (32, 64, 5, 2)])
+def test_bounded_wait_expires_cleanly(dev, cfg):
+    """With the loads withheld and a limit of 300 polls every tensor-core block with work gives up its first wait:
+    the kernel returns, counts[3] carries MIE_ERR_WAIT_EXPIRED, the tensor memory is free again (the next launch of the
+    same kernel runs and is correct), and the runner-level check raises."""
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import check_device_errors
+    cin, cout, k, s = cfg
+    fl.config.tensor_cores = "auto"
+    n, h, w = 1, 40, 56
+    layer = _layer(dev, cin, cout, k, s, "relu")
+    wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()
+    g = torch.Generator().manual_seed(5)
+    x0 = torch.randn(n, cin, h, w, generator=g)
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        res = R.conv_dense(x0, wt, b, s, k // 2)
+        dx = sparse_delta(g, (n, cin, h, w), 0.3)
+        nat.set_option(nat.OPT_TC_SPIN_LIMIT, 300)
+        nat.set_option(nat.OPT_TC_WITHHOLD_LOADS, 1)
+        layer([cl(dx, dev), None])
+        assert layer.conv2d.last_used_tensor_cores
+        torch.cuda.synchronize()                         # returns: nothing waits forever
+        plan = layer.conv2d._plan(n, h, w, dev)
+        assert int(plan.counts[3]) & nat.ERR_WAIT_EXPIRED
+        with pytest.raises(nat.MieError, match="wait ran out"):
+            check_device_errors(layer)
+        nat.set_option(nat.OPT_TC_SPIN_LIMIT, 0)
+        nat.set_option(nat.OPT_TC_WITHHOLD_LOADS, 0)
+        # the aborted launch wrote no output and did not touch the reservoir: the same step now runs normally
+        dy, m = layer([cl(dx, dev), None])
+        torch.cuda.synchronize()
+        want, _ = R.act_incr(res, R.conv_delta_tf32(dx, wt, s, k // 2), "relu")
+        assert float((dy.cpu() - want).abs().max()) <= 2e-5 * max(float(want.abs().max()), 1.0)
+        assert int(plan.counts[3]) == 0
+        check_device_errors(layer)
+
+
+def test_runner_check_names_the_layer(dev):
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200.incr_modules.fireflownet_incr import FireFlowNetIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    net = FireFlowNetIncr(dict(base_num_channels=16, kernel_size=3, mask_output=False), 2, compat="exact").to(dev).eval()
+    run = IncrementalRunner(net, use_graph=False)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, 2, 32, 40, generator=g)
+    run.refresh(cl(x, dev))
+    run.step(cl(x + sparse_delta(g, x.shape, 0.2), dev))
+    run.check()
+    plan = next(iter(net.E2.conv2d._plans.values()))
+    plan.counts[3] = nat.ERR_BAD_TILE
+    with pytest.raises(nat.MieError, match="E2.conv2d"):
+        run.check()
+    run.check()
+
+
+# ------------------------------------------------------------------------------------------------
+# thresholded layers: FP32 kernel by default, the deep-layer shapes of E2Depth
+# ------------------------------------------------------------------------------------------------
+DEEP = [
+    # cin, cout, k, s, h, w, addend
+    (256, 256, 3, 1, 33, 44, True),     # residual block convolution (with the residual sum)
+    (256, 128, 5, 1, 66, 88, False),    # decoder 0 behind its upsample
+    (128, 256, 5, 2, 66, 88, False),    # encoder 2
+    (64, 128, 5, 2, 132, 176, False),   # encoder 1
+]
+
+
+def _thresholded_run(dev, cfg, tc_thresholded, steps=5, thr=0.02):
+    """One thresholded layer with carry over a few partially active steps; returns per-step (delta, mask, total sent)."""
+    from maskedincrementeval_b200 import fields as fl
+    cin, cout, k, s, h, w, with_addend = cfg
+    fl.config.threshold, fl.config.carry, fl.config.tc_thresholded = thr, True, tc_thresholded
+    layer = _layer(dev, cin, cout, k, s, "relu", seed=3)
+    g = torch.Generator().manual_seed(cin + cout + k + s)
+    x0 = torch.randn(1, cin, h, w, generator=g) * 0.5
+    out = []
+    with torch.no_grad():
+        pre = layer.conv2d.forward_refresh_reservoirs(cl(x0, dev))
+        ho, wo = pre.shape[2:]
+        r0 = torch.randn(1, cout, ho, wo, generator=g) * 0.3 if with_addend else None
+        if with_addend:
+            pre = pre + cl(r0, dev)
+        layer.activation.forward_refresh_reservoirs(pre)
+        sent = torch.relu(pre).clone()
+        for step, frac in enumerate([0.05, 0.3, 0.0, 0.02, 1.0][:steps]):
+            dx = sparse_delta(g, (1, cin, h, w), frac, std=0.1)
+            addend = None
+            if with_addend:
+                addend = [cl(sparse_delta(g, (1, cout, ho, wo), frac * 0.5, std=0.05), dev), None]
+            dy, m = layer(([cl(dx, dev), None]), addend)
+            sent += dy
+            out.append((dy.clone(), m.pixel_mask().clone(), sent.clone(), layer.conv2d.last_used_tensor_cores))
+        truth = torch.relu(layer.activation.in_res.reservoir).clone()
+    return out, truth
+
+
+@pytest.mark.parametrize("cfg", DEEP)
+def test_thresholded_deep_layers_fp32_routed(dev, cfg):
+    """Default routing: a thresholded layer never takes the tensor-core kernels, even when the filter has a
+    tensor-core copy; the FP32 kernel keeps the carry invariant (total sent within the threshold of the true output),
+    withheld pixels are exact zeros and the mask is exactly the set of non-zero pixels."""
+    from maskedincrementeval_b200 import fields as fl
+    fl.config.tensor_cores = "auto"
+    steps, truth = _thresholded_run(dev, cfg, tc_thresholded=False)
+    for dy, pm, sent, used_tc in steps:
+        assert not used_tc
+        assert torch.equal(pm, (dy != 0).any(1, keepdim=True).to(torch.uint8))
+    assert float((steps[-1][2] - truth).abs().max()) <= 0.02 + 1e-5
+
+
+def test_thresholded_odd_channel_count_same_on_both_settings(dev):
+    """96 output channels with a threshold: no kernel holds every channel of a pixel in one block at that width, on
+    either path, so the layer is refused the same way whether or not thresholded tensor-core layers are enabled
+    (a block-local send decision would drop channels of a sent pixel for good)."""
+    from maskedincrementeval_b200 import fields as fl
+    fl.config.tensor_cores = "auto"
+    for flag in (False, True):
+        with pytest.raises(NotImplementedError):
+            _thresholded_run(dev, (64, 96, 3, 1, 24, 40, False), tc_thresholded=flag, steps=1)
+
+
+def test_carry_dropped_when_threshold_switched_off(dev):
+    """threshold 0.05 -> 0 -> 0.05: the steps run lossless in between do not advance the carry buffer, so it is dropped
+    and rebuilt; the total sent stays within the threshold of the true output after the switch back."""
+    from maskedincrementeval_b200 import fields as fl
+    fl.config.tensor_cores = "off"
+    layer = _layer(dev, 16, 32, 3, 1, "tanh")
+    g = torch.Generator().manual_seed(2)
+    x0 = torch.randn(1, 16, 24, 32, generator=g)
+    with torch.no_grad():
+        sent = layer.forward_refresh_reservoirs(cl(x0, dev)).clone()
+        for thr in (0.05, 0.05, 0.0, 0.0, 0.05, 0.05):
+            fl.config.threshold = thr
+            dy, _ = layer([cl(sparse_delta(g, x0.shape, 0.2, std=0.1), dev), None])
+            sent += dy
+            truth = torch.tanh(layer.activation.in_res.reservoir)
+            assert float((sent - truth).abs().max()) <= 0.05 + 1e-5
+            if thr == 0.0:
+                assert layer.activation.emitted is None
+
+
+# ------------------------------------------------------------------------------------------------
+# split precision on wide layers
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cfg", [(32, 32, 3, 1, 40, 56), (64, 32, 3, 2, 32, 48), (130, 32, 3, 1, 24, 40), (32, 64, 5, 1, 24, 32)])
+def test_split_precision_matches_fp32(dev, cfg):
+    """precision="split": the tensor-core result is the fp32 convolution (2e-5 of the range), not the TF32 one."""
+    from maskedincrementeval_b200 import fields as fl
+    cin, cout, k, s, h, w = cfg
+    fl.config.tensor_cores = "auto"
+    layer = _layer(dev, cin, cout, k, s, "relu", seed=4)
+    layer.conv2d.precision = "split"
+    wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()
+    g = torch.Generator().manual_seed(7)
+    x0 = torch.randn(1, cin, h, w, generator=g)
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        res = R.conv_dense(x0, wt, b, s, k // 2)
+        for frac in (0.1, 1.0, 0.0, 0.03):
+            dx = sparse_delta(g, (1, cin, h, w), frac) * 4.0
+            dy, m = layer([cl(dx, dev), None])
+            assert layer.conv2d.last_used_tensor_cores
+            want, _ = R.act_incr(res, R.conv_delta(dx, wt, s, k // 2), "relu")
+            scale = max(float(want.abs().max()), 1.0)
+            assert float((dy.cpu() - want).abs().max()) <= 2e-5 * scale, float((dy.cpu() - want).abs().max()) / scale
+            res = layer.activation.in_res.reservoir.cpu().contiguous()
+            pm = m.pixel_mask().cpu()
+            assert float((dy.cpu() * (1 - pm.float())).abs().max()) == 0.0
