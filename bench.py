@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload ("e2depth_260x346_b1", BASELINE config 3): the E2Depth recurrent UNet (5-bin voxel input,
+Workload ("e2depth_260x346_b1"): the E2Depth recurrent UNet (5-bin voxel input,
 head 32 ch, 3 ConvLSTM encoders 64/128/256, 2 residual blocks, 3 decoders, sigmoid head), random-init
 weights (PyTorch's default convolution init, what the reference's random-init network has), one event
 stream per GPU.  Every window draws 30k synthetic events from 10 drifting edge segments plus 5% uniform
@@ -20,8 +20,9 @@ over ranks and the value is the sum of the streams' timesteps divided by it.
 The JSON line also carries
   e2e          the same metric through IncrementalRunner.step_host with the voxel grid in pinned host memory
                and the accumulated prediction read back to the host every step (copies on side streams)
-  roofline     the masked conv3x3 32->32 + incremental ReLU kernel of BASELINE config 1 (260x346, 5%
-               active pixels, drifting blobs), timed alone: algorithmic bytes touched / launch time
+  roofline     the masked conv3x3 32->32 + incremental ReLU kernel (batch 1, 260x346, 5% active pixels placed
+               as drifting blobs), timed alone: algorithmic bytes touched / launch time
+  roofline_kernels  the same figure for the other kernels of a step, each at its size in this network
   cpu_baseline the CPU restatement of the reference's incremental E2Depth step on this box's host cores
   dense        the dense recompute (forward_refresh_reservoirs every step, cuDNN) for context
 """
@@ -133,14 +134,39 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's incremental step
 # --------------------------------------------------------------------------------------------------
+def load_generators():
+    """The seeded input generators, loaded by file path: importing them through the package would load the CUDA
+    library, which the CPU arm must not touch."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mie_bench_generators",
+                                                  os.path.join(ROOT, "maskedincrementeval_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def workload_config(args, world: int):
+    """The `config` object both arms print: same keys, same workload, same seeds."""
+    return {"workload": WORKLOAD, "streams_per_gpu": args.streams,
+            "resolution": f"{H}x{W}, reflection-padded to a multiple of 8", "events_per_window": EVENTS,
+            "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold, "tensor_cores": args.tensor_cores,
+            "weights": "random init (nn.Conv2d default), seed 0", "frames_seed": FRAMES_SEED,
+            "parallelism": f"{world} x independent streams"}
+
+
+FRAMES_SEED = 100
+
+
 def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 25.0):
-    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+    gen = load_generators()
     from oracle.restatement import E2DepthOracle
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    sd = seeded_state_dict(e2depth_shapes(), seed=0, init="default")
-    net = E2DepthOracle(sd, compat="reference")
-    frames = voxel_sequence(1, H, W, warmup + steps + 1, EVENTS, SEGMENTS, seed=0)
+    sd = gen.seeded_state_dict(e2depth_shapes(), seed=0, init="default")
+    # the intended wiring (skips summed), as the GPU arm runs; the reference's as-written wiring differs by three tensor
+    # sums and costs the same
+    net = E2DepthOracle(sd, compat="exact")
+    frames = gen.voxel_sequence(1, H, W, warmup + steps + 1, EVENTS, SEGMENTS, seed=FRAMES_SEED)
     frames = [f.contiguous() for f in frames]
     with torch.no_grad():
         net.refresh(frames[0])
@@ -169,8 +195,9 @@ def run_reference_impl(args):
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": cb["steps"], "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "note": "the reference's own (activity-independent) incremental step, "
-                       "restated on CPU; the reference checkout does not exist on this box"},
+            "config": dict(workload_config(args, 1), note="the reference's own (activity-independent) incremental "
+                           "step, restated on CPU (bit-identical to the reference where both run); threshold and "
+                           "tensor_cores do not apply to it"),
             "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -185,7 +212,7 @@ def l2_flusher(dev):
 
 
 def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
-    """BASELINE config 1: conv3x3 32->32 + incremental ReLU, 260x346, batch 1, 16 drifting-blob deltas at 5%."""
+    """conv3x3 32->32 + incremental ReLU, 260x346, batch 1, 16 drifting-blob deltas at 5% active pixels."""
     from maskedincrementeval_b200 import _native as nat
     from maskedincrementeval_b200 import fields as fl
     from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
@@ -304,7 +331,9 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
             if ln.startswith("dram_bytes_per_launch:"):
                 traffic = float(ln.split(":")[1])
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": ("conv_tc_kernel" if conv.last_used_tensor_cores else "conv_tiles_kernel<3,1,4,1>") + " (conv3x3 32->32 + ReLU, 260x346)",
+            "traffic": traffic, "traffic_source": "recorded: dram__bytes_read.sum + dram__bytes_write.sum per launch from the "
+            "committed ncu capture of this kernel (profiles/conv_tc_c1_conv3x3_260x346.md), not measured in this run",
+            "peak_kind": f"of {peak_kind}", "kernel": ("conv_tc_kernel" if conv.last_used_tensor_cores else "conv_tiles_kernel<3,1,4,1>") + " (conv3x3 32->32 + ReLU, 260x346)",
             "bytes_per_launch": sum(byts) / len(byts), "us_per_launch": 1e6 * tot_t / len(times),
             "active_tiles_mean": sum(tiles) / len(tiles), "tiles_total": fl.n_tiles(1, H, W),
             "active_pixel_frac": sum(px) / len(px), "fp32_tflops": sum(flops) / tot_t / 1e12, "launches": len(times),
@@ -337,6 +366,7 @@ def run_ours(args):
     mie.config.compat = "exact"
     mie.config.threshold = args.threshold
     mie.config.tensor_cores = args.tensor_cores
+    mie.config.tc_thresholded = bool(args.tc_thresholded)
     streams = args.streams
     K, Wm = args.steps, args.warmup
     flow = args.net != "e2depth"
@@ -389,9 +419,9 @@ def run_ours(args):
     my_streams = streams_of_rank(streams * world, world, rank)   # global stream ids of this rank
     n_frames = Wm + K + 3
     if flow:
-        frames_host = count_image_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
+        frames_host = count_image_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=FRAMES_SEED + my_streams[0])
     else:
-        frames_host = voxel_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=100 + my_streams[0])
+        frames_host = voxel_sequence(len(my_streams), H, W, n_frames, EVENTS, SEGMENTS, seed=FRAMES_SEED + my_streams[0])
     frames_pinned = [f.pin_memory() for f in frames_host]
     frames_dev = [f.to(dev) for f in frames_host]
     in_bytes = frames_host[0].numel() * 4
@@ -429,6 +459,10 @@ def run_ours(args):
     clocks = sampler.stop()
     dev_s = sum(a.elapsed_time(b) for a, b in ev) * 1e-3
     y_incr = first(run.output).clone()
+    run.check()     # no kernel of the timed steps skipped a tile-list entry or gave up a wait
+    # fraction of input pixels that changed between consecutive frames of the timed region (mean over the steps)
+    input_activity = float(torch.stack([((frames_dev[2 + Wm + i] - frames_dev[1 + Wm + i]) != 0).any(1).float().mean()
+                                        for i in range(K)]).mean())
 
     # parity of what was just timed: accumulated incremental output vs a dense recompute of the last frame
     dense = make_net()
@@ -479,11 +513,10 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": 1e3 * dev_s / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "streams_per_gpu": streams, "resolution": f"{H}x{W}, reflection-padded to a multiple of 8",
-                       "events_per_window": EVENTS, "segments": SEGMENTS, "compat": "exact", "threshold": args.threshold, "tensor_cores": args.tensor_cores,
-                       "weights": "random init (nn.Conv2d default), seed 0", "parallelism": f"{world} x independent streams",
-                       "l2": "flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
-                       "execution": "one CUDA graph replay per step"},
+            "config": dict(workload_config(args, world),
+                           input_active_pixel_frac=input_activity,
+                           l2="flushed with a 256 MB write before every timed step; one CUDA-event pair per step",
+                           execution="one CUDA graph replay per step"),
             "clocks": clocks, "gpu_launches": launches_per_step * K,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes,
                     "d2h_bytes_per_step": out_bytes, "ms_per_step": 1e3 * e2e_s / K},
@@ -571,10 +604,13 @@ def main():
     ap.add_argument("--events", type=int, default=EVENTS)
     ap.add_argument("--segments", type=int, default=SEGMENTS)
     ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet", "delayedevflownet", "objdet"],
-                    help="secondary measurements of the flow networks (BASELINE config 5: 256x336 two-channel event-count "
-                         "images, 20k events per window); the headline is e2depth")
+                    help="secondary measurements of the flow networks (256x336 two-channel event-count images, 20k events "
+                         "per window); the headline is e2depth")
     ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
                     help="off keeps every convolution on the FP32 path (secondary measurements)")
+    ap.add_argument("--tc-thresholded", action="store_true",
+                    help="with --threshold > 0: let thresholded layers of 32/64/128/256 channels use the tensor cores "
+                         "(default: they run on the FP32 kernel)")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
     args = ap.parse_args()

@@ -280,7 +280,15 @@ int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, f
 int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sensor_h, int sensor_w,
                         float *voxel, int64_t v_ps, int H, int W, int pad_left, int pad_top, void *stream);
 
-/* Split-precision copy of a narrow delta field (C <= a few channels) for the tensor-core convolution, which
+/* Two-channel image of signed event counts of one window: channel 0 = number of events with polarity -1, channel 1 =
+ * with polarity +1, per pixel, as event_histogram (data_fetchers/utils/util.py:62-75) builds on the host with
+ * np.add.at -- the input representation of the flow networks.  events as for mie_events_to_voxel (the time stamp is
+ * not used); image: [1, 2, H, W] channels-last with pixel stride i_ps >= 2, zeroed by this call; (pad_left, pad_top)
+ * place the sensor image inside a larger field. */
+int mie_events_to_count_image(const float *events, int n_events, int sensor_h, int sensor_w, float *image,
+                              int64_t i_ps, int H, int W, int pad_left, int pad_top, void *stream);
+
+/* Split-precision copy of a delta field for the tensor-core convolution, which
  * truncates its inputs to TF32: with half = C rounded up to 8,
  *   out[c] = d[c],  out[half + c] = d[c] - tf32_trunc(d[c]),  out[2*half + c] = d[c];
  * the other channels of `out` (pixel stride out_ps >= 3*half, zero-initialised by the caller) are not written.

@@ -72,6 +72,7 @@ SIGNATURES = {
     "mie_accumulate": (_i, [_vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
     "mie_delta_mask": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp]),
     "mie_events_to_voxel": (_i, [_vp, _i, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
+    "mie_events_to_count_image": (_i, [_vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mie_maxpool_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mie_reflect_border": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mie_split_tf32": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp]),

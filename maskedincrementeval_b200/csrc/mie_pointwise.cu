@@ -783,6 +783,23 @@ __global__ void __launch_bounds__(256) events_to_voxel_kernel(const float *__res
   }
 }
 
+// Signed event counts: channel 0 counts the events of polarity -1, channel 1 those of polarity +1 (any other
+// polarity value is dropped, as the reference's two boolean selections do).  Counts are small integers, exact in
+// fp32, so the atomic summation order does not show.
+__global__ void __launch_bounds__(256) events_to_counts_kernel(const float *__restrict__ ev, int n_events, int sh, int sw,
+                                                               float *__restrict__ img, int64_t ps, int W, int pl, int pt) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_events; i += gridDim.x * blockDim.x) {
+    const float4 e = *reinterpret_cast<const float4 *>(ev + 4 * (size_t)i);
+    const int xi = (int)e.y, yi = (int)e.z;
+    if (xi < 0 || xi >= sw || yi < 0 || yi >= sh) continue;
+    const int ch = (e.w == 1.0f) ? 1 : ((e.w == -1.0f) ? 0 : -1);
+    if (ch < 0) continue;
+    atomicAdd(img + ((int64_t)(yi + pt) * W + (xi + pl)) * ps + ch, 1.0f);
+  }
+}
+
 __global__ void __launch_bounds__(256) kfenced_kernel(const float *__restrict__ dx, int64_t dx_ps, float *__restrict__ carry,
                                                       int64_t c_ps, float k, float *__restrict__ q, int64_t q_ps,
                                                       unsigned *__restrict__ bits32, int N, int C, int H, int W) {
@@ -1011,6 +1028,21 @@ extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bi
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
   launch_chained(events_to_voxel_kernel, dim3(blocks), dim3(256), 0, st, events, n_events, num_bins, sensor_h, sensor_w, voxel, v_ps, H, W, pad_left,
                                                  pad_top);
+  return check_launch();
+}
+
+extern "C" int mie_events_to_count_image(const float *events, int n_events, int sensor_h, int sensor_w, float *image,
+                                         int64_t i_ps, int H, int W, int pad_left, int pad_top, void *stream) {
+  if (!image || n_events < 0 || sensor_h <= 0 || sensor_w <= 0 || H <= 0 || W <= 0 || i_ps < 2) return MIE_EINVAL;
+  if (pad_left < 0 || pad_top < 0 || sensor_h + pad_top > H || sensor_w + pad_left > W) return MIE_EINVAL;
+  if (n_events > 0 && (!events || !aligned16(events))) return events ? MIE_EALIGN : MIE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(image, 0, (size_t)H * W * i_ps * sizeof(float), st);
+  if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
+  if (n_events == 0) return MIE_OK;
+  int blocks = divup(n_events, 256);
+  if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
+  launch_chained(events_to_counts_kernel, dim3(blocks), dim3(256), 0, st, events, n_events, sensor_h, sensor_w, image, i_ps, W, pad_left, pad_top);
   return check_launch();
 }
 

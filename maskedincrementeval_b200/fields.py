@@ -307,6 +307,20 @@ def events_to_voxel(events: torch.Tensor, num_bins: int, sensor_hw, out: torch.T
     return out
 
 
+def events_to_count_image(events: torch.Tensor, sensor_hw, out: torch.Tensor, pad_left: int = 0, pad_top: int = 0):
+    """Count one window of events ([n,4] float32 on the device: t, x, y, polarity) into ``out`` ([1,2,H,W]
+    channels-last: negative counts, positive counts), as the reference's ``event_histogram`` does on the host."""
+    if events.dtype != torch.float32 or not events.is_cuda or not events.is_contiguous():
+        raise RuntimeError("events must be a contiguous float32 CUDA tensor [n, 4]")
+    n, c, h, w = out.shape
+    if n != 1 or c != 2:
+        raise RuntimeError("the count image is [1, 2, H, W]")
+    nat.check(nat.lib.mie_events_to_count_image(events.data_ptr(), events.shape[0], sensor_hw[0], sensor_hw[1],
+                                                out.data_ptr(), pixel_stride(out), h, w, pad_left, pad_top,
+                                                nat.stream_ptr(out.device)), "events_to_count_image")
+    return out
+
+
 def maxpool_incr(d, m: TileMask, res, out, out_bits, k: int, stride: int, pad: int) -> TileMask:
     """out = maxpool(res + d) - maxpool(res); the reservoir is left as it is (advance it with ``accumulate``)."""
     n, c, h, w = d.shape

@@ -146,12 +146,15 @@ class nnReservedActivation(NonlinearPointOpIncr):
 
     def carry_buffer(self, thr: float) -> Optional[torch.Tensor]:
         """The buffer of what has been sent so far; created from the reservoir when first needed."""
-        if thr <= 0.0 or not config.carry:
-            # A step without the carry does not advance this buffer, so it must not survive into a later thresholded
-            # step (it would inject everything that happened in between as one spurious delta): drop it, and let the
-            # next thresholded step rebuild it from the reservoir.
-            self.emitted = None
+        if not config.carry:
+            self.emitted = None      # a step without the carry does not advance it: it must not survive into a later one
             return None
+        if thr <= 0.0 and self.emitted is None:
+            return None              # never thresholded since the last refresh: nothing is pending
+        # Once a thresholded step has run, the buffer stays in use until the next refresh, also while the threshold
+        # is 0: those steps send what is pending at the pixels they touch (dy = f(x + dx) - sent, every non-zero
+        # change is sent) and keep the buffer current, so a later thresholded step starts from the truth.  A buffer
+        # that was left behind instead would inject everything that happened in between as one spurious delta.
         r = self.in_res.reservoir
         if self.emitted is None or self.emitted.shape != r.shape or self.emitted.device != r.device:
             self.emitted = self.op(r).contiguous(memory_format=torch.channels_last)
@@ -192,10 +195,10 @@ class nnReservedActivation(NonlinearPointOpIncr):
         out = self.op(x)
         self.in_res.update_reservoir(x)
         if self.emitted is not None:
-            if self.emitted.shape == out.shape:
+            if self.emitted.shape == out.shape and self.thr() > 0.0 and config.carry:
                 self.emitted.copy_(out)
             else:
-                self.emitted = None
+                self.emitted = None      # nothing is pending after a refresh: a lossless layer needs no carry
         return out
 
 

@@ -52,13 +52,28 @@ class IncrementalRunner:
                    it is the first)
     use_graph      replay the incremental step as a CUDA graph (captured on the second incremental step)
     refresh_every  dense refresh period in frames (None: only when ``refresh`` is called)
+    feedback       feed the recurrent state back (E2Depth only).  The reference's drivers pass ``prev_states=None``
+                   to every incremental step (``run_e2depth_continuous_dataset.py:70``), so as driven the network
+                   computes f(x_t, zero state) - f(x_{t-1}, zero state).  With ``feedback=True`` the runner implements
+                   the protocol ``UNetRecurrentIncr.forward`` is written for (``e2depth_incr.py:410-419``): the
+                   reservoirs a refresh leaves behind are evaluated at (x_0, s_prev), so the first incremental step
+                   is given the state delta ``s_0 - s_prev`` (the dense states themselves after a refresh from the
+                   zero state), every later step the state deltas the step before returned; the accumulated output then
+                   follows the dense recurrent trajectory ``y_t, s_t = refresh(x_t, s_{t-1})``.  The accumulated dense
+                   states are kept too, so a scheduled refresh continues the trajectory instead of restarting it.
+                   Meaningful with ``compat="exact"`` only (as written, the reference's cell delta is a list of four).
     """
 
-    def __init__(self, model, use_graph: bool = True, refresh_every: Optional[int] = None):
+    def __init__(self, model, use_graph: bool = True, refresh_every: Optional[int] = None, feedback: bool = False):
         self.model = model
         self.use_graph = use_graph
         self.refresh_every = refresh_every
         self.takes_states = hasattr(model, "unetrecurrent") or hasattr(model, "encoders") and hasattr(model, "head")
+        if feedback and not self.takes_states:
+            raise ValueError("feedback=True needs a network that takes recurrent states (E2Depth)")
+        self.feedback = feedback
+        self._states = None        # accumulated dense (h, c) per encoder
+        self._prev_incr = None     # state deltas handed to the next incremental step: [(dh, mask_h, dc, mask_c)]
         self._x_prev = self._x_in = self._dx = None
         self._y: List[torch.Tensor] = []
         self._graph = None
@@ -76,14 +91,21 @@ class IncrementalRunner:
         check_device_errors(self.model)
 
     # -- dense pass ------------------------------------------------------------------------------
-    def refresh(self, x: torch.Tensor):
+    def refresh(self, x: torch.Tensor, reset_states: bool = True):
+        """Dense pass on frame ``x``.  ``reset_states=False`` (feedback mode) continues from the accumulated recurrent
+        state instead of the zero state."""
         self.check()
         x = fl.as_channels_last(x)
         if hasattr(self.model, "reset_states"):
             self.model.reset_states()
+        prev = None
+        if self.feedback and not reset_states and self._states is not None:
+            prev = [(h.clone(), c.clone()) for h, c in self._states]
         with torch.no_grad():
-            out = self.model.forward_refresh_reservoirs(x, None) if self.takes_states else \
+            out = self.model.forward_refresh_reservoirs(x, prev) if self.takes_states else \
                 self.model.forward_refresh_reservoirs(x)
+        if self.feedback:
+            self._set_states(out[1], prev)
         ys = _dense_of(out)
         if self._x_prev is None or self._x_prev.shape != x.shape:
             self._x_prev = x.clone(memory_format=torch.channels_last)
@@ -106,12 +128,53 @@ class IncrementalRunner:
         self._frame = 1
         return self._y[0] if len(self._y) == 1 else self._y
 
+    # -- recurrent-state feedback ------------------------------------------------------------------
+    def _set_states(self, states, prev) -> None:
+        """After a refresh that returned the dense ``states`` from the dense ``prev`` (None: zero state): keep the
+        states, and make ``states - prev`` the state delta of the next incremental step."""
+        new_shape = self._states is None or any(a[0].shape != b[0].shape for a, b in zip(self._states, states))
+        if new_shape:
+            self._states = [(fl.as_channels_last(h.detach().clone()), fl.as_channels_last(c.detach().clone()))
+                            for h, c in states]
+            self._prev_incr = []
+            for h, c in self._states:
+                n, _, hh, ww = h.shape
+                self._prev_incr.append((torch.zeros_like(h), fl.new_bits(n, hh, ww, h.device),
+                                        torch.zeros_like(c), fl.new_bits(n, hh, ww, h.device)))
+            self._graph = None
+        else:
+            for (h, c), (hn, cn) in zip(self._states, states):
+                h.copy_(hn)
+                c.copy_(cn)
+        for i, ((h, c), (dh, bh, dc, bc)) in enumerate(zip(self._states, self._prev_incr)):
+            dh.copy_(h if prev is None else h - prev[i][0])
+            dc.copy_(c if prev is None else c - prev[i][1])
+            fl.mask_from_delta(dh, 0.0, bh)
+            fl.mask_from_delta(dc, 0.0, bc)
+
+    def _feed_back(self, states_incr) -> None:
+        """After an incremental step: accumulate its state deltas and keep a copy for the next step (the network's own
+        buffers are overwritten by that step while it still reads them)."""
+        for (h, c), (dh, bh, dc, bc), ((sh, mh), (sc, mc)) in zip(self._states, self._prev_incr, states_incr):
+            fl.accumulate(h, sh, mh)
+            fl.accumulate(c, sc, mc)
+            dh.copy_(sh)
+            bh.copy_(mh.bits)
+            dc.copy_(sc)
+            bc.copy_(mc.bits)
+
     # -- incremental pass ------------------------------------------------------------------------
     def _step_body(self):
         # input delta, previous-frame update and input mask in one kernel
         m_in = fl.delta_mask(self._x_in, self._x_prev, self._dx, self._dx_bits, fl.config.input_threshold)
         x_incr = (self._dx, m_in)
-        out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
+        if self.feedback:
+            prev = [([dh, TileMask(bh, *dh.shape[:1], *dh.shape[2:])], [dc, TileMask(bc, *dc.shape[:1], *dc.shape[2:])])
+                    for dh, bh, dc, bc in self._prev_incr]
+            out = self.model(x_incr, prev)
+            self._feed_back(out[1])
+        else:
+            out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
         for y, d in zip(self._y, _deltas_of(out)):
             m = d[1]
             if isinstance(m, TileMask):
@@ -123,7 +186,7 @@ class IncrementalRunner:
         if self._x_prev is None:
             raise RuntimeError("call refresh() on the first frame")
         if self.refresh_every and self._frame % self.refresh_every == 0:
-            return self.refresh(x)
+            return self.refresh(x, reset_states=not self.feedback)
         self._x_in.copy_(x, non_blocking=True)
         return self._advance()
 
@@ -149,8 +212,10 @@ class IncrementalRunner:
         return self._y[0] if len(self._y) == 1 else self._y
 
     # -- raw events in ------------------------------------------------------------------------------
-    def step_events(self, events, sensor_hw, num_bins: Optional[int] = None):
-        """One incremental step fed with the raw events of a window instead of a voxel grid.
+    def step_events(self, events, sensor_hw, num_bins: Optional[int] = None, representation: str = "voxel"):
+        """One incremental step fed with the raw events of a window instead of a voxel grid
+        (``representation="counts"``: instead of a two-channel signed count image, the flow networks' input,
+        binned as the reference's ``event_histogram`` does).
 
         ``events``: one device tensor [n_events, 4] (t in [0,1), x, y, polarity) per stream.  The events are binned
         on the device straight into the network's input buffer (temporal-bilinear, spatial-nearest, as the
@@ -168,7 +233,12 @@ class IncrementalRunner:
         pl, pt = (w - sw) // 2, (h - sh) // 2
         for s, ev in enumerate(events):
             grid = self._x_in[s:s + 1]
-            fl.events_to_voxel(ev, num_bins or c, (sh, sw), grid, pl, pt)
+            if representation == "counts":
+                fl.events_to_count_image(ev, (sh, sw), grid, pl, pt)
+            elif representation == "voxel":
+                fl.events_to_voxel(ev, num_bins or c, (sh, sw), grid, pl, pt)
+            else:
+                raise ValueError("representation must be 'voxel' or 'counts'")
             if (h, w) != (sh, sw):
                 fl.reflect_border(grid, (sh, sw), pl, pt)
         return self._advance()

@@ -33,12 +33,12 @@ import types
 import torch
 import torch.nn as nn
 
-# where a checkout of the reference lives; MIE_REFERENCE_ROOT overrides the default location
-DEFAULT_ROOT = os.environ.get("MIE_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# where a checkout of the reference lives: named by the caller or by MIE_REFERENCE_ROOT, never guessed
+DEFAULT_ROOT = os.environ.get("MIE_REFERENCE_ROOT", "")
 
 
 def reference_available(root: str = DEFAULT_ROOT) -> bool:
-    return os.path.isfile(os.path.join(root, "incr_modules", "mask_incr_modules.py"))
+    return bool(root) and os.path.isfile(os.path.join(root, "incr_modules", "mask_incr_modules.py"))
 
 
 class _NullStream:

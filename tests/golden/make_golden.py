@@ -213,7 +213,42 @@ def main(ref_root: str = DEFAULT_ROOT):
             d = _sparse_delta(g, x.shape, frac=frac)
             out[f"d{s}"], out[f"dy{s}"] = _np(d), _np(net([d, None])[0])
         np.savez_compressed(os.path.join(OUT, tag + ".npz"), **out)
+    binning_golden(ref_root)
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))
+
+
+def binning_golden(ref_root: str):
+    """Event binning of the reference's data fetchers (``data_fetchers/utils/util.py:62-110``): the voxel grid of
+    ``events_to_voxel_grid_absT`` and the count image of ``event_histogram`` on seeded event windows, including
+    polarity 0 (counted as -1 by the voxel grid, dropped by the histogram), a time stamp in the last bin and an empty
+    window.  The module is loaded by path; ``np.int`` (removed from numpy 2, used at ``util.py:64-65``) is aliased to
+    ``int`` for the call."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_data_util", os.path.join(ref_root, "data_fetchers", "utils", "util.py"))
+    util = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(util)
+    if not hasattr(np, "int"):
+        np.int = int
+    from maskedincrementeval_b200.synthetic import EdgeEventStream
+    out = {}
+    h, w, bins = 40, 56, 5
+    stream = EdgeEventStream(h, w, 3000, 6, seed=71)
+    for i in range(3):
+        ev = stream.window()                           # [n, 4]: t in [0, 1), x, y, p in {-1, +1}
+        if i == 1:
+            ev[:7, 3] = 0.0                            # polarity 0
+            ev[7, 0] = 0.999999                        # lands in the last bin with almost all its weight
+            ev[8, 0] = 0.0
+        if i == 2:
+            ev = ev[:0]                                # empty window
+        out[f"ev{i}"] = ev.copy()
+        ns = ev.copy()
+        ns[:, 0] = ns[:, 0] * 1e9                      # the reference takes nanoseconds, a start time and a window length
+        out[f"vox{i}"] = np.asarray(util.events_to_voxel_grid_absT(ns, bins, h, w, 1.0, 0.0), dtype=np.float32).copy()
+        hist = util.event_histogram(ev.copy(), w, h) if ev.shape[0] else np.zeros((h, w, 2), np.float32)
+        out[f"hist{i}"] = np.asarray(hist, dtype=np.float32)       # [H, W, 2] = (negative, positive)
+    out["hwb"] = np.array([h, w, bins])
+    np.savez_compressed(os.path.join(OUT, "binning.npz"), **out)
 
 
 if __name__ == "__main__":

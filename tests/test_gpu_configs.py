@@ -42,7 +42,7 @@ def rel_err(a, b):
 
 
 class Chain(torch.nn.Module):
-    """BASELINE config 2: conv3x3 32->64 stride 2, sigmoid, conv3x3 64->64, tanh, x2 nearest upsample, skip-add."""
+    """Layer chain: conv3x3 32->64 stride 2, sigmoid, conv3x3 64->64, tanh, x2 nearest upsample, skip-add."""
 
     def __init__(self):
         super().__init__()

@@ -1,0 +1,133 @@
+"""Drift over 64 timesteps at full size: the accumulated incremental output of every network against a dense
+recompute of the same network on the same frame (compat="exact"), with the FP32 kernels only (bar 1e-4 of the output
+range) and with the tensor-core path enabled (bar 2e-3), the steps replayed as a CUDA graph as the runner does in
+production.  Two weight initialisations: PyTorch's default (what the reference's random-init networks have; the signal
+decays about tenfold per level, so the deep layers see changes of 1e-5) and Kaiming-normal (unit gain: every layer
+carries signal).  After the last step the persistent state of every layer -- each activation's accumulated
+pre-activation, the ConvLSTM gate and cell state -- is compared with the state the dense recompute leaves behind, layer
+by layer, so that an error in a deep layer cannot hide behind the decay.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from maskedincrementeval_b200.synthetic import count_image_sequence, seeded_state_dict, voxel_sequence  # noqa: E402
+from test_oracle import e2depth_shapes, flow_shapes_delayed, flow_shapes_ev, flow_shapes_fire  # noqa: E402
+
+STEPS = 64
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True, params=["off", "auto"])
+def tc_mode(request):
+    from maskedincrementeval_b200 import fields as fl
+    old = (fl.config.tensor_cores, fl.config.compat)
+    fl.config.tensor_cores = request.param
+    yield request.param
+    fl.config.tensor_cores, fl.config.compat = old
+
+
+def tol():
+    from maskedincrementeval_b200 import fields as fl
+    return 1e-4 if fl.config.tensor_cores == "off" else 2e-3
+
+
+def rel_err(a, b):
+    rng = max(float(b.max() - b.min()), 1e-12)
+    return float((a - b).abs().max()) / rng
+
+
+def layer_states(net):
+    """name -> persistent pre-activation state of every stateful layer."""
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLSTMIncr
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import nnReservedActivation
+    out = {}
+    for name, m in net.named_modules():
+        if isinstance(m, ConvLSTMIncr) and m._g is not None:
+            out[name + ".gates"], out[name + ".cell"] = m._g, m._cell
+        elif isinstance(m, nnReservedActivation) and m.in_res.reservoir is not None and m.in_res.reservoir.dim() == 4:
+            if ".recurrent_block." in "." + name + "." and ("sigmoid" in name or "tanh" in name):
+                continue        # views of the ConvLSTM gate state, compared above
+            out[name] = m.in_res.reservoir
+    return out
+
+
+def run_drift(dev, make, sd, frames, first_of, check_at=(1, 16, 32, 48, STEPS)):
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    net, dense = make().to(dev).eval(), make().to(dev).eval()
+    net.load_state_dict(sd), dense.load_state_dict(sd)
+    run = IncrementalRunner(net, use_graph=True)
+    worst = 0.0
+    with torch.no_grad():
+        run.refresh(frames[0])
+        for i in range(1, len(frames)):
+            y = run.step(frames[i])
+            if i in check_at:
+                if hasattr(dense, "reset_states"):
+                    dense.reset_states()
+                yd = first_of(dense, frames[i])
+                ys = y if isinstance(y, (list, tuple)) else [y]
+                yds = yd if isinstance(yd, (list, tuple)) else [yd]
+                for a, b in zip(ys, yds):
+                    worst = max(worst, rel_err(a, b))
+        run.check()
+    assert run.graph_replays >= len(frames) - 3
+    # layer by layer: the state the incremental steps accumulated against the state of the dense pass just made
+    per_layer = {}
+    si, sd_ = layer_states(net), layer_states(dense)
+    assert si.keys() == sd_.keys() and len(si) >= 4
+    for k in si:
+        per_layer[k] = rel_err(si[k], sd_[k])
+    return worst, per_layer
+
+
+def e2depth_dense(m, x):
+    return m.forward_refresh_reservoirs(x, None)[0]
+
+
+@pytest.mark.parametrize("init", ["default", "kaiming_normal"])
+def test_e2depth_264x352_64_steps(dev, init):
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    make = lambda: E2VIDRecurrentIncr(dict(num_bins=5, num_encoders=3, base_num_channels=32, num_residual_blocks=2,
+                                           skip_type="sum", norm=None, use_upsample_conv=True, compat="exact"))
+    sd = seeded_state_dict(e2depth_shapes(32), 0, init)
+    frames = [f.to(dev) for f in voxel_sequence(1, 260, 346, STEPS + 1, 30000, 10, seed=21)]
+    worst, per_layer = run_drift(dev, make, sd, frames, e2depth_dense)
+    assert worst <= tol(), worst
+    bad = {k: v for k, v in per_layer.items() if v > tol()}
+    assert not bad, bad
+
+
+def flow_dense(m, x):
+    out = m.forward_refresh_reservoirs(x)
+    return list(out["flow"]) if isinstance(out, dict) else list(out)
+
+
+@pytest.mark.parametrize("net_name", ["fireflownet", "evflownet", "delayedevflownet"])
+@pytest.mark.parametrize("init", ["default", "kaiming_normal"])
+def test_flow_nets_256x336_64_steps(dev, net_name, init):
+    kw = dict(base_num_channels=32, kernel_size=3, mask_output=False)
+    if net_name == "fireflownet":
+        from maskedincrementeval_b200.incr_modules.fireflownet_incr import FireFlowNetIncr
+        make, shapes, streams = (lambda: FireFlowNetIncr(kw, 2, compat="exact")), flow_shapes_fire(32), 2
+    elif net_name == "evflownet":
+        from maskedincrementeval_b200.incr_modules.evflownet_incr import MultiResUNetRecurrentIncr
+        make, shapes, streams = (lambda: MultiResUNetRecurrentIncr(compat="exact")), flow_shapes_ev(), 1
+    else:
+        from maskedincrementeval_b200.incr_modules.delayedevflownet_incr import DelayedEVFlowNetIncr
+        make, shapes, streams = (lambda: DelayedEVFlowNetIncr(kw, 2, compat="exact")), flow_shapes_delayed(32), 1
+    sd = seeded_state_dict(shapes, 2, init)
+    frames = [f.to(dev) for f in count_image_sequence(streams, 256, 336, STEPS + 1, 20000, 10, seed=22)]
+    worst, per_layer = run_drift(dev, make, sd, frames, flow_dense)
+    assert worst <= tol(), worst
+    bad = {k: v for k, v in per_layer.items() if v > tol()}
+    assert not bad, bad

@@ -222,6 +222,43 @@ def test_driver_protocol_with_graph_replay(dev):
     assert run.graph_replays >= 3
 
 
+def test_runner_state_feedback_tracks_dense_recurrence(dev):
+    """IncrementalRunner(feedback=True): the state deltas of every step are fed to the next one (after a refresh, the
+    dense states themselves), so the accumulated output follows the dense recurrent trajectory
+    y_t, s_t = refresh(x_t, s_{t-1}) -- the protocol UNetRecurrentIncr.forward takes its prev_states_incr for
+    (e2depth_incr.py:410-419), which none of the reference's drivers exercises.  Weights at twice the Kaiming scale so
+    that the recurrent layers carry signal; a scheduled refresh in the middle continues the trajectory."""
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    cfg = dict(num_bins=5, num_encoders=3, base_num_channels=8, num_residual_blocks=2, skip_type="sum", norm=None,
+               use_upsample_conv=True, compat="exact")
+    sd = seeded_state_dict(e2depth_shapes(8), 9, "kaiming_normal", gain=2.0)
+    net, dense = E2VIDRecurrentIncr(cfg).to(dev).eval(), E2VIDRecurrentIncr(cfg).to(dev).eval()
+    net.load_state_dict(sd), dense.load_state_dict(sd)
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(1, 5, 64, 96, generator=g)
+    run = IncrementalRunner(net, use_graph=True, feedback=True, refresh_every=6)
+    with torch.no_grad():
+        y = run.refresh(cl(x, dev))
+        yd, s = dense.forward_refresh_reservoirs(cl(x, dev), None)
+        close(y, yd, 1e-6)
+        worst, moved = 0.0, 0.0
+        for step in range(10):
+            x = x + sparse_delta(g, x.shape, 0.1)
+            y = run.step(cl(x, dev))
+            s_prev = [(h.clone(), c.clone()) for h, c in s]
+            yd, s = dense.forward_refresh_reservoirs(cl(x, dev), s_prev)
+            y0, _ = dense.forward_refresh_reservoirs(cl(x, dev), None)     # what the feedback-free protocol tracks
+            rng = float(yd.max() - yd.min())
+            worst = max(worst, float((y - yd).abs().max()) / rng)
+            moved = max(moved, float((y0 - yd).abs().max()) / rng)
+            for (h, c), (hr, cr) in zip(s, run._states):
+                close(hr, h, TOL(), rng=2.0)
+        assert worst <= TOL(), worst
+        assert moved > max(10 * worst, 1e-3)   # the recurrent state matters here: without feedback the output differs
+    assert run.graph_replays >= 4
+
+
 def test_runner_step_host_matches_step(dev):
     """The pipelined host interface (uploads and downloads on side streams, no host wait) produces the outputs of
     the plain step() loop, and every step's prediction arrives in its pinned buffer."""

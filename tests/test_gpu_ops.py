@@ -525,6 +525,29 @@ def test_events_to_voxel_matches_host_binning(dev):
     assert float(out.abs().sum() - got.abs().sum()) == 0.0   # nothing outside the sensor area
 
 
+def test_event_binning_kernels_match_reference_golden(dev, golden):
+    """mie_events_to_voxel and mie_events_to_count_image against vectors made by the reference's host binning
+    (``data_fetchers/utils/util.py:62-110``): counts exact; voxel weights to fp32 rounding of the time stamp and the
+    atomic summation order.  Polarity 0 counts as -1 in the voxel grid and is dropped by the count image."""
+    from maskedincrementeval_b200 import fields as fl
+    g = golden("binning")
+    h, w, bins = (int(v) for v in g["hwb"])
+    for i in range(3):
+        ev = torch.from_numpy(g[f"ev{i}"].astype("float32")).contiguous().to(dev)
+        vox = fl.new_field(1, bins, h + 8, w + 16, dev)
+        vox.fill_(7.0)                                        # the call zeroes its output
+        fl.events_to_voxel(ev, bins, (h, w), vox, 8, 4)
+        got = vox[0, :, 4:4 + h, 8:8 + w].cpu()
+        want = T(g[f"vox{i}"])
+        assert float((got - want).abs().max()) <= 2e-5 * max(float(want.abs().max()), 1.0)
+        assert float(vox.abs().sum() - got.abs().sum()) == 0.0      # nothing outside the sensor area
+        img = fl.new_field(1, 2, h + 8, w + 16, dev)
+        img.fill_(7.0)
+        fl.events_to_count_image(ev, (h, w), img, 8, 4)
+        assert torch.equal(img[0, :, 4:4 + h, 8:8 + w].cpu(), T(g[f"hist{i}"]).permute(2, 0, 1))
+        assert float(img.sum()) == float(T(g[f"hist{i}"]).sum())
+
+
 def test_kfenced_kernel_golden(dev, golden):
     from maskedincrementeval_b200.incr_modules.mask_incr_modules import KFencedMaskModule
     g = golden("misc_ops")

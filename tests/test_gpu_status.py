@@ -230,9 +230,10 @@ def test_thresholded_odd_channel_count_same_on_both_settings(dev):
             _thresholded_run(dev, (64, 96, 3, 1, 24, 40, False), tc_thresholded=flag, steps=1)
 
 
-def test_carry_dropped_when_threshold_switched_off(dev):
-    """threshold 0.05 -> 0 -> 0.05: the steps run lossless in between do not advance the carry buffer, so it is dropped
-    and rebuilt; the total sent stays within the threshold of the true output after the switch back."""
+def test_carry_survives_threshold_toggle(dev):
+    """threshold 0.05 -> 0 -> 0.05: once a thresholded step has run, the carry buffer stays in use while the threshold
+    is 0 (those steps send what is pending where they touch), so the total sent stays within the threshold of the true
+    output throughout; a refresh under threshold 0 drops the buffer."""
     from maskedincrementeval_b200 import fields as fl
     fl.config.tensor_cores = "off"
     layer = _layer(dev, 16, 32, 3, 1, "tanh")
@@ -246,8 +247,14 @@ def test_carry_dropped_when_threshold_switched_off(dev):
             sent += dy
             truth = torch.tanh(layer.activation.in_res.reservoir)
             assert float((sent - truth).abs().max()) <= 0.05 + 1e-5
-            if thr == 0.0:
-                assert layer.activation.emitted is None
+            assert layer.activation.emitted is not None
+        fl.config.threshold = 0.0
+        layer.forward_refresh_reservoirs(cl(x0, dev))
+        assert layer.activation.emitted is None
+        fl.config.carry = False
+        fl.config.threshold = 0.05
+        layer([cl(sparse_delta(g, x0.shape, 0.2, std=0.1), dev), None])
+        assert layer.activation.emitted is None
 
 
 # ------------------------------------------------------------------------------------------------

@@ -377,3 +377,16 @@ def test_live_reference_e2depth_and_flow():
             close(orc.step(d)[0], net([d, None], None)[0][0], 2e-6)
         ev = ref.evflownet.MultiResUNetRecurrentIncr().eval()
         assert {k: tuple(v.shape) for k, v in ev.state_dict().items()} == flow_shapes_ev()
+
+
+def test_host_binning_matches_reference_golden(golden):
+    """``synthetic.events_to_voxel_grid`` / ``events_to_count_image`` against vectors the reference's own
+    ``events_to_voxel_grid_absT`` / ``event_histogram`` (``data_fetchers/utils/util.py:62-110``) produced:
+    bit for bit, including polarity 0, the last-bin time stamp and the empty window."""
+    from maskedincrementeval_b200.synthetic import events_to_count_image, events_to_voxel_grid
+    g = golden("binning")
+    h, w, bins = (int(v) for v in g["hwb"])
+    for i in range(3):
+        ev = g[f"ev{i}"]
+        assert np.array_equal(events_to_voxel_grid(ev.copy(), bins, h, w), g[f"vox{i}"])
+        assert np.array_equal(events_to_count_image(ev.copy(), h, w), g[f"hist{i}"].transpose(2, 0, 1))
