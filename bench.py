@@ -343,6 +343,153 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
                      "timing": "one launch per CUDA-event pair, L2 flushed before each"}}
 
 
+def roofline_other_kernels(dev, peak_gbs, peak_kind):
+    """Achieved bandwidth of the kernels of a step other than the convolutions, each at a size it has in this network
+    and at full activity (what the lossless headline run gives them).  Every kernel is launched over several
+    independent sets of buffers that together exceed L2 twice over, back to back inside one CUDA graph, so each
+    launch finds its data in DRAM; the figure is algorithmic bytes / mean launch time."""
+    from maskedincrementeval_b200 import _native as nat
+    from maskedincrementeval_b200 import fields as fl
+    out = []
+    g = torch.Generator().manual_seed(0)
+
+    def field(n, c, h, w, scale=0.1):
+        return (torch.randn(n, c, h, w, generator=g) * scale).to(dev).contiguous(memory_format=torch.channels_last)
+
+    def full_bits(n, h, w):
+        return fl.mask_from_delta(torch.ones(n, 1, h, w, device=dev).contiguous(memory_format=torch.channels_last), 0.0)
+
+    def measure(name, workload, bytes_per_launch, make_set, launch, note=""):
+        set_bytes = max(bytes_per_launch, 1)
+        n_sets = max(2, min(64, int(2.2 * 126e6 / set_bytes) + 1))
+        sets = [make_set() for _ in range(n_sets)]
+        st = torch.cuda.Stream(dev)
+        st.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(st), torch.no_grad():
+            for s_ in sets:
+                launch(s_)
+            st.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                for s_ in sets:
+                    launch(s_)
+            graph.replay()
+            passes = 6
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(passes):
+                graph.replay()
+            e1.record(st)
+            e1.synchronize()
+        torch.cuda.current_stream(dev).wait_stream(st)
+        us = 1e3 * e0.elapsed_time(e1) / (passes * n_sets)
+        gbs = bytes_per_launch / (us * 1e-6) / 1e9
+        out.append({"kernel": name, "workload": workload, "bound": "hbm", "bytes_per_launch": bytes_per_launch,
+                    "us_per_launch": us, "achieved": gbs, "peak": peak_gbs, "unit": "GB/s", "frac": gbs / peak_gbs,
+                    "peak_kind": f"of {peak_kind}", "launches": passes * n_sets, "buffer_sets": n_sets, "note": note})
+
+    # ConvLSTM point kernel, encoder 0 (64 channels at 132x176), no previous-cell input as the drivers run it
+    n, c, h, w = 1, 64, 132, 176
+    px = n * h * w
+    def lstm_set():
+        m = full_bits(n, h, w)
+        return dict(dg=field(n, 4 * c, h, w), m=m, gs=field(n, 4 * c, h, w, 1.0), cell=field(n, c, h, w, 1.0),
+                    dh=fl.new_field(n, c, h, w, dev), dc=fl.new_field(n, c, h, w, dev), hb=fl.new_bits(n, h, w, dev),
+                    cb=fl.new_bits(n, h, w, dev))
+    def lstm_launch(s_):
+        nat.check(nat.lib.mie_convlstm_point(s_["dg"].data_ptr(), 4 * c, s_["m"].bits.data_ptr(), s_["gs"].data_ptr(), 4 * c,
+                                             None, 0, None, None, 0, s_["cell"].data_ptr(), c, s_["dh"].data_ptr(), c,
+                                             s_["hb"].data_ptr(), s_["dc"].data_ptr(), c, s_["cb"].data_ptr(), n, c, h, w, 1, 0.0,
+                                             nat.stream_ptr(dev)), "convlstm_point")
+    measure("convlstm_point_vec_kernel", f"ConvLSTM point ops, {c} ch, {h}x{w}, all pixels active",
+            px * c * 4 * (4 + 4 + 4 + 2 + 2), lstm_set, lstm_launch,
+            "per pixel and channel: 4 gate deltas read, 4 gate states read + written, cell read + written, 2 outputs written")
+
+    # x2 bilinear upsample of (a + b), decoder 2's input (64 channels, 132x176 -> 264x352)
+    def up_set():
+        return dict(a=field(n, c, h, w), b=field(n, c, h, w), ma=full_bits(n, h, w), mb=full_bits(n, h, w),
+                    out=fl.new_field(n, c, 2 * h, 2 * w, dev), ob=fl.new_bits(n, 2 * h, 2 * w, dev))
+    measure("upsample2x_vec_kernel", f"x2 bilinear upsample of the sum of two fields, {c} ch, {h}x{w} -> {2 * h}x{2 * w}",
+            px * c * 4 * 2 + 4 * px * c * 4, up_set,
+            lambda s_: fl.upsample2x(s_["a"], s_["ma"], s_["b"], s_["mb"], s_["out"], s_["ob"]),
+            "both inputs read once, output written once (each input pixel feeds four outputs out of cache)")
+
+    # stand-alone incremental activation, 32 channels at 264x352
+    n2, c2, h2, w2 = 1, 32, 264, 352
+    px2 = n2 * h2 * w2
+    def act_set():
+        return dict(d=field(n2, c2, h2, w2), m=full_bits(n2, h2, w2), res=field(n2, c2, h2, w2, 1.0),
+                    out=fl.new_field(n2, c2, h2, w2, dev), ob=fl.new_bits(n2, h2, w2, dev))
+    measure("act_incr_kernel", f"incremental ReLU, {c2} ch, {h2}x{w2}, all pixels active", px2 * c2 * 4 * 4, act_set,
+            lambda s_: fl.act_incr(s_["d"], s_["m"], s_["res"], None, s_["out"], s_["ob"], nat.ACT_RELU, 0.0),
+            "delta read, reservoir read + written, output written")
+
+    # incremental product, 64 channels at 132x176
+    def mul_set():
+        return dict(d1=field(n, c, h, w), d2=field(n, c, h, w), m1=full_bits(n, h, w), m2=full_bits(n, h, w),
+                    x1=field(n, c, h, w, 1.0), x2=field(n, c, h, w, 1.0), out=fl.new_field(n, c, h, w, dev),
+                    ob=fl.new_bits(n, h, w, dev))
+    measure("mul_incr_kernel", f"incremental product, {c} ch, {h}x{w}, all pixels active", px * c * 4 * 7, mul_set,
+            lambda s_: fl.mul_incr(s_["d1"], s_["m1"], s_["x1"], s_["d2"], s_["m2"], s_["x2"], s_["out"], s_["ob"]),
+            "2 deltas read, 2 reservoirs read + written, output written")
+
+    # skip sum of two fields, 32 channels at 264x352
+    def add_set():
+        return dict(a=field(n2, c2, h2, w2), b=field(n2, c2, h2, w2), ma=full_bits(n2, h2, w2), mb=full_bits(n2, h2, w2),
+                    out=fl.new_field(n2, c2, h2, w2, dev), ob=fl.new_bits(n2, h2, w2, dev))
+    measure("add_vec_kernel", f"sum of two delta fields, {c2} ch, {h2}x{w2}", px2 * c2 * 4 * 3, add_set,
+            lambda s_: fl.add(s_["a"], s_["ma"], s_["b"], s_["mb"], s_["out"], s_["ob"]))
+
+    # channel concatenation (input + previous hidden state of a ConvLSTM), 64 + 64 channels at 132x176
+    def cat_set():
+        return dict(a=field(n, c, h, w), b=field(n, c, h, w), ma=full_bits(n, h, w), mb=full_bits(n, h, w),
+                    out=fl.new_field(n, 2 * c, h, w, dev), ob=fl.new_bits(n, h, w, dev))
+    measure("cat2_kernel", f"channel concatenation {c} + {c} ch, {h}x{w}", px * c * 4 * 4, cat_set,
+            lambda s_: fl.cat2(s_["a"], s_["ma"], s_["b"], s_["mb"], s_["out"], s_["ob"]))
+
+    # output accumulation y += dy, 1 channel at 264x352 (the prediction)
+    def acc_set():
+        return dict(y=field(n2, 1, h2, w2, 1.0), d=field(n2, 1, h2, w2), m=full_bits(n2, h2, w2))
+    measure("accumulate_kernel", f"y += dy, 1 ch, {h2}x{w2}", px2 * 4 * 3, acc_set,
+            lambda s_: fl.accumulate(s_["y"], s_["d"], s_["m"]), "latency-bound at this size (1.1 MB)")
+
+    # input delta + mask, 5 voxel bins at 264x352 (pixel stride 8)
+    def dm_set():
+        full = torch.zeros(n2, 8, h2, w2, device=dev).contiguous(memory_format=torch.channels_last)
+        return dict(x=field(n2, 5, h2, w2, 1.0), xp=field(n2, 5, h2, w2, 1.0), dx=full[:, :5], bits=fl.new_bits(n2, h2, w2, dev))
+    measure("delta_mask_kernel", f"input delta, previous-frame update and mask, 5 bins, {h2}x{w2}", px2 * 5 * 4 * 4, dm_set,
+            lambda s_: fl.delta_mask(s_["x"], s_["xp"], s_["dx"], s_["bits"], 0.0),
+            "frame read, previous frame read + written, delta written")
+
+    # mask words of a 32-channel field
+    def mw_set():
+        return dict(d=field(n2, c2, h2, w2), bits=fl.new_bits(n2, h2, w2, dev))
+    measure("mask_words_kernel", f"tile words of a {c2}-channel field, {h2}x{w2}", px2 * c2 * 4 + fl.n_tiles(n2, h2, w2) * 8, mw_set,
+            lambda s_: fl.mask_from_delta(s_["d"], 1e-3, s_["bits"]))
+
+    # split-precision copy of a 32-channel field (the pass in front of a split-precision convolution)
+    def sp_set():
+        return dict(d=field(n2, c2, h2, w2), m=full_bits(n2, h2, w2), out=fl.new_field(n2, 3 * c2, h2, w2, dev),
+                    ob=fl.new_bits(n2, h2, w2, dev))
+    measure("split_tf32_kernel", f"split-precision copy, {c2} ch, {h2}x{w2}", px2 * c2 * 4 * 4, sp_set,
+            lambda s_: fl.split_tf32(s_["d"], s_["m"], s_["out"], s_["ob"]), "field read, three copies written")
+
+    # tile dilation of a full 33x44-tile mask for a 3x3 convolution: a latency-bound single-block kernel
+    def dil_set():
+        nt = fl.n_tiles(n2, h2, w2)
+        return dict(m=full_bits(n2, h2, w2), ob=fl.new_bits(n2, h2, w2, dev), lst=torch.zeros(nt, dtype=torch.int32, device=dev),
+                    stale=torch.zeros(nt, dtype=torch.int32, device=dev), cnt=torch.zeros(4, dtype=torch.int32, device=dev),
+                    flags=torch.zeros(nt, dtype=torch.uint8, device=dev))
+    def dil_launch(s_):
+        nat.check(nat.lib.mie_tiles_dilate(s_["m"].bits.data_ptr(), n2, h2, w2, h2, w2, 3, 1, 1, None, s_["ob"].data_ptr(),
+                                           s_["lst"].data_ptr(), s_["stale"].data_ptr(), s_["cnt"].data_ptr(),
+                                           s_["flags"].data_ptr(), nat.stream_ptr(dev)), "tiles_dilate")
+    nt = fl.n_tiles(n2, h2, w2)
+    measure("tiles_dilate_kernel", f"dilated tile set + ordered lists, {nt} tiles, 3x3", nt * (9 * 8 + 8 + 8 + 4), dil_set, dil_launch,
+            "latency-bound: a few KB of words; the figure is launch latency, not bandwidth")
+    return out
+
+
 def run_ours(args):
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))
@@ -378,6 +525,9 @@ def run_ours(args):
     def build_net():
         if args.net == "fireflownet":
             return FireFlowNetIncr(dict(base_num_channels=32, kernel_size=3, mask_output=False), 2, compat="exact")
+        if args.net == "recfireflownet":
+            from maskedincrementeval_b200.incr_modules.fireflownet_incr import RecurrentFireFlowNetIncr
+            return RecurrentFireFlowNetIncr(dict(base_num_channels=32, kernel_size=3, mask_output=False), 2, compat="exact")
         if args.net == "evflownet":
             return MultiResUNetRecurrentIncr(compat="exact")
         if args.net == "delayedevflownet":
@@ -533,6 +683,7 @@ def run_ours(args):
         if world == 1 and not flow:
             peak, kind = load_peaks()
             line["roofline"] = roofline_conv3x3(dev, peak, kind)
+            line["roofline_kernels"] = roofline_other_kernels(dev, peak, kind)
             # dense recompute (the >=10x target's denominator), same frames
             def time_dense(tf32):
                 torch.backends.cudnn.allow_tf32 = tf32
@@ -603,7 +754,7 @@ def main():
     ap.add_argument("--size", default="260x346", help="sensor resolution HxW (secondary measurements; the headline is 260x346)")
     ap.add_argument("--events", type=int, default=EVENTS)
     ap.add_argument("--segments", type=int, default=SEGMENTS)
-    ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "evflownet", "delayedevflownet", "objdet"],
+    ap.add_argument("--net", default="e2depth", choices=["e2depth", "fireflownet", "recfireflownet", "evflownet", "delayedevflownet", "objdet"],
                     help="secondary measurements of the flow networks (256x336 two-channel event-count images, 20k events "
                          "per window); the headline is e2depth")
     ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
@@ -613,6 +764,8 @@ def main():
                          "(default: they run on the FP32 kernel)")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
+    ap.add_argument("--roofline-kernels-only", action="store_true",
+                    help="run only the point-operation kernels at their sizes in this network and print their roofline objects")
     args = ap.parse_args()
     H, W = (int(v) for v in args.size.split("x"))
     EVENTS, SEGMENTS = args.events, args.segments
@@ -624,12 +777,15 @@ def main():
         WORKLOAD = f"{args.net}_{H}x{W}_b{args.streams}"
     elif (H, W) != (260, 346) or args.streams != 1:
         WORKLOAD = f"e2depth_{H}x{W}_b{args.streams}"
-    if args.roofline_only:
+    if args.roofline_only or args.roofline_kernels_only:
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(0)
         torch.backends.cudnn.allow_tf32 = False
         peak, kind = load_peaks()
-        print(json.dumps(roofline_conv3x3(dev, peak, kind, repeats=1)))
+        if args.roofline_only:
+            print(json.dumps(roofline_conv3x3(dev, peak, kind, repeats=1)))
+        else:
+            print(json.dumps(roofline_other_kernels(dev, peak, kind)))
         return
     if args.warmup < 3:
         args.warmup = 3

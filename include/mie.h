@@ -199,20 +199,21 @@ int mie_conv_increment_ext(const float *x_incr, const void *mask, int mask_elem_
  * whose input words are all zero (clearing stale output there) and keep the zero invariant.
  * ------------------------------------------------------------------------------------------- */
 
-/* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx; out mask = any_c |dy| > thr.
- * nnReservedActivation.forward, incr_modules/mask_incr_modules.py:248-251.
+/* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx when `accumulate` is non-zero; out mask = any_c |dy| > thr.
+ * accumulate = 1: nnReservedActivation.forward, incr_modules/mask_incr_modules.py:248-251;
+ * accumulate = 0: NonlinearPointOpIncr.forward against a reservoir some other module advances, :101-103 (no carry then).
  * in/out may alias (in place) when in_ps == out_ps. */
 int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
                  float *emitted, int64_t emitted_ps, float *out, int64_t out_ps, uint64_t *out_bits,
-                 int N, int C, int H, int W, int op, float thr, void *stream);
+                 int N, int C, int H, int W, int op, float thr, int accumulate, void *stream);
 
-/* out = (d2 + x2)*d1 + x1*d2; x1 += d1; x2 += d2.  Either delta may be null (all zero).
- * IncrPointwiseMultiply + nnReservedMultiplication.forward,
- * incr_modules/mask_incr_functional.py:52-54, incr_modules/mask_incr_modules.py:71-75. */
+/* out = (d2 + x2)*d1 + x1*d2; with `accumulate` non-zero also x1 += d1; x2 += d2.  Either delta may be null (all zero).
+ * accumulate = 0: IncrPointwiseMultiply, incr_modules/mask_incr_functional.py:52-54 (reservoirs only read);
+ * accumulate = 1: nnReservedMultiplication.forward, incr_modules/mask_incr_modules.py:71-75. */
 int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x1, int64_t x1_ps,
                  const float *d2, int64_t d2_ps, const uint64_t *bits2, float *x2, int64_t x2_ps,
                  float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, float thr,
-                 void *stream);
+                 int accumulate, void *stream);
 
 /* The point-wise part of ConvLSTMIncr.forward (incr_modules/e2depth_incr.py:103-120) in one pass:
  * gate pre-activation deltas dg [N,4C,H,W] (order in, remember, out, cell) are folded into the

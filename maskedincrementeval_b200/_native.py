@@ -61,8 +61,8 @@ SIGNATURES = {
     "mie_activation_increment": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "mie_conv_increment_workspace_bytes": (_i64, [_i, _i, _i, _i, _i, _i, _i]),
     "mie_conv_increment_ext": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i64, _vp]),
-    "mie_act_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp]),
-    "mie_mul_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp]),
+    "mie_act_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "mie_mul_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mie_convlstm_point": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp,
                                 _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp]),
     "mie_upsample2x": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),

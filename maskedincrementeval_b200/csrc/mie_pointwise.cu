@@ -56,7 +56,7 @@ __device__ __forceinline__ void or_word(unsigned *s_lo_hi, int p) {
 __global__ void __launch_bounds__(1024) act_incr_kernel(
     const float *in, int64_t in_ps, const uint64_t *__restrict__ in_bits, float *__restrict__ res,
     int64_t res_ps, float *__restrict__ emitted, int64_t em_ps, float *out, int64_t out_ps, uint64_t *out_bits,
-    int N, int C, int H, int W, int op, float thr) {
+    int N, int C, int H, int W, int op, float thr, int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
   __shared__ unsigned s_w[2];
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
         const float d = in[pix * in_ps + c];
         const float x = res[pix * res_ps + c];
         const float xn = x + d;
-        res[pix * res_ps + c] = xn;
+        if (accumulate) res[pix * res_ps + c] = xn;
         const float base = emitted ? emitted[pix * em_ps + c] : act_apply(op, x);
         dy = act_apply(op, xn) - base;
         if (fabsf(dy) > thr) or_word(s_w, p);
@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
 __global__ void __launch_bounds__(1024) mul_incr_kernel(
     const float *__restrict__ d1, int64_t d1_ps, const uint64_t *__restrict__ bits1, float *__restrict__ x1, int64_t x1_ps,
     const float *__restrict__ d2, int64_t d2_ps, const uint64_t *__restrict__ bits2, float *__restrict__ x2, int64_t x2_ps,
-    float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W, float thr) {
+    float *__restrict__ out, int64_t out_ps, uint64_t *__restrict__ out_bits, int N, int C, int H, int W, float thr,
+    int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
   __shared__ unsigned s_w[2];
@@ -145,8 +146,8 @@ __global__ void __launch_bounds__(1024) mul_incr_kernel(
         const float b = ((w2 >> p) & 1ull) ? d2[pix * d2_ps + c] : 0.0f;
         const float v1 = x1[pix * x1_ps + c], v2 = x2[pix * x2_ps + c];
         d = (b + v2) * a + v1 * b;
-        if (a != 0.0f) x1[pix * x1_ps + c] = v1 + a;
-        if (b != 0.0f) x2[pix * x2_ps + c] = v2 + b;
+        if (accumulate && a != 0.0f) x1[pix * x1_ps + c] = v1 + a;
+        if (accumulate && b != 0.0f) x2[pix * x2_ps + c] = v2 + b;
         if (fabsf(d) > thr) or_word(s_w, p);
       }
       out[pix * out_ps + c] = d;
@@ -885,28 +886,30 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict
 
 extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
                             float *emitted, int64_t emitted_ps, float *out, int64_t out_ps, uint64_t *out_bits, int N,
-                            int C, int H, int W, int op, float thr, void *stream) {
+                            int C, int H, int W, int op, float thr, int accumulate, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (!accumulate && emitted) return MIE_EINVAL;   // a carry without an advancing reservoir would send the same change again
   if (op < MIE_ACT_NONE || op > MIE_ACT_TANH) return MIE_EINVAL;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(res, res_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (emitted && emitted_ps < C) return MIE_EINVAL;
   if (in == out && in_ps != out_ps) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   launch_chained(act_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
-      in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr);
+      in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr, accumulate ? 1 : 0);
   return check_launch();
 }
 
 extern "C" int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x1, int64_t x1_ps,
                             const float *d2, int64_t d2_ps, const uint64_t *bits2, float *x2, int64_t x2_ps, float *out,
-                            int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, float thr, void *stream) {
+                            int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W, float thr, int accumulate,
+                            void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
   MIE_CHECK_FIELD(x1, x1_ps, C); MIE_CHECK_FIELD(x2, x2_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (d1 && (!bits1 || d1_ps < C)) return MIE_EINVAL;
   if (d2 && (!bits2 || d2_ps < C)) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   launch_chained(mul_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
-      d1, d1_ps, bits1, x1, x1_ps, d2, d2_ps, bits2, x2, x2_ps, out, out_ps, out_bits, N, C, H, W, thr);
+      d1, d1_ps, bits1, x1, x1_ps, d2, d2_ps, bits2, x2, x2_ps, out, out_ps, out_bits, N, C, H, W, thr, accumulate ? 1 : 0);
   return check_launch();
 }
 

@@ -199,23 +199,23 @@ def act_code(op) -> int:
     return ACT_CODES[name]
 
 
-def act_incr(d, m: TileMask, res, emitted, out, out_bits, op_code: int, thr: float) -> TileMask:
+def act_incr(d, m: TileMask, res, emitted, out, out_bits, op_code: int, thr: float, accumulate: bool = True) -> TileMask:
     n, c, h, w = d.shape
     nat.check(nat.lib.mie_act_incr(d.data_ptr(), pixel_stride(d), m.bits.data_ptr(), res.data_ptr(), pixel_stride(res),
                                    nat.ptr(emitted), pixel_stride(emitted) if emitted is not None else 0,
                                    out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w, op_code,
-                                   float(thr), nat.stream_ptr(d.device)), "act_incr")
+                                   float(thr), 1 if accumulate else 0, nat.stream_ptr(d.device)), "act_incr")
     return TileMask(out_bits, n, h, w)
 
 
-def mul_incr(d1, m1, x1, d2, m2, x2, out, out_bits, thr: float = 0.0) -> TileMask:
+def mul_incr(d1, m1, x1, d2, m2, x2, out, out_bits, thr: float = 0.0, accumulate: bool = True) -> TileMask:
     n, c, h, w = x1.shape
     nat.check(nat.lib.mie_mul_incr(
         nat.ptr(d1), pixel_stride(d1) if d1 is not None else 0, m1.bits.data_ptr() if m1 is not None else None,
         x1.data_ptr(), pixel_stride(x1),
         nat.ptr(d2), pixel_stride(d2) if d2 is not None else 0, m2.bits.data_ptr() if m2 is not None else None,
         x2.data_ptr(), pixel_stride(x2), out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w,
-        float(thr), nat.stream_ptr(x1.device)), "mul_incr")
+        float(thr), 1 if accumulate else 0, nat.stream_ptr(x1.device)), "mul_incr")
     return TileMask(out_bits, n, h, w)
 
 

@@ -63,17 +63,14 @@ _scratch = Scratch()
 
 
 def IncrPointwiseMultiply(x1_incr: Masked, x1: IncrementReserve, x2_incr: Masked, x2: IncrementReserve) -> Masked:
-    """d(x1*x2) = (dx2 + x2)*dx1 + x1*dx2 without touching the reservoirs (reference ``:52-54``).
-
-    The fused kernel also accumulates, so this stand-alone form evaluates on copies of the operands."""
+    """d(x1*x2) = (dx2 + x2)*dx1 + x1*dx2; the reservoirs are only read (reference ``:52-54``)."""
     d1, m1 = fl.resolve(x1_incr, _scratch, "ipm1")
     d2, m2 = fl.resolve(x2_incr, _scratch, "ipm2")
     n, c, h, w = d1.shape
     out = fl.new_field(n, c, h, w, d1.device)
     bits = fl.new_bits(n, h, w, d1.device)
-    r1 = x1.reservoir.clone(memory_format=torch.channels_last)
-    r2 = x2.reservoir.clone(memory_format=torch.channels_last)
-    m = fl.mul_incr(d1, m1, r1, d2, m2, r2, out, bits)
+    m = fl.mul_incr(d1, m1, fl.as_channels_last(x1.reservoir), d2, m2, fl.as_channels_last(x2.reservoir), out, bits,
+                    accumulate=False)
     return [out, m]
 
 

@@ -118,10 +118,7 @@ class NonlinearPointOpIncr(IncrementMaskModule):
         return self.op(x)
 
     def _nonlin(self, x_incr: Masked):
-        keep = self.reservoir_in.reservoir.clone()
-        out = nnReservedActivation._run(self, x_incr, self.reservoir_in)
-        self.reservoir_in.reservoir.copy_(keep)
-        return out
+        return nnReservedActivation._run(self, x_incr, self.reservoir_in, accumulate=False)
 
 
 class nnReservedActivation(NonlinearPointOpIncr):
@@ -161,7 +158,7 @@ class nnReservedActivation(NonlinearPointOpIncr):
         return self.emitted
 
     @staticmethod
-    def _run(self, x_incr: Masked, reserve: IncrementReserve):
+    def _run(self, x_incr: Masked, reserve: IncrementReserve, accumulate: bool = True):
         d = x_incr[0]
         nat.require_cuda(d, "x_incr")
         code = fl.act_code(self.op)
@@ -173,6 +170,8 @@ class nnReservedActivation(NonlinearPointOpIncr):
             if not (d.is_contiguous() and res.is_contiguous()):
                 raise RuntimeError("x_incr must be contiguous")  # CHECK_CONTIGUOUS, include/checks.h:7
             out = torch.empty_like(d)
+            if not accumulate:
+                res = res.clone()    # the dense any-shape entry point always advances what it is given
             nat.check(nat.lib.mie_activation_increment(res.data_ptr(), d.data_ptr(), out.data_ptr(), d.numel(), code,
                                                        nat.stream_ptr(d.device)), "activation_increment")
             return [out, x_incr[1]]
@@ -185,7 +184,7 @@ class nnReservedActivation(NonlinearPointOpIncr):
         bits = sc.get("out.bits", (fl.n_tiles(n, h, w),), torch.int64, d.device)
         thr = self.thr() if isinstance(self, nnReservedActivation) else 0.0
         em = self.carry_buffer(thr) if isinstance(self, nnReservedActivation) else None
-        mo = fl.act_incr(d, m, res, em, out, bits, code, thr)
+        mo = fl.act_incr(d, m, res, em, out, bits, code, thr, accumulate)
         return [out, mo]
 
     def forward(self, x_incr: Masked):

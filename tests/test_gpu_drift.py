@@ -6,6 +6,11 @@ decays about tenfold per level, so the deep layers see changes of 1e-5) and Kaim
 carries signal).  After the last step the persistent state of every layer -- each activation's accumulated
 pre-activation, the ConvLSTM gate and cell state -- is compared with the state the dense recompute leaves behind, layer
 by layer, so that an error in a deep layer cannot hide behind the decay.
+
+With unit-gain weights plain TF32 inputs (2^-11 relative per element, a property of the format, not of the kernels)
+leave each layer's state 2-3e-3 of its range off after 64 steps, and EV-FlowNet's output 5e-3: at that
+initialisation the tensor-core run uses split precision (``set_precision(net, "split")``), which is what the library
+offers for such networks, and is then held to the same 2e-3 bar.
 """
 import pytest
 import torch
@@ -61,10 +66,14 @@ def layer_states(net):
     return out
 
 
-def run_drift(dev, make, sd, frames, first_of, check_at=(1, 16, 32, 48, STEPS)):
+def run_drift(dev, make, sd, frames, first_of, init, check_at=(1, 16, 32, 48, STEPS)):
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import set_precision
     from maskedincrementeval_b200.runtime import IncrementalRunner
     net, dense = make().to(dev).eval(), make().to(dev).eval()
     net.load_state_dict(sd), dense.load_state_dict(sd)
+    if init == "kaiming_normal" and fl.config.tensor_cores == "auto":
+        set_precision(net, "split")
     run = IncrementalRunner(net, use_graph=True)
     worst = 0.0
     with torch.no_grad():
@@ -101,7 +110,7 @@ def test_e2depth_264x352_64_steps(dev, init):
                                            skip_type="sum", norm=None, use_upsample_conv=True, compat="exact"))
     sd = seeded_state_dict(e2depth_shapes(32), 0, init)
     frames = [f.to(dev) for f in voxel_sequence(1, 260, 346, STEPS + 1, 30000, 10, seed=21)]
-    worst, per_layer = run_drift(dev, make, sd, frames, e2depth_dense)
+    worst, per_layer = run_drift(dev, make, sd, frames, e2depth_dense, init)
     assert worst <= tol(), worst
     bad = {k: v for k, v in per_layer.items() if v > tol()}
     assert not bad, bad
@@ -127,7 +136,7 @@ def test_flow_nets_256x336_64_steps(dev, net_name, init):
         make, shapes, streams = (lambda: DelayedEVFlowNetIncr(kw, 2, compat="exact")), flow_shapes_delayed(32), 1
     sd = seeded_state_dict(shapes, 2, init)
     frames = [f.to(dev) for f in count_image_sequence(streams, 256, 336, STEPS + 1, 20000, 10, seed=22)]
-    worst, per_layer = run_drift(dev, make, sd, frames, flow_dense)
+    worst, per_layer = run_drift(dev, make, sd, frames, flow_dense, init)
     assert worst <= tol(), worst
     bad = {k: v for k, v in per_layer.items() if v > tol()}
     assert not bad, bad
