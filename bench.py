@@ -712,6 +712,79 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def threshold_study(args):
+    """Threshold / accuracy / speed table for E2Depth 260x346, one stream: for every variant 64 incremental steps after
+    a refresh (graph replay, L2 flushed before each timed step), the error of the accumulated output against a dense
+    recompute of the last frame, and the activity of every layer.  Variants: lossless; input threshold only;
+    activation thresholds with carry, on the FP32 kernel (default routing) and on the tensor cores; the reference's
+    k-fenced quantiser in front of every convolution.  One JSON line per variant on stdout, as each completes."""
+    import maskedincrementeval_b200 as mie
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    steps = 64
+    frames = [f.to(dev) for f in voxel_sequence(1, H, W, steps + 3, EVENTS, SEGMENTS, seed=FRAMES_SEED)]
+    flush = l2_flusher(dev)
+    st = torch.cuda.current_stream(dev)
+    variants = [dict(name="lossless")]
+    variants += [dict(name=f"input threshold {t:g}", input_threshold=t) for t in (0.05, 0.2)]
+    variants += [dict(name=f"activation threshold {t:g} + carry, FP32 kernel for thresholded layers", threshold=t)
+                 for t in (1e-5, 1e-4, 3e-4, 1e-3, 1e-2)]
+    variants += [dict(name=f"k-fenced quantiser, step {k:g}, in front of every convolution", kfenced_step=k) for k in (1e-4, 1e-3, 1e-2)]
+    if args.tc_thresholded:
+        variants += [dict(name=f"activation threshold {t:g} + carry, tensor cores for thresholded layers", threshold=t,
+                          tc_thresholded=True) for t in (1e-2, 1e-3, 3e-4, 1e-4, 1e-5)]
+    rows = []
+    for init in ("default", "kaiming_normal"):
+        sd = seeded_state_dict(e2depth_shapes(), seed=0, init=init)
+        for v in variants:
+            mie.config.compat = "exact"
+            mie.config.tensor_cores = "auto"
+            mie.config.threshold = v.get("threshold", 0.0)
+            mie.config.input_threshold = v.get("input_threshold", 0.0)
+            mie.config.kfenced_step = v.get("kfenced_step")
+            mie.config.tc_thresholded = v.get("tc_thresholded", False)
+            mie.config.carry = True
+            net = E2VIDRecurrentIncr(dict(E2DEPTH_CFG)).to(dev).eval()
+            dense = E2VIDRecurrentIncr(dict(E2DEPTH_CFG)).to(dev).eval()
+            net.load_state_dict(sd), dense.load_state_dict(sd)
+            run = IncrementalRunner(net, use_graph=True)
+            with torch.no_grad():
+                run.refresh(frames[0])
+                ts = []
+                for i in range(1, steps + 1):
+                    flush()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(st)
+                    run.step(frames[i])
+                    e1.record(st)
+                    ts.append((e0, e1))
+                torch.cuda.synchronize()
+                run.check()
+                y = run.output.clone()
+                mie.config.threshold, mie.config.input_threshold, mie.config.kfenced_step = 0.0, 0.0, None
+                yd = dense.forward_refresh_reservoirs(frames[steps], None)[0]
+                mie.config.threshold = v.get("threshold", 0.0)
+                mie.config.input_threshold = v.get("input_threshold", 0.0)
+                mie.config.kfenced_step = v.get("kfenced_step")
+                rng = float(yd.max() - yd.min())
+                err = float((y - yd).abs().max()) / max(rng, 1e-12)
+                ms = sum(a.elapsed_time(b) for a, b in ts[3:]) / len(ts[3:])
+                act = activity_table(net, run, frames[steps + 1], dev)
+            row = {"threshold_study": v["name"], "init": init, "ms_per_step": ms, "error_over_range_after_64_steps": err,
+                   "inside_2e-3": err <= 2e-3, "inside_1e-4": err <= 1e-4,
+                   "active_tiles_by_layer": {k: a.get("tiles") for k, a in act.items() if "tiles" in a},
+                   "active_pixels_by_layer": {k: a.get("px") for k, a in act.items()}}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+    mie.config.threshold, mie.config.input_threshold, mie.config.kfenced_step, mie.config.tc_thresholded = 0.0, 0.0, None, False
+    return rows
+
+
 def activity_table(net, run, frame, dev):
     """Active pixel / tile fractions of each convolution's input on one more (eager) step."""
     from maskedincrementeval_b200.fields import TileMask
@@ -721,6 +794,9 @@ def activity_table(net, run, frame, dev):
     def hook(name):
         def f(mod, inp, out):
             m = out[1] if isinstance(out, (list, tuple)) and isinstance(out[1], TileMask) else None
+            if m is None and isinstance(out, (list, tuple)) and isinstance(out[0], (list, tuple)) and \
+                    len(out[0]) == 2 and isinstance(out[0][1], TileMask):
+                m = out[0][1]       # recurrent encoders return ([delta, mask], state)
             if m is not None:
                 rows[name] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4),
                               "tiles": round(int((m.bits != 0).sum()) / m.bits.numel(), 4)}
@@ -764,6 +840,9 @@ def main():
                          "(default: they run on the FP32 kernel)")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the conv3x3 32->32 + ReLU kernel of config 1 and print its roofline object")
+    ap.add_argument("--threshold-study", action="store_true",
+                    help="E2Depth 260x346: threshold / accuracy / speed table over 64 steps (one JSON line per variant); "
+                         "with --tc-thresholded also the variants that run thresholded layers on the tensor cores")
     ap.add_argument("--roofline-kernels-only", action="store_true",
                     help="run only the point-operation kernels at their sizes in this network and print their roofline objects")
     args = ap.parse_args()
@@ -786,6 +865,9 @@ def main():
             print(json.dumps(roofline_conv3x3(dev, peak, kind, repeats=1)))
         else:
             print(json.dumps(roofline_other_kernels(dev, peak, kind)))
+        return
+    if args.threshold_study:
+        threshold_study(args)
         return
     if args.warmup < 3:
         args.warmup = 3

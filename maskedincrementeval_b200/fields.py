@@ -36,6 +36,11 @@ class IncrConfig:
                      E2Depth's accumulated output to about 1e-5); "off" keeps every convolution on the FP32 path
     compat           "reference": networks wired as the reference is written; "exact": as intended, which
                      makes the accumulated incremental output equal to a dense recompute
+    kfenced_step     None (default): the quantiser every convolution owns stays unused, as in the reference
+                     (``mask_incr_modules.py:157`` builds it, ``:166`` has its call commented out).  A positive value
+                     switches it on where the reference meant it to sit: each convolution's input delta passes through
+                     T = carry + dx; q = k*floor(0.5 + T/k); carry = T - q with this quantisation step k, and the
+                     convolution sees q (one more kernel per convolution; what is rounded away stays pending)
     tc_thresholded   False (default): thresholded convolutions (threshold > 0, with or without carry) run on the FP32
                      kernel; True lets layers of 32/64/128/256 output channels use the tensor cores in that mode too
     """
@@ -45,6 +50,7 @@ class IncrConfig:
     compat: str = "reference"
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
     tc_thresholded: bool = False
+    kfenced_step: Optional[float] = None
 
 
 config = IncrConfig()

@@ -365,6 +365,8 @@ class nnConvIncr(nn.Conv2d):
         """conv(dx) [* batch-norm scale] [+ addend] [-> incremental activation], one dilation launch and one
         convolution launch."""
         sc = self._scratch
+        if config.kfenced_step:
+            x_incr = self._quantise_input(x_incr)
         d, m = fl.resolve(x_incr, sc, "in")
         n, cin, hin, win = d.shape
         cin_eff = cin_limit or self.in_channels
@@ -419,6 +421,16 @@ class nnConvIncr(nn.Conv2d):
     def forward(self, x_incr):
         return self.forward_fused(x_incr)
 
+    def _quantise_input(self, x_incr: Masked) -> Masked:
+        """The reference's k-fenced quantiser in front of the convolution (``:157``, ``:166``), with the absolute
+        step ``config.kfenced_step``; its carry starts at zero after a refresh."""
+        kf, d = self.kf, x_incr[0]
+        r = kf.delta.reservoir
+        if r is None or r.shape != d.shape or r.device != d.device:
+            kf.delta.update_reservoir(torch.zeros_like(d, memory_format=torch.channels_last))
+        kf._k_host = float(config.kfenced_step)
+        return kf(x_incr)
+
     def error_words(self):
         """``[(geometry, counts tensor)]`` of every plan: word 3 of ``counts`` holds the MIE_ERR_* bits the kernels
         raised since it was last cleared (see ``check_device_errors``)."""
@@ -426,7 +438,10 @@ class nnConvIncr(nn.Conv2d):
 
     def forward_refresh_reservoirs(self, x):
         # The reference also resets its (never applied) quantiser here, which costs a norm and a
-        # zero tensor of the input's size per convolution (``:193``); nothing reads either.
+        # zero tensor of the input's size per convolution (``:193``); nothing reads either.  When the quantiser is
+        # switched on (config.kfenced_step) its carry is cleared instead.
+        if config.kfenced_step and self.kf.delta.reservoir is not None:
+            self.kf.delta.reservoir.zero_()
         return nn.Conv2d.forward(self, x)
 
 
