@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(256) mask_words_kernel(const T *__restrict__ s
       const int c4 = C >> 2;
       const int per_row = cols * c4;
       const int total = rows * per_row;
-      for (int i = lane; i < total; i += 32) {
+#pragma unroll 4
+      for (int i = lane; i < total; i += 32) {   // independent 16-byte loads: four in flight per lane
         const int r = i / per_row, rem = i - r * per_row;
         const int px = rem / c4, q = rem - px * c4;
         const float4 v = *reinterpret_cast<const float4 *>(

@@ -432,6 +432,122 @@ __global__ void __launch_bounds__(PW_THREADS) convlstm_point_vec_kernel(
   }
 }
 
+// Incremental activation, float4 over channels, one block per tile (the output mask needs every channel of a pixel).
+// All loads of a thread's elements are issued before the first dependent store, so that a thread has up to
+// 2 x (2..3) 16-byte loads in flight instead of one scalar load at a time.
+template <int OP>
+__global__ void __launch_bounds__(256) act_incr_vec_kernel(
+    const float *in, int64_t in_ps, const uint64_t *__restrict__ in_bits, float *__restrict__ res, int64_t res_ps,
+    float *__restrict__ emitted, int64_t em_ps, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W,
+    float thr, int accumulate) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  __shared__ unsigned s_w[2];
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int q4 = C >> 2, total = 64 * q4;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t win = in_bits[t];
+    const TileGeom g = tile_geom(t, H, W);
+    if (win == 0ull) {
+      if (out_bits[t] != 0ull) {  // uniform across the block
+        __syncthreads();
+        zero_tile4(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int e0 = threadIdx.x; e0 < total; e0 += 2 * blockDim.x) {
+      int p[2], c[2];
+      bool ok[2], on[2];
+      int64_t pix[2];
+      float4 d[2], x[2], b[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int e = e0 + u * blockDim.x;
+        p[u] = e / q4;
+        c[u] = (e - p[u] * q4) * 4;
+        ok[u] = e < total && pix_valid(g, p[u]);
+        on[u] = ok[u] && ((win >> p[u]) & 1ull);
+        pix[u] = ok[u] ? pix_index(g, p[u], H, W) : 0;
+        if (on[u]) {
+          d[u] = ld4(in + pix[u] * in_ps + c[u]);
+          x[u] = ld4(res + pix[u] * res_ps + c[u]);
+          if (emitted) b[u] = ld4(emitted + pix[u] * em_ps + c[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (!ok[u]) continue;
+        float4 dy = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (on[u]) {
+          const float4 xn = f4add(x[u], d[u]);
+          if (accumulate) st4(res + pix[u] * res_ps + c[u], xn);
+          if (!emitted) b[u] = make_float4(act_t<OP>(x[u].x), act_t<OP>(x[u].y), act_t<OP>(x[u].z), act_t<OP>(x[u].w));
+          dy = make_float4(act_t<OP>(xn.x) - b[u].x, act_t<OP>(xn.y) - b[u].y, act_t<OP>(xn.z) - b[u].z, act_t<OP>(xn.w) - b[u].w);
+          if (fabsf(dy.x) > thr || fabsf(dy.y) > thr || fabsf(dy.z) > thr || fabsf(dy.w) > thr) or_word(s_w, p[u]);
+        }
+        st4(out + pix[u] * out_ps + c[u], dy);
+      }
+    }
+    __syncthreads();
+    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (thr > 0.0f || emitted) {
+      // second pass: withheld pixels are written as zero; sent pixels are added to the carry
+      for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        const int pp = e / q4, cc = (e - pp * q4) * 4;
+        if (!pix_valid(g, pp) || !((win >> pp) & 1ull)) continue;
+        const int64_t px = pix_index(g, pp, H, W);
+        if ((wout >> pp) & 1ull) {
+          if (emitted) st4(emitted + px * em_ps + cc, f4add(ld4(emitted + px * em_ps + cc), ld4(out + px * out_ps + cc)));
+        } else {
+          st4(out + px * out_ps + cc, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+    }
+    if (threadIdx.x == 0) out_bits[t] = wout;
+    __syncthreads();
+  }
+}
+
+// Channel concatenation, float4 over channels: work item = (tile, block of 64 output channels).
+__global__ void __launch_bounds__(PW_THREADS) cat2_vec_kernel(
+    const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, int ca, const float *__restrict__ b,
+    int64_t b_ps, const uint64_t *__restrict__ b_bits, int cb, float *__restrict__ out, int64_t out_ps,
+    uint64_t *out_bits, int N, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int C = ca + cb;
+  const int ncb = (C + 63) / 64;
+  const int n_items = ntiles * ncb;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int t = item / ncb, blk = item - t * ncb;
+    const uint64_t wa = a_bits[t], wb = b_bits[t], w = wa | wb;
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (blk == 0 && out_bits[t] != 0ull) {   // only this block reads or writes the word
+        __syncthreads();
+        zero_tile4(out, out_ps, C, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+    const int c_lo = blk * 64, q4 = (min(C, c_lo + 64) - c_lo) >> 2;
+    for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+      const int p = e / q4, c = c_lo + (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < ca) { if ((wa >> p) & 1ull) v = ld4(a + pix * a_ps + c); }
+      else { if ((wb >> p) & 1ull) v = ld4(b + pix * b_ps + (c - ca)); }
+      st4(out + pix * out_ps + c, v);
+    }
+    if (blk == 0 && threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
 __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
@@ -829,6 +945,37 @@ __global__ void __launch_bounds__(256) kfenced_kernel(const float *__restrict__ 
   }
 }
 
+// The quantiser with float4 over channels, one block per tile: a thread-per-pixel loop over several hundred channels
+// (the deep layers of a UNet) runs at a few per cent of the memory bandwidth.
+__global__ void __launch_bounds__(256) kfenced_vec_kernel(const float *__restrict__ dx, int64_t dx_ps, float *__restrict__ carry,
+                                                          int64_t c_ps, float k, float *__restrict__ q, int64_t q_ps,
+                                                          uint64_t *__restrict__ bits, int N, int C, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  __shared__ unsigned s_w[2];
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int q4 = C >> 2, total = 64 * q4;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const TileGeom g = tile_geom(t, H, W);
+    __syncthreads();
+    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      const int p = e / q4, c = (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      const float4 T = f4add(ld4(carry + pix * c_ps + c), ld4(dx + pix * dx_ps + c));
+      const float4 f = make_float4(k * floorf(0.5f + T.x / k), k * floorf(0.5f + T.y / k), k * floorf(0.5f + T.z / k),
+                                   k * floorf(0.5f + T.w / k));
+      st4(carry + pix * c_ps + c, make_float4(T.x - f.x, T.y - f.y, T.z - f.z, T.w - f.w));
+      st4(q + pix * q_ps + c, f);
+      if (f.x != 0.0f || f.y != 0.0f || f.z != 0.0f || f.w != 0.0f) or_word(s_w, p);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0];
+  }
+}
+
 }  // namespace
 
 extern "C" int mie_activation_increment(float *X, const float *in_incr, float *out_incr, int64_t n, int op, void *stream) {
@@ -894,6 +1041,22 @@ extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_b
   if (emitted && emitted_ps < C) return MIE_EINVAL;
   if (in == out && in_ps != out_ps) return MIE_EINVAL;
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  const bool vec = C % 4 == 0 && in_ps % 4 == 0 && res_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(in) && aligned16(res) &&
+                   aligned16(out) && (!emitted || (emitted_ps % 4 == 0 && aligned16(emitted)));
+  if (vec) {
+    const dim3 grid(tile_grid(ntiles)), block(256);
+    cudaStream_t st = (cudaStream_t)stream;
+#define MIE_ACT_VEC(OP) launch_chained(act_incr_vec_kernel<OP>, grid, block, 0, st, in, in_ps, in_bits, res, res_ps, emitted, \
+                                       emitted_ps, out, out_ps, out_bits, N, C, H, W, thr, accumulate ? 1 : 0)
+    switch (op) {
+      case MIE_ACT_RELU: MIE_ACT_VEC(MIE_ACT_RELU); break;
+      case MIE_ACT_SIGMOID: MIE_ACT_VEC(MIE_ACT_SIGMOID); break;
+      case MIE_ACT_TANH: MIE_ACT_VEC(MIE_ACT_TANH); break;
+      default: MIE_ACT_VEC(MIE_ACT_NONE); break;
+    }
+#undef MIE_ACT_VEC
+    return check_launch();
+  }
   launch_chained(act_incr_kernel, dim3(tile_grid(ntiles)), dim3(wide_threads(ntiles, C)), 0, (cudaStream_t)stream, 
       in, in_ps, in_bits, res, res_ps, emitted, emitted_ps, out, out_ps, out_bits, N, C, H, W, op, thr, accumulate ? 1 : 0);
   return check_launch();
@@ -991,6 +1154,11 @@ extern "C" int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, in
   if (N <= 0 || ca <= 0 || cb <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, ca); MIE_CHECK_FIELD(b, b_ps, cb); MIE_CHECK_FIELD(out, out_ps, ca + cb);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  if (ca % 4 == 0 && cb % 4 == 0 && a_ps % 4 == 0 && b_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
+    launch_chained(cat2_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(ca + cb, 64))), dim3(PW_THREADS), 0, (cudaStream_t)stream,
+                   a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out, out_ps, out_bits, N, H, W);
+    return check_launch();
+  }
   launch_chained(cat2_kernel, dim3(item_grid((int64_t)ntiles * divup(ca + cb, CBS))), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
                                                                           out_ps, out_bits, N, H, W);
   return check_launch();
@@ -1157,6 +1325,11 @@ extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(k > 0.0f)) return MIE_EINVAL;
   MIE_CHECK_FIELD(dx, dx_ps, C); MIE_CHECK_FIELD(carry, c_ps, C); MIE_CHECK_FIELD(q, q_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  if (C >= 16 && C % 4 == 0 && dx_ps % 4 == 0 && c_ps % 4 == 0 && q_ps % 4 == 0 && aligned16(dx) && aligned16(carry) && aligned16(q)) {
+    launch_chained(kfenced_vec_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, dx, dx_ps, carry, c_ps, k, q, q_ps,
+                   bits, N, C, H, W);
+    return check_launch();
+  }
   int blocks = divup(ntiles, 4);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
   launch_chained(kfenced_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, dx, dx_ps, carry, c_ps, k, q, q_ps,

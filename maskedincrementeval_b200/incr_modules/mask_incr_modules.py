@@ -373,7 +373,11 @@ class nnConvIncr(nn.Conv2d):
         if cin != cin_eff:
             raise RuntimeError(f"expected {cin_eff} input channels, got {cin}")
         plan = self._plan(n, hin, win, d.device)
-        split = self._split_input(cin)
+        # Split precision is only meaningful on the tensor cores, which truncate the three channel blocks as the scheme
+        # assumes; a thresholded layer that is routed to the FP32 kernel must see the plain input and filter.
+        thresholded = activation is not None and (activation.thr() > 0.0 or
+                                                  (config.carry and activation.emitted is not None))
+        split = self._split_input(cin) and (config.tc_thresholded or not thresholded)
         wbuf, cp, op, wtc = self._weights(cin_limit, split, bn)
         if split:
             c3 = 3 * ((cin + 7) // 8 * 8)
@@ -414,8 +418,11 @@ class nnConvIncr(nn.Conv2d):
             a.act, a.thr, a.res, a.res_ps, a.emitted, a.emitted_ps = nat.ACT_NONE, 0.0, None, 0, None, 0
         if a.thr > 0.0 or a.emitted:
             nat.set_option(nat.OPT_TC_THRESHOLDED, 1 if config.tc_thresholded else 0)
-        nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
         self.last_used_tensor_cores = bool(nat.lib.mie_conv_uses_tensor_cores(C.byref(a)))
+        if split and not self.last_used_tensor_cores:
+            raise RuntimeError("a split-precision convolution did not qualify for the tensor cores (its three channel "
+                               "blocks only add up to the fp32 result there); set precision=None on this layer")
+        nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
         return [plan.out, plan.mask]
 
     def forward(self, x_incr):

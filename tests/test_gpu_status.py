@@ -219,6 +219,21 @@ def test_thresholded_deep_layers_fp32_routed(dev, cfg):
     assert float((steps[-1][2] - truth).abs().max()) <= 0.02 + 1e-5
 
 
+def test_thresholded_narrow_input_layer_on_fp32_kernel_is_plain_fp32(dev):
+    """The 5-channel 5x5 head takes split precision on the tensor cores; with a threshold it is routed to the FP32
+    kernel, which must then see the plain input and filter (the three channel blocks of the split only add up to the
+    fp32 result under the tensor cores' truncation): identical output to the run with the tensor cores switched off."""
+    from maskedincrementeval_b200 import fields as fl
+    outs = []
+    for mode in ("auto", "off"):
+        fl.config.tensor_cores = mode
+        steps, _ = _thresholded_run(dev, (5, 32, 5, 1, 40, 56, False), tc_thresholded=False, steps=4, thr=1e-3)
+        assert not any(s[3] for s in steps)
+        outs.append(steps)
+    for a, b in zip(*outs):
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
 def test_thresholded_odd_channel_count_same_on_both_settings(dev):
     """96 output channels with a threshold: no kernel holds every channel of a pixel in one block at that width, on
     either path, so the layer is refused the same way whether or not thresholded tensor-core layers are enabled
