@@ -1,20 +1,21 @@
 """Incremental EV-FlowNet: multi-resolution recurrent UNet with ConvGRU encoders
 (reference: ``incr_modules/evflownet_incr.py:1-497``).
 
-``compat="reference"`` reproduces the reference as written: inside a residual block one activation module
-(one reservoir) serves both activations and the residual delta is lost because a list is extended with
-``+=`` (``:221-226``, ``:261-263``).  ``compat="exact"`` gives the second activation its own reservoir and adds the
-residual, which makes the accumulated incremental output equal to a dense recompute.
+Every class states its topology once (``_run``) and is evaluated by the dense or the incremental interpreter of
+``_algebra``; class names, constructor arguments and ``state_dict`` keys are the reference's.
+
+``compat="reference"`` reproduces the reference as written: inside a residual block one activation module (one
+reservoir) serves both activations and the residual delta is lost because a list is extended with ``+=``
+(``:221-226``, ``:261-263``).  ``compat="exact"`` gives the second activation its own reservoir and adds the residual,
+which makes the accumulated incremental output equal to a dense recompute.
 """
 from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
-from .. import _native as nat
-from .. import fields as fl
-from ..fields import Scratch, TileMask, config
+from ..fields import Scratch, config
+from ._algebra import DENSE, INCR
 from .mask_incr_modules import (nnBatchNorm2dIncr, nnConvIncr, nnReservedActivation, nnReservedMultiplication,
                                 nnSigmoidIncr, nnTanhIncr)
 
@@ -28,27 +29,16 @@ def _compat(module) -> str:
 
 def skip_concat(x1, x2):
     """Zero-pad x1 to x2's spatial size and concatenate along channels (reference ``:9-14``); dense tensors."""
-    diffY = x2.size()[2] - x1.size()[2]
-    diffX = x2.size()[3] - x1.size()[3]
-    padding = nn.ZeroPad2d((diffX // 2, diffX - diffX // 2, diffY // 2, diffY - diffY // 2))
-    x1 = padding(x1)
-    return torch.cat([x1, x2], dim=1)
+    return DENSE.cat(x1, x2)
 
 
 def skip_concat_incr(x1_incr, x2_incr, scratch: Scratch, key: str):
     """Channel concatenation of two delta fields of equal spatial size, masks OR-ed."""
-    a, ma = fl.resolve(x1_incr, scratch, key + ".a")
-    b, mb = fl.resolve(x2_incr, scratch, key + ".b")
-    if a.shape[2:] != b.shape[2:]:
-        raise NotImplementedError("incremental skip_concat needs equal spatial sizes (pad the input to a multiple of 16)")
-    n, ca, h, w = a.shape
-    c = ca + b.shape[1]
-    # pixel stride rounded up to 4 floats (the decoders see 2·C + 2 channels): 16-byte pixel addresses are what the
-    # convolution's vector loads and TMA need; the padding channels are never written and stay zero
-    full = scratch.get(key, (n, (c + 3) // 4 * 4, h, w), torch.float32, a.device, channels_last=True)
-    out = full[:, :c]
-    bits = scratch.get(key + ".bits", (fl.n_tiles(n, h, w),), torch.int64, a.device)
-    return [out, fl.cat2(a, ma, b, mb, out, bits)]
+    return INCR.cat(x1_incr, x2_incr, scratch, key)
+
+
+def _activation(name):
+    return nnReservedActivation(getattr(torch, name)) if name is not None and hasattr(torch, name) else None
 
 
 class ConvGRUIncr(nn.Module):
@@ -61,51 +51,42 @@ class ConvGRUIncr(nn.Module):
 
     def __init__(self, input_size, hidden_size, kernel_size, activation=None):
         super().__init__()
-        padding = kernel_size // 2
-        self.input_size = input_size
-        self.hidden_size = hidden_size
-        self.reset_gate = nnConvIncr(input_size + hidden_size, hidden_size, kernel_size, padding=padding)
-        self.update_gate = nnConvIncr(input_size + hidden_size, hidden_size, kernel_size, padding=padding)
-        self.out_gate = nnConvIncr(input_size + hidden_size, hidden_size, kernel_size, padding=padding)
         assert activation is None, "ConvGRU activation cannot be set (just for compatibility)"
-        nn.init.orthogonal_(self.reset_gate.weight)
-        nn.init.orthogonal_(self.update_gate.weight)
-        nn.init.orthogonal_(self.out_gate.weight)
-        nn.init.constant_(self.reset_gate.bias, 0.0)
-        nn.init.constant_(self.update_gate.bias, 0.0)
-        nn.init.constant_(self.out_gate.bias, 0.0)
-        self.sigmoid1 = nnSigmoidIncr()
-        self.sigmoid2 = nnSigmoidIncr()
-        self.tanh = nnTanhIncr()
+        self.input_size, self.hidden_size = input_size, hidden_size
+        gates = ("reset_gate", "update_gate", "out_gate")
+        for name in gates:          # built first, initialised afterwards: the order in which the reference draws
+            setattr(self, name, nnConvIncr(input_size + hidden_size, hidden_size, kernel_size, padding=kernel_size // 2))
+        for name in gates:
+            nn.init.orthogonal_(getattr(self, name).weight)
+        for name in gates:
+            nn.init.constant_(getattr(self, name).bias, 0.0)
+        self.sigmoid1, self.sigmoid2, self.tanh = nnSigmoidIncr(), nnSigmoidIncr(), nnTanhIncr()
         self.mult = nnReservedMultiplication()
         self._scratch = Scratch()
 
     def forward(self, input_incr, prev_state):
         if prev_state is None:
-            update = self.update_gate.forward_fused(input_incr, self.sigmoid1, cin_limit=self.input_size)
-            out_inputs = self.out_gate.forward_fused(input_incr, self.tanh, cin_limit=self.input_size)
-            new_state = self.mult(out_inputs, update)
-            return new_state, new_state
-        stacked = skip_concat_incr(input_incr, prev_state, self._scratch, "stacked")
-        update = self.update_gate.forward_fused(stacked, self.sigmoid1)
-        out_inputs = self.out_gate.forward_fused(stacked, self.tanh)
-        diff = [out_inputs[0] - prev_state[0], None]
-        new_state = [prev_state[0] + self.mult(diff, update)[0], None]
-        return new_state, new_state
+            update = INCR.conv(self.update_gate, input_incr, self.sigmoid1, cin_limit=self.input_size)
+            candidate = INCR.conv(self.out_gate, input_incr, self.tanh, cin_limit=self.input_size)
+            state = self.mult(candidate, update)
+            return state, state
+        stacked = INCR.cat(input_incr, prev_state, self._scratch, "stacked")
+        update = INCR.conv(self.update_gate, stacked, self.sigmoid1)
+        candidate = INCR.conv(self.out_gate, stacked, self.tanh)
+        moved = self.mult([candidate[0] - prev_state[0], None], update)
+        state = [prev_state[0] + moved[0], None]
+        return state, state
 
     def forward_refresh_reservoirs(self, x, prev_state):
-        batch_size = x.data.size()[0]
-        spatial_size = x.data.size()[2:]
         if prev_state is None:
-            state_size = [batch_size, self.hidden_size] + list(spatial_size)
-            prev_state = torch.zeros(state_size, dtype=x.dtype, device=x.device).to(memory_format=torch.channels_last)
-        stacked_inputs = torch.cat([x, prev_state], dim=1)
-        update = self.sigmoid1.forward_refresh_reservoirs(self.update_gate.forward_refresh_reservoirs(stacked_inputs))
-        reset = self.sigmoid2.forward_refresh_reservoirs(self.reset_gate.forward_refresh_reservoirs(stacked_inputs))
-        out_inputs = self.tanh.forward_refresh_reservoirs(
-            self.out_gate.forward_refresh_reservoirs(torch.cat([x, prev_state * reset], dim=1)))
-        new_state = prev_state + self.mult.forward_refresh_reservoirs(out_inputs - prev_state, update)
-        return new_state, new_state
+            prev_state = x.new_zeros((x.shape[0], self.hidden_size) + tuple(x.shape[2:])).contiguous(
+                memory_format=torch.channels_last)
+        stacked = torch.cat([x, prev_state], dim=1)
+        update = DENSE.conv(self.update_gate, stacked, self.sigmoid1)
+        reset = DENSE.conv(self.reset_gate, stacked, self.sigmoid2)
+        candidate = DENSE.conv(self.out_gate, torch.cat([x, prev_state * reset], dim=1), self.tanh)
+        state = prev_state + DENSE.mul(self.mult, candidate - prev_state, update)
+        return state, state
 
 
 class ConvLayerIncr(nn.Module):
@@ -113,39 +94,30 @@ class ConvLayerIncr(nn.Module):
 
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, activation="relu", norm=None,
                  BN_momentum=0.1, w_scale=None, padding=None):
-        super(ConvLayerIncr, self).__init__()
-        bias = False if norm == "BN" else True
-        if padding is None:
-            padding = kernel_size // 2
-        self.conv2d = nnConvIncr(in_channels, out_channels, kernel_size, stride, padding, bias=bias)
+        super().__init__()
+        if norm == "IN":
+            raise NotImplementedError
+        padding = kernel_size // 2 if padding is None else padding
+        self.conv2d = nnConvIncr(in_channels, out_channels, kernel_size, stride, padding, bias=norm != "BN")
         if w_scale is not None:
             nn.init.uniform_(self.conv2d.weight, -w_scale, w_scale)
             nn.init.zeros_(self.conv2d.bias)
-        if activation is not None:
-            if hasattr(torch, activation):
-                activation = getattr(torch, activation)
-                self.activation = nnReservedActivation(activation)
-        else:
+        if activation is None:
             self.activation = None
+        elif hasattr(torch, activation):      # an unknown name leaves the attribute unset, as in the reference (``:117-121``)
+            self.activation = _activation(activation)
         self.norm = norm
         if norm == "BN":
             self.norm_layer = nnBatchNorm2dIncr(out_channels, momentum=BN_momentum)
-        elif norm == "IN":
-            raise NotImplementedError
+
+    def _run(self, ops, x):
+        return ops.conv(self.conv2d, x, self.activation, norm=self.norm_layer if self.norm == "BN" else None)
 
     def forward(self, x):
-        if self.norm in ["BN", "IN"]:
-            out = self.norm_layer(self.conv2d(x))
-            return self.activation(out) if self.activation is not None else out
-        return self.conv2d.forward_fused(x, self.activation)
+        return self._run(INCR, x)
 
     def forward_refresh_reservoirs(self, x):
-        out = self.conv2d.forward_refresh_reservoirs(x)
-        if self.norm in ["BN", "IN"]:
-            out = self.norm_layer.forward_refresh_reservoirs(out)
-        if self.activation is not None:
-            out = self.activation.forward_refresh_reservoirs(out)
-        return out
+        return self._run(DENSE, x)
 
 
 class RecurrentConvLayerIncr(nn.Module):
@@ -159,15 +131,16 @@ class RecurrentConvLayerIncr(nn.Module):
         self.recurrent_block = ConvGRUIncr(input_size=out_channels, hidden_size=out_channels, kernel_size=3,
                                            activation=activation_rec)
 
+    def _run(self, ops, x, prev_state):
+        x = self.conv._run(ops, x)
+        gru = self.recurrent_block
+        return gru(x, prev_state) if ops.incremental else gru.forward_refresh_reservoirs(x, prev_state)
+
     def forward(self, x, prev_state):
-        x = self.conv(x)
-        x, state = self.recurrent_block(x, prev_state)
-        return x, state
+        return self._run(INCR, x, prev_state)
 
     def forward_refresh_reservoirs(self, x, prev_state):
-        x = self.conv.forward_refresh_reservoirs(x)
-        x, state = self.recurrent_block.forward_refresh_reservoirs(x, prev_state)
-        return x, state
+        return self._run(DENSE, x, prev_state)
 
 
 class ResidualBlockIncr(nn.Module):
@@ -175,101 +148,67 @@ class ResidualBlockIncr(nn.Module):
 
     def __init__(self, in_channels, out_channels, stride=1, activation="relu", downsample=None, norm=None,
                  BN_momentum=0.1, compat: Optional[str] = None):
-        super(ResidualBlockIncr, self).__init__()
-        bias = False if norm == "BN" else True
-        self.conv1 = nnConvIncr(in_channels, out_channels, kernel_size=3, stride=stride, padding=1, bias=bias)
-        if activation is not None:
-            if hasattr(torch, activation):
-                activation = getattr(torch, activation)
-                self.activation = nnReservedActivation(activation)
-                # second reservoir, used only when compat == "exact"
-                self.activation2 = nnReservedActivation(activation)
-        else:
-            self.activation = None
-            self.activation2 = None
+        super().__init__()
+        if norm == "IN":
+            raise NotImplementedError
+        self.conv1 = nnConvIncr(in_channels, out_channels, kernel_size=3, stride=stride, padding=1, bias=norm != "BN")
+        # the reference's one activation module, and a second reservoir that only compat == "exact" uses
+        self.activation, self.activation2 = _activation(activation), _activation(activation)
         self.norm = norm
         if norm == "BN":
             self.bn1 = nnBatchNorm2dIncr(out_channels, momentum=BN_momentum)
             self.bn2 = nnBatchNorm2dIncr(out_channels, momentum=BN_momentum)
-        elif norm == "IN":
-            raise NotImplementedError
-        self.conv2 = nnConvIncr(out_channels, out_channels, kernel_size=3, stride=1, padding=1, bias=bias)
+        self.conv2 = nnConvIncr(out_channels, out_channels, kernel_size=3, stride=1, padding=1, bias=norm != "BN")
         self.downsample = downsample
         self.compat = compat
 
-    def forward(self, x):
-        if self.norm in ["BN", "IN"]:
+    def _run(self, ops, x):
+        bn = self.norm == "BN"
+        if bn and ops.incremental:
             raise NotImplementedError("batch-norm inside the incremental residual block has no fused kernel")
         exact = _compat(self) == "exact"
         residual = x
         if self.downsample:
-            residual = self.downsample(x)
-        out1 = self.conv1.forward_fused(x, self.activation)
-        if exact:
-            out2 = self.conv2.forward_fused(out1, self.activation2, addend=residual)
-        else:
-            out2 = self.conv2.forward_fused(out1, self.activation)
+            residual = self.downsample(x) if ops.incremental else self.downsample.forward_refresh_reservoirs(x)
+        out1 = ops.conv(self.conv1, x, self.activation, norm=self.bn1 if bn else None)
+        # as written, the incremental pass loses the residual and re-uses the first activation's reservoir
+        keep_residual = exact or not ops.incremental
+        out2 = ops.conv(self.conv2, out1, self.activation2 if exact else self.activation,
+                        addend=residual if keep_residual else None, norm=self.bn2 if bn else None)
         return out2, out1
 
+    def forward(self, x):
+        return self._run(INCR, x)
+
     def forward_refresh_reservoirs(self, x):
-        exact = _compat(self) == "exact"
-        residual = x
-        out1 = self.conv1.forward_refresh_reservoirs(x)
-        if self.norm in ["BN", "IN"]:
-            out1 = self.bn1.forward_refresh_reservoirs(out1)
-        if self.activation is not None:
-            out1 = self.activation.forward_refresh_reservoirs(out1)
-        out2 = self.conv2.forward_refresh_reservoirs(out1)
-        if self.norm in ["BN", "IN"]:
-            out2 = self.bn2.forward_refresh_reservoirs(out2)
-        if self.downsample:
-            residual = self.downsample.forward_refresh_reservoirs(x)
-        out2 = out2 + residual
-        if self.activation is not None:
-            act2 = self.activation2 if exact else self.activation
-            out2 = act2.forward_refresh_reservoirs(out2)
-        return out2, out1
+        return self._run(DENSE, x)
 
 
 class UpsampleConvLayerIncr(nn.Module):
     """x2 bilinear upsample of the delta, convolution, incremental activation (reference ``:297-344``)."""
 
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, activation="relu", padding=None, norm=None):
-        super(UpsampleConvLayerIncr, self).__init__()
-        bias = False if norm == "BN" else True
-        if padding is None:
-            padding = kernel_size // 2
-        self.conv2d = nnConvIncr(in_channels, out_channels, kernel_size, stride, padding, bias=bias)
-        if activation is not None:
-            activation = getattr(torch, activation)
-            self.activation = nnReservedActivation(activation)
-        else:
-            self.activation = None
+        super().__init__()
+        if norm == "IN":
+            raise NotImplementedError
+        padding = kernel_size // 2 if padding is None else padding
+        self.conv2d = nnConvIncr(in_channels, out_channels, kernel_size, stride, padding, bias=norm != "BN")
+        self.activation = None if activation is None else nnReservedActivation(getattr(torch, activation))
         self.norm = norm
         if norm == "BN":
             self.norm_layer = nnBatchNorm2dIncr(out_channels)
-        elif norm == "IN":
-            raise NotImplementedError
         self._scratch = Scratch()
 
+    def _run(self, ops, x):
+        up = ops.upsample2x(x, None, self._scratch, pad4=True)      # 2*C + 2 input channels: 16-byte pixel stride
+        norm = self.norm_layer if (self.norm == "BN" and not ops.incremental) else None
+        return ops.conv(self.conv2d, up, self.activation, norm=norm)
+
     def forward(self, x):
-        sc = self._scratch
-        d, m = fl.resolve(x, sc, "in")
-        n, c, h, w = d.shape
-        # pixel stride rounded up to 4 floats (2·C + 2 input channels): see skip_concat_incr
-        up = sc.get("up", (n, (c + 3) // 4 * 4, 2 * h, 2 * w), torch.float32, d.device, channels_last=True)[:, :c]
-        ub = sc.get("up.bits", (fl.n_tiles(n, 2 * h, 2 * w),), torch.int64, d.device)
-        mu = fl.upsample2x(d, m, None, None, up, ub, nat.UP_BILINEAR)
-        return self.conv2d.forward_fused([up, mu], self.activation)
+        return self._run(INCR, x)
 
     def forward_refresh_reservoirs(self, x):
-        x_upsampled = F.interpolate(x, scale_factor=2, mode="bilinear", align_corners=False)
-        out = self.conv2d.forward_refresh_reservoirs(x_upsampled)
-        if self.norm in ["BN", "IN"]:
-            out = self.norm_layer.forward_refresh_reservoirs(out)
-        if self.activation is not None:
-            out = self.activation.forward_refresh_reservoirs(out)
-        return out
+        return self._run(DENSE, x)
 
 
 class MultiResUNetRecurrentIncr(nn.Module):
@@ -278,107 +217,60 @@ class MultiResUNetRecurrentIncr(nn.Module):
 
     def __init__(self, compat: Optional[str] = None):
         super().__init__()
-        self.final_activation = 'tanh'
-        self.w_scale_pred = None
-        self.num_encoders = 4
-        self.num_residual_blocks = 2
-        self.ff_act, self.rec_act = ['relu', None]
+        # fixed hyper-parameters (reference ``:351-365``)
+        self.final_activation, self.w_scale_pred = 'tanh', None
+        self.num_encoders, self.num_residual_blocks = 4, 2
+        self.ff_act, self.rec_act = 'relu', None
         self.skip_ftn = skip_concat
-        self.kernel_size = 3
-        self.num_bins = 2
-        self.norm = None
-        self.base_num_channels = 32
-        self.channel_multiplier = 2
-        self.num_output_channels = 2
+        self.kernel_size, self.num_bins, self.norm = 3, 2, None
+        self.base_num_channels, self.channel_multiplier, self.num_output_channels = 32, 2, 2
         self.compat = compat
-        self.encoder_input_sizes = [int(self.base_num_channels * pow(self.channel_multiplier, i))
-                                    for i in range(self.num_encoders)]
-        self.encoder_output_sizes = [int(self.base_num_channels * pow(self.channel_multiplier, i + 1))
-                                     for i in range(self.num_encoders)]
-        self.max_num_channels = self.encoder_output_sizes[-1]
-        self.encoders = self.build_recurrent_encoders()
-        self.resblocks = self.build_resblocks()
-        self.decoders = self.build_multires_prediction_decoders()
-        self.preds = self.build_multires_prediction_layer()
+        widths = [int(self.base_num_channels * self.channel_multiplier ** i) for i in range(self.num_encoders + 1)]
+        self.encoder_input_sizes, self.encoder_output_sizes = widths[:-1], widths[1:]
+        self.max_num_channels = top = widths[-1]
+        k, out_c = self.kernel_size, self.num_output_channels
+        self.encoders = nn.ModuleList(
+            RecurrentConvLayerIncr(self.num_bins if i == 0 else ci, co, kernel_size=k, stride=2, activation_ff=self.ff_act,
+                                   activation_rec=self.rec_act, norm=self.norm)
+            for i, (ci, co) in enumerate(zip(widths[:-1], widths[1:])))
+        self.resblocks = nn.ModuleList(ResidualBlockIncr(top, top, activation=self.ff_act, norm=self.norm)
+                                       for _ in range(self.num_residual_blocks))
+        # decoder i reads the concatenation [previous prediction (from the second level on) | features | skip]
+        self.decoders = nn.ModuleList(
+            UpsampleConvLayerIncr(2 * ci + (out_c if i else 0), co, kernel_size=k, activation=self.ff_act, norm=self.norm)
+            for i, (ci, co) in enumerate(zip(reversed(widths[1:]), reversed(widths[:-1]))))
+        self.preds = nn.ModuleList(ConvLayerIncr(co, out_c, 1, activation=self.final_activation, norm=self.norm)
+                                   for co in reversed(widths[:-1]))
         self.num_states = self.num_encoders
         self.states = [None] * self.num_states
         self._scratch = Scratch()
-
-    def build_recurrent_encoders(self):
-        encoders = nn.ModuleList()
-        for i, (input_size, output_size) in enumerate(zip(self.encoder_input_sizes, self.encoder_output_sizes)):
-            if i == 0:
-                input_size = self.num_bins
-            encoders.append(RecurrentConvLayerIncr(input_size, output_size, kernel_size=self.kernel_size, stride=2,
-                                                   activation_ff=self.ff_act, activation_rec=self.rec_act,
-                                                   norm=self.norm))
-        return encoders
-
-    def build_resblocks(self):
-        resblocks = nn.ModuleList()
-        for i in range(self.num_residual_blocks):
-            resblocks.append(ResidualBlockIncr(self.max_num_channels, self.max_num_channels, activation=self.ff_act,
-                                               norm=self.norm))
-        return resblocks
-
-    def build_multires_prediction_layer(self):
-        preds = nn.ModuleList()
-        for output_size in reversed(self.encoder_input_sizes):
-            preds.append(ConvLayerIncr(output_size, self.num_output_channels, 1, activation=self.final_activation,
-                                       norm=self.norm))
-        return preds
-
-    def build_multires_prediction_decoders(self):
-        decoder_input_sizes = reversed(self.encoder_output_sizes)
-        decoder_output_sizes = reversed(self.encoder_input_sizes)
-        decoders = nn.ModuleList()
-        for i, (input_size, output_size) in enumerate(zip(decoder_input_sizes, decoder_output_sizes)):
-            prediction_channels = 0 if i == 0 else self.num_output_channels
-            decoders.append(UpsampleConvLayerIncr(2 * input_size + prediction_channels, output_size,
-                                                  kernel_size=self.kernel_size, activation=self.ff_act, norm=self.norm))
-        return decoders
 
     def reset_states(self):
         """Forget the recurrent state the dense pass carries from call to call (reference ``:478-480``)."""
         self.states = [None] * self.num_states
 
-    def forward(self, x_incr):
-        c = _compat(self)
+    def _run(self, ops, x):
         for rb in self.resblocks:
-            rb.compat = c
-        states_incr = [None] * self.num_states
+            rb.compat = _compat(self)
+        # the incremental pass starts every call from a zero state delta (``:451``); the dense pass carries its state
+        states = [None] * self.num_states if ops.incremental else self.states
         blocks = []
         for i, encoder in enumerate(self.encoders):
-            x_incr, state = encoder(x_incr, states_incr[i])
-            blocks.append(x_incr)
-            states_incr[i] = state
+            x, states[i] = encoder._run(ops, x, states[i])
+            blocks.append(x)
         for resblock in self.resblocks:
-            x_incr, _ = resblock(x_incr)
+            x, _ = resblock._run(ops, x)
         predictions = []
         for i, (decoder, pred) in enumerate(zip(self.decoders, self.preds)):
-            x_incr = skip_concat_incr(x_incr, blocks[self.num_encoders - i - 1], self._scratch, f"skip{i}")
-            if i > 0:
-                x_incr = skip_concat_incr(predictions[-1], x_incr, self._scratch, f"pskip{i}")
-            x_incr = decoder(x_incr)
-            predictions.append(pred(x_incr))
+            x = ops.cat(x, blocks.pop(), self._scratch, f"skip{i}")
+            if predictions:
+                x = ops.cat(predictions[-1], x, self._scratch, f"pskip{i}")
+            x = decoder._run(ops, x)
+            predictions.append(pred._run(ops, x))
         return predictions
 
+    def forward(self, x_incr):
+        return self._run(INCR, x_incr)
+
     def forward_refresh_reservoirs(self, x):
-        c = _compat(self)
-        for rb in self.resblocks:
-            rb.compat = c
-        blocks = []
-        for i, encoder in enumerate(self.encoders):
-            x, state = encoder.forward_refresh_reservoirs(x, self.states[i])
-            blocks.append(x)
-            self.states[i] = state
-        for resblock in self.resblocks:
-            x, _ = resblock.forward_refresh_reservoirs(x)
-        predictions = []
-        for i, (decoder, pred) in enumerate(zip(self.decoders, self.preds)):
-            x = self.skip_ftn(x, blocks[self.num_encoders - i - 1])
-            if i > 0:
-                x = self.skip_ftn(predictions[-1], x)
-            x = decoder.forward_refresh_reservoirs(x)
-            predictions.append(pred.forward_refresh_reservoirs(x))
-        return predictions
+        return self._run(DENSE, x)
