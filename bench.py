@@ -549,8 +549,18 @@ def run_ours(args):
         net.load_state_dict(sd)
         return net
 
-    def dense_out(model, x):
-        """Finest-scale dense output of one full pass (what the runner accumulates first)."""
+    def dense_out(model, x, how="library"):
+        """Finest-scale dense output of one full pass (what the runner accumulates first); ``how`` = "library" runs it on
+        PyTorch's dense operators (cuDNN: the comparator the incremental path is checked and timed against), "native" on
+        this library's kernels (what IncrementalRunner.refresh does)."""
+        old = mie.config.refresh
+        mie.config.refresh = how
+        try:
+            return _dense_out(model, x)
+        finally:
+            mie.config.refresh = old
+
+    def _dense_out(model, x):
         with torch.no_grad():
             if not flow:
                 return model.forward_refresh_reservoirs(x, None)[0]
@@ -702,8 +712,27 @@ def run_ours(args):
                         ts.append(e0.elapsed_time(e1))
                 torch.backends.cudnn.allow_tf32 = False
                 return sum(ts) / len(ts)
+            def time_native_refresh():
+                with torch.no_grad():
+                    for i in range(2):
+                        dense_out(dense, frames_dev[i], "native")
+                    torch.cuda.synchronize()
+                    ts = []
+                    for i in range(min(K, 10)):
+                        flush()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(st)
+                        dense_out(dense, frames_dev[2 + i], "native")
+                        e1.record(st)
+                        e1.synchronize()
+                        ts.append(e0.elapsed_time(e1))
+                return sum(ts) / len(ts)
             line["dense"] = {"ms_per_step_fp32": time_dense(False), "ms_per_step_tf32": time_dense(True),
-                             "note": "forward_refresh_reservoirs every step (cuDNN), same frames; context only"}
+                             "note": "forward_refresh_reservoirs every step on PyTorch's dense operators (cuDNN), same "
+                                     "frames; context only",
+                             "refresh_native_ms": time_native_refresh(),
+                             "refresh_native_note": "the same dense pass on this library's FP32 kernels (what a refresh "
+                                                    "costs in IncrementalRunner), eager launches"}
             line["activity"] = activity_table(net, run, frames_dev[2 + Wm + K], dev)
             line["cpu_baseline"] = {k: v for k, v in cpu_reference_arm(20, 2).items()
                                     if k in ("value", "unit", "cores", "kind", "sample")}

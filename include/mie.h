@@ -153,6 +153,13 @@ typedef struct mie_conv_args {
    * rounded).  When given, and the layer qualifies (Cin*k*k >= 256, 16-byte aligned channel strides, ...), the
    * convolution runs on the tensor cores (tcgen05, TF32 inputs, FP32 accumulation); otherwise on the FP32 path. */
   const float *wpacked_tc;
+  /* Dense evaluation (the refresh pass, nnConvIncr.forward_refresh_reservoirs + the activation's,
+   * incr_modules/mask_incr_modules.py:182-196, 253-256): with `refresh` non-zero the input is a dense tensor, not a
+   * delta: d = conv + bias (+ addend); *res = d (set, not advanced); out = f(d) (act == NONE: out = d); every pixel of
+   * every listed tile is written and marked in the tile words.  Needs thr == 0 and no carry buffer; always runs on the
+   * FP32 kernel.  `bias` (cout floats, may be null) is only read in this mode or when given. */
+  const float *bias;
+  int refresh;
 } mie_conv_args;
 
 int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);

@@ -36,6 +36,7 @@ class ConvArgs(C.Structure):
         ("emitted", _vp), ("emitted_ps", _i64),
         ("addend", _vp), ("addend_ps", _i64),
         ("wpacked_tc", _vp),
+        ("bias", _vp), ("refresh", _i),
     ]
 
 

@@ -34,6 +34,8 @@ struct ConvParams {
   const float *addend; int64_t addend_ps;
   int in_vec;   // input can be staged with 16-byte cp.async
   int io_vec;   // epilogue tensors can be accessed as float4
+  const float *bias;   // per output channel, added before the activation (dense evaluation only)
+  int refresh;         // dense evaluation: the reservoir is set instead of advanced, the output is f(conv + bias)
 };
 
 constexpr int CC = 8;  // input channels per chunk
@@ -242,9 +244,14 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
         const int oy = ty * 8 + r;
         if (oy >= p.hout) continue;
         const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
-        bool any_d = false;
+        bool any_d = p.refresh != 0;
 #pragma unroll
         for (int j = 0; j < CPT; ++j) any_d |= (acc[r][j] != 0.0f);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < CPT; ++j)
+            if (co + j < p.cout) acc[r][j] += p.bias[co + j];
+        }
         if (p.addend) {
 #pragma unroll
           for (int j = 0; j < CPT; ++j)
@@ -262,11 +269,12 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
               for (int h = 0; h < CPT / 4; ++h) {
                 if (co + h * 4 < p.cout) {
                   float4 *rp = reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4);
-                  const float4 x = *rp;
+                  const float4 x = p.refresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *rp;
                   const float4 xn = make_float4(x.x + acc[r][h * 4], x.y + acc[r][h * 4 + 1], x.z + acc[r][h * 4 + 2], x.w + acc[r][h * 4 + 3]);
                   if (any_d) *rp = xn;
                   float4 base;
-                  if (p.emitted) base = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
+                  if (p.refresh) base = make_float4(0.f, 0.f, 0.f, 0.f);
+                  else if (p.emitted) base = *reinterpret_cast<const float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4);
                   else base = make_float4(act_apply(p.act, x.x), act_apply(p.act, x.y), act_apply(p.act, x.z), act_apply(p.act, x.w));
                   acc[r][h * 4 + 0] = act_apply(p.act, xn.x) - base.x;
                   acc[r][h * 4 + 1] = act_apply(p.act, xn.y) - base.y;
@@ -279,15 +287,15 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
               for (int j = 0; j < CPT; ++j)
                 if (co + j < p.cout) {
                   float *rp = p.res + pix * p.res_ps + co + j;
-                  const float x = *rp, xn = x + acc[r][j];
+                  const float x = p.refresh ? 0.0f : *rp, xn = x + acc[r][j];
                   if (any_d) *rp = xn;
-                  const float base = p.emitted ? p.emitted[pix * p.emitted_ps + co + j] : act_apply(p.act, x);
+                  const float base = p.refresh ? 0.0f : (p.emitted ? p.emitted[pix * p.emitted_ps + co + j] : act_apply(p.act, x));
                   acc[r][j] = act_apply(p.act, xn) - base;
                 }
             }
           }
         }
-        bool f = false;
+        bool f = p.refresh != 0;   // a dense evaluation marks every pixel it wrote
 #pragma unroll
         for (int j = 0; j < CPT; ++j) f |= (co + j < p.cout) && (fabsf(acc[r][j]) > p.thr);
         if (f) rowflags |= 1u << r;
@@ -413,9 +421,10 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
           for (int j = 0; j < SMALL_COUT; ++j) acc[j] += v * s_w[c * SMALL_COUT + j];
         }
       }
-      bool any_d = false;
+      bool any_d = p.refresh != 0;
 #pragma unroll
       for (int j = 0; j < SMALL_COUT; ++j) {
+        if (j < p.cout && p.bias) acc[j] += p.bias[j];
         if (j < p.cout && p.addend) acc[j] += p.addend[pix * p.addend_ps + j];
         any_d |= (j < p.cout) && (acc[j] != 0.0f);
       }
@@ -426,9 +435,9 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
         if (j < p.cout && p.act != MIE_ACT_NONE) {
           if (any_d || p.emitted) {
             float *rp = p.res + pix * p.res_ps + j;
-            const float x = *rp, xn = x + acc[j];
+            const float x = p.refresh ? 0.0f : *rp, xn = x + acc[j];
             if (any_d) *rp = xn;
-            const float base = p.emitted ? p.emitted[pix * p.emitted_ps + j] : act_apply(p.act, x);
+            const float base = p.refresh ? 0.0f : (p.emitted ? p.emitted[pix * p.emitted_ps + j] : act_apply(p.act, x));
             dy[j] = act_apply(p.act, xn) - base;
           } else {
             dy[j] = 0.0f;
@@ -436,6 +445,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
         }
         flag |= (j < p.cout) && fabsf(dy[j]) > p.thr;
       }
+      flag |= p.refresh != 0;
 #pragma unroll
       for (int j = 0; j < SMALL_COUT; ++j)
         if (j < p.cout) {
@@ -529,6 +539,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (a->act != MIE_ACT_NONE && !a->res) return MIE_EINVAL;
   if (a->act < 0 || a->act > MIE_ACT_TANH) return MIE_EINVAL;
   if (a->act == MIE_ACT_NONE && a->emitted) return MIE_EINVAL;
+  if (a->refresh && (a->thr != 0.0f || a->emitted)) return MIE_EINVAL;
   if (a->stride < 1 || a->stride > 2) return MIE_EUNSUPPORTED;
   if (!aligned16(a->wpacked)) return MIE_EALIGN;
   if (a->wpacked_tc && !aligned16(a->wpacked_tc)) return MIE_EALIGN;
@@ -543,6 +554,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   p.act = a->act; p.thr = a->thr;
   p.res = a->res; p.res_ps = a->res_ps; p.emitted = a->emitted; p.emitted_ps = a->emitted_ps;
   p.addend = a->addend; p.addend_ps = a->addend_ps;
+  p.bias = a->bias; p.refresh = a->refresh ? 1 : 0;
   // 16-byte staging reads whole channel quads: with cin % 4 != 0 the last quad reaches into the pixel's
   // padding channels (in_ps >= cin rounded up to 4), which meet zero filter rows and must be finite
   p.in_vec = (a->in_ps % 4 == 0) && aligned16(a->in) && (a->in_ps >= (a->cin + 3) / 4 * 4);

@@ -976,6 +976,7 @@ bool halo_enabled() {
 // Whether the tensor-core path can take this convolution (host-side rules only).
 bool tc_eligible(const mie_conv_args *a) {
   if (!a->wpacked_tc) return false;
+  if (a->refresh || a->bias) return false;   // dense evaluation (full fp32, bias, reservoir set) is the FP32 kernel's
   if (!(a->stride == 1 || a->stride == 2)) return false;
   if (a->k != 1 && a->k != 3 && a->k != 5 && a->k != 7) return false;
   if (a->in_ps % 4 || !aligned16(a->in)) return false;                           // TMA: 16-byte strides and base

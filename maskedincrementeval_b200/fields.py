@@ -41,6 +41,9 @@ class IncrConfig:
                      switches it on where the reference meant it to sit: each convolution's input delta passes through
                      T = carry + dx; q = k*floor(0.5 + T/k); carry = T - q with this quantisation step k, and the
                      convolution sees q (one more kernel per convolution; what is rounded away stays pending)
+    refresh          "native" (default): the networks' dense pass (forward_refresh_reservoirs) runs on this library's
+                     FP32 kernels in dense-evaluation mode -- every tile listed, bias added, state set instead of
+                     advanced; "library": it runs on PyTorch's dense operators (cuDNN), as the reference's does
     tc_thresholded   False (default): thresholded convolutions (threshold > 0, with or without carry) run on the FP32
                      kernel; True lets layers of 32/64/128/256 output channels use the tensor cores in that mode too
     """
@@ -51,6 +54,7 @@ class IncrConfig:
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
     tc_thresholded: bool = False
     kfenced_step: Optional[float] = None
+    refresh: str = "native"
 
 
 config = IncrConfig()
@@ -150,6 +154,42 @@ def mask_from_tensor(m: torch.Tensor, bits: Optional[torch.Tensor] = None) -> Ti
     nat.check(nat.lib.mie_mask_from_mask(m.data_ptr(), m.element_size(), ps, c, n, h, w, bits.data_ptr(),
                                          nat.stream_ptr(m.device)), "mask_from_mask")
     return TileMask(bits, n, h, w)
+
+
+_full_masks: Dict[Tuple, "TileMask"] = {}
+
+
+def full_mask(n: int, h: int, w: int, device) -> "TileMask":
+    """The mask with every pixel of an [n, *, h, w] field set (ragged edge tiles: only the pixels that exist).  Cached per
+    geometry; what a dense tensor carries when it is fed to the kernels as if it were a delta."""
+    key = (n, h, w, str(device))
+    m = _full_masks.get(key)
+    if m is None:
+        th, tw = -(-h // TILE), -(-w // TILE)
+        rows = torch.tensor([min(TILE, h - ty * TILE) for ty in range(th)])
+        cols = torch.tensor([min(TILE, w - tx * TILE) for tx in range(tw)])
+        rowbits = (1 << cols) - 1                                    # one byte per row of the tile
+        words = torch.zeros(th, tw, dtype=torch.int64)
+        for r in range(TILE):
+            words |= torch.where(rows.view(-1, 1) > r, rowbits.view(1, -1), torch.zeros(1, 1, dtype=torch.int64)) << (8 * r)
+        bits = words.view(1, th, tw).expand(n, th, tw).contiguous().view(-1).to(device)
+        m = _full_masks[key] = TileMask(bits, n, h, w)
+    return m
+
+
+def reset_delta_state(model) -> None:
+    """Zero every persistent delta buffer and tile-word array of ``model`` (the module-owned ``Scratch`` buffers and
+    the convolution plans).  Called after a dense pass that ran through the kernels: it leaves dense values where the
+    incremental steps expect deltas that are exactly zero."""
+    for m in model.modules():
+        sc = m.__dict__.get("_scratch")
+        if isinstance(sc, Scratch):
+            for t in sc._b.values():
+                t.zero_()
+        for plan in getattr(m, "_plans", {}).values() if hasattr(m, "_plans") else ():
+            plan.out.zero_()
+            plan.out_bits.zero_()
+            plan.counts[:3].zero_()
 
 
 class Scratch:

@@ -7,7 +7,10 @@ operator vocabulary below, and is evaluated by one of two interpreters:
            of the module it is given (the reference's ``forward_refresh_reservoirs`` protocol,
            ``incr_modules/mask_incr_modules.py:182-196, 253-256, 77-81``);
 ``INCR``   values are ``[delta, TileMask]`` pairs; each operator is one fused libmie launch over the active tiles
-           (the reference's ``forward`` protocol, ``mask_incr_modules.py:164-179, 248-251, 71-75``).
+           (the reference's ``forward`` protocol, ``mask_incr_modules.py:164-179, 248-251, 71-75``);
+``NATIVE`` the dense pass again, but on this library's kernels: values are ``[dense tensor, full mask]`` pairs, every
+           tile is listed, convolutions run in dense-evaluation mode (bias added, state set instead of advanced, full
+           fp32).  No cuDNN on the path; a network's refresh then costs a few incremental steps instead of sixty.
 
 The reference writes every network twice (a dense and an incremental method per class, kept consistent by hand, which
 is where its skip-connection and residual quirks come from); here the two passes cannot drift apart, and a quirk the
@@ -34,7 +37,17 @@ def _zero_pad_to(x: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
 
 class DenseOps:
     """Dense interpreter: tensors in, tensors out, state refilled."""
-    incremental = False
+    incremental = False     # the pass is an incremental step
+    pairs = False           # values are [tensor, mask] pairs
+
+    def lift(self, x):
+        return x
+
+    def lower(self, v):
+        return v
+
+    def lstm(self, cell, x, prev_state):
+        return cell.forward_refresh_reservoirs(x, prev_state)
 
     def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
         y = conv.forward_refresh_reservoirs(x)
@@ -65,6 +78,16 @@ class DenseOps:
 class IncrOps:
     """Incremental interpreter: ``[delta, TileMask]`` pairs in and out, one fused launch per operator."""
     incremental = True
+    pairs = True
+
+    def lift(self, x):
+        return x
+
+    def lower(self, v):
+        return v
+
+    def lstm(self, cell, x, prev_state):
+        return cell(x, prev_state)
 
     def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
         if norm is not None:      # batch-norm between convolution and activation: not fused
@@ -111,4 +134,47 @@ class IncrOps:
         return [up, fl.upsample2x(d, m, s, ms, up, ub, nat.UP_BILINEAR)]
 
 
-DENSE, INCR = DenseOps(), IncrOps()
+class NativeDenseOps(IncrOps):
+    """Dense interpreter on the library's own kernels: the point operators of ``IncrOps`` with every pixel active,
+    convolutions in dense-evaluation mode.  Values are ``[dense tensor, full mask]`` pairs; ``lift`` / ``lower`` convert
+    at the network's boundary.  The buffers the operators write are the modules' persistent delta buffers, so the caller
+    clones what it keeps (``lower``) and zeroes them afterwards (``fields.reset_delta_state``)."""
+    incremental = False
+    pairs = True
+
+    def lift(self, x):
+        if x is None or isinstance(x, (list, tuple)):
+            return x
+        x = fl.as_channels_last(x)
+        n, _, h, w = x.shape
+        return [x, fl.full_mask(n, h, w, x.device)]
+
+    def lower(self, v):
+        return v[0].clone()
+
+    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
+        if norm is not None:
+            raise NotImplementedError("batch-norm layers take the library dense pass (config.refresh = 'library')")
+        return conv.forward_fused(x, act, addend, cin_limit=cin_limit, refresh=True)
+
+    def act(self, act, x):
+        return [act.forward_refresh_reservoirs(x[0]), x[1]]
+
+    def mul(self, mult, a, b):
+        return [mult.forward_refresh_reservoirs(a[0], b[0]), a[1]]
+
+    def lstm(self, cell, x, prev_state):
+        return cell.refresh_native(x, prev_state)
+
+
+DENSE, INCR, NATIVE = DenseOps(), IncrOps(), NativeDenseOps()
+
+
+def dense_ops(module, x) -> DenseOps:
+    """The interpreter a network's dense pass uses: the kernels when ``config.refresh == "native"``, the input lives on
+    a CUDA device and the network has no normalisation layers; PyTorch's dense operators otherwise."""
+    if fl.config.refresh == "native" and x.is_cuda and getattr(module, "norm", None) is None:
+        return NATIVE
+    if fl.config.refresh not in ("native", "library"):
+        raise ValueError("config.refresh must be 'native' or 'library'")
+    return DENSE

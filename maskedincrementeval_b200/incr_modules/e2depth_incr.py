@@ -19,7 +19,7 @@ import torch.nn as nn
 from .. import _native as nat
 from .. import fields as fl
 from ..fields import Scratch, TileMask, config
-from ._algebra import DENSE, INCR
+from ._algebra import DENSE, INCR, NATIVE, dense_ops
 from .masked_types import DenseT, Masked
 from .mask_incr_modules import (IncrementReserve, KFencedMaskModule, PointwiseMultiplyIncr, nnBatchNorm2dIncr,  # noqa: F401
                                 nnConvIncr, nnReluIncr, nnReservedActivation, nnReservedMultiplication,
@@ -120,6 +120,47 @@ class ConvLSTMIncr(nn.Module):
             0.0, nat.stream_ptr(dev)), "convlstm_point")
         return [dh, TileMask(hb, n, h, w)], [dc, TileMask(cb, n, h, w)]
 
+    def refresh_native(self, x_pair, prev_state):
+        """The dense LSTM step on the kernels: with the three state tensors zeroed, the incremental point kernel fed
+        the dense gate pre-activations (and the dense previous cell as a delta against zero) computes
+        cell = sigmoid(i) * tanh(g) + sigmoid(f) * c_prev and hidden = sigmoid(o) * tanh(cell) -- every "old" term
+        of its product rules is sigmoid(0) = 1/2 or tanh(0) = 0 -- and leaves ``g``, ``cell`` and ``cprev`` refilled.
+        Returns ``([hidden, mask], [cell, mask])`` in the cell's persistent buffers."""
+        sc = self._scratch
+        x, mx = x_pair
+        n, _, h, w = x.shape
+        C, dev = self.hidden_size, x.device
+        shapes = ((n, 4 * C, h, w), (n, C, h, w), (n, C, h, w))
+        bufs = []
+        for buf, shape in zip((self._g, self._cell, self._cprev), shapes):
+            if buf is None or tuple(buf.shape) != shape or buf.device != dev:
+                buf = fl.new_field(*shape, dev)
+            else:
+                buf.zero_()
+            bufs.append(buf)
+        self._g, self._cell, self._cprev = bufs
+        dcp = mcp = None
+        if prev_state is None:
+            dg, mg = self.Gates.forward_fused([x, mx], cin_limit=self.input_size, refresh=True)
+        else:
+            (h_prev, mh), (dcp, mcp) = prev_state
+            dg, mg = self.Gates.forward_fused(INCR.cat([x, mx], [h_prev, mh], sc, "stacked"), refresh=True)
+        self._cprev_zero = prev_state is None
+        dh = sc.get("dh", (n, C, h, w), torch.float32, dev, channels_last=True)
+        dc = sc.get("dc", (n, C, h, w), torch.float32, dev, channels_last=True)
+        hb = sc.get("dh.bits", (fl.n_tiles(n, h, w),), torch.int64, dev)
+        cb = sc.get("dc.bits", (fl.n_tiles(n, h, w),), torch.int64, dev)
+        nat.check(nat.lib.mie_convlstm_point(
+            dg.data_ptr(), fl.pixel_stride(dg), mg.bits.data_ptr(), self._g.data_ptr(), fl.pixel_stride(self._g),
+            nat.ptr(dcp), fl.pixel_stride(dcp) if dcp is not None else 0, mcp.bits.data_ptr() if mcp is not None else None,
+            self._cprev.data_ptr() if dcp is not None else None, fl.pixel_stride(self._cprev),
+            self._cell.data_ptr(), fl.pixel_stride(self._cell), dh.data_ptr(), fl.pixel_stride(dh), hb.data_ptr(),
+            dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1, 0.0, nat.stream_ptr(dev)), "convlstm_point")
+        for i, mod in enumerate((self.sigmoid1, self.sigmoid2, self.sigmoid3, self.tanh1)):
+            mod.in_res.reservoir = self._g[:, i * C:(i + 1) * C]
+        self.tanh2.in_res.reservoir = self._cell
+        return [dh, TileMask(hb, n, h, w)], [dc, TileMask(cb, n, h, w)]
+
     def forward_refresh_reservoirs(self, input_, prev_state):
         """Dense LSTM step; refills ``g``, ``cell`` and ``cprev`` in place (stable addresses across refreshes)."""
         C = self.hidden_size
@@ -162,9 +203,7 @@ class RecurrentConvLayerIncr(nn.Module):
         self.recurrent_block = ConvLSTMIncr(input_size=out_channels, hidden_size=out_channels, kernel_size=3)
 
     def _run(self, ops, x, prev_state):
-        x = self.conv._run(ops, x)
-        cell = self.recurrent_block
-        state = cell(x, prev_state) if ops.incremental else cell.forward_refresh_reservoirs(x, prev_state)
+        state = ops.lstm(self.recurrent_block, self.conv._run(ops, x), prev_state)
         return state[0], state
 
     def forward(self, x_incr, prev_state_incr):
@@ -295,7 +334,7 @@ class UNetRecurrentIncr(BaseUNetIncr):
             x = block._run(ops, x)
         for dec in self.decoders:
             skip = blocks.pop()
-            if ops.incremental:
+            if ops.pairs:
                 x = dec._run(ops, x, skip if skips else None)      # the sum happens inside the upsample kernel
             else:
                 x = dec._run(ops, x + skip)
@@ -309,7 +348,15 @@ class UNetRecurrentIncr(BaseUNetIncr):
         return self._run(INCR, x_incr, prev_states_incr)
 
     def forward_refresh_reservoirs(self, x: DenseT, prev_states):
-        return self._run(DENSE, x, prev_states)
+        ops = dense_ops(self, x)
+        if ops is not NATIVE:
+            return self._run(DENSE, x, prev_states)
+        prev = None if prev_states is None else [None if s is None else (NATIVE.lift(s[0]), NATIVE.lift(s[1]))
+                                                 for s in prev_states]
+        pred, states = self._run(NATIVE, NATIVE.lift(x), prev)
+        out = NATIVE.lower(pred), [(NATIVE.lower(h), NATIVE.lower(c)) for h, c in states]
+        fl.reset_delta_state(self)       # the kernels left dense values where the next step expects zero deltas
+        return out
 
 
 class E2VIDRecurrentIncr(nn.Module):

@@ -361,11 +361,17 @@ class nnConvIncr(nn.Conv2d):
 
     def forward_fused(self, x_incr: Masked, activation: "Optional[nnReservedActivation]" = None,
                       addend: Optional[Masked] = None, cin_limit: Optional[int] = None,
-                      bn: "Optional[nn.BatchNorm2d]" = None) -> Masked:
+                      bn: "Optional[nn.BatchNorm2d]" = None, refresh: bool = False) -> Masked:
         """conv(dx) [* batch-norm scale] [+ addend] [-> incremental activation], one dilation launch and one
-        convolution launch."""
+        convolution launch.
+
+        ``refresh=True`` is the dense evaluation of the same layer on the same kernels: the input pair carries a dense
+        tensor, the bias is added, the activation's reservoir is set to conv + bias (+ addend) and the output is
+        f(reservoir) -- in full fp32, whatever ``config.tensor_cores`` says."""
         sc = self._scratch
-        if config.kfenced_step:
+        if refresh and bn is not None:
+            raise NotImplementedError("dense evaluation with a folded batch-norm")
+        if config.kfenced_step and not refresh:
             x_incr = self._quantise_input(x_incr)
         d, m = fl.resolve(x_incr, sc, "in")
         n, cin, hin, win = d.shape
@@ -377,7 +383,7 @@ class nnConvIncr(nn.Conv2d):
         # assumes; a thresholded layer that is routed to the FP32 kernel must see the plain input and filter.
         thresholded = activation is not None and (activation.thr() > 0.0 or
                                                   (config.carry and activation.emitted is not None))
-        split = self._split_input(cin) and (config.tc_thresholded or not thresholded)
+        split = self._split_input(cin) and (config.tc_thresholded or not thresholded) and not refresh
         wbuf, cp, op, wtc = self._weights(cin_limit, split, bn)
         if split:
             c3 = 3 * ((cin + 7) // 8 * 8)
@@ -402,15 +408,20 @@ class nnConvIncr(nn.Conv2d):
                   "tiles_dilate")
         a.in_, a.in_ps, a.cin = d.data_ptr(), fl.pixel_stride(d), cin
         a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, self.out_channels, op
-        a.wpacked_tc = wtc.data_ptr() if (wtc is not None and config.tensor_cores == "auto") else None
+        a.wpacked_tc = wtc.data_ptr() if (wtc is not None and config.tensor_cores == "auto" and not refresh) else None
+        a.refresh = 1 if refresh else 0
+        a.bias = self.bias.data_ptr() if (refresh and self.bias is not None) else None
         if activation is not None:
             res = activation.in_res.reservoir
+            if refresh and (res is None or res.shape != plan.out.shape or res.device != plan.out.device):
+                activation.in_res.update_reservoir(plan.out)       # allocates; the kernel overwrites it
+                res = activation.in_res.reservoir
             if res is None:
                 raise RuntimeError("forward_refresh_reservoirs must run before the first incremental step")
             if res.shape != plan.out.shape:
                 raise RuntimeError("activation reservoir does not match the convolution output")
-            thr = activation.thr()
-            em = activation.carry_buffer(thr)
+            thr = 0.0 if refresh else activation.thr()
+            em = None if refresh else activation.carry_buffer(thr)
             a.act, a.thr = fl.act_code(activation.op), thr
             a.res, a.res_ps = res.data_ptr(), fl.pixel_stride(res)
             a.emitted, a.emitted_ps = (em.data_ptr(), fl.pixel_stride(em)) if em is not None else (None, 0)
@@ -423,6 +434,11 @@ class nnConvIncr(nn.Conv2d):
             raise RuntimeError("a split-precision convolution did not qualify for the tensor cores (its three channel "
                                "blocks only add up to the fp32 result there); set precision=None on this layer")
         nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
+        if refresh and activation is not None and activation.emitted is not None:
+            if activation.emitted.shape == plan.out.shape and activation.thr() > 0.0 and config.carry:
+                activation.emitted.copy_(plan.out)      # what has been sent so far = f(reservoir)
+            else:
+                activation.emitted = None
         return [plan.out, plan.mask]
 
     def forward(self, x_incr):

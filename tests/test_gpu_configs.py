@@ -162,3 +162,38 @@ def test_config5_flow_nets_track_dense(dev):
         yds = dense.forward_refresh_reservoirs(frames[-1])
     for y, yd in zip(ys, yds):
         assert rel_err(y, yd) <= tol()
+
+
+def test_native_refresh_matches_library_refresh_full_size(dev):
+    """The dense pass on the library's own kernels (dense-evaluation mode, every tile listed) against the same pass on
+    PyTorch's dense operators, E2Depth at 264x352, from the zero state and from a given recurrent state: the
+    prediction, the returned states and every layer's persistent state within 1e-5 of their range; afterwards every
+    delta buffer is zero again, so the next incremental step starts clean."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import nnConvIncr
+    from test_gpu_drift import layer_states
+    frames = [f.to(dev) for f in voxel_sequence(1, 260, 346, 2, 30000, 10, seed=31)]
+    nets = {}
+    old = fl.config.refresh
+    try:
+        for how in ("native", "library"):
+            fl.config.refresh = how
+            net = _e2depth(dev)
+            with torch.no_grad():
+                y0, s0 = net.forward_refresh_reservoirs(frames[0], None)
+                y1, s1 = net.forward_refresh_reservoirs(frames[1], [(h.clone(), c.clone()) for h, c in s0])
+            nets[how] = (net, y0.clone(), y1.clone(), s1)
+    finally:
+        fl.config.refresh = old
+    (na, ya0, ya1, sa), (nb, yb0, yb1, sb) = nets["native"], nets["library"]
+    assert rel_err(ya0, yb0) <= 1e-5 and rel_err(ya1, yb1) <= 1e-5
+    for (ha, ca), (hb, cb) in zip(sa, sb):
+        assert rel_err(ha, hb) <= 1e-5 and rel_err(ca, cb) <= 1e-5
+    la, lb = layer_states(na), layer_states(nb)
+    assert la.keys() == lb.keys()
+    for k in la:
+        assert rel_err(la[k], lb[k]) <= 1e-5, k
+    for m in na.modules():
+        if isinstance(m, nnConvIncr):
+            for plan in m._plans.values():
+                assert float(plan.out.abs().max()) == 0.0 and int(plan.out_bits.abs().max()) == 0
