@@ -49,6 +49,9 @@ class DenseOps:
     def lstm(self, cell, x, prev_state):
         return cell.forward_refresh_reservoirs(x, prev_state)
 
+    def gru(self, cell, x, prev_state):
+        return cell.forward_refresh_reservoirs(x, prev_state)
+
     def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
         y = conv.forward_refresh_reservoirs(x)
         if norm is not None:
@@ -87,6 +90,9 @@ class IncrOps:
         return v
 
     def lstm(self, cell, x, prev_state):
+        return cell(x, prev_state)
+
+    def gru(self, cell, x, prev_state):
         return cell(x, prev_state)
 
     def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
@@ -166,6 +172,9 @@ class NativeDenseOps(IncrOps):
     def lstm(self, cell, x, prev_state):
         return cell.refresh_native(x, prev_state)
 
+    def gru(self, cell, x, prev_state):
+        return cell.refresh_native(x, prev_state)
+
 
 DENSE, INCR, NATIVE = DenseOps(), IncrOps(), NativeDenseOps()
 
@@ -173,8 +182,32 @@ DENSE, INCR, NATIVE = DenseOps(), IncrOps(), NativeDenseOps()
 def dense_ops(module, x) -> DenseOps:
     """The interpreter a network's dense pass uses: the kernels when ``config.refresh == "native"``, the input lives on
     a CUDA device and the network has no normalisation layers; PyTorch's dense operators otherwise."""
-    if fl.config.refresh == "native" and x.is_cuda and getattr(module, "norm", None) is None:
+    carried = any(s is not None for s in getattr(module, "states", None) or ())   # a ConvGRU state kept from the last call
+    if fl.config.refresh == "native" and x.is_cuda and getattr(module, "norm", None) is None and not carried:
         return NATIVE
     if fl.config.refresh not in ("native", "library"):
         raise ValueError("config.refresh must be 'native' or 'library'")
     return DENSE
+
+
+
+def run_dense(network, x, *extra):
+    """A network's dense pass: ``network._run`` under the interpreter ``dense_ops`` picks; with the native one the
+    input is lifted to a pair, every tensor of the result is cloned out of the modules' buffers, and those buffers
+    are zeroed for the incremental steps that follow."""
+    ops = dense_ops(network, x)
+    if ops is not NATIVE:
+        return network._run(DENSE, x, *extra)
+
+    def lower(v):
+        if isinstance(v, dict):
+            return {k: lower(u) for k, u in v.items()}
+        if isinstance(v, (list, tuple)) and len(v) == 2 and torch.is_tensor(v[0]) and isinstance(v[1], fl.TileMask):
+            return NATIVE.lower(v)
+        if isinstance(v, (list, tuple)):
+            return type(v)(lower(u) for u in v)
+        return v
+
+    out = lower(network._run(NATIVE, NATIVE.lift(x), *extra))
+    fl.reset_delta_state(network)
+    return out

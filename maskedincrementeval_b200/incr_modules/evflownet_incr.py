@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from ..fields import Scratch, config
-from ._algebra import DENSE, INCR
+from ._algebra import DENSE, INCR, run_dense
 from .mask_incr_modules import (nnBatchNorm2dIncr, nnConvIncr, nnReservedActivation, nnReservedMultiplication,
                                 nnSigmoidIncr, nnTanhIncr)
 
@@ -77,6 +77,18 @@ class ConvGRUIncr(nn.Module):
         state = [prev_state[0] + moved[0], None]
         return state, state
 
+    def refresh_native(self, x_pair, prev_state):
+        """The dense GRU step from the zero state on the kernels: with h_prev = 0 the reset gate has no effect and the
+        new state is tanh(out_gate(x)) * sigmoid(update_gate(x)); both gate convolutions read the first ``input_size``
+        channels only.  (A carried state takes the library pass: see ``_algebra.dense_ops``.)"""
+        from ._algebra import NATIVE
+        if prev_state is not None:
+            raise NotImplementedError("the dense ConvGRU step on the kernels starts from the zero state")
+        update = NATIVE.conv(self.update_gate, x_pair, self.sigmoid1, cin_limit=self.input_size)
+        candidate = NATIVE.conv(self.out_gate, x_pair, self.tanh, cin_limit=self.input_size)
+        state = NATIVE.mul(self.mult, candidate, update)
+        return state, state
+
     def forward_refresh_reservoirs(self, x, prev_state):
         if prev_state is None:
             prev_state = x.new_zeros((x.shape[0], self.hidden_size) + tuple(x.shape[2:])).contiguous(
@@ -133,8 +145,7 @@ class RecurrentConvLayerIncr(nn.Module):
 
     def _run(self, ops, x, prev_state):
         x = self.conv._run(ops, x)
-        gru = self.recurrent_block
-        return gru(x, prev_state) if ops.incremental else gru.forward_refresh_reservoirs(x, prev_state)
+        return ops.gru(self.recurrent_block, x, prev_state)
 
     def forward(self, x, prev_state):
         return self._run(INCR, x, prev_state)
@@ -253,7 +264,7 @@ class MultiResUNetRecurrentIncr(nn.Module):
         for rb in self.resblocks:
             rb.compat = _compat(self)
         # the incremental pass starts every call from a zero state delta (``:451``); the dense pass carries its state
-        states = [None] * self.num_states if ops.incremental else self.states
+        states = [None] * self.num_states if ops.incremental else list(self.states)
         blocks = []
         for i, encoder in enumerate(self.encoders):
             x, states[i] = encoder._run(ops, x, states[i])
@@ -267,10 +278,11 @@ class MultiResUNetRecurrentIncr(nn.Module):
                 x = ops.cat(predictions[-1], x, self._scratch, f"pskip{i}")
             x = decoder._run(ops, x)
             predictions.append(pred._run(ops, x))
-        return predictions
+        return predictions, states
 
     def forward(self, x_incr):
-        return self._run(INCR, x_incr)
+        return self._run(INCR, x_incr)[0]
 
     def forward_refresh_reservoirs(self, x):
-        return self._run(DENSE, x)
+        predictions, self.states = run_dense(self, x)
+        return predictions

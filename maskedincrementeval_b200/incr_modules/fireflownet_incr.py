@@ -7,6 +7,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
+from ._algebra import INCR, run_dense
 from .evflownet_incr import ConvGRUIncr, ConvLayerIncr, ResidualBlockIncr
 from .mask_incr_modules import nnConvIncr, set_precision  # noqa: F401  (nnConvIncr is imported by the reference too)
 
@@ -34,27 +35,21 @@ class FireFlowNetIncr(nn.Module):
         if self.compat is not None:
             self.R1.compat = self.R2.compat = self.compat
 
+    def _run(self, ops, x):
+        self._sync_compat()
+        x = self.E2._run(ops, self.E1._run(ops, x))
+        x, _ = self.R1._run(ops, x)
+        x = self.E3._run(ops, x)
+        x, _ = self.R2._run(ops, x)
+        return {"flow": [self.pred._run(ops, x)]}
+
     def forward_refresh_reservoirs(self, x):
         """x: N x num_bins x H x W dense input.  Returns {"flow": [N x 2 x H x W]}."""
-        self._sync_compat()
-        x = self.E1.forward_refresh_reservoirs(x)
-        x = self.E2.forward_refresh_reservoirs(x)
-        x, _ = self.R1.forward_refresh_reservoirs(x)
-        x = self.E3.forward_refresh_reservoirs(x)
-        x, _ = self.R2.forward_refresh_reservoirs(x)
-        flow = self.pred.forward_refresh_reservoirs(x)
-        return {"flow": [flow]}
+        return run_dense(self, x)
 
     def forward(self, x_incr):
         """x_incr: [delta, mask].  Returns {"flow": [[delta_flow, mask]]}."""
-        self._sync_compat()
-        x_incr = self.E1(x_incr)
-        x_incr = self.E2(x_incr)
-        x_incr, _ = self.R1(x_incr)
-        x_incr = self.E3(x_incr)
-        x_incr, _ = self.R2(x_incr)
-        flow = self.pred(x_incr)
-        return {"flow": [flow]}
+        return self._run(INCR, x_incr)
 
 
 class RecurrentFireFlowNetIncr(nn.Module):
@@ -91,20 +86,19 @@ class RecurrentFireFlowNetIncr(nn.Module):
         if self.compat is not None:
             self.R1.compat = self.R2.compat = self.compat
 
-    def forward_refresh_reservoirs(self, x):
+    def _run(self, ops, x):
         self._sync_compat()
-        x = self.E1.forward_refresh_reservoirs(x)
-        x, self.states[0] = self.G1.forward_refresh_reservoirs(x, self.states[0])
-        x, _ = self.R1.forward_refresh_reservoirs(x)
-        x, self.states[1] = self.G2.forward_refresh_reservoirs(x, self.states[1])
-        x, _ = self.R2.forward_refresh_reservoirs(x)
-        return {"flow": [self.pred.forward_refresh_reservoirs(x)]}
+        states = [None, None] if ops.incremental else list(self.states)
+        x = self.E1._run(ops, x)
+        x, states[0] = ops.gru(self.G1, x, states[0])
+        x, _ = self.R1._run(ops, x)
+        x, states[1] = ops.gru(self.G2, x, states[1])
+        x, _ = self.R2._run(ops, x)
+        return {"flow": [self.pred._run(ops, x)]}, states
+
+    def forward_refresh_reservoirs(self, x):
+        out, self.states = run_dense(self, x)
+        return out
 
     def forward(self, x_incr):
-        self._sync_compat()
-        x_incr = self.E1(x_incr)
-        x_incr, _ = self.G1(x_incr, None)
-        x_incr, _ = self.R1(x_incr)
-        x_incr, _ = self.G2(x_incr, None)
-        x_incr, _ = self.R2(x_incr)
-        return {"flow": [self.pred(x_incr)]}
+        return self._run(INCR, x_incr)[0]
