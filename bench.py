@@ -409,7 +409,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
     def up_set():
         return dict(a=field(n, c, h, w), b=field(n, c, h, w), ma=full_bits(n, h, w), mb=full_bits(n, h, w),
                     out=fl.new_field(n, c, 2 * h, 2 * w, dev), ob=fl.new_bits(n, 2 * h, 2 * w, dev))
-    measure("upsample2x_vec_kernel", f"x2 bilinear upsample of the sum of two fields, {c} ch, {h}x{w} -> {2 * h}x{2 * w}",
+    measure("upsample2x_tile_kernel", f"x2 bilinear upsample of the sum of two fields, {c} ch, {h}x{w} -> {2 * h}x{2 * w}",
             px * c * 4 * 2 + 4 * px * c * 4, up_set,
             lambda s_: fl.upsample2x(s_["a"], s_["ma"], s_["b"], s_["mb"], s_["out"], s_["ob"]),
             "both inputs read once, output written once (each input pixel feeds four outputs out of cache)")
@@ -420,7 +420,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
     def act_set():
         return dict(d=field(n2, c2, h2, w2), m=full_bits(n2, h2, w2), res=field(n2, c2, h2, w2, 1.0),
                     out=fl.new_field(n2, c2, h2, w2, dev), ob=fl.new_bits(n2, h2, w2, dev))
-    measure("act_incr_kernel", f"incremental ReLU, {c2} ch, {h2}x{w2}, all pixels active", px2 * c2 * 4 * 4, act_set,
+    measure("act_incr_vec_kernel", f"incremental ReLU, {c2} ch, {h2}x{w2}, all pixels active", px2 * c2 * 4 * 4, act_set,
             lambda s_: fl.act_incr(s_["d"], s_["m"], s_["res"], None, s_["out"], s_["ob"], nat.ACT_RELU, 0.0),
             "delta read, reservoir read + written, output written")
 
@@ -429,7 +429,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
         return dict(d1=field(n, c, h, w), d2=field(n, c, h, w), m1=full_bits(n, h, w), m2=full_bits(n, h, w),
                     x1=field(n, c, h, w, 1.0), x2=field(n, c, h, w, 1.0), out=fl.new_field(n, c, h, w, dev),
                     ob=fl.new_bits(n, h, w, dev))
-    measure("mul_incr_kernel", f"incremental product, {c} ch, {h}x{w}, all pixels active", px * c * 4 * 7, mul_set,
+    measure("mul_incr_vec_kernel", f"incremental product, {c} ch, {h}x{w}, all pixels active", px * c * 4 * 7, mul_set,
             lambda s_: fl.mul_incr(s_["d1"], s_["m1"], s_["x1"], s_["d2"], s_["m2"], s_["x2"], s_["out"], s_["ob"]),
             "2 deltas read, 2 reservoirs read + written, output written")
 
@@ -444,7 +444,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
     def cat_set():
         return dict(a=field(n, c, h, w), b=field(n, c, h, w), ma=full_bits(n, h, w), mb=full_bits(n, h, w),
                     out=fl.new_field(n, 2 * c, h, w, dev), ob=fl.new_bits(n, h, w, dev))
-    measure("cat2_kernel", f"channel concatenation {c} + {c} ch, {h}x{w}", px * c * 4 * 4, cat_set,
+    measure("cat2_vec_kernel", f"channel concatenation {c} + {c} ch, {h}x{w}", px * c * 4 * 4, cat_set,
             lambda s_: fl.cat2(s_["a"], s_["ma"], s_["b"], s_["mb"], s_["out"], s_["ob"]))
 
     # output accumulation y += dy, 1 channel at 264x352 (the prediction)

@@ -1215,6 +1215,47 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict
   }
 }
 
+// The same with float4 over channels (C and half multiples of 4): four independent 16-byte loads in flight per thread.
+__global__ void __launch_bounds__(256) split_tf32_vec_kernel(const float *__restrict__ in, int64_t in_ps,
+                                                             const uint64_t *__restrict__ in_bits, int C, int half,
+                                                             float *__restrict__ out, int64_t out_ps,
+                                                             uint64_t *__restrict__ out_bits, int N, int H, int W) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
+  const int q4 = C >> 2;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t w = in_bits[t];
+    const TileGeom g = tile_geom(t, H, W);
+    if (w == 0ull) {
+      if (out_bits[t] != 0ull) {   // held data last step: back to zero
+        __syncthreads();
+        zero_tile4(out, out_ps, 3 * half, g, H, W);
+        if (threadIdx.x == 0) out_bits[t] = 0ull;
+      }
+      continue;
+    }
+#pragma unroll 4
+    for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
+      const int p = e / q4, c = (e - p * q4) * 4;
+      if (!pix_valid(g, p)) continue;
+      const int64_t pix = pix_index(g, p, H, W);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if ((w >> p) & 1ull) v = ld4(in + pix * in_ps + c);
+      const float4 lo = make_float4(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u),
+                                    v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u),
+                                    v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u),
+                                    v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u));
+      float *o = out + pix * out_ps + c;
+      st4(o, v);
+      st4(o + half, lo);
+      st4(o + 2 * half, v);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = w;
+  }
+}
+
 #define MIE_CHECK_FIELD(ptr, ps, C) if (!(ptr) || (ps) < (C)) return MIE_EINVAL
 
 extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_bits, float *res, int64_t res_ps,
@@ -1541,6 +1582,11 @@ extern "C" int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in
   const int half = divup(C, 8) * 8;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(out, out_ps, 3 * half);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
+  if (C % 4 == 0 && in_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(in) && aligned16(out)) {
+    launch_chained(split_tf32_vec_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, in, in_ps, in_bits, C, half, out,
+                   out_ps, out_bits, N, H, W);
+    return check_launch();
+  }
   launch_chained(split_tf32_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, in, in_ps, in_bits, C, half, out, out_ps, out_bits,
                                                                         N, H, W);
   return check_launch();
