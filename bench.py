@@ -815,34 +815,34 @@ def threshold_study(args):
 
 
 def activity_table(net, run, frame, dev):
-    """Active pixel / tile fractions of each convolution's input on one more (eager) step."""
+    """Active pixel / tile fractions of each layer's output delta on one more (eager) step, read from the masks the
+    layers leave behind."""
     from maskedincrementeval_b200.fields import TileMask
     rows = {}
-    hooks = []
 
-    def hook(name):
-        def f(mod, inp, out):
-            m = out[1] if isinstance(out, (list, tuple)) and isinstance(out[1], TileMask) else None
-            if m is None and isinstance(out, (list, tuple)) and isinstance(out[0], (list, tuple)) and \
-                    len(out[0]) == 2 and isinstance(out[0][1], TileMask):
-                m = out[0][1]       # recurrent encoders return ([delta, mask], state)
-            if m is not None:
-                rows[name] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4),
-                              "tiles": round(int((m.bits != 0).sum()) / m.bits.numel(), 4)}
-        return f
+    def put(name, m):
+        if isinstance(m, TileMask):
+            rows[name] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4),
+                          "tiles": round(int((m.bits != 0).sum()) / m.bits.numel(), 4)}
+
+    def conv_mask(conv):
+        plans = list(conv._plans.values())
+        return plans[-1].mask if plans else None
+
     u = net.unetrecurrent
-    named = [("head", u.head)] + [(f"enc{i}", e) for i, e in enumerate(u.encoders)] + \
-            [(f"res{i}", r) for i, r in enumerate(u.resblocks)] + [(f"dec{i}", d) for i, d in enumerate(u.decoders)]
-    for n, mod in named:
-        hooks.append(mod.register_forward_hook(hook(n)))
     with torch.no_grad():
         dx = (frame - run._x_prev).contiguous(memory_format=torch.channels_last)
         rows["input"] = {"px": round(float((dx != 0).any(1).float().mean()), 4)}
         out = net((dx, None), None)
+        put("head", conv_mask(u.head.conv2d))
+        for i, (enc, st) in enumerate(zip(u.encoders, out[1])):
+            put(f"enc{i}", st[0][1])
+        for i, r in enumerate(u.resblocks):
+            put(f"res{i}", conv_mask(r.conv2))
+        for i, d in enumerate(u.decoders):
+            put(f"dec{i}", conv_mask(d.conv2d))
         m = out[0][1]
         rows["pred"] = {"px": round(m.active_pixels() / (m.n * m.h * m.w), 4)}
-    for h in hooks:
-        h.remove()
     return rows
 
 
