@@ -48,8 +48,8 @@ enum {
 
 /* Process-wide options (host).  No counterpart in the reference. */
 enum {
-  /* 1: thresholded convolutions (thr > 0 or a carry buffer) may run on the tensor cores when their channel count
-   *    is 32, 64, 128 or 256; 0 (default): they run on the FP32 kernel. */
+  /* 1: thresholded convolutions (thr > 0 or a carry buffer) may run on the tensor cores; 0 (default): they run on
+   *    the FP32 kernel. */
   MIE_OPT_TC_THRESHOLDED = 1,
   /* iterations after which a barrier wait of the tensor-core kernels gives up; 0 restores the default (2^20) */
   MIE_OPT_TC_SPIN_LIMIT = 2,
@@ -61,6 +61,10 @@ int mie_set_option(int option, int value);
 int mie_get_option(int option, int *value /* host */);
 
 enum { MIE_ACT_NONE = 0, MIE_ACT_RELU = 1, MIE_ACT_SIGMOID = 2, MIE_ACT_TANH = 3 };
+/* Thresholded layers send or withhold a pixel's output channels in groups of this many consecutive channels (a layer of
+ * up to 32 channels decides per pixel).  Small enough that a convolution's channel blocks stay as narrow as in
+ * lossless mode -- a whole-pixel decision would force one thread block to hold every channel of a pixel. */
+#define MIE_THR_GROUP 32
 enum { MIE_UP_BILINEAR = 0, MIE_UP_NEAREST = 1 };
 
 int mie_version(void);
@@ -143,8 +147,9 @@ typedef struct mie_conv_args {
   float *out; int64_t out_ps; uint64_t *out_bits;
   /* fused epilogue: d = conv (+ addend); act==NONE: dy = d; else with x = *res:
    *   dy = f(x + d) - (emitted ? *emitted : f(x));  *res = x + d;
-   * a pixel is sent when any channel has |dy| > thr; withheld pixels are written as 0;
-   * when `emitted` is given it accumulates what was sent. */
+   * thr > 0: the decision unit is a pixel's group of MIE_THR_GROUP consecutive output channels: a group is sent when
+   * one of its channels has |dy| > thr, a withheld group is written as 0; the pixel's mask bit is set when one of its
+   * groups is sent; when `emitted` is given it accumulates what was sent. */
   int act; float thr;
   float *res; int64_t res_ps;
   float *emitted; int64_t emitted_ps;
@@ -206,7 +211,8 @@ int mie_conv_increment_ext(const float *x_incr, const void *mask, int mask_elem_
  * whose input words are all zero (clearing stale output there) and keep the zero invariant.
  * ------------------------------------------------------------------------------------------- */
 
-/* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx when `accumulate` is non-zero; out mask = any_c |dy| > thr.
+/* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx when `accumulate` is non-zero; send decision per pixel and
+ * group of MIE_THR_GROUP channels as in mie_conv_tiles; out mask = a group of the pixel was sent.  C <= 2048.
  * accumulate = 1: nnReservedActivation.forward, incr_modules/mask_incr_modules.py:248-251;
  * accumulate = 0: NonlinearPointOpIncr.forward against a reservoir some other module advances, :101-103 (no carry then).
  * in/out may alias (in place) when in_ps == out_ps. */

@@ -302,6 +302,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
     // combine the per-pixel flags of all channels handled by this block
+    unsigned lo_w = 0, hi_w = 0;   // this warp's flags: pixels of the tile with a change above the threshold in its channels
     {
       unsigned lo = 0, hi = 0;
 #pragma unroll
@@ -310,6 +311,8 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       for (int r = 4; r < 8; ++r) if ((rowflags >> r) & 1u) hi |= 1u << ((r - 4) * 8 + pc);
       lo = __reduce_or_sync(0xffffffffu, lo);
       hi = __reduce_or_sync(0xffffffffu, hi);
+      lo_w = lo;
+      hi_w = hi;
       if (WN > 1) {
         if (lane == 0 && (lo | hi)) atomicOr(&s_bits[ts], ((unsigned long long)hi << 32) | lo);
         __syncthreads();
@@ -319,20 +322,22 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
     const unsigned long long word = s_bits[ts];
+    // Send decision of a thresholded layer: per pixel and per group of 32 consecutive output channels.  With 8
+    // channels per thread a warp covers exactly one group, so its own reduced flags decide; with 4 (the 32-channel
+    // block shape) the block is one group and the block-wide word decides.
+    const unsigned long long group_word = (CPT == 8) ? (((unsigned long long)hi_w << 32) | lo_w) : word;
     if (t >= 0) {
       if (lane == 0 && wn == 0 && word) {
         if (n_cblk > 1) atomicOr(p.out_bits + t, word);
         else p.out_bits[t] = word;
       }
-      // when the channels of a tile are split over several blocks the pixel decision is local to the
-      // block; the host only allows that split with thr == 0, where a withheld pixel is all zeros anyway
       if (ox < p.wout) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           const int oy = ty * 8 + r;
           if (oy >= p.hout) continue;
           const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
-          const bool send = (word >> (r * 8 + pc)) & 1ull;
+          const bool send = (group_word >> (r * 8 + pc)) & 1ull;
           if (p.io_vec) {
 #pragma unroll
             for (int h = 0; h < CPT / 4; ++h)
@@ -570,16 +575,10 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
     return check_launch();
   }
 
-  // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels, except that a
-  // thresholded fused activation needs every channel of a pixel in one block
-  int wt, wn;
-  const bool need_all = (a->thr > 0.0f);
-  if (a->cout_pad == 32) { wt = 4; wn = 1; }
-  else if (!need_all) { wt = 4; wn = 2; if (a->cout_pad % 64) { wt = 4; wn = 1; } }
-  else if (a->cout_pad == 64) { wt = 4; wn = 2; }
-  else if (a->cout_pad == 128) { wt = 2; wn = 4; }
-  else if (a->cout_pad == 256) { wt = 1; wn = 8; }
-  else return MIE_EUNSUPPORTED;  // thresholding across more than 256 output channels
+  // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels.  (A thresholded fused activation
+  // decides per 32-channel group, which both shapes hold in one warp or one block.)
+  int wt = 4, wn = 2;
+  if (a->cout_pad == 32 || a->cout_pad % 64) wn = 1;
 
   const int64_t max_items64 = (int64_t)divup(a->max_tiles, wt) * (a->cout_pad / (32 * wn));
   const int max_items = (int)(max_items64 > (1 << 30) ? (1 << 30) : max_items64);

@@ -283,7 +283,6 @@ __device__ __forceinline__ void tmem_ld16_sum(unsigned taddr, unsigned acc2, flo
 __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, unsigned taddr, bool valid, int64_t pix,
                                                   int co0, unsigned long long *acc_empty_bar, int lane, unsigned acc2 = 0,
                                                   int c_lo = 0, int c_hi = 1 << 30) {
-      bool flag = false;
       // does this pixel carry any change?  (pixels of an active tile outside the dilated support are all
       // zero: they skip the reservoir read-modify-write)
       bool any_d = true;
@@ -299,32 +298,37 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
           for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
       }
       c_hi = min(c_hi, NB);
+      // Thresholded layers decide per pixel and per group of MIE_THR_GROUP = 32 consecutive output channels whether the
+      // group is sent; [c_lo, c_hi) starts on a group boundary and spans whole groups (the host sees to it), so the
+      // decision is local to this thread.  gmask bit g: group g of this thread's range has a channel with |dy| > thr.
+      unsigned gmask = 0;
       for (int c = c_lo; c < c_hi; c += 16) {
         float v[16];
         tmem_ld16_sum(taddr + c, acc2, v);  // every lane of the warp takes part (aligned), valid or not
-        if (valid && co0 + c < p.cout) flag |= tc_epilogue_group(p, v, pix, co0 + c, any_d);
+        if (valid && co0 + c < p.cout && tc_epilogue_group(p, v, pix, co0 + c, any_d)) gmask |= 1u << ((c - c_lo) >> 5);
       }
       // the accumulator has been read: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar);
-      // thresholded mode: withheld pixels become zero, sent pixels are added to the carry.  The host only
-      // selects this kernel with thr > 0 when one block holds every channel of a pixel.
-      if (valid && (p.thr > 0.0f || p.emitted) && c_lo == 0) {
-        const int cend = min(NB, p.cout - co0);
-        if (!flag) {
-          for (int c = 0; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-        } else if (p.emitted) {
-          for (int c = 0; c < cend; c += 4) {
-            const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
-            float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
-            float4 e = *ep;
-            e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
-            *ep = e;
+      // thresholded mode: withheld groups become zero, sent groups are added to the carry
+      if (valid && (p.thr > 0.0f || p.emitted)) {
+        for (int cg = c_lo; cg < c_hi && co0 + cg < p.cout; cg += 32) {
+          const int cend = min(min(cg + 32, c_hi), p.cout - co0);
+          if (!((gmask >> ((cg - c_lo) >> 5)) & 1u)) {
+            for (int c = cg; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else if (p.emitted) {
+            for (int c = cg; c < cend; c += 4) {
+              const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
+              float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
+              float4 e = *ep;
+              e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
+              *ep = e;
+            }
           }
         }
       }
-      return valid && flag;
+      return valid && gmask != 0u;
 }
 
 // ---- coalesced epilogue (lossless layers: no threshold, no carry) ----------------------------------------------
@@ -651,9 +655,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     // =========================== epilogue (warps 4..11) ===========================
     const int q = warp & 3;
     const int half = (warp - 4) >> 2;                  // which half of the block's channels this warp stores
-    // one thread must see every channel of a pixel to decide whether it is sent: thresholded layers leave the
-    // whole pixel to the first warp of the pair
-    const bool whole = p.thr > 0.0f || p.emitted != nullptr || NB < 32;
+    // a thresholded layer decides per 32-channel group, so the two warps of a pair may only split the block's
+    // channels on a group boundary: blocks of 32 channels leave the whole pixel to the first warp of the pair
+    const bool whole = NB < 32 || ((p.thr > 0.0f || p.emitted != nullptr) && NB < 64);
     const int c_lo = whole ? (half ? NB : 0) : half * (NB >> 1);
     const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
@@ -990,14 +994,11 @@ bool tc_eligible(const mie_conv_args *a) {
   if (a->addend && (a->addend_ps % 4 || !aligned16(a->addend))) return false;
   if (a->cout_pad % 16) return false;
   if (a->thr > 0.0f || a->emitted) {
-    // Thresholded layers (a pixel is sent or withheld as a whole, optionally with a carry buffer) run on the FP32
-    // kernel unless MIE_OPT_TC_THRESHOLDED is set: a full-network run of that mode on these kernels once ended in a
-    // device fault whose cause was not found.  When enabled, one block must hold every channel of a pixel
-    // (nb == cout_pad), which the block-width choice below only guarantees for these widths -- the same ones the FP32
-    // kernel accepts.
+    // Thresholded layers (groups of 32 channels of a pixel are sent or withheld, optionally with a carry buffer) run
+    // on the FP32 kernel unless MIE_OPT_TC_THRESHOLDED is set.  The send decision needs whole groups in one block:
+    // cout_pad is a multiple of 32 and the block width chosen below never drops under 32.
     if (!g_opt_tc_thresholded) return false;
-    const int cp = a->cout_pad;
-    if (!(cp == 32 || cp == 64 || cp == 128 || cp == 256)) return false;
+    if (a->cout_pad % 32) return false;
   }
   // Too shallow to pay off.  (The 5x5 head of E2Depth, 5 -> 32 channels, would run 3x faster here than on the
   // FP32 path, but it sees the raw input delta: truncating O(1) values to TF32 every step random-walks in the
@@ -1029,9 +1030,9 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   int nb = 256;
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
-  const bool whole_pixel = a->thr > 0.0f || a->emitted;   // tc_eligible admitted it: cout_pad is a power of two <= 256
-  while (nb > 32 && !whole_pixel && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
-  if (whole_pixel && nb != a->cout_pad) return MIE_EUNSUPPORTED;
+  const bool thresholded = a->thr > 0.0f || a->emitted;
+  while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
+  if (thresholded && nb % 32) return MIE_EUNSUPPORTED;   // a block must hold whole 32-channel groups
   p.nb = nb;
   int acc_cols = 32;
   while (acc_cols < nb) acc_cols <<= 1;

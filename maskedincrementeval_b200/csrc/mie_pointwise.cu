@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
     int N, int C, int H, int W, int op, float thr, int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
+  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 32 channels have a change above the threshold
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
       }
       continue;
     }
-    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    if (threadIdx.x < 64) s_g[threadIdx.x] = 0ull;
     __syncthreads();
     for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
       const int p = e / C, c = e - p * C;
@@ -86,26 +87,30 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
         if (accumulate) res[pix * res_ps + c] = xn;
         const float base = emitted ? emitted[pix * em_ps + c] : act_apply(op, x);
         dy = act_apply(op, xn) - base;
-        if (fabsf(dy) > thr) or_word(s_w, p);
+        if (fabsf(dy) > thr) atomicOr(&s_g[p], 1ull << (c >> 5));
       }
       out[pix * out_ps + c] = dy;
     }
     __syncthreads();
-    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (threadIdx.x < 64) {   // the tile word: a pixel is active when one of its groups is sent
+      const unsigned bal = __ballot_sync(0xffffffffu, s_g[threadIdx.x] != 0ull);
+      if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = bal;
+    }
     if (thr > 0.0f || emitted) {
-      // second pass: withheld pixels are written as zero; sent pixels are added to the carry
+      // second pass: withheld groups are written as zero; sent groups are added to the carry
       for (int e = threadIdx.x; e < 64 * C; e += blockDim.x) {
         const int p = e / C, c = e - p * C;
         if (!pix_valid(g, p) || !((win >> p) & 1ull)) continue;
         const int64_t pix = pix_index(g, p, H, W);
-        if ((wout >> p) & 1ull) {
+        if ((s_g[p] >> (c >> 5)) & 1ull) {
           if (emitted) emitted[pix * em_ps + c] += out[pix * out_ps + c];
         } else {
           out[pix * out_ps + c] = 0.0f;
         }
       }
     }
-    if (threadIdx.x == 0) out_bits[t] = wout;
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0];
     __syncthreads();
   }
 }
@@ -442,6 +447,7 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
     float thr, int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
+  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 32 channels have a change above the threshold
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int q4 = C >> 2, total = 64 * q4;
@@ -456,7 +462,7 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
       }
       continue;
     }
-    if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+    if (threadIdx.x < 64) s_g[threadIdx.x] = 0ull;
     __syncthreads();
     for (int e0 = threadIdx.x; e0 < total; e0 += 2 * blockDim.x) {
       int p[2], c[2];
@@ -486,27 +492,32 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
           if (accumulate) st4(res + pix[u] * res_ps + c[u], xn);
           if (!emitted) b[u] = make_float4(act_t<OP>(x[u].x), act_t<OP>(x[u].y), act_t<OP>(x[u].z), act_t<OP>(x[u].w));
           dy = make_float4(act_t<OP>(xn.x) - b[u].x, act_t<OP>(xn.y) - b[u].y, act_t<OP>(xn.z) - b[u].z, act_t<OP>(xn.w) - b[u].w);
-          if (fabsf(dy.x) > thr || fabsf(dy.y) > thr || fabsf(dy.z) > thr || fabsf(dy.w) > thr) or_word(s_w, p[u]);
+          if (fabsf(dy.x) > thr || fabsf(dy.y) > thr || fabsf(dy.z) > thr || fabsf(dy.w) > thr)
+            atomicOr(&s_g[p[u]], 1ull << (c[u] >> 5));
         }
         st4(out + pix[u] * out_ps + c[u], dy);
       }
     }
     __syncthreads();
-    const uint64_t wout = ((uint64_t)s_w[1] << 32) | s_w[0];
+    if (threadIdx.x < 64) {   // the tile word: a pixel is active when one of its groups is sent
+      const unsigned bal = __ballot_sync(0xffffffffu, s_g[threadIdx.x] != 0ull);
+      if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = bal;
+    }
     if (thr > 0.0f || emitted) {
-      // second pass: withheld pixels are written as zero; sent pixels are added to the carry
+      // second pass: withheld groups are written as zero; sent groups are added to the carry
       for (int e = threadIdx.x; e < total; e += blockDim.x) {
         const int pp = e / q4, cc = (e - pp * q4) * 4;
         if (!pix_valid(g, pp) || !((win >> pp) & 1ull)) continue;
         const int64_t px = pix_index(g, pp, H, W);
-        if ((wout >> pp) & 1ull) {
+        if ((s_g[pp] >> (cc >> 5)) & 1ull) {
           if (emitted) st4(emitted + px * em_ps + cc, f4add(ld4(emitted + px * em_ps + cc), ld4(out + px * out_ps + cc)));
         } else {
           st4(out + px * out_ps + cc, make_float4(0.f, 0.f, 0.f, 0.f));
         }
       }
     }
-    if (threadIdx.x == 0) out_bits[t] = wout;
+    __syncthreads();
+    if (threadIdx.x == 0) out_bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0];
     __syncthreads();
   }
 }
@@ -1263,6 +1274,7 @@ extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_b
                             int C, int H, int W, int op, float thr, int accumulate, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
   if (!accumulate && emitted) return MIE_EINVAL;   // a carry without an advancing reservoir would send the same change again
+  if (C > 2048) return MIE_ETOOBIG;                // 64 channel groups per pixel in the kernels' flag words
   if (op < MIE_ACT_NONE || op > MIE_ACT_TANH) return MIE_EINVAL;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(res, res_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (emitted && emitted_ps < C) return MIE_EINVAL;

@@ -28,7 +28,8 @@ def conv_out_hw(h: int, w: int, k: int, stride: int, pad: int) -> Tuple[int, int
 class IncrConfig:
     """Library-wide defaults; a module reads them when it runs, so they can be changed between steps.
 
-    threshold        activation outputs with max_c |dy| <= threshold at a pixel are withheld (0 = lossless)
+    threshold        a pixel's group of 32 consecutive output channels is withheld while every |dy| in it is <= threshold
+                     (0 = lossless; layers of up to 32 channels decide per pixel)
     carry            keep what was withheld and send it once it grows past the threshold (bounded error)
     input_threshold  threshold used when a mask has to be derived from a bare delta tensor
     tensor_cores     "auto" runs convolutions whose reduction depth Cin*k*k is at least 256 on the tensor cores
@@ -45,7 +46,7 @@ class IncrConfig:
                      FP32 kernels in dense-evaluation mode -- every tile listed, bias added, state set instead of
                      advanced; "library": it runs on PyTorch's dense operators (cuDNN), as the reference's does
     tc_thresholded   False (default): thresholded convolutions (threshold > 0, with or without carry) run on the FP32
-                     kernel; True lets layers of 32/64/128/256 output channels use the tensor cores in that mode too
+                     kernel; True lets them use the tensor cores in that mode too
     """
     threshold: float = 0.0
     carry: bool = True

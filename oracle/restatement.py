@@ -83,21 +83,31 @@ def act_incr(res: Tensor, dx: Tensor, op: str) -> Tuple[Tensor, Tensor]:
     return dy, res + dx
 
 
-def act_incr_thresholded(res: Tensor, emitted: Tensor, dx: Tensor, op: str, thr: float
+THRESHOLD_GROUP = 32   # channels per send decision of a thresholded layer (MIE_THR_GROUP in include/mie.h)
+
+
+def act_incr_thresholded(res: Tensor, emitted: Tensor, dx: Tensor, op: str, thr: float, touched: Tensor = None
                          ) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     """Thresholded incremental nonlinearity with residual carry (this library's extension; at
     thr = 0 it equals ``act_incr``).
 
-    ``emitted`` is the sum of all output deltas sent downstream so far.  dy = f(res+dx) - emitted; a
-    pixel is sent when any channel has |dy| > thr, otherwise its dy is withheld (zero) and stays in
-    the carry.  Only pixels whose input changed are evaluated.  Returns dy, mask, res', emitted'."""
+    ``emitted`` is the sum of all output deltas sent downstream so far.  dy = f(res+dx) - emitted.  The decision unit
+    is a pixel's group of ``THRESHOLD_GROUP`` consecutive channels: a group is sent when one of its channels has
+    |dy| > thr, otherwise its dy is withheld (zero) and stays in the carry; a pixel is active when one of its groups is
+    sent.  Only pixels whose input changed (``touched``, default: any channel of dx non-zero) are evaluated.
+    Returns dy, pixel mask, res', emitted'."""
     f = _OPS[op]
     new = res + dx
     dy = f(new) - emitted
-    touched = (dx != 0).any(dim=1, keepdim=True)
-    send = ((dy.abs() > thr).any(dim=1, keepdim=True)) & touched
+    if touched is None:
+        touched = (dx != 0).any(dim=1, keepdim=True)
+    n, c, h, w = dy.shape
+    pad = (-c) % THRESHOLD_GROUP
+    over = torch.nn.functional.pad(dy.abs() > thr, (0, 0, 0, 0, 0, pad))
+    group_send = over.view(n, -1, THRESHOLD_GROUP, h, w).any(dim=2, keepdim=True)          # [n, groups, 1, h, w]
+    send = group_send.expand(-1, -1, THRESHOLD_GROUP, -1, -1).reshape(n, c + pad, h, w)[:, :c] & touched
     dy = torch.where(send, dy, torch.zeros_like(dy))
-    return dy, send.to(torch.uint8), new, emitted + dy
+    return dy, send.any(dim=1, keepdim=True).to(torch.uint8), new, emitted + dy
 
 
 def mul_incr(x1: Tensor, dx1: Tensor, x2: Tensor, dx2: Tensor) -> Tuple[Tensor, Tensor, Tensor]:

@@ -202,6 +202,8 @@ def _thresholded_run(dev, cfg, tc_thresholded, steps=5, thr=0.02):
             sent += dy
             out.append((dy.clone(), m.pixel_mask().clone(), sent.clone(), layer.conv2d.last_used_tensor_cores))
         truth = torch.relu(layer.activation.in_res.reservoir).clone()
+        from maskedincrementeval_b200.incr_modules.mask_incr_modules import check_device_errors
+        check_device_errors(layer)
     return out, truth
 
 
@@ -234,15 +236,63 @@ def test_thresholded_narrow_input_layer_on_fp32_kernel_is_plain_fp32(dev):
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
 
 
-def test_thresholded_odd_channel_count_same_on_both_settings(dev):
-    """96 output channels with a threshold: no kernel holds every channel of a pixel in one block at that width, on
-    either path, so the layer is refused the same way whether or not thresholded tensor-core layers are enabled
-    (a block-local send decision would drop channels of a sent pixel for good)."""
+def test_thresholded_channel_count_off_a_power_of_two(dev):
+    """96 output channels with a threshold: three groups of 32 channels, each decided on its own, on the FP32 kernel
+    (three blocks of 32 channels) and on the tensor cores (blocks of 32): the carry invariant holds on both."""
     from maskedincrementeval_b200 import fields as fl
     fl.config.tensor_cores = "auto"
     for flag in (False, True):
-        with pytest.raises(NotImplementedError):
-            _thresholded_run(dev, (64, 96, 3, 1, 24, 40, False), tc_thresholded=flag, steps=1)
+        steps, truth = _thresholded_run(dev, (64, 96, 3, 1, 24, 40, False), tc_thresholded=flag, steps=4)
+        assert all(s[3] == flag for s in steps)
+        assert float((steps[-1][2] - truth).abs().max()) <= 0.02 + (2e-3 if flag else 1e-5)
+        for dy, pm, _, _ in steps:
+            assert torch.equal(pm, (dy != 0).any(1, keepdim=True).to(torch.uint8))
+
+
+@pytest.mark.parametrize("channels", [72, 70, 8, 160])
+@pytest.mark.parametrize("op", ["relu", "tanh"])
+def test_thresholded_groups_match_oracle(dev, channels, op):
+    """The send decision of a thresholded activation is per pixel and per group of 32 consecutive channels: values,
+    pixel mask, reservoir and carry against the CPU restatement, on the float4 kernel (channel counts that are
+    multiples of 4) and on the scalar one (70)."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import nnReservedActivation
+    fl.config.carry = True
+    thr = 0.05
+    g = torch.Generator().manual_seed(channels)
+    x = torch.randn(2, channels, 19, 27, generator=g)
+    act = nnReservedActivation(getattr(torch, op), threshold=thr)
+    with torch.no_grad():
+        act.forward_refresh_reservoirs(cl(x, dev))
+        res, em = x.clone(), R._OPS[op](x)
+        groups_differ = False
+        for step in range(8):
+            dx = sparse_delta(g, x.shape, 0.3, std=0.04)
+            dy, m = act([cl(dx, dev), None])
+            want, wm, res, em = R.act_incr_thresholded(res, em, dx, op, thr)
+            assert torch.equal(m.pixel_mask().cpu(), wm)
+            assert float((dy.cpu() - want).abs().max()) <= 1e-5
+            assert float((act.emitted.cpu() - em).abs().max()) <= 1e-5
+            if channels > 32:
+                g0, g1 = (want[:, :32] != 0).any(1), (want[:, 32:64] != 0).any(1)
+                groups_differ |= bool((g0 != g1).any())
+        assert channels <= 32 or groups_differ      # the groups of a pixel really are decided independently
+
+
+@pytest.mark.parametrize("cfg", DEEP)
+def test_thresholded_tensor_core_layers_against_fp32_kernel(dev, cfg):
+    """Thresholded layers on the tensor cores (opt-in) at the deep-layer shapes of E2Depth, partially active, with carry
+    and residual addend: same carry invariant as the FP32 kernel, pixel masks that differ only where a change sits within
+    the TF32 error of the threshold, and a clean error word."""
+    from maskedincrementeval_b200 import fields as fl
+    fl.config.tensor_cores = "auto"
+    a, ta = _thresholded_run(dev, cfg, tc_thresholded=True)
+    b, tb = _thresholded_run(dev, cfg, tc_thresholded=False)
+    assert all(s[3] for s in a) and not any(s[3] for s in b)
+    assert float((a[-1][2] - ta).abs().max()) <= 0.02 + 2e-3
+    differing = sum(int((x[1] != y[1]).sum()) for x, y in zip(a, b))
+    total = sum(x[1].numel() for x in a)
+    assert differing <= 0.01 * total, (differing, total)
 
 
 def test_carry_survives_threshold_toggle(dev):
