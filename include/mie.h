@@ -62,9 +62,10 @@ int mie_get_option(int option, int *value /* host */);
 
 enum { MIE_ACT_NONE = 0, MIE_ACT_RELU = 1, MIE_ACT_SIGMOID = 2, MIE_ACT_TANH = 3 };
 /* Thresholded layers send or withhold a pixel's output channels in groups of this many consecutive channels (a layer of
- * up to 32 channels decides per pixel).  Small enough that a convolution's channel blocks stay as narrow as in
- * lossless mode -- a whole-pixel decision would force one thread block to hold every channel of a pixel. */
-#define MIE_THR_GROUP 32
+ * up to 16 channels decides per pixel).  It is the unit the convolution epilogues work in, so a group is decided by the
+ * thread that computed it, in one pass, and a convolution's channel blocks stay as narrow as in lossless mode -- a
+ * whole-pixel decision would force one thread block to hold every channel of a pixel. */
+#define MIE_THR_GROUP 16
 enum { MIE_UP_BILINEAR = 0, MIE_UP_NEAREST = 1 };
 
 int mie_version(void);
@@ -212,7 +213,7 @@ int mie_conv_increment_ext(const float *x_incr, const void *mask, int mask_elem_
  * ------------------------------------------------------------------------------------------- */
 
 /* dy = f(res + dx) - (emitted ? emitted : f(res)); res += dx when `accumulate` is non-zero; send decision per pixel and
- * group of MIE_THR_GROUP channels as in mie_conv_tiles; out mask = a group of the pixel was sent.  C <= 2048.
+ * group of MIE_THR_GROUP channels as in mie_conv_tiles; out mask = a group of the pixel was sent.  C <= 1024.
  * accumulate = 1: nnReservedActivation.forward, incr_modules/mask_incr_modules.py:248-251;
  * accumulate = 0: NonlinearPointOpIncr.forward against a reservoir some other module advances, :101-103 (no carry then).
  * in/out may alias (in place) when in_ps == out_ps. */

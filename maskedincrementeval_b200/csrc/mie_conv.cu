@@ -302,7 +302,6 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
     // combine the per-pixel flags of all channels handled by this block
-    unsigned lo_w = 0, hi_w = 0;   // this warp's flags: pixels of the tile with a change above the threshold in its channels
     {
       unsigned lo = 0, hi = 0;
 #pragma unroll
@@ -311,8 +310,6 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       for (int r = 4; r < 8; ++r) if ((rowflags >> r) & 1u) hi |= 1u << ((r - 4) * 8 + pc);
       lo = __reduce_or_sync(0xffffffffu, lo);
       hi = __reduce_or_sync(0xffffffffu, hi);
-      lo_w = lo;
-      hi_w = hi;
       if (WN > 1) {
         if (lane == 0 && (lo | hi)) atomicOr(&s_bits[ts], ((unsigned long long)hi << 32) | lo);
         __syncthreads();
@@ -322,10 +319,11 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
     const unsigned long long word = s_bits[ts];
-    // Send decision of a thresholded layer: per pixel and per group of 32 consecutive output channels.  With 8
-    // channels per thread a warp covers exactly one group, so its own reduced flags decide; with 4 (the 32-channel
-    // block shape) the block is one group and the block-wide word decides.
-    const unsigned long long group_word = (CPT == 8) ? (((unsigned long long)hi_w << 32) | lo_w) : word;
+    // Send decision of a thresholded layer: per pixel and per group of MIE_THR_GROUP = 16 consecutive output channels.
+    // A thread holds CPT channels of 8 pixels (one tile column); the lanes that hold the other channels of the same
+    // group and column are 8 (CPT = 8: two lanes per group) or 8, 16 and 24 (CPT = 4: the warp is one group) away.
+    unsigned groupflags = rowflags | __shfl_xor_sync(0xffffffffu, rowflags, 8);
+    if (CPT == 4) groupflags |= __shfl_xor_sync(0xffffffffu, groupflags, 16);
     if (t >= 0) {
       if (lane == 0 && wn == 0 && word) {
         if (n_cblk > 1) atomicOr(p.out_bits + t, word);
@@ -337,7 +335,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
           const int oy = ty * 8 + r;
           if (oy >= p.hout) continue;
           const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
-          const bool send = (group_word >> (r * 8 + pc)) & 1ull;
+          const bool send = (groupflags >> r) & 1u;
           if (p.io_vec) {
 #pragma unroll
             for (int h = 0; h < CPT / 4; ++h)
@@ -576,7 +574,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   }
 
   // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels.  (A thresholded fused activation
-  // decides per 32-channel group, which both shapes hold in one warp or one block.)
+  // decides per 16-channel group, which both shapes hold inside one warp.)
   int wt = 4, wn = 2;
   if (a->cout_pad == 32 || a->cout_pad % 64) wn = 1;
 

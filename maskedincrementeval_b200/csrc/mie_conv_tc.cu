@@ -235,24 +235,35 @@ __device__ __forceinline__ bool tc_epilogue_group_t(const TcParams &p, const flo
       }
     }
   }
+  // The 16 channels of this call are one send-decision group of a thresholded layer (MIE_THR_GROUP): all four quads
+  // are evaluated first, then written -- as computed when the group is sent (and added to the carry), as zeros when it
+  // is withheld.  A lossless layer (thr == 0, no carry) sends every group.
+  float4 o[4];
 #pragma unroll
   for (int h = 0; h < 4; ++h) {
     if (h >= nq) continue;
-    float4 o = d[h];
+    o[h] = d[h];
     if (ACT != MIE_ACT_NONE) {
       if (any_d) {
         const float4 xn = f4add(x[h], d[h]);
         *reinterpret_cast<float4 *>(p.res + pix * p.res_ps + co + h * 4) = xn;
         if (!p.emitted)
           base[h] = make_float4(tc_act<ACT>(p.act, x[h].x), tc_act<ACT>(p.act, x[h].y), tc_act<ACT>(p.act, x[h].z), tc_act<ACT>(p.act, x[h].w));
-        o = make_float4(tc_act<ACT>(p.act, xn.x) - base[h].x, tc_act<ACT>(p.act, xn.y) - base[h].y,
-                        tc_act<ACT>(p.act, xn.z) - base[h].z, tc_act<ACT>(p.act, xn.w) - base[h].w);
+        o[h] = make_float4(tc_act<ACT>(p.act, xn.x) - base[h].x, tc_act<ACT>(p.act, xn.y) - base[h].y,
+                           tc_act<ACT>(p.act, xn.z) - base[h].z, tc_act<ACT>(p.act, xn.w) - base[h].w);
       } else {
-        o = make_float4(0.f, 0.f, 0.f, 0.f);
+        o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    flag |= fabsf(o.x) > p.thr || fabsf(o.y) > p.thr || fabsf(o.z) > p.thr || fabsf(o.w) > p.thr;
-    *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = o;
+    flag |= fabsf(o[h].x) > p.thr || fabsf(o[h].y) > p.thr || fabsf(o[h].z) > p.thr || fabsf(o[h].w) > p.thr;
+  }
+  const bool withheld = !flag && (p.thr > 0.0f || p.emitted != nullptr);
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    if (h >= nq) continue;
+    *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co + h * 4) = withheld ? make_float4(0.f, 0.f, 0.f, 0.f) : o[h];
+    if (ACT != MIE_ACT_NONE && p.emitted && flag)
+      *reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co + h * 4) = f4add(base[h], o[h]);
   }
   return flag;
 }
@@ -298,37 +309,17 @@ __device__ __forceinline__ bool tc_epilogue_pixel(const TcParams &p, int NB, uns
           for (int c = 0; c < NB && co0 + c < p.cout; ++c) any_d |= (p.addend[pix * p.addend_ps + co0 + c] != 0.0f);
       }
       c_hi = min(c_hi, NB);
-      // Thresholded layers decide per pixel and per group of MIE_THR_GROUP = 32 consecutive output channels whether the
-      // group is sent; [c_lo, c_hi) starts on a group boundary and spans whole groups (the host sees to it), so the
-      // decision is local to this thread.  gmask bit g: group g of this thread's range has a channel with |dy| > thr.
-      unsigned gmask = 0;
+      bool flag = false;    // some group of this thread's channel range was sent
       for (int c = c_lo; c < c_hi; c += 16) {
         float v[16];
         tmem_ld16_sum(taddr + c, acc2, v);  // every lane of the warp takes part (aligned), valid or not
-        if (valid && co0 + c < p.cout && tc_epilogue_group(p, v, pix, co0 + c, any_d)) gmask |= 1u << ((c - c_lo) >> 5);
+        if (valid && co0 + c < p.cout) flag |= tc_epilogue_group(p, v, pix, co0 + c, any_d);
       }
       // the accumulator has been read: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar);
-      // thresholded mode: withheld groups become zero, sent groups are added to the carry
-      if (valid && (p.thr > 0.0f || p.emitted)) {
-        for (int cg = c_lo; cg < c_hi && co0 + cg < p.cout; cg += 32) {
-          const int cend = min(min(cg + 32, c_hi), p.cout - co0);
-          if (!((gmask >> ((cg - c_lo) >> 5)) & 1u)) {
-            for (int c = cg; c < cend; c += 4) *reinterpret_cast<float4 *>(p.out + pix * p.out_ps + co0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-          } else if (p.emitted) {
-            for (int c = cg; c < cend; c += 4) {
-              const float4 d = *reinterpret_cast<const float4 *>(p.out + pix * p.out_ps + co0 + c);
-              float4 *ep = reinterpret_cast<float4 *>(p.emitted + pix * p.emitted_ps + co0 + c);
-              float4 e = *ep;
-              e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
-              *ep = e;
-            }
-          }
-        }
-      }
-      return valid && gmask != 0u;
+      return valid && flag;
 }
 
 // ---- coalesced epilogue (lossless layers: no threshold, no carry) ----------------------------------------------
@@ -655,9 +646,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     // =========================== epilogue (warps 4..11) ===========================
     const int q = warp & 3;
     const int half = (warp - 4) >> 2;                  // which half of the block's channels this warp stores
-    // a thresholded layer decides per 32-channel group, so the two warps of a pair may only split the block's
-    // channels on a group boundary: blocks of 32 channels leave the whole pixel to the first warp of the pair
-    const bool whole = NB < 32 || ((p.thr > 0.0f || p.emitted != nullptr) && NB < 64);
+    // the two warps of a pair split the block's channels in halves of at least one 16-channel group (the unit of the
+    // epilogue and of a thresholded layer's send decision); narrower blocks leave the pixel to the first warp
+    const bool whole = NB < 32;
     const int c_lo = whole ? (half ? NB : 0) : half * (NB >> 1);
     const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
@@ -994,11 +985,10 @@ bool tc_eligible(const mie_conv_args *a) {
   if (a->addend && (a->addend_ps % 4 || !aligned16(a->addend))) return false;
   if (a->cout_pad % 16) return false;
   if (a->thr > 0.0f || a->emitted) {
-    // Thresholded layers (groups of 32 channels of a pixel are sent or withheld, optionally with a carry buffer) run
-    // on the FP32 kernel unless MIE_OPT_TC_THRESHOLDED is set.  The send decision needs whole groups in one block:
-    // cout_pad is a multiple of 32 and the block width chosen below never drops under 32.
+    // Thresholded layers (groups of 16 channels of a pixel are sent or withheld, optionally with a carry buffer) run
+    // on the FP32 kernel unless MIE_OPT_TC_THRESHOLDED is set.  The epilogue works in 16-channel groups, which are the
+    // decision unit, so any block width takes part.
     if (!g_opt_tc_thresholded) return false;
-    if (a->cout_pad % 32) return false;
   }
   // Too shallow to pay off.  (The 5x5 head of E2Depth, 5 -> 32 channels, would run 3x faster here than on the
   // FP32 path, but it sees the raw input delta: truncating O(1) values to TF32 every step random-walks in the
@@ -1030,9 +1020,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   int nb = 256;
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
-  const bool thresholded = a->thr > 0.0f || a->emitted;
   while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
-  if (thresholded && nb % 32) return MIE_EUNSUPPORTED;   // a block must hold whole 32-channel groups
   p.nb = nb;
   int acc_cols = 32;
   while (acc_cols < nb) acc_cols <<= 1;

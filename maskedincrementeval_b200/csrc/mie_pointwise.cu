@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
     int N, int C, int H, int W, int op, float thr, int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
-  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 32 channels have a change above the threshold
+  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 16 channels have a change above the threshold
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
         if (accumulate) res[pix * res_ps + c] = xn;
         const float base = emitted ? emitted[pix * em_ps + c] : act_apply(op, x);
         dy = act_apply(op, xn) - base;
-        if (fabsf(dy) > thr) atomicOr(&s_g[p], 1ull << (c >> 5));
+        if (fabsf(dy) > thr) atomicOr(&s_g[p], 1ull << (c >> 4));
       }
       out[pix * out_ps + c] = dy;
     }
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(1024) act_incr_kernel(
         const int p = e / C, c = e - p * C;
         if (!pix_valid(g, p) || !((win >> p) & 1ull)) continue;
         const int64_t pix = pix_index(g, p, H, W);
-        if ((s_g[p] >> (c >> 5)) & 1ull) {
+        if ((s_g[p] >> (c >> 4)) & 1ull) {
           if (emitted) emitted[pix * em_ps + c] += out[pix * out_ps + c];
         } else {
           out[pix * out_ps + c] = 0.0f;
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
     float thr, int accumulate) {
   grid_dependency_wait();
   grid_dependency_trigger();
-  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 32 channels have a change above the threshold
+  __shared__ unsigned long long s_g[64];   // per pixel: which groups of 16 channels have a change above the threshold
   __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int q4 = C >> 2, total = 64 * q4;
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
           if (!emitted) b[u] = make_float4(act_t<OP>(x[u].x), act_t<OP>(x[u].y), act_t<OP>(x[u].z), act_t<OP>(x[u].w));
           dy = make_float4(act_t<OP>(xn.x) - b[u].x, act_t<OP>(xn.y) - b[u].y, act_t<OP>(xn.z) - b[u].z, act_t<OP>(xn.w) - b[u].w);
           if (fabsf(dy.x) > thr || fabsf(dy.y) > thr || fabsf(dy.z) > thr || fabsf(dy.w) > thr)
-            atomicOr(&s_g[p[u]], 1ull << (c[u] >> 5));
+            atomicOr(&s_g[p[u]], 1ull << (c[u] >> 4));
         }
         st4(out + pix[u] * out_ps + c[u], dy);
       }
@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(256) act_incr_vec_kernel(
         const int pp = e / q4, cc = (e - pp * q4) * 4;
         if (!pix_valid(g, pp) || !((win >> pp) & 1ull)) continue;
         const int64_t px = pix_index(g, pp, H, W);
-        if ((s_g[pp] >> (cc >> 5)) & 1ull) {
+        if ((s_g[pp] >> (cc >> 4)) & 1ull) {
           if (emitted) st4(emitted + px * em_ps + cc, f4add(ld4(emitted + px * em_ps + cc), ld4(out + px * out_ps + cc)));
         } else {
           st4(out + px * out_ps + cc, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -1274,7 +1274,7 @@ extern "C" int mie_act_incr(const float *in, int64_t in_ps, const uint64_t *in_b
                             int C, int H, int W, int op, float thr, int accumulate, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits || !(thr >= 0.0f)) return MIE_EINVAL;
   if (!accumulate && emitted) return MIE_EINVAL;   // a carry without an advancing reservoir would send the same change again
-  if (C > 2048) return MIE_ETOOBIG;                // 64 channel groups per pixel in the kernels' flag words
+  if (C > 1024) return MIE_ETOOBIG;                // 64 channel groups per pixel in the kernels' flag words
   if (op < MIE_ACT_NONE || op > MIE_ACT_TANH) return MIE_EINVAL;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(res, res_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   if (emitted && emitted_ps < C) return MIE_EINVAL;

@@ -28,8 +28,8 @@ def conv_out_hw(h: int, w: int, k: int, stride: int, pad: int) -> Tuple[int, int
 class IncrConfig:
     """Library-wide defaults; a module reads them when it runs, so they can be changed between steps.
 
-    threshold        a pixel's group of 32 consecutive output channels is withheld while every |dy| in it is <= threshold
-                     (0 = lossless; layers of up to 32 channels decide per pixel)
+    threshold        a pixel's group of 16 consecutive output channels is withheld while every |dy| in it is <= threshold
+                     (0 = lossless; layers of up to 16 channels decide per pixel)
     carry            keep what was withheld and send it once it grows past the threshold (bounded error)
     input_threshold  threshold used when a mask has to be derived from a bare delta tensor
     tensor_cores     "auto" runs convolutions whose reduction depth Cin*k*k is at least 256 on the tensor cores

@@ -83,7 +83,7 @@ def act_incr(res: Tensor, dx: Tensor, op: str) -> Tuple[Tensor, Tensor]:
     return dy, res + dx
 
 
-THRESHOLD_GROUP = 32   # channels per send decision of a thresholded layer (MIE_THR_GROUP in include/mie.h)
+THRESHOLD_GROUP = 16   # channels per send decision of a thresholded layer (MIE_THR_GROUP in include/mie.h)
 
 
 def act_incr_thresholded(res: Tensor, emitted: Tensor, dx: Tensor, op: str, thr: float, touched: Tensor = None

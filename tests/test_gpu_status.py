@@ -237,7 +237,7 @@ def test_thresholded_narrow_input_layer_on_fp32_kernel_is_plain_fp32(dev):
 
 
 def test_thresholded_channel_count_off_a_power_of_two(dev):
-    """96 output channels with a threshold: three groups of 32 channels, each decided on its own, on the FP32 kernel
+    """96 output channels with a threshold: six groups of 16 channels, each decided on its own, on the FP32 kernel
     (three blocks of 32 channels) and on the tensor cores (blocks of 32): the carry invariant holds on both."""
     from maskedincrementeval_b200 import fields as fl
     fl.config.tensor_cores = "auto"
@@ -252,7 +252,7 @@ def test_thresholded_channel_count_off_a_power_of_two(dev):
 @pytest.mark.parametrize("channels", [72, 70, 8, 160])
 @pytest.mark.parametrize("op", ["relu", "tanh"])
 def test_thresholded_groups_match_oracle(dev, channels, op):
-    """The send decision of a thresholded activation is per pixel and per group of 32 consecutive channels: values,
+    """The send decision of a thresholded activation is per pixel and per group of 16 consecutive channels: values,
     pixel mask, reservoir and carry against the CPU restatement, on the float4 kernel (channel counts that are
     multiples of 4) and on the scalar one (70)."""
     from maskedincrementeval_b200 import fields as fl
@@ -273,10 +273,10 @@ def test_thresholded_groups_match_oracle(dev, channels, op):
             assert torch.equal(m.pixel_mask().cpu(), wm)
             assert float((dy.cpu() - want).abs().max()) <= 1e-5
             assert float((act.emitted.cpu() - em).abs().max()) <= 1e-5
-            if channels > 32:
-                g0, g1 = (want[:, :32] != 0).any(1), (want[:, 32:64] != 0).any(1)
+            if channels > 16:
+                g0, g1 = (want[:, :16] != 0).any(1), (want[:, 16:32] != 0).any(1)
                 groups_differ |= bool((g0 != g1).any())
-        assert channels <= 32 or groups_differ      # the groups of a pixel really are decided independently
+        assert channels <= 16 or groups_differ      # the groups of a pixel really are decided independently
 
 
 @pytest.mark.parametrize("cfg", DEEP)
