@@ -237,14 +237,20 @@ int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x
  *   cell   [N,C,H,W]   accumulated cell (reservoir of the second tanh)
  *   dc_prev/dcp_bits   incoming previous-cell delta, may be null
  *   dh, dc             outgoing hidden and cell deltas; their masks are the union of the incoming masks
- *                      (gate delta | previous-cell delta), pixel for pixel; thr is reserved and must be 0
+ *                      (gate delta | previous-cell delta), pixel for pixel
+ *   h_sent / thr       thresholded hidden output (no counterpart in the reference): with h_sent given ([N,C,H,W], what
+ *                      has been sent so far; the dense hidden state right after a refresh) the hidden delta is
+ *                      dh = h_new - h_sent, a pixel's group of MIE_THR_GROUP channels is sent (and h_sent advanced)
+ *                      when one of its |dh| exceeds thr and written as 0 otherwise, and the hidden mask is the set of
+ *                      pixels with a sent group.  Needs C % 16 == 0 and 16-byte aligned strides.  thr > 0 needs h_sent
  *   sum_m2             1: cell delta = m1 + m2 (dense-exact); 0: m1 only, as the reference computes
  *                      (its `+` concatenates two lists, e2depth_incr.py:113) */
 int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, float *g, int64_t g_ps,
                        const float *dc_prev, int64_t dcp_ps, const uint64_t *dcp_bits,
                        float *cprev, int64_t cprev_ps, float *cell, int64_t cell_ps,
                        float *dh, int64_t dh_ps, uint64_t *dh_bits, float *dc, int64_t dc_ps,
-                       uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2, float thr, void *stream);
+                       uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2, float thr, float *h_sent,
+                       int64_t hs_ps, void *stream);
 
 /* out[N,C,2H,2W] = up2(a (+ b)); bilinear (align_corners=False) or nearest.  b may be null.
  * interpolate_from_module, incr_modules/mask_incr_functional.py:76-78; the sum is the skip

@@ -357,7 +357,8 @@ __device__ __forceinline__ void zero_tile4(float *out, int64_t ps, int C, const 
 }
 
 __device__ __forceinline__ void lstm_elem(float gi, float gf, float go, float gc, float di, float df, float dob, float dcg,
-                                          float cp_o, float Dcp, bool use_cp, float c_o, int sum_m2, float &o_h, float &o_c) {
+                                          float cp_o, float Dcp, bool use_cp, float c_o, int sum_m2, float &o_h, float &o_c,
+                                          float &h_new) {
   const float i_o = sigmoidf_acc(gi), f_o = sigmoidf_acc(gf), o_o = sigmoidf_acc(go), g_o = tanhf(gc);
   const float Di = sigmoidf_acc(gi + di) - i_o, Df = sigmoidf_acc(gf + df) - f_o;
   const float Do = sigmoidf_acc(go + dob) - o_o, Dg = tanhf(gc + dcg) - g_o;
@@ -368,6 +369,7 @@ __device__ __forceinline__ void lstm_elem(float gi, float gf, float go, float gc
   const float Dtc = tanhf(c_o + Dc) - tc_o;
   o_h = (Dtc + tc_o) * Do + o_o * Dtc;
   o_c = Dc;
+  h_new = (o_o + Do) * (tc_o + Dtc);   // the hidden value itself: what a thresholded cell differences against what it sent
 }
 
 __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
@@ -375,9 +377,15 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
     const float *__restrict__ dcp, int64_t dcp_ps, const uint64_t *__restrict__ dcp_bits, float *__restrict__ cprev,
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
     uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2,
-    int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */) {
+    int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */,
+    float *__restrict__ hsent, int64_t hs_ps, float thr) {
+  // Thresholded mode (hsent != null; the host then makes a work item hold every channel of a tile, cbw == C, C a
+  // multiple of 16): the hidden delta is taken against what has been sent so far, dh = h_new - hsent, and a pixel's
+  // group of 16 channels is sent (and added to hsent) when one of its |dh| exceeds thr, else written as zero; the
+  // hidden mask is then the set of pixels with a sent group.  The cell delta and its mask stay lossless.
   grid_dependency_wait();
   grid_dependency_trigger();
+  __shared__ unsigned s_w[2];
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
   const int ncb = (C + cbw - 1) / cbw;
   const int n_items = ntiles * ncb;
@@ -399,13 +407,21 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
       }
       continue;
     }
+    if (hsent) {
+      __syncthreads();
+      if (threadIdx.x < 2) s_w[threadIdx.x] = 0u;
+      __syncthreads();
+    }
     const int c_lo = cb * cbw, q4 = (min(C, c_lo + cbw) - c_lo) >> 2;
+    // thresholded mode: q4 is a multiple of 4, so 64 * q4 is a multiple of the block size and a warp's lanes 4k..4k+3
+    // hold the four quads of one 16-channel group of one pixel: no lane leaves the loop before the shuffles below
     for (int e = threadIdx.x; e < 64 * q4; e += blockDim.x) {
       const int p = e / q4, c = c_lo + (e - p * q4) * 4;
-      if (!pix_valid(g, p)) continue;
-      const int64_t pix = pix_index(g, p, H, W);
-      float4 oh = make_float4(0.f, 0.f, 0.f, 0.f), oc = oh;
-      if ((win >> p) & 1ull) {
+      const bool ok = pix_valid(g, p);
+      const int64_t pix = ok ? pix_index(g, p, H, W) : 0;
+      float4 oh = make_float4(0.f, 0.f, 0.f, 0.f), oc = oh, hn = oh;
+      const bool on = ok && ((win >> p) & 1ull);
+      if (on) {
         const bool hg = (wg >> p) & 1ull;
         float *gp = gres + pix * g_ps + c;
         const float4 gi = ld4(gp), gf = ld4(gp + C), go = ld4(gp + 2 * C), gc = ld4(gp + 3 * C);
@@ -424,16 +440,39 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
           }
         }
         const float4 co = ld4(cell + pix * cell_ps + c);
-        lstm_elem(gi.x, gf.x, go.x, gc.x, di.x, df.x, dob.x, dcg.x, cpo.x, Dcp.x, cprev != nullptr, co.x, sum_m2, oh.x, oc.x);
-        lstm_elem(gi.y, gf.y, go.y, gc.y, di.y, df.y, dob.y, dcg.y, cpo.y, Dcp.y, cprev != nullptr, co.y, sum_m2, oh.y, oc.y);
-        lstm_elem(gi.z, gf.z, go.z, gc.z, di.z, df.z, dob.z, dcg.z, cpo.z, Dcp.z, cprev != nullptr, co.z, sum_m2, oh.z, oc.z);
-        lstm_elem(gi.w, gf.w, go.w, gc.w, di.w, df.w, dob.w, dcg.w, cpo.w, Dcp.w, cprev != nullptr, co.w, sum_m2, oh.w, oc.w);
+        lstm_elem(gi.x, gf.x, go.x, gc.x, di.x, df.x, dob.x, dcg.x, cpo.x, Dcp.x, cprev != nullptr, co.x, sum_m2, oh.x, oc.x, hn.x);
+        lstm_elem(gi.y, gf.y, go.y, gc.y, di.y, df.y, dob.y, dcg.y, cpo.y, Dcp.y, cprev != nullptr, co.y, sum_m2, oh.y, oc.y, hn.y);
+        lstm_elem(gi.z, gf.z, go.z, gc.z, di.z, df.z, dob.z, dcg.z, cpo.z, Dcp.z, cprev != nullptr, co.z, sum_m2, oh.z, oc.z, hn.z);
+        lstm_elem(gi.w, gf.w, go.w, gc.w, di.w, df.w, dob.w, dcg.w, cpo.w, Dcp.w, cprev != nullptr, co.w, sum_m2, oh.w, oc.w, hn.w);
         st4(cell + pix * cell_ps + c, f4add(co, oc));
       }
-      st4(dh + pix * dh_ps + c, oh);
-      st4(dc + pix * dc_ps + c, oc);
+      if (hsent) {
+        float4 sent = make_float4(0.f, 0.f, 0.f, 0.f);
+        bool over = false;
+        if (on) {
+          sent = ld4(hsent + pix * hs_ps + c);
+          oh = make_float4(hn.x - sent.x, hn.y - sent.y, hn.z - sent.z, hn.w - sent.w);
+          over = fabsf(oh.x) > thr || fabsf(oh.y) > thr || fabsf(oh.z) > thr || fabsf(oh.w) > thr;
+        }
+        unsigned bal = __ballot_sync(0xffffffffu, over);
+        const bool send = (bal >> ((threadIdx.x & 31) & ~3)) & 0xFu;   // any of the four lanes of this pixel's group
+        if (on) {
+          if (send) { st4(hsent + pix * hs_ps + c, hn); or_word(s_w, p); }
+          else oh = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      if (ok) {
+        st4(dh + pix * dh_ps + c, oh);
+        st4(dc + pix * dc_ps + c, oc);
+      }
     }
-    if (cb == 0 && threadIdx.x == 0) { dh_bits[t] = win; dc_bits[t] = win; }
+    if (hsent) {
+      __syncthreads();
+      if (threadIdx.x == 0) { dh_bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0]; dc_bits[t] = win; }
+    } else if (cb == 0 && threadIdx.x == 0) {
+      dh_bits[t] = win;
+      dc_bits[t] = win;
+    }
   }
 }
 
@@ -1325,9 +1364,10 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
                                   const float *dc_prev, int64_t dcp_ps, const uint64_t *dcp_bits, float *cprev,
                                   int64_t cprev_ps, float *cell, int64_t cell_ps, float *dh, int64_t dh_ps,
                                   uint64_t *dh_bits, float *dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H,
-                                  int W, int sum_m2, float thr, void *stream) {
-  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits) return MIE_EINVAL;
-  if (thr != 0.0f) return MIE_EUNSUPPORTED;  // the cell's outputs are not thresholded
+                                  int W, int sum_m2, float thr, float *h_sent, int64_t hs_ps, void *stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (h_sent && hs_ps < C) return MIE_EINVAL;
+  if (thr > 0.0f && !h_sent) return MIE_EINVAL;     // withholding without a record of what was sent would lose it
   MIE_CHECK_FIELD(dg, dg_ps, 4 * C); MIE_CHECK_FIELD(g, g_ps, 4 * C); MIE_CHECK_FIELD(cell, cell_ps, C);
   MIE_CHECK_FIELD(dh, dh_ps, C); MIE_CHECK_FIELD(dc, dc_ps, C);
   if (dc_prev && (!dcp_bits || dcp_ps < C || !cprev)) return MIE_EINVAL;
@@ -1336,14 +1376,17 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
   const bool vec = C % 4 == 0 && dg_ps % 4 == 0 && g_ps % 4 == 0 && cell_ps % 4 == 0 && dh_ps % 4 == 0 &&
                    dc_ps % 4 == 0 && aligned16(dg) && aligned16(g) && aligned16(cell) && aligned16(dh) && aligned16(dc) &&
                    (!dc_prev || (dcp_ps % 4 == 0 && aligned16(dc_prev))) && (!cprev || (cprev_ps % 4 == 0 && aligned16(cprev)));
+  if (h_sent && !(vec && C % 16 == 0 && hs_ps % 4 == 0 && aligned16(h_sent))) return MIE_EUNSUPPORTED;
   if (vec) {
     // each element costs ~11 vector loads and 10 transcendentals: on the small fields of a UNet's deep levels a
-    // block of 64 px x 32 ch leaves most SMs with one block of four sequential rounds; narrower items fix that
+    // block of 64 px x 32 ch leaves most SMs with one block of four sequential rounds; narrower items fix that.
+    // A thresholded cell decides per pixel over channel groups and writes a value-dependent mask: one block per tile.
     int cbw = CB;
     while (cbw > 8 && (int64_t)ntiles * divup(C, cbw) < (int64_t)MIE_SM_COUNT * 8) cbw >>= 1;
+    if (h_sent) cbw = C;
     launch_chained(convlstm_point_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, cbw))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
-        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw);
+        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw, h_sent, hs_ps, thr);
     return check_launch();
   }
   launch_chained(convlstm_point_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, 

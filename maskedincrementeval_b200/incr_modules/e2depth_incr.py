@@ -87,8 +87,8 @@ class ConvLSTMIncr(nn.Module):
         self.tanh1, self.tanh2 = nnTanhIncr(), nnTanhIncr()
         self.compat = None
         self._scratch = Scratch()
-        self._g = self._cell = self._cprev = None
-        self._cprev_zero = True
+        self._g = self._cell = self._cprev = self._hsent = None
+        self._cprev_zero, self._hsent_valid = True, False
 
     def forward(self, input_incr: Masked, prev_state_incr):
         if self._g is None:
@@ -111,14 +111,45 @@ class ConvLSTMIncr(nn.Module):
         hb = sc.get("dh.bits", (fl.n_tiles(n, h, w),), torch.int64, dev)
         cb = sc.get("dc.bits", (fl.n_tiles(n, h, w),), torch.int64, dev)
         use_cprev = not self._cprev_zero
+        thr, hs = self._hidden_carry()
         nat.check(nat.lib.mie_convlstm_point(
             dg.data_ptr(), fl.pixel_stride(dg), mg.bits.data_ptr(), self._g.data_ptr(), fl.pixel_stride(self._g),
             nat.ptr(dcp), fl.pixel_stride(dcp) if dcp is not None else 0, mcp.bits.data_ptr() if mcp is not None else None,
             self._cprev.data_ptr() if use_cprev else None, fl.pixel_stride(self._cprev),
             self._cell.data_ptr(), fl.pixel_stride(self._cell), dh.data_ptr(), fl.pixel_stride(dh), hb.data_ptr(),
             dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1 if _compat(self) == "exact" else 0,
-            0.0, nat.stream_ptr(dev)), "convlstm_point")
+            thr, nat.ptr(hs), fl.pixel_stride(hs) if hs is not None else 0, nat.stream_ptr(dev)), "convlstm_point")
         return [dh, TileMask(hb, n, h, w)], [dc, TileMask(cb, n, h, w)]
+
+    def _refill_hidden_carry(self, hidden):
+        """After a refresh: everything is sent, the carry buffer (if one exists) equals the new hidden state.  Refilled
+        in place and at once, not on the next step: that step may be a CUDA-graph replay that runs no host code."""
+        if self._hsent is not None and self._hsent.shape == hidden.shape and self._hsent.device == hidden.device:
+            self._hsent.copy_(hidden)
+            self._hsent_valid = True
+        else:
+            self._hsent_valid = False
+
+    def _hidden_carry(self):
+        """``(threshold, buffer of the hidden state sent so far)`` for a thresholded step, ``(0, None)`` for a lossless
+        one.  With ``config.threshold > 0`` and ``config.carry`` the cell's hidden output is thresholded like an
+        activation's: its delta is taken against what has been sent, groups of 16 channels whose change stays under
+        the threshold are withheld and remain pending.  The buffer is rebuilt from the state (sigmoid(o) * tanh(cell),
+        the hidden value itself) whenever a thresholded step follows a refresh or a lossless step; what was pending at
+        that moment is sent with it."""
+        thr = float(config.threshold)
+        if thr <= 0.0 or not config.carry or self.hidden_size % 16:
+            self._hsent_valid = False       # a lossless step does not advance the buffer
+            return 0.0, None
+        if not self._hsent_valid:
+            C = self.hidden_size
+            hidden = torch.sigmoid(self._g[:, 2 * C:3 * C]) * torch.tanh(self._cell)
+            if self._hsent is None or self._hsent.shape != hidden.shape or self._hsent.device != hidden.device:
+                self._hsent = hidden.contiguous(memory_format=torch.channels_last)
+            else:
+                self._hsent.copy_(hidden)   # in place: a captured step keeps pointing at this buffer
+            self._hsent_valid = True
+        return thr, self._hsent
 
     def refresh_native(self, x_pair, prev_state):
         """The dense LSTM step on the kernels: with the three state tensors zeroed, the incremental point kernel fed
@@ -155,7 +186,8 @@ class ConvLSTMIncr(nn.Module):
             nat.ptr(dcp), fl.pixel_stride(dcp) if dcp is not None else 0, mcp.bits.data_ptr() if mcp is not None else None,
             self._cprev.data_ptr() if dcp is not None else None, fl.pixel_stride(self._cprev),
             self._cell.data_ptr(), fl.pixel_stride(self._cell), dh.data_ptr(), fl.pixel_stride(dh), hb.data_ptr(),
-            dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1, 0.0, nat.stream_ptr(dev)), "convlstm_point")
+            dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1, 0.0, None, 0, nat.stream_ptr(dev)), "convlstm_point")
+        self._refill_hidden_carry(dh)
         for i, mod in enumerate((self.sigmoid1, self.sigmoid2, self.sigmoid3, self.tanh1)):
             mod.in_res.reservoir = self._g[:, i * C:(i + 1) * C]
         self.tanh2.in_res.reservoir = self._cell
@@ -179,6 +211,7 @@ class ConvLSTMIncr(nn.Module):
         self._g, self._cell, self._cprev = (self._store(b, v) for b, v in ((self._g, gates), (self._cell, cell),
                                                                           (self._cprev, c_prev)))
         self._cprev_zero = zero_state
+        self._refill_hidden_carry(hidden)
         for i, mod in enumerate((self.sigmoid1, self.sigmoid2, self.sigmoid3, self.tanh1)):
             mod.in_res.reservoir = self._g[:, i * C:(i + 1) * C]
         self.tanh2.in_res.reservoir = self._cell

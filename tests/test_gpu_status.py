@@ -295,6 +295,48 @@ def test_thresholded_tensor_core_layers_against_fp32_kernel(dev, cfg):
     assert differing <= 0.01 * total, (differing, total)
 
 
+@pytest.mark.parametrize("hidden", [16, 64])
+def test_thresholded_convlstm_hidden_output(dev, hidden):
+    """A thresholded ConvLSTM sends its hidden delta against what it has sent so far, in groups of 16 channels: the total
+    sent stays within the threshold of the true hidden state (recomputed from the cell's own state), withheld groups
+    are exact zeros, the hidden mask is the set of pixels with a sent group, and the cell state itself is not
+    thresholded -- it follows the lossless cell exactly."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLSTMIncr
+    from maskedincrementeval_b200.synthetic import seeded_state_dict
+    thr = 0.01
+    fl.config.tensor_cores = "off"
+    g = torch.Generator().manual_seed(hidden)
+    cells = []
+    for _ in range(2):
+        cell = ConvLSTMIncr(hidden, hidden, 3).to(dev).eval()
+        cell.compat = "exact"
+        cell.load_state_dict(seeded_state_dict({k: tuple(v.shape) for k, v in cell.state_dict().items()}, 5, "kaiming_normal"))
+        cells.append(cell)
+    lossy, exact = cells
+    x = torch.randn(2, hidden, 27, 35, generator=g)
+    with torch.no_grad():
+        h0, _ = lossy.forward_refresh_reservoirs(cl(x, dev), None)
+        exact.forward_refresh_reservoirs(cl(x, dev), None)
+        sent = h0.clone()
+        withheld_some = False
+        for step in range(8):
+            dx = cl(sparse_delta(g, x.shape, 0.2, std=0.05), dev)
+            fl.config.threshold, fl.config.carry = thr, True
+            (dh, mh), (dc, mc) = lossy([dx, None], None)
+            fl.config.threshold = 0.0
+            (dh_e, _), (dc_e, _) = exact([dx, None], None)
+            sent += dh
+            C = hidden
+            truth = torch.sigmoid(lossy._g[:, 2 * C:3 * C]) * torch.tanh(lossy._cell)
+            assert float((sent - truth).abs().max()) <= thr + 1e-5
+            assert float((dc - dc_e).abs().max()) <= 1e-6 and float((lossy._cell - exact._cell).abs().max()) <= 1e-6
+            pm = mh.pixel_mask()
+            assert torch.equal(pm, (dh != 0).any(1, keepdim=True).to(torch.uint8))
+            withheld_some |= bool(((dh == 0).all(1, keepdim=True) & (dh_e != 0).any(1, keepdim=True)).any())
+        assert withheld_some
+
+
 def test_carry_survives_threshold_toggle(dev):
     """threshold 0.05 -> 0 -> 0.05: once a thresholded step has run, the carry buffer stays in use while the threshold
     is 0 (those steps send what is pending where they touch), so the total sent stays within the threshold of the true
