@@ -400,7 +400,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
         nat.check(nat.lib.mie_convlstm_point(s_["dg"].data_ptr(), 4 * c, s_["m"].bits.data_ptr(), s_["gs"].data_ptr(), 4 * c,
                                              None, 0, None, None, 0, s_["cell"].data_ptr(), c, s_["dh"].data_ptr(), c,
                                              s_["hb"].data_ptr(), s_["dc"].data_ptr(), c, s_["cb"].data_ptr(), n, c, h, w, 1, 0.0,
-                                             None, 0, nat.stream_ptr(dev)), "convlstm_point")
+                                             None, 0, None, nat.stream_ptr(dev)), "convlstm_point")
     measure("convlstm_point_vec_kernel", f"ConvLSTM point ops, {c} ch, {h}x{w}, all pixels active",
             px * c * 4 * (4 + 4 + 4 + 2 + 2), lstm_set, lstm_launch,
             "per pixel and channel: 4 gate deltas read, 4 gate states read + written, cell read + written, 2 outputs written")

@@ -243,6 +243,8 @@ int mie_mul_incr(const float *d1, int64_t d1_ps, const uint64_t *bits1, float *x
  *                      dh = h_new - h_sent, a pixel's group of MIE_THR_GROUP channels is sent (and h_sent advanced)
  *                      when one of its |dh| exceeds thr and written as 0 otherwise, and the hidden mask is the set of
  *                      pixels with a sent group.  Needs C % 16 == 0 and 16-byte aligned strides.  thr > 0 needs h_sent
+ *   thr_scratch        with h_sent: 12 bytes per tile (N*TH*TW tiles), 8-byte aligned, zero before the first call; the
+ *                      kernel leaves it zero (the channel blocks of a tile combine their mask bits through it)
  *   sum_m2             1: cell delta = m1 + m2 (dense-exact); 0: m1 only, as the reference computes
  *                      (its `+` concatenates two lists, e2depth_incr.py:113) */
 int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, float *g, int64_t g_ps,
@@ -250,7 +252,7 @@ int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, 
                        float *cprev, int64_t cprev_ps, float *cell, int64_t cell_ps,
                        float *dh, int64_t dh_ps, uint64_t *dh_bits, float *dc, int64_t dc_ps,
                        uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2, float thr, float *h_sent,
-                       int64_t hs_ps, void *stream);
+                       int64_t hs_ps, void *thr_scratch, void *stream);
 
 /* out[N,C,2H,2W] = up2(a (+ b)); bilinear (align_corners=False) or nearest.  b may be null.
  * interpolate_from_module, incr_modules/mask_incr_functional.py:76-78; the sum is the skip

@@ -65,7 +65,7 @@ SIGNATURES = {
     "mie_act_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "mie_mul_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mie_convlstm_point": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp,
-                                _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp, _i64, _vp]),
+                                _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp, _i64, _vp, _vp]),
     "mie_upsample2x": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),
     "mie_upsample": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mie_add": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),

@@ -378,11 +378,13 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
     int64_t cprev_ps, float *__restrict__ cell, int64_t cell_ps, float *__restrict__ dh, int64_t dh_ps,
     uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2,
     int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */,
-    float *__restrict__ hsent, int64_t hs_ps, float thr) {
-  // Thresholded mode (hsent != null; the host then makes a work item hold every channel of a tile, cbw == C, C a
-  // multiple of 16): the hidden delta is taken against what has been sent so far, dh = h_new - hsent, and a pixel's
-  // group of 16 channels is sent (and added to hsent) when one of its |dh| exceeds thr, else written as zero; the
-  // hidden mask is then the set of pixels with a sent group.  The cell delta and its mask stay lossless.
+    float *__restrict__ hsent, int64_t hs_ps, float thr, unsigned long long *__restrict__ acc_words,
+    int *__restrict__ tickets) {
+  // Thresholded mode (hsent != null, C and cbw multiples of 16): the hidden delta is taken against what has been sent
+  // so far, dh = h_new - hsent, and a pixel's group of 16 channels is sent (and added to hsent) when one of its |dh|
+  // exceeds thr, else written as zero; the hidden mask is then the set of pixels with a sent group.  The channel blocks
+  // of a tile OR their pixels into acc_words[t] and draw a ticket; the block that draws the last one publishes the word
+  // and leaves both scratch entries zero for the next launch.  The cell delta and its mask stay lossless.
   grid_dependency_wait();
   grid_dependency_trigger();
   __shared__ unsigned s_w[2];
@@ -468,7 +470,21 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
     }
     if (hsent) {
       __syncthreads();
-      if (threadIdx.x == 0) { dh_bits[t] = ((uint64_t)s_w[1] << 32) | s_w[0]; dc_bits[t] = win; }
+      if (threadIdx.x == 0) {
+        const unsigned long long mine = ((unsigned long long)s_w[1] << 32) | s_w[0];
+        if (ncb == 1) {
+          dh_bits[t] = mine;
+          dc_bits[t] = win;
+        } else {
+          if (mine) atomicOr(&acc_words[t], mine);
+          __threadfence();
+          if (atomicAdd(&tickets[t], 1) == ncb - 1) {      // every other block of this tile has contributed
+            dh_bits[t] = atomicExch(&acc_words[t], 0ull);
+            dc_bits[t] = win;
+            tickets[t] = 0;
+          }
+        }
+      }
     } else if (cb == 0 && threadIdx.x == 0) {
       dh_bits[t] = win;
       dc_bits[t] = win;
@@ -1364,9 +1380,11 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
                                   const float *dc_prev, int64_t dcp_ps, const uint64_t *dcp_bits, float *cprev,
                                   int64_t cprev_ps, float *cell, int64_t cell_ps, float *dh, int64_t dh_ps,
                                   uint64_t *dh_bits, float *dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H,
-                                  int W, int sum_m2, float thr, float *h_sent, int64_t hs_ps, void *stream) {
+                                  int W, int sum_m2, float thr, float *h_sent, int64_t hs_ps, void *thr_scratch,
+                                  void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits || !(thr >= 0.0f)) return MIE_EINVAL;
-  if (h_sent && hs_ps < C) return MIE_EINVAL;
+  if (h_sent && (hs_ps < C || !thr_scratch)) return MIE_EINVAL;
+  if (thr_scratch && (reinterpret_cast<uintptr_t>(thr_scratch) & 7)) return MIE_EALIGN;
   if (thr > 0.0f && !h_sent) return MIE_EINVAL;     // withholding without a record of what was sent would lose it
   MIE_CHECK_FIELD(dg, dg_ps, 4 * C); MIE_CHECK_FIELD(g, g_ps, 4 * C); MIE_CHECK_FIELD(cell, cell_ps, C);
   MIE_CHECK_FIELD(dh, dh_ps, C); MIE_CHECK_FIELD(dc, dc_ps, C);
@@ -1380,13 +1398,14 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
   if (vec) {
     // each element costs ~11 vector loads and 10 transcendentals: on the small fields of a UNet's deep levels a
     // block of 64 px x 32 ch leaves most SMs with one block of four sequential rounds; narrower items fix that.
-    // A thresholded cell decides per pixel over channel groups and writes a value-dependent mask: one block per tile.
     int cbw = CB;
     while (cbw > 8 && (int64_t)ntiles * divup(C, cbw) < (int64_t)MIE_SM_COUNT * 8) cbw >>= 1;
-    if (h_sent) cbw = C;
+    if (h_sent && cbw < 16) cbw = 16;     // a work item holds whole 16-channel groups
+    unsigned long long *acc_words = static_cast<unsigned long long *>(thr_scratch);
+    int *tickets = thr_scratch ? reinterpret_cast<int *>(acc_words + ntiles) : nullptr;
     launch_chained(convlstm_point_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, cbw))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
-        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw, h_sent, hs_ps, thr);
+        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw, h_sent, hs_ps, thr, acc_words, tickets);
     return check_launch();
   }
   launch_chained(convlstm_point_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
