@@ -48,7 +48,7 @@ enum {
 
 /* Process-wide options (host).  No counterpart in the reference. */
 enum {
-  /* 1: thresholded convolutions (thr > 0 or a carry buffer) may run on the tensor cores; 0 (default): they run on
+  /* 1 (default): thresholded convolutions (thr > 0 or a carry buffer) may run on the tensor cores; 0: they run on
    *    the FP32 kernel. */
   MIE_OPT_TC_THRESHOLDED = 1,
   /* iterations after which a barrier wait of the tensor-core kernels gives up; 0 restores the default (2^20) */

@@ -939,7 +939,7 @@ bool encode(EncodeTiledFn fn, CUtensorMap *m, int rank, const void *base, const 
 }
 
 // Process-wide options of the tensor-core path (mie_set_option / mie_get_option).
-int g_opt_tc_thresholded = 0;               // MIE_OPT_TC_THRESHOLDED
+int g_opt_tc_thresholded = 1;               // MIE_OPT_TC_THRESHOLDED
 unsigned g_opt_spin_limit = SPIN_LIMIT;     // MIE_OPT_TC_SPIN_LIMIT
 int g_opt_withhold_loads = 0;               // MIE_OPT_TC_WITHHOLD_LOADS
 

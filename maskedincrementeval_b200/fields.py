@@ -45,15 +45,15 @@ class IncrConfig:
     refresh          "native" (default): the networks' dense pass (forward_refresh_reservoirs) runs on this library's
                      FP32 kernels in dense-evaluation mode -- every tile listed, bias added, state set instead of
                      advanced; "library": it runs on PyTorch's dense operators (cuDNN), as the reference's does
-    tc_thresholded   False (default): thresholded convolutions (threshold > 0, with or without carry) run on the FP32
-                     kernel; True lets them use the tensor cores in that mode too
+    tc_thresholded   True (default): thresholded convolutions (threshold > 0, with or without carry) use the tensor
+                     cores like lossless ones; False routes them to the FP32 kernel
     """
     threshold: float = 0.0
     carry: bool = True
     input_threshold: float = 0.0
     compat: str = "reference"
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
-    tc_thresholded: bool = False
+    tc_thresholded: bool = True
     kfenced_step: Optional[float] = None
     refresh: str = "native"
 

@@ -464,7 +464,7 @@ def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
     old, old_flag = fl.config.threshold, fl.config.tc_thresholded
     try:
         fl.config.threshold = 0.02
-        fl.config.tc_thresholded = True      # thresholded layers take the FP32 kernel unless this is set
+        fl.config.tc_thresholded = True      # the default: thresholded layers use the tensor cores too
         layers = []
         for mode in ("auto", "off"):
             torch.manual_seed(0)
@@ -488,7 +488,7 @@ def test_tensor_core_thresholded_matches_fp32_path_masks(dev):
     finally:
         fl.config.threshold, fl.config.tc_thresholded = old, old_flag
         from maskedincrementeval_b200 import _native as nat
-        nat.set_option(nat.OPT_TC_THRESHOLDED, 0)
+        nat.set_option(nat.OPT_TC_THRESHOLDED, 1)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -33,7 +33,7 @@ def restore_config():
         setattr(fl.config, k, v)
     nat.set_option(nat.OPT_TC_SPIN_LIMIT, 0)
     nat.set_option(nat.OPT_TC_WITHHOLD_LOADS, 0)
-    nat.set_option(nat.OPT_TC_THRESHOLDED, 0)
+    nat.set_option(nat.OPT_TC_THRESHOLDED, 1)
 
 
 def cl(t, dev):
