@@ -400,7 +400,7 @@ def roofline_other_kernels(dev, peak_gbs, peak_kind):
         nat.check(nat.lib.mie_convlstm_point(s_["dg"].data_ptr(), 4 * c, s_["m"].bits.data_ptr(), s_["gs"].data_ptr(), 4 * c,
                                              None, 0, None, None, 0, s_["cell"].data_ptr(), c, s_["dh"].data_ptr(), c,
                                              s_["hb"].data_ptr(), s_["dc"].data_ptr(), c, s_["cb"].data_ptr(), n, c, h, w, 1, 0.0,
-                                             None, 0, None, nat.stream_ptr(dev)), "convlstm_point")
+                                             None, 0, None, None, nat.stream_ptr(dev)), "convlstm_point")
     measure("convlstm_point_vec_kernel", f"ConvLSTM point ops, {c} ch, {h}x{w}, all pixels active",
             px * c * 4 * (4 + 4 + 4 + 2 + 2), lstm_set, lstm_launch,
             "per pixel and channel: 4 gate deltas read, 4 gate states read + written, cell read + written, 2 outputs written")
@@ -514,6 +514,7 @@ def run_ours(args):
     mie.config.threshold = args.threshold
     mie.config.tensor_cores = args.tensor_cores
     mie.config.tc_thresholded = bool(args.tc_thresholded)
+    mie.config.tail_dilation = bool(args.tail_dilation)
     streams = args.streams
     K, Wm = args.steps, args.warmup
     flow = args.net != "e2depth"
@@ -903,6 +904,9 @@ def main():
                          "per window); the headline is e2depth")
     ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
                     help="off keeps every convolution on the FP32 path (secondary measurements)")
+    ap.add_argument("--tail-dilation", action=argparse.BooleanOptionalAction, default=False,
+                    help="tile dilations ride in the tail of the kernel that produces their input mask instead of running "
+                         "as separate launches (fewer launches, measured slower)")
     ap.add_argument("--tc-thresholded", action=argparse.BooleanOptionalAction, default=True,
                     help="with --threshold > 0: thresholded layers use the tensor cores (default) or, with "
                          "--no-tc-thresholded, the FP32 kernel")

@@ -55,7 +55,11 @@ enum {
   MIE_OPT_TC_SPIN_LIMIT = 2,
   /* self-test of the expiry path: 1 makes the tensor-core kernels' producers issue no loads, so that the first wait
    * of every block with work runs out and MIE_ERR_WAIT_EXPIRED is raised; the launch writes no output */
-  MIE_OPT_TC_WITHHOLD_LOADS = 3
+  MIE_OPT_TC_WITHHOLD_LOADS = 3,
+  /* counter of the kernels this library has enqueued for the step path (every launch of the kernels behind the entry
+   * points below except the one-off packing kernels); mie_set_option stores a value (0 resets), mie_get_option reads
+   * it modulo 2^31 */
+  MIE_OPT_LAUNCH_COUNT = 4
 };
 int mie_set_option(int option, int value);
 int mie_get_option(int option, int *value /* host */);
@@ -129,6 +133,25 @@ int mie_tiles_dilate_static(const uint64_t *in_bits, int N, int Hin, int Win, in
                             int stride, int pad, const uint64_t *union_bits, uint64_t *out_bits,
                             int32_t *list, int32_t *stale, int32_t *counts, void *stream);
 
+/* A tile dilation carried by the kernel that produces its input ("tail job").  No counterpart in the reference.
+ * mie_tiles_dilate depends on nothing but tile words that the launch before it has just written, and at the sizes of
+ * one camera stream it is a single thread block: a launch per convolution spent on a few hundred words.  An entry
+ * point that takes a `tail` argument (host pointer, may be null) has the last thread block of its kernel to finish
+ * run the job after the grid's own work: same arguments as mie_tiles_dilate, same results as a mie_tiles_dilate
+ * launch placed directly after that kernel in the stream -- which the caller then leaves out.
+ *  - in_bits must be the tile words that entry point writes (its out_bits / dh_bits); union_bits, if any, must be
+ *    complete before the launch;
+ *  - counts[2] (the ticket) must be 0 on entry and is 0 on exit; flags is scratch of N*THo*TWo bytes;
+ *  - a job of more than MIE_TAIL_MAX_TILES output tiles, or one given to a call whose kernel variant cannot carry
+ *    it, is enqueued as a separate mie_tiles_dilate launch by the entry point itself: on return the dilation is in the
+ *    stream either way. */
+#define MIE_TAIL_MAX_TILES 2048
+typedef struct mie_tail_job {
+  const uint64_t *in_bits; int N, Hin, Win, Hout, Wout, k, stride, pad;
+  const uint64_t *union_bits; uint64_t *out_bits;
+  int32_t *list; int32_t *stale; int32_t *counts; uint8_t *flags;
+} mie_tail_job;
+
 /* ---------------------------------------------------------------------------------------------
  * Masked delta convolution with fused incremental activation.
  * Replaces conv{1x1,3x3,5x5,7x7}_increment_ext (ops.cpp:51-114 -> ext_conv.cu:28-417) and, when
@@ -166,6 +189,8 @@ typedef struct mie_conv_args {
    * FP32 kernel.  `bias` (cout floats, may be null) is only read in this mode or when given. */
   const float *bias;
   int refresh;
+  /* optional tile dilation of the next convolution, run in this kernel's tail (in_bits == out_bits of this call) */
+  const mie_tail_job *tail;
 } mie_conv_args;
 
 int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);
@@ -252,32 +277,34 @@ int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t *dg_bits, 
                        float *cprev, int64_t cprev_ps, float *cell, int64_t cell_ps,
                        float *dh, int64_t dh_ps, uint64_t *dh_bits, float *dc, int64_t dc_ps,
                        uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2, float thr, float *h_sent,
-                       int64_t hs_ps, void *thr_scratch, void *stream);
+                       int64_t hs_ps, void *thr_scratch, const mie_tail_job *tail /* reads dh_bits; may be null */,
+                       void *stream);
 
 /* out[N,C,2H,2W] = up2(a (+ b)); bilinear (align_corners=False) or nearest.  b may be null.
  * interpolate_from_module, incr_modules/mask_incr_functional.py:76-78; the sum is the skip
  * connection the networks apply just before (incr_modules/e2depth_incr.py:430). */
 int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                    const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C,
-                   int H, int W, int mode, void *stream);
+                   int H, int W, int mode, const mie_tail_job *tail /* reads out_bits; may be null */, void *stream);
 
 /* The same for a scale of 1 (a masked copy), 2, 4, 8 or 16: out[N,C,scale*H,scale*W].  F.interpolate(delta, size=highest_resolution,
  * mode="bilinear", align_corners=False) on the multi-resolution predictions and decoder outputs,
  * incr_modules/delayedevflownet_incr.py:260-268. */
 int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                  const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C,
-                 int H, int W, int scale, int mode, void *stream);
+                 int H, int W, int scale, int mode, const mie_tail_job *tail /* reads out_bits; may be null */,
+                 void *stream);
 
 /* out = a + b, out mask = mask_a | mask_b.  Skip / residual sum of two delta fields. */
 int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
             const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
-            int W, void *stream);
+            int W, const mie_tail_job *tail /* reads out_bits; may be null */, void *stream);
 
 /* out[..., 0:ca] = a, out[..., ca:ca+cb] = b; out mask = mask_a | mask_b.  Channel concatenation
  * (torch.cat in incr_modules/e2depth_incr.py:100 and skip_concat, incr_modules/evflownet_incr.py:9-14). */
 int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, int ca, const float *b, int64_t b_ps,
              const uint64_t *b_bits, int cb, float *out, int64_t out_ps, uint64_t *out_bits, int N, int H,
-             int W, void *stream);
+             int W, const mie_tail_job *tail /* reads out_bits; may be null */, void *stream);
 
 /* y += d over the active tiles of d.  The caller-side accumulation of the driver loop
  * (run_e2depth_continuous_dataset.py:74) and IncrementReserve.accumulate
@@ -293,7 +320,8 @@ int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const u
  * are written as 0 and keep their x_prev, so nothing is lost, only deferred.
  * The driver's `x = event_tensor - event_tensor_prev` (run_e2depth_continuous_dataset.py:66) plus the mask. */
 int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
-                   uint64_t *bits, int N, int C, int H, int W, float thr, void *stream);
+                   uint64_t *bits, int N, int C, int H, int W, float thr,
+                   const mie_tail_job *tail /* reads bits; may be null */, void *stream);
 
 /* Voxel grid of one window of events: temporal-bilinear, spatial-nearest accumulation, as
  * events_to_voxel_grid_absT (data_fetchers/utils/util.py:78-110).  events: [n_events][4] floats
@@ -320,7 +348,8 @@ int mie_events_to_count_image(const float *events, int n_events, int sensor_h, i
  * first call) remembers which tiles of `out` hold data so that they are zeroed again when their input tile goes
  * inactive.  No counterpart in the reference. */
 int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int C, float *out, int64_t out_ps,
-                   uint64_t *out_bits, int N, int H, int W, void *stream);
+                   uint64_t *out_bits, int N, int H, int W, const mie_tail_job *tail /* reads out_bits; may be null */,
+                   void *stream);
 
 /* Fills the border of a [1,C,H,W] channels-last field by reflection of the sensor_h x sensor_w image that sits at
  * (pad_top, pad_left) inside it -- the index arithmetic of torch.nn.ReflectionPad2d, which the reference's driver

@@ -18,9 +18,18 @@ OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ETOOBIG = 0, -1, -2, -3, -4, -5
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 UP_BILINEAR, UP_NEAREST = 0, 1
 ERR_BAD_TILE, ERR_WAIT_EXPIRED = 1, 2
-OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS = 1, 2, 3
+OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS, OPT_LAUNCH_COUNT = 1, 2, 3, 4
+TAIL_MAX_TILES = 2048     # MIE_TAIL_MAX_TILES
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+
+class TailJob(C.Structure):
+    """``mie_tail_job`` of include/mie.h, field for field: a tile dilation carried by the kernel that produces its input."""
+    _fields_ = [
+        ("in_bits", _vp), ("N", _i), ("Hin", _i), ("Win", _i), ("Hout", _i), ("Wout", _i), ("k", _i), ("stride", _i),
+        ("pad", _i), ("union_bits", _vp), ("out_bits", _vp), ("list", _vp), ("stale", _vp), ("counts", _vp), ("flags", _vp),
+    ]
 
 
 class ConvArgs(C.Structure):
@@ -37,6 +46,7 @@ class ConvArgs(C.Structure):
         ("addend", _vp), ("addend_ps", _i64),
         ("wpacked_tc", _vp),
         ("bias", _vp), ("refresh", _i),
+        ("tail", _vp),
     ]
 
 
@@ -65,18 +75,18 @@ SIGNATURES = {
     "mie_act_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "mie_mul_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mie_convlstm_point": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp,
-                                _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp, _i64, _vp, _vp]),
-    "mie_upsample2x": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),
-    "mie_upsample": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp]),
-    "mie_add": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
-    "mie_cat2": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp]),
+                                _vp, _i64, _vp, _i, _i, _i, _i, _i, _f, _vp, _i64, _vp, _vp, _vp]),
+    "mie_upsample2x": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "mie_upsample": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "mie_add": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "mie_cat2": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp, _vp]),
     "mie_accumulate": (_i, [_vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
-    "mie_delta_mask": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp]),
+    "mie_delta_mask": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
     "mie_events_to_voxel": (_i, [_vp, _i, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mie_events_to_count_image": (_i, [_vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mie_maxpool_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mie_reflect_border": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _i, _i, _vp]),
-    "mie_split_tf32": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp]),
+    "mie_split_tf32": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp, _vp]),
     "mie_kfenced": (_i, [_vp, _i64, _vp, _i64, _f, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
 }
 
@@ -101,26 +111,21 @@ class MieError(RuntimeError):
     pass
 
 
-_launches = 0
-
-
 def launch_count() -> int:
-    """Kernels of this library enqueued through `check` since the last reset (host-side counter)."""
-    return _launches
+    """Kernels the library has enqueued since the last reset: counted inside the library, per launch (an entry
+    point that enqueues two kernels counts two)."""
+    return get_option(OPT_LAUNCH_COUNT)
 
 
 def reset_launch_count() -> None:
-    global _launches
-    _launches = 0
+    set_option(OPT_LAUNCH_COUNT, 0)
 
 
-def check(status: int, what: str = "", launches: int = 1) -> None:
+def check(status: int, what: str = "") -> None:
     """Map a libmie status to the exception class the reference raises for the same condition:
     unsupported kernel size / stride -> NotImplementedError (ext/pointops/pointops_functional.py:41),
     everything else -> RuntimeError (TORCH_CHECK, include/checks.h:6-8)."""
     if status == OK:
-        global _launches
-        _launches += launches
         return
     msg = lib.mie_status_string(status).decode()
     if status == ECUDA:
@@ -131,12 +136,12 @@ def check(status: int, what: str = "", launches: int = 1) -> None:
 
 
 def set_option(option: int, value: int) -> None:
-    check(lib.mie_set_option(option, int(value)), "set_option", 0)
+    check(lib.mie_set_option(option, int(value)), "set_option")
 
 
 def get_option(option: int) -> int:
     v = C.c_int()
-    check(lib.mie_get_option(option, C.byref(v)), "get_option", 0)
+    check(lib.mie_get_option(option, C.byref(v)), "get_option")
     return v.value
 
 

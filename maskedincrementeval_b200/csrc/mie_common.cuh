@@ -14,6 +14,9 @@ namespace mie {
 // Records the text of a failed CUDA runtime call for mie_last_cuda_error(); defined in mie_mask.cu.
 void set_cuda_error(cudaError_t e);
 
+// Kernels enqueued through launch_chained() since the last reset (MIE_OPT_LAUNCH_COUNT); defined in mie_mask.cu.
+extern unsigned long long g_launch_count;
+
 static inline int check_launch() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -51,7 +54,8 @@ static inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   cfg.attrs = attr;
   cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
-  (void)e;  // picked up by check_launch() through cudaGetLastError()
+  if (e == cudaSuccess) __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  // a failure is picked up by check_launch() through cudaGetLastError()
 }
 
 static inline int divup(int a, int b) { return (a + b - 1) / b; }
@@ -150,6 +154,159 @@ __device__ void block_ordered_compact2(Flag flag, int n, int32_t *listA, int32_t
   }
   *na = s_ba;
   *nb = s_bb;
+}
+
+// ---------------------------------------------------------------------------------------------
+// dilated output-tile set of a convolution: the per-tile test shared by the dilation kernels and the tail job
+// ---------------------------------------------------------------------------------------------
+// Bit j of the result is set when input row (base + j) feeds one of the valid output rows
+// [o0, o0 + cnt) of a tile: rows o*stride - pad + t for t in [0, k).
+__device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride, int pad, int base, int limit) {
+  if (stride <= k) {
+    // consecutive outputs read adjacent or overlapping input ranges: their union is one interval [lo, hi)
+    const int lo = max(o0 * stride - pad, 0), hi = min((o0 + cnt - 1) * stride - pad + k, limit);
+    if (hi <= lo) return 0u;
+    return ((1u << (hi - base)) - 1u) & ~((1u << (lo - base)) - 1u);   // 0 <= lo - base < hi - base <= 21
+  }
+  unsigned set = 0;
+  for (int o = 0; o < cnt; ++o)
+    for (int t = 0; t < k; ++t) {
+      const int i = (o0 + o) * stride - pad + t;
+      if (i >= 0 && i < limit) set |= 1u << (i - base);
+    }
+  return set;
+}
+
+// 0: inactive, 1: active, 2: inactive now but the output tile holds data from the previous step (stale).
+// Also clears the output word.
+__device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *in_bits, int Hin, int Win, int Hout,
+                                               int Wout, int k, int stride, int pad,
+                                               const uint64_t *union_bits, uint64_t *out_bits) {
+  const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
+  const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
+  const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+  const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
+  const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
+  // issued before the neighbourhood test so that the three latencies overlap
+  const uint64_t prev = out_bits ? __ldcg(out_bits + t) : 0ull;
+  const uint64_t uni = union_bits ? __ldcg(union_bits + t) : 0ull;
+  const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
+  const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
+  bool active = false;
+  if (rset && cset) {
+    const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
+    const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
+    // The receptive field spans at most 7 * stride + k <= 21 rows / columns = at most 4 x 4 input tiles.  All their
+    // words are loaded before any is tested: with an early exit each load waited for the test of the one before --
+    // a chain of up to nine round trips to L2 or DRAM per thread, which was this kernel's whole run time.
+    const int ity0 = ylo >> 3, ity1 = yhi >> 3, itx0 = xlo >> 3, itx1 = xhi >> 3;
+    uint64_t w[4][4];
+#pragma unroll
+    for (int dy = 0; dy < 4; ++dy)
+#pragma unroll
+      for (int dx = 0; dx < 4; ++dx) {
+        const int ity = ity0 + dy, itx = itx0 + dx;
+        w[dy][dx] = (ity <= ity1 && itx <= itx1) ? __ldcg(in_bits + ((int64_t)n * THi + ity) * TWi + itx) : 0ull;
+      }
+    unsigned selr[4], selc[4];
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      // bits of rset / cset that fall into input tile ity0 + d / itx0 + d, as an 8-bit row / column selection
+      const int jr = (ity0 + d) * 8 - ybase, jc = (itx0 + d) * 8 - xbase;   // in (-8, 32)
+      selr[d] = (jr >= 0 ? (jr < 32 ? rset >> jr : 0u) : rset << -jr) & 0xFFu;
+      selc[d] = (jc >= 0 ? (jc < 32 ? cset >> jc : 0u) : cset << -jc) & 0xFFu;
+    }
+    uint64_t hit = 0ull;
+#pragma unroll
+    for (int dy = 0; dy < 4; ++dy) {
+      // row selection spread to bytes: byte py = 0xFF when row py is selected
+      uint64_t rowsel = 0ull;
+#pragma unroll
+      for (int py = 0; py < 8; ++py)
+        if ((selr[dy] >> py) & 1u) rowsel |= 0xFFull << (py * 8);
+#pragma unroll
+      for (int dx = 0; dx < 4; ++dx) hit |= w[dy][dx] & rowsel & (0x0101010101010101ull * (uint64_t)selc[dx]);
+    }
+    active = hit != 0ull;
+  }
+  if (uni != 0ull) active = true;
+  uint8_t f = active ? 1 : 0;
+  if (out_bits) {
+    if (!active && prev != 0ull) f = 2;
+    if (prev != 0ull) out_bits[t] = 0ull;
+  }
+  return f;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Tail job: the tile dilation of the NEXT convolution, run by the last thread block of the kernel that produces
+// that convolution's input mask (see mie_tail_job in mie.h).  Every thread of every block of the producing kernel
+// calls run_tail_job() once, as its last action, with no thread having left the kernel before; blockDim.x must be a
+// multiple of 32.  All loads of mask words are L2-coherent (__ldcg): the words were written by other blocks of the
+// same launch.
+// ---------------------------------------------------------------------------------------------
+constexpr int TAIL_MAX_TILES = MIE_TAIL_MAX_TILES;   // larger fields keep the separate, multi-block dilation launch
+
+// Arguments by value (registers): a reference to a kernel parameter would make the caller copy its whole parameter
+// block to local memory.
+static __device__ __noinline__ void run_tail_job_last(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout,
+                                                      int k, int stride, int pad, const uint64_t *union_bits,
+                                                      uint64_t *out_bits, int32_t *list, int32_t *stale, int32_t *counts,
+                                                      uint8_t *flags) {
+  const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
+  for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
+    flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
+  __syncthreads();
+  int na, ns;
+  block_ordered_compact2([&](int i) { return (int)__ldcg(flags + i); }, ntiles, list, stale, &na, &ns);
+  if (threadIdx.x == 0) {
+    counts[0] = na;
+    counts[1] = ns;
+    counts[2] = 0;
+  }
+}
+
+__device__ __forceinline__ void run_tail_job(const mie_tail_job &j) {
+  if (j.list == nullptr) return;          // uniform over the grid
+  __shared__ int s_tail_last;
+  __threadfence();                        // this thread's mask words and data, before the ticket
+  __syncthreads();
+  if (threadIdx.x == 0)
+    s_tail_last = atomicAdd(&j.counts[2], 1) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1;
+  __syncthreads();
+  if (!s_tail_last) return;
+  __threadfence();
+  run_tail_job_last(j.in_bits, j.N, j.Hin, j.Win, j.Hout, j.Wout, j.k, j.stride, j.pad, j.union_bits, j.out_bits, j.list,
+                    j.stale, j.counts, j.flags);
+}
+
+// ---- host side of the tail job -----------------------------------------------------------------------------------
+// An entry point with a `tail` argument (1) validates it (tail_check: the job must read the tile words this call
+// writes), (2) hands tail_for_kernel() to a kernel that ends in run_tail_job() -- an empty job when there is none or
+// when it is too large for one block -- and (3) finishes with tail_after_launch(), which enqueues the separate
+// dilation launch whenever the kernel did not carry the job.  Either way the dilation is in the stream on return.
+static inline bool tail_fits(const mie_tail_job *t) {
+  return (int64_t)t->N * divup(t->Hout, 8) * divup(t->Wout, 8) <= TAIL_MAX_TILES;
+}
+static inline int tail_check(const mie_tail_job *t, const void *produced_bits) {
+  if (!t) return MIE_OK;
+  if (!t->in_bits || !t->list || !t->counts || !t->flags || t->N <= 0 || t->Hin <= 0 || t->Win <= 0 || t->Hout <= 0 || t->Wout <= 0)
+    return MIE_EINVAL;
+  if (t->k < 1 || t->k > 7 || t->stride < 1 || t->stride > 2 || t->pad < 0 || t->pad > t->k) return MIE_EINVAL;
+  if (t->out_bits && !t->stale) return MIE_EINVAL;
+  if (static_cast<const void *>(t->in_bits) != produced_bits) return MIE_EINVAL;
+  return MIE_OK;
+}
+static inline mie_tail_job tail_for_kernel(const mie_tail_job *t) {
+  mie_tail_job j = {};
+  if (t && tail_fits(t)) j = *t;
+  return j;
+}
+static inline int tail_after_launch(int status, const mie_tail_job *t, bool kernel_carries_tails, void *stream) {
+  if (status != MIE_OK || !t || (kernel_carries_tails && tail_fits(t))) return status;
+  return mie_tiles_dilate(t->in_bits, t->N, t->Hin, t->Win, t->Hout, t->Wout, t->k, t->stride, t->pad, t->union_bits,
+                          t->out_bits, t->list, t->stale, t->counts, t->flags, stream);
 }
 
 }  // namespace mie

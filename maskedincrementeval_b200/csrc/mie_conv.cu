@@ -36,6 +36,7 @@ struct ConvParams {
   int io_vec;   // epilogue tensors can be accessed as float4
   const float *bias;   // per output channel, added before the activation (dense evaluation only)
   int refresh;         // dense evaluation: the reservoir is set instead of advanced, the output is f(conv + bias)
+  mie_tail_job tail;   // the next convolution's tile dilation, run by the last block (list == nullptr: none)
 };
 
 constexpr int CC = 8;  // input channels per chunk
@@ -363,6 +364,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
   }
+  run_tail_job(p.tail);
 }
 
 
@@ -460,6 +462,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
     const unsigned half = __ballot_sync(0xffffffffu, flag);
     if (lane == 0 && half) bits32[2 * (size_t)t + ((px >> 5) & 1)] = half;
   }
+  run_tail_job(p.tail);
 }
 
 template <int K, int S, int WT, int WN, int CPT = 8>
@@ -546,7 +549,8 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (a->stride < 1 || a->stride > 2) return MIE_EUNSUPPORTED;
   if (!aligned16(a->wpacked)) return MIE_EALIGN;
   if (a->wpacked_tc && !aligned16(a->wpacked_tc)) return MIE_EALIGN;
-  if (tc_eligible(a)) return launch_conv_tc(a, (cudaStream_t)stream);
+  if (tail_check(a->tail, a->out_bits) != MIE_OK) return MIE_EINVAL;
+  if (tc_eligible(a)) return tail_after_launch(launch_conv_tc(a, (cudaStream_t)stream), a->tail, true, stream);
 
   ConvParams p;
   p.in = a->in; p.in_ps = a->in_ps; p.cin = a->cin; p.hin = a->hin; p.win = a->win;
@@ -558,6 +562,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   p.res = a->res; p.res_ps = a->res_ps; p.emitted = a->emitted; p.emitted_ps = a->emitted_ps;
   p.addend = a->addend; p.addend_ps = a->addend_ps;
   p.bias = a->bias; p.refresh = a->refresh ? 1 : 0;
+  p.tail = tail_for_kernel(a->tail);
   // 16-byte staging reads whole channel quads: with cin % 4 != 0 the last quad reaches into the pixel's
   // padding channels (in_ps >= cin rounded up to 4), which meet zero filter rows and must be finite
   p.in_vec = (a->in_ps % 4 == 0) && aligned16(a->in) && (a->in_ps >= (a->cin + 3) / 4 * 4);
@@ -570,7 +575,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
     if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
     p.in_vec = p.in_vec && (a->cin % 4 == 0 || a->in_ps >= (a->cin + 3) / 4 * 4);
     launch_chained(conv1x1_small_kernel, dim3(blocks), dim3(256), (size_t)a->cin * SMALL_COUT * sizeof(float), (cudaStream_t)stream, p);
-    return check_launch();
+    return tail_after_launch(check_launch(), a->tail, true, stream);
   }
 
   // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels.  (A thresholded fused activation
@@ -582,7 +587,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   const int max_items = (int)(max_items64 > (1 << 30) ? (1 << 30) : max_items64);
   cudaStream_t st = (cudaStream_t)stream;
   const int k = a->k, s = a->stride;
-#define MIE_CASE(KK, SS) if (k == KK && s == SS) return dispatch_w<KK, SS>(p, wt, wn, max_items, st)
+#define MIE_CASE(KK, SS) if (k == KK && s == SS) return tail_after_launch(dispatch_w<KK, SS>(p, wt, wn, max_items, st), a->tail, true, stream)
   MIE_CASE(1, 1); MIE_CASE(1, 2); MIE_CASE(3, 1); MIE_CASE(3, 2);
   MIE_CASE(5, 1); MIE_CASE(5, 2); MIE_CASE(7, 1); MIE_CASE(7, 2);
 #undef MIE_CASE

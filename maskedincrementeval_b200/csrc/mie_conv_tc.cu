@@ -47,6 +47,7 @@ struct TcParams {
   int issuers;   // halo kernel: 1 or 2 MMA-issuing warps (2: stages alternate, one accumulator each)
   unsigned spin_limit;   // iterations after which a barrier wait gives up (MIE_OPT_TC_SPIN_LIMIT)
   int withhold_loads;    // self-test: the producers issue nothing, so the first wait runs out (MIE_OPT_TC_WITHHOLD_LOADS)
+  mie_tail_job tail;     // the next convolution's tile dilation, run by the last block (list == nullptr: none)
 };
 
 namespace {
@@ -700,6 +701,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
+  run_tail_job(p.tail);
 }
 
 // COALESCED: the epilogue variant (and its 8 KB of staging buffers) is a compile-time choice, so that the wide-block
@@ -907,6 +909,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
+  run_tail_job(p.tail);
 }
 
 
@@ -1013,6 +1016,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.out = a->out; p.out_ps = a->out_ps; p.out_bits32 = reinterpret_cast<unsigned int *>(a->out_bits);
   p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
   p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
+  p.tail = tail_for_kernel(a->tail);
   // channels per block: as wide as fits 256 accumulator columns; narrowed (down to 32) only while the layer
   // could not keep about half of the SMs busy even at full activity -- the small-image layers of a UNet have
   // a few dozen tiles but thousands of reduction steps.  Measured on B200: a pipeline stage costs about
@@ -1179,6 +1183,7 @@ extern "C" int mie_set_option(int option, int value) {
       g_opt_spin_limit = value == 0 ? SPIN_LIMIT : (unsigned)value;
       return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: g_opt_withhold_loads = value ? 1 : 0; return MIE_OK;
+    case MIE_OPT_LAUNCH_COUNT: __atomic_store_n(&g_launch_count, (unsigned long long)(value < 0 ? 0 : value), __ATOMIC_RELAXED); return MIE_OK;
     default: return MIE_EINVAL;
   }
 }
@@ -1189,6 +1194,7 @@ extern "C" int mie_get_option(int option, int *value) {
     case MIE_OPT_TC_THRESHOLDED: *value = g_opt_tc_thresholded; return MIE_OK;
     case MIE_OPT_TC_SPIN_LIMIT: *value = (int)g_opt_spin_limit; return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: *value = g_opt_withhold_loads; return MIE_OK;
+    case MIE_OPT_LAUNCH_COUNT: *value = (int)(__atomic_load_n(&g_launch_count, __ATOMIC_RELAXED) & 0x7FFFFFFFull); return MIE_OK;
     default: return MIE_EINVAL;
   }
 }

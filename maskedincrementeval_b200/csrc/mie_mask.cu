@@ -6,6 +6,8 @@
 
 namespace mie {
 static thread_local char g_cuda_err[256] = "";
+unsigned long long g_launch_count = 0;
+
 void set_cuda_error(cudaError_t e) {
   snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
 }
@@ -183,85 +185,6 @@ extern "C" int mie_mask_expand(const uint64_t *bits, int N, int H, int W, uint8_
 // ---------------------------------------------------------------------------------------------
 // dilated output-tile set of a convolution, plus the stale list, in one launch
 // ---------------------------------------------------------------------------------------------
-// Bit j of the result is set when input row (base + j) feeds one of the valid output rows
-// [o0, o0 + cnt) of a tile: rows o*stride - pad + t for t in [0, k).
-__device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride, int pad, int base, int limit) {
-  if (stride <= k) {
-    // consecutive outputs read adjacent or overlapping input ranges: their union is one interval [lo, hi)
-    const int lo = max(o0 * stride - pad, 0), hi = min((o0 + cnt - 1) * stride - pad + k, limit);
-    if (hi <= lo) return 0u;
-    return ((1u << (hi - base)) - 1u) & ~((1u << (lo - base)) - 1u);   // 0 <= lo - base < hi - base <= 21
-  }
-  unsigned set = 0;
-  for (int o = 0; o < cnt; ++o)
-    for (int t = 0; t < k; ++t) {
-      const int i = (o0 + o) * stride - pad + t;
-      if (i >= 0 && i < limit) set |= 1u << (i - base);
-    }
-  return set;
-}
-
-// 0: inactive, 1: active, 2: inactive now but the output tile holds data from the previous step (stale).
-// Also clears the output word.
-__device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *__restrict__ in_bits, int Hin, int Win, int Hout,
-                                               int Wout, int k, int stride, int pad,
-                                               const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits) {
-  const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
-  const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
-  const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
-  const int rows = min(8, Hout - ty * 8), cols = min(8, Wout - tx * 8);
-  const int ybase = ty * 8 * stride - pad, xbase = tx * 8 * stride - pad;  // span <= 7*stride + k <= 21 < 32
-  // issued before the neighbourhood test so that the three latencies overlap
-  const uint64_t prev = out_bits ? out_bits[t] : 0ull;
-  const uint64_t uni = union_bits ? union_bits[t] : 0ull;
-  const unsigned rset = feed_set(ty * 8, rows, k, stride, pad, ybase, Hin);
-  const unsigned cset = feed_set(tx * 8, cols, k, stride, pad, xbase, Win);
-  bool active = false;
-  if (rset && cset) {
-    const int ylo = ybase + __ffs(rset) - 1, yhi = ybase + 31 - __clz(rset);
-    const int xlo = xbase + __ffs(cset) - 1, xhi = xbase + 31 - __clz(cset);
-    // The receptive field spans at most 7 * stride + k <= 21 rows / columns = at most 4 x 4 input tiles.  All their
-    // words are loaded before any is tested: with an early exit each load waited for the test of the one before --
-    // a chain of up to nine round trips to L2 or DRAM per thread, which was this kernel's whole run time.
-    const int ity0 = ylo >> 3, ity1 = yhi >> 3, itx0 = xlo >> 3, itx1 = xhi >> 3;
-    uint64_t w[4][4];
-#pragma unroll
-    for (int dy = 0; dy < 4; ++dy)
-#pragma unroll
-      for (int dx = 0; dx < 4; ++dx) {
-        const int ity = ity0 + dy, itx = itx0 + dx;
-        w[dy][dx] = (ity <= ity1 && itx <= itx1) ? in_bits[((int64_t)n * THi + ity) * TWi + itx] : 0ull;
-      }
-    unsigned selr[4], selc[4];
-#pragma unroll
-    for (int d = 0; d < 4; ++d) {
-      // bits of rset / cset that fall into input tile ity0 + d / itx0 + d, as an 8-bit row / column selection
-      const int jr = (ity0 + d) * 8 - ybase, jc = (itx0 + d) * 8 - xbase;   // in (-8, 32)
-      selr[d] = (jr >= 0 ? (jr < 32 ? rset >> jr : 0u) : rset << -jr) & 0xFFu;
-      selc[d] = (jc >= 0 ? (jc < 32 ? cset >> jc : 0u) : cset << -jc) & 0xFFu;
-    }
-    uint64_t hit = 0ull;
-#pragma unroll
-    for (int dy = 0; dy < 4; ++dy) {
-      // row selection spread to bytes: byte py = 0xFF when row py is selected
-      uint64_t rowsel = 0ull;
-#pragma unroll
-      for (int py = 0; py < 8; ++py)
-        if ((selr[dy] >> py) & 1u) rowsel |= 0xFFull << (py * 8);
-#pragma unroll
-      for (int dx = 0; dx < 4; ++dx) hit |= w[dy][dx] & rowsel & (0x0101010101010101ull * (uint64_t)selc[dx]);
-    }
-    active = hit != 0ull;
-  }
-  if (uni != 0ull) active = true;
-  uint8_t f = active ? 1 : 0;
-  if (out_bits) {
-    if (!active && prev != 0ull) f = 2;
-    if (prev != 0ull) out_bits[t] = 0ull;
-  }
-  return f;
-}
-
 __global__ void __launch_bounds__(256) tiles_dilate_kernel(
     const uint64_t *__restrict__ in_bits, int N, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
     const uint64_t *__restrict__ union_bits, uint64_t *__restrict__ out_bits, int32_t *__restrict__ list,

@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
     uint64_t *dh_bits, float *__restrict__ dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H, int W, int sum_m2,
     int cbw /* channels per work item: 32, or fewer on small fields so that every SM gets several blocks */,
     float *__restrict__ hsent, int64_t hs_ps, float thr, unsigned long long *__restrict__ acc_words,
-    int *__restrict__ tickets) {
+    int *__restrict__ tickets, const mie_tail_job tail) {
   // Thresholded mode (hsent != null, C and cbw multiples of 16): the hidden delta is taken against what has been sent
   // so far, dh = h_new - hsent, and a pixel's group of 16 channels is sent (and added to hsent) when one of its |dh|
   // exceeds thr, else written as zero; the hidden mask is then the set of pixels with a sent group.  The channel blocks
@@ -490,6 +490,7 @@ __global__ void __launch_bounds__(PW_THREADS, 6) convlstm_point_vec_kernel(
       dc_bits[t] = win;
     }
   }
+  run_tail_job(tail);
 }
 
 // Incremental activation, float4 over channels, one block per tile (the output mask needs every channel of a pixel).
@@ -659,7 +660,7 @@ __global__ void __launch_bounds__(256) mul_incr_vec_kernel(
 __global__ void __launch_bounds__(PW_THREADS) cat2_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, int ca, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, int cb, float *__restrict__ out, int64_t out_ps,
-    uint64_t *out_bits, int N, int H, int W) {
+    uint64_t *out_bits, int N, int H, int W, const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
@@ -691,6 +692,7 @@ __global__ void __launch_bounds__(PW_THREADS) cat2_vec_kernel(
     }
     if (blk == 0 && threadIdx.x == 0) out_bits[t] = w;
   }
+  run_tail_job(tail);
 }
 
 __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
@@ -816,7 +818,7 @@ constexpr int UP_WIN = 6;
 __global__ void __launch_bounds__(PW_THREADS) upsample2x_tile_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
-    int C, int H, int W, int mode) {
+    int C, int H, int W, int mode, const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int Ho = 2 * H, Wo = 2 * W;
@@ -910,12 +912,13 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_tile_kernel(
     }
     if (cb == 0 && tid == 0) out_bits[t] = wout;
   }
+  run_tail_job(tail);
 }
 
 __global__ void __launch_bounds__(PW_THREADS) add_vec_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
-    int C, int H, int W) {
+    int C, int H, int W, const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
@@ -945,6 +948,7 @@ __global__ void __launch_bounds__(PW_THREADS) add_vec_kernel(
     }
     if (cb == 0 && threadIdx.x == 0) out_bits[t] = w;
   }
+  run_tail_job(tail);
 }
 
 // Block size of the kernels that keep one block per tile (their output mask needs every channel of a pixel):
@@ -1107,7 +1111,8 @@ int launch_act_dense(float *X, const float *in, float *out, int64_t n, cudaStrea
 // one thread per pixel, 64 threads per tile, 4 tiles per block; the ballot of a warp is half a tile word
 __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict__ x, int64_t x_ps, float *__restrict__ xp,
                                                          int64_t xp_ps, float *__restrict__ dx, int64_t dx_ps,
-                                                         unsigned *__restrict__ bits32, int N, int C, int H, int W, float thr) {
+                                                         unsigned *__restrict__ bits32, int N, int C, int H, int W, float thr,
+                                                         const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
@@ -1131,6 +1136,7 @@ __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict
     const unsigned half = __ballot_sync(0xffffffffu, a);
     if (lane == 0) bits32[2 * (size_t)t + ((p >> 5) & 1)] = half;
   }
+  run_tail_job(tail);
 }
 
 __global__ void __launch_bounds__(256) events_to_voxel_kernel(const float *__restrict__ ev, int n_events, int bins, int sh,
@@ -1251,7 +1257,8 @@ extern "C" int mie_activation_increment(float *X, const float *in_incr, float *o
 __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict__ in, int64_t in_ps,
                                                          const uint64_t *__restrict__ in_bits, int C, int half,
                                                          float *__restrict__ out, int64_t out_ps,
-                                                         uint64_t *__restrict__ out_bits, int N, int H, int W) {
+                                                         uint64_t *__restrict__ out_bits, int N, int H, int W,
+                                                         const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
@@ -1279,13 +1286,15 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict
     __syncthreads();
     if (threadIdx.x == 0) out_bits[t] = w;
   }
+  run_tail_job(tail);
 }
 
 // The same with float4 over channels (C and half multiples of 4): four independent 16-byte loads in flight per thread.
 __global__ void __launch_bounds__(256) split_tf32_vec_kernel(const float *__restrict__ in, int64_t in_ps,
                                                              const uint64_t *__restrict__ in_bits, int C, int half,
                                                              float *__restrict__ out, int64_t out_ps,
-                                                             uint64_t *__restrict__ out_bits, int N, int H, int W) {
+                                                             uint64_t *__restrict__ out_bits, int N, int H, int W,
+                                                             const mie_tail_job tail) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const int ntiles = N * ((H + 7) >> 3) * ((W + 7) >> 3);
@@ -1320,6 +1329,7 @@ __global__ void __launch_bounds__(256) split_tf32_vec_kernel(const float *__rest
     __syncthreads();
     if (threadIdx.x == 0) out_bits[t] = w;
   }
+  run_tail_job(tail);
 }
 
 #define MIE_CHECK_FIELD(ptr, ps, C) if (!(ptr) || (ps) < (C)) return MIE_EINVAL
@@ -1381,8 +1391,9 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
                                   int64_t cprev_ps, float *cell, int64_t cell_ps, float *dh, int64_t dh_ps,
                                   uint64_t *dh_bits, float *dc, int64_t dc_ps, uint64_t *dc_bits, int N, int C, int H,
                                   int W, int sum_m2, float thr, float *h_sent, int64_t hs_ps, void *thr_scratch,
-                                  void *stream) {
+                                  const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !dg_bits || !dh_bits || !dc_bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (tail_check(tail, dh_bits) != MIE_OK) return MIE_EINVAL;
   if (h_sent && (hs_ps < C || !thr_scratch)) return MIE_EINVAL;
   if (thr_scratch && (reinterpret_cast<uintptr_t>(thr_scratch) & 7)) return MIE_EALIGN;
   if (thr > 0.0f && !h_sent) return MIE_EINVAL;     // withholding without a record of what was sent would lose it
@@ -1405,19 +1416,20 @@ extern "C" int mie_convlstm_point(const float *dg, int64_t dg_ps, const uint64_t
     int *tickets = thr_scratch ? reinterpret_cast<int *>(acc_words + ntiles) : nullptr;
     launch_chained(convlstm_point_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, cbw))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
-        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw, h_sent, hs_ps, thr, acc_words, tickets);
-    return check_launch();
+        dc_ps, dc_bits, N, C, H, W, sum_m2, cbw, h_sent, hs_ps, thr, acc_words, tickets, tail_for_kernel(tail));
+    return tail_after_launch(check_launch(), tail, true, stream);
   }
   launch_chained(convlstm_point_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
       dg, dg_ps, dg_bits, g, g_ps, dc_prev, dcp_ps, dcp_bits, cprev, cprev_ps, cell, cell_ps, dh, dh_ps, dh_bits, dc,
       dc_ps, dc_bits, N, C, H, W, sum_m2, thr);
-  return check_launch();
+  return tail_after_launch(check_launch(), tail, false, stream);
 }
 
 extern "C" int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                               const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
-                              int W, int scale, int mode, void *stream) {
+                              int W, int scale, int mode, const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !out_bits) return MIE_EINVAL;
+  if (tail_check(tail, out_bits) != MIE_OK) return MIE_EINVAL;
   if (mode != MIE_UP_BILINEAR && mode != MIE_UP_NEAREST) return MIE_EINVAL;
   if (scale < 1 || scale > 16 || (scale & (scale - 1))) return MIE_EUNSUPPORTED;   // powers of two: 1/scale is exact (1 copies)
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
@@ -1426,55 +1438,57 @@ extern "C" int mie_upsample(const float *a, int64_t a_ps, const uint64_t *a_bits
   if (scale == 2 && C % 4 == 0 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) &&
       (!b || (b_ps % 4 == 0 && aligned16(b)))) {
     launch_chained(upsample2x_tile_kernel, dim3(item_grid((int64_t)ntiles * divup(C, CB))), dim3(PW_THREADS), 0, (cudaStream_t)stream,
-        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode);
-    return check_launch();
+        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode, tail_for_kernel(tail));
+    return tail_after_launch(check_launch(), tail, true, stream);
   }
   if (C >= 4 && a_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(out) && (!b || (b_ps % 4 == 0 && aligned16(b)))) {
     launch_chained(upsample2x_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, CB))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
         a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, mode, scale);
-    return check_launch();
+    return tail_after_launch(check_launch(), tail, false, stream);
   }
   launch_chained(upsample2x_kernel, dim3(item_grid((int64_t)ntiles * divup(C, 64))), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, b, b_ps, b_bits, out,
                                                                                 out_ps, out_bits, N, C, H, W, mode, scale);
-  return check_launch();
+  return tail_after_launch(check_launch(), tail, false, stream);
 }
 
 extern "C" int mie_upsample2x(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                               const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H,
-                              int W, int mode, void *stream) {
-  return mie_upsample(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, 2, mode, stream);
+                              int W, int mode, const mie_tail_job *tail, void *stream) {
+  return mie_upsample(a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, 2, mode, tail, stream);
 }
 
 extern "C" int mie_add(const float *a, int64_t a_ps, const uint64_t *a_bits, const float *b, int64_t b_ps,
                        const uint64_t *b_bits, float *out, int64_t out_ps, uint64_t *out_bits, int N, int C, int H, int W,
-                       void *stream) {
+                       const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
+  if (tail_check(tail, out_bits) != MIE_OK) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, C); MIE_CHECK_FIELD(b, b_ps, C); MIE_CHECK_FIELD(out, out_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   if (C % 4 == 0 && a_ps % 4 == 0 && b_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
     launch_chained(add_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(C, CB))), dim3(PW_THREADS), 0, (cudaStream_t)stream, 
-        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W);
-    return check_launch();
+        a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps, out_bits, N, C, H, W, tail_for_kernel(tail));
+    return tail_after_launch(check_launch(), tail, true, stream);
   }
   launch_chained(add_kernel, dim3(tile_grid(ntiles)), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, b, b_ps, b_bits, out, out_ps,
                                                                          out_bits, N, C, H, W);
-  return check_launch();
+  return tail_after_launch(check_launch(), tail, false, stream);
 }
 
 extern "C" int mie_cat2(const float *a, int64_t a_ps, const uint64_t *a_bits, int ca, const float *b, int64_t b_ps,
                         const uint64_t *b_bits, int cb, float *out, int64_t out_ps, uint64_t *out_bits, int N, int H,
-                        int W, void *stream) {
+                        int W, const mie_tail_job *tail, void *stream) {
   if (N <= 0 || ca <= 0 || cb <= 0 || H <= 0 || W <= 0 || !a_bits || !b_bits || !out_bits) return MIE_EINVAL;
+  if (tail_check(tail, out_bits) != MIE_OK) return MIE_EINVAL;
   MIE_CHECK_FIELD(a, a_ps, ca); MIE_CHECK_FIELD(b, b_ps, cb); MIE_CHECK_FIELD(out, out_ps, ca + cb);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   if (ca % 4 == 0 && cb % 4 == 0 && a_ps % 4 == 0 && b_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
     launch_chained(cat2_vec_kernel, dim3(item_grid((int64_t)ntiles * divup(ca + cb, 64))), dim3(PW_THREADS), 0, (cudaStream_t)stream,
-                   a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out, out_ps, out_bits, N, H, W);
-    return check_launch();
+                   a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out, out_ps, out_bits, N, H, W, tail_for_kernel(tail));
+    return tail_after_launch(check_launch(), tail, true, stream);
   }
   launch_chained(cat2_kernel, dim3(item_grid((int64_t)ntiles * divup(ca + cb, CBS))), dim3(PW_THREADS), 0, (cudaStream_t)stream, a, a_ps, a_bits, ca, b, b_ps, b_bits, cb, out,
                                                                           out_ps, out_bits, N, H, W);
-  return check_launch();
+  return tail_after_launch(check_launch(), tail, false, stream);
 }
 
 extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const uint64_t *d_bits, int N, int C,
@@ -1487,15 +1501,17 @@ extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_
 }
 
 extern "C" int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
-                              uint64_t *bits, int N, int C, int H, int W, float thr, void *stream) {
+                              uint64_t *bits, int N, int C, int H, int W, float thr, const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(thr >= 0.0f)) return MIE_EINVAL;
+  if (tail_check(tail, bits) != MIE_OK) return MIE_EINVAL;
   MIE_CHECK_FIELD(x, x_ps, C); MIE_CHECK_FIELD(x_prev, xp_ps, C); MIE_CHECK_FIELD(dx, dx_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   int blocks = divup(ntiles, 4);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
   launch_chained(delta_mask_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, x_ps, x_prev, xp_ps, dx, dx_ps,
-                                                              reinterpret_cast<unsigned *>(bits), N, C, H, W, thr);
-  return check_launch();
+                                                              reinterpret_cast<unsigned *>(bits), N, C, H, W, thr,
+                                                              tail_for_kernel(tail));
+  return tail_after_launch(check_launch(), tail, true, stream);
 }
 
 extern "C" int mie_events_to_voxel(const float *events, int n_events, int num_bins, int sensor_h, int sensor_w, float *voxel,
@@ -1651,19 +1667,20 @@ extern "C" int mie_kfenced(const float *dx, int64_t dx_ps, float *carry, int64_t
 }
 
 extern "C" int mie_split_tf32(const float *in, int64_t in_ps, const uint64_t *in_bits, int C, float *out, int64_t out_ps,
-                              uint64_t *out_bits, int N, int H, int W, void *stream) {
+                              uint64_t *out_bits, int N, int H, int W, const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !in_bits || !out_bits) return MIE_EINVAL;
+  if (tail_check(tail, out_bits) != MIE_OK) return MIE_EINVAL;
   const int half = divup(C, 8) * 8;
   MIE_CHECK_FIELD(in, in_ps, C); MIE_CHECK_FIELD(out, out_ps, 3 * half);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   if (C % 4 == 0 && in_ps % 4 == 0 && out_ps % 4 == 0 && aligned16(in) && aligned16(out)) {
     launch_chained(split_tf32_vec_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, in, in_ps, in_bits, C, half, out,
-                   out_ps, out_bits, N, H, W);
-    return check_launch();
+                   out_ps, out_bits, N, H, W, tail_for_kernel(tail));
+    return tail_after_launch(check_launch(), tail, true, stream);
   }
   launch_chained(split_tf32_kernel, dim3(tile_grid(ntiles)), dim3(256), 0, (cudaStream_t)stream, in, in_ps, in_bits, C, half, out, out_ps, out_bits,
-                                                                        N, H, W);
-  return check_launch();
+                                                                        N, H, W, tail_for_kernel(tail));
+  return tail_after_launch(check_launch(), tail, true, stream);
 }
 
 extern "C" int mie_maxpool_incr(const float *d, int64_t d_ps, const uint64_t *d_bits, const float *res, int64_t res_ps,

@@ -8,6 +8,7 @@ from the delta on first use), a bool/uint8/int32 tensor, or a ``TileMask``.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -45,6 +46,9 @@ class IncrConfig:
     refresh          "native" (default): the networks' dense pass (forward_refresh_reservoirs) runs on this library's
                      FP32 kernels in dense-evaluation mode -- every tile listed, bias added, state set instead of
                      advanced; "library": it runs on PyTorch's dense operators (cuDNN), as the reference's does
+    tail_dilation    True: a convolution's tile dilation rides in the tail of the kernel that produces its input mask
+                     (one launch less per convolution; measured slower than the separate launch when launches overlap
+                     through programmatic dependent launch, so it is off by default); False: separate launch
     tc_thresholded   True (default): thresholded convolutions (threshold > 0, with or without carry) use the tensor
                      cores like lossless ones; False routes them to the FP32 kernel
     """
@@ -54,6 +58,7 @@ class IncrConfig:
     compat: str = "reference"
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
     tc_thresholded: bool = True
+    tail_dilation: bool = False
     kfenced_step: Optional[float] = None
     refresh: str = "native"
 
@@ -124,6 +129,106 @@ class TileMask:
 
     def active_pixels(self) -> int:
         return int(self.pixel_mask().sum().item())
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Tail jobs: a convolution's tile dilation, carried by the kernel that produces the convolution's input mask
+# (``mie_tail_job`` in include/mie.h).  The consumer builds the job and runs the dilation itself the first time; it
+# then *offers* the job under the address of its input's tile words.  From the next step on, the wrapper of whatever
+# launch writes those words *takes* the job and passes it to the entry point, and the consumer, finding the job
+# *carried*, leaves its own launch out.  Every step of a network runs the same launches in the same order, so after
+# one step the pairing is stable (and it is what a captured CUDA graph replays).
+# ---------------------------------------------------------------------------------------------------------------
+class TailJob:
+    """One offered dilation: the C structure, the plan it fills (weakly: when the plan dies the offer is withdrawn, so
+    that no kernel writes into its released buffers), the input tensors it reads (strongly: their addresses cannot be
+    reused while the offer stands), and whether a producer carried it since the consumer last looked."""
+    __slots__ = ("c", "key", "plan", "carried", "keep", "__weakref__")
+
+    def __init__(self, plan, in_bits: torch.Tensor, union_bits: Optional[torch.Tensor], n, hin, win, k, s, p):
+        self.c = nat.TailJob(in_bits.data_ptr(), n, hin, win, plan.hout, plan.wout, k, s, p,
+                             union_bits.data_ptr() if union_bits is not None else None, plan.out_bits.data_ptr(),
+                             plan.list.data_ptr(), plan.stale.data_ptr(), plan.counts.data_ptr(), plan.flags.data_ptr())
+        self.key, self.plan, self.carried = in_bits.data_ptr(), weakref.ref(plan), False
+        self.keep = (in_bits, union_bits)
+
+    def matches(self, in_bits: torch.Tensor, union_bits: Optional[torch.Tensor]) -> bool:
+        return self.c.in_bits == in_bits.data_ptr() and \
+            (self.c.union_bits or 0) == (union_bits.data_ptr() if union_bits is not None else 0)
+
+
+_tail_jobs: Dict[int, TailJob] = {}
+_produced_at: Dict[int, int] = {}       # tile-word address -> launch counter of the launch that last wrote it
+_launch_counter = [0]
+
+
+def take_tail(out_bits: torch.Tensor):
+    """Called by the wrapper of every launch that writes ``out_bits`` and can carry a tail job: the job offered for
+    these words as a pointer for the entry point's ``tail`` argument, or None."""
+    key = out_bits.data_ptr()
+    _launch_counter[0] += 1
+    _produced_at[key] = _launch_counter[0]
+    job = _tail_jobs.get(key)
+    if job is None or not config.tail_dilation:
+        return None
+    if job.carried:
+        # the consumer did not run since the job was last carried: its lists were rebuilt and never read.  Stop
+        # pairing; the consumer starts from a cleared output when it runs again.
+        job.carried = False
+        plan = job.plan()
+        if plan is not None:
+            plan.needs_clear = True
+        del _tail_jobs[key]
+        return None
+    job.carried = True
+    return C.addressof(job.c)
+
+
+def tail_carried(job: Optional[TailJob]) -> bool:
+    """Consumer side: True when a producer's kernel ran this job since the last call (then the lists are ready)."""
+    if job is not None and job.carried:
+        job.carried = False
+        return True
+    return False
+
+
+def offer_tail(job: TailJob) -> None:
+    """Consumer side, after running the dilation itself: offer the job to the producer of its input words, unless
+    another consumer holds that slot, the union mask is not known to be written before the input's producer runs, or
+    the field is too large for one block."""
+    if not config.tail_dilation or job.key in _tail_jobs:
+        return
+    if job.c.N * ((job.c.Hout + 7) // 8) * ((job.c.Wout + 7) // 8) > nat.TAIL_MAX_TILES:
+        return
+    at = _produced_at.get(job.key)
+    if at is None:
+        return                                  # words written by something that cannot carry a job
+    if job.c.union_bits:
+        u = _produced_at.get(job.c.union_bits)
+        if u is None or u > at:
+            return
+    plan = job.plan()
+    if plan is None:
+        return
+    _tail_jobs[job.key] = job
+    weakref.finalize(plan, _withdraw, job.key, weakref.ref(job))
+
+
+def _withdraw(key: int, job_ref) -> None:
+    if _tail_jobs.get(key) is job_ref():
+        _tail_jobs.pop(key, None)
+
+
+def withdraw_tail(job: Optional[TailJob]) -> None:
+    """Consumer side: the job is no longer the one its plan uses (the input or the union mask changed)."""
+    if job is not None and _tail_jobs.get(job.key) is job:
+        del _tail_jobs[job.key]
+
+
+def forget_tails() -> None:
+    """Drop every offered job (the buffers they point to are about to be released)."""
+    _tail_jobs.clear()
+    _produced_at.clear()
 
 
 def mask_from_delta(x: torch.Tensor, thr: float = 0.0, bits: Optional[torch.Tensor] = None) -> TileMask:
@@ -271,7 +376,8 @@ def upsample2x(a, ma: TileMask, b, mb: Optional[TileMask], out, out_bits, mode: 
     nat.check(nat.lib.mie_upsample2x(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), nat.ptr(b),
                                      pixel_stride(b) if b is not None else 0,
                                      mb.bits.data_ptr() if mb is not None else None, out.data_ptr(), pixel_stride(out),
-                                     out_bits.data_ptr(), n, c, h, w, mode, nat.stream_ptr(a.device)), "upsample2x")
+                                     out_bits.data_ptr(), n, c, h, w, mode, take_tail(out_bits),
+                                     nat.stream_ptr(a.device)), "upsample2x")
     return TileMask(out_bits, n, 2 * h, 2 * w)
 
 
@@ -279,7 +385,7 @@ def upsample(a, ma: TileMask, out, out_bits, scale: int, mode: int = nat.UP_BILI
     """out[N,C,scale*H,scale*W] = interpolate(a) for scale in {2,4,8,16}."""
     n, c, h, w = a.shape
     nat.check(nat.lib.mie_upsample(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), None, 0, None, out.data_ptr(),
-                                   pixel_stride(out), out_bits.data_ptr(), n, c, h, w, scale, mode,
+                                   pixel_stride(out), out_bits.data_ptr(), n, c, h, w, scale, mode, take_tail(out_bits),
                                    nat.stream_ptr(a.device)), "upsample")
     return TileMask(out_bits, n, scale * h, scale * w)
 
@@ -288,7 +394,7 @@ def add(a, ma: TileMask, b, mb: TileMask, out, out_bits) -> TileMask:
     n, c, h, w = a.shape
     nat.check(nat.lib.mie_add(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), b.data_ptr(), pixel_stride(b),
                               mb.bits.data_ptr(), out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, c, h, w,
-                              nat.stream_ptr(a.device)), "add")
+                              take_tail(out_bits), nat.stream_ptr(a.device)), "add")
     return TileMask(out_bits, n, h, w)
 
 
@@ -297,7 +403,7 @@ def cat2(a, ma: TileMask, b, mb: TileMask, out, out_bits) -> TileMask:
     cb = b.shape[1]
     nat.check(nat.lib.mie_cat2(a.data_ptr(), pixel_stride(a), ma.bits.data_ptr(), ca, b.data_ptr(), pixel_stride(b),
                                mb.bits.data_ptr(), cb, out.data_ptr(), pixel_stride(out), out_bits.data_ptr(), n, h, w,
-                               nat.stream_ptr(a.device)), "cat2")
+                               take_tail(out_bits), nat.stream_ptr(a.device)), "cat2")
     return TileMask(out_bits, n, h, w)
 
 
@@ -312,7 +418,7 @@ def pack_conv_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
     cout, cin, k, k2 = weight.shape
     assert k == k2
     cp, op, nf = C.c_int(), C.c_int(), C.c_int64()
-    nat.check(nat.lib.mie_conv_pack_dims(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims", 0)
+    nat.check(nat.lib.mie_conv_pack_dims(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims")
     w = weight.detach().contiguous()
     buf = torch.empty(nf.value, dtype=torch.float32, device=weight.device)
     nat.check(nat.lib.mie_pack_conv_weights(w.data_ptr(), cout, cin, k, buf.data_ptr(), nat.stream_ptr(weight.device)),
@@ -325,7 +431,7 @@ def pack_conv_weights_tc(weight: torch.Tensor) -> torch.Tensor:
     cout, cin, k, k2 = weight.shape
     assert k == k2
     cp, op, nf = C.c_int(), C.c_int(), C.c_int64()
-    nat.check(nat.lib.mie_conv_pack_dims_tc(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims_tc", 0)
+    nat.check(nat.lib.mie_conv_pack_dims_tc(cin, cout, k, C.byref(cp), C.byref(op), C.byref(nf)), "pack_dims_tc")
     w = weight.detach().contiguous()
     buf = torch.empty(nf.value, dtype=torch.float32, device=weight.device)
     nat.check(nat.lib.mie_pack_conv_weights_tc(w.data_ptr(), cout, cin, k, buf.data_ptr(),
@@ -337,8 +443,8 @@ def delta_mask(x: torch.Tensor, x_prev: torch.Tensor, dx: torch.Tensor, bits: to
     """dx = x - x_prev, x_prev = x and the mask of dx in one kernel (pixels with every |dx| <= thr are deferred)."""
     n, c, h, w = x.shape
     nat.check(nat.lib.mie_delta_mask(x.data_ptr(), pixel_stride(x), x_prev.data_ptr(), pixel_stride(x_prev), dx.data_ptr(),
-                                     pixel_stride(dx), bits.data_ptr(), n, c, h, w, float(thr), nat.stream_ptr(x.device)),
-              "delta_mask")
+                                     pixel_stride(dx), bits.data_ptr(), n, c, h, w, float(thr), take_tail(bits),
+                                     nat.stream_ptr(x.device)), "delta_mask")
     return TileMask(bits, n, h, w)
 
 
@@ -391,7 +497,8 @@ def split_tf32(d: torch.Tensor, m: TileMask, out: torch.Tensor, out_bits: torch.
     on the active tiles."""
     n, c, h, w = d.shape
     nat.check(nat.lib.mie_split_tf32(d.data_ptr(), pixel_stride(d), m.bits.data_ptr(), c, out.data_ptr(), pixel_stride(out),
-                                     out_bits.data_ptr(), n, h, w, nat.stream_ptr(d.device)), "split_tf32")
+                                     out_bits.data_ptr(), n, h, w, take_tail(out_bits), nat.stream_ptr(d.device)),
+              "split_tf32")
     return TileMask(out_bits, n, h, w)
 
 

@@ -120,7 +120,7 @@ class ConvLSTMIncr(nn.Module):
             dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1 if _compat(self) == "exact" else 0,
             thr, nat.ptr(hs), fl.pixel_stride(hs) if hs is not None else 0,
             sc.get("hidden.mask.scratch", (2 * fl.n_tiles(n, h, w),), torch.int64, dev).data_ptr() if hs is not None else None,
-            nat.stream_ptr(dev)), "convlstm_point")
+            fl.take_tail(hb), nat.stream_ptr(dev)), "convlstm_point")
         return [dh, TileMask(hb, n, h, w)], [dc, TileMask(cb, n, h, w)]
 
     def _refill_hidden_carry(self, hidden):
@@ -188,7 +188,8 @@ class ConvLSTMIncr(nn.Module):
             nat.ptr(dcp), fl.pixel_stride(dcp) if dcp is not None else 0, mcp.bits.data_ptr() if mcp is not None else None,
             self._cprev.data_ptr() if dcp is not None else None, fl.pixel_stride(self._cprev),
             self._cell.data_ptr(), fl.pixel_stride(self._cell), dh.data_ptr(), fl.pixel_stride(dh), hb.data_ptr(),
-            dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1, 0.0, None, 0, None, nat.stream_ptr(dev)), "convlstm_point")
+            dc.data_ptr(), fl.pixel_stride(dc), cb.data_ptr(), n, C, h, w, 1, 0.0, None, 0, None, fl.take_tail(hb),
+            nat.stream_ptr(dev)), "convlstm_point")
         self._refill_hidden_carry(dh)
         for i, mod in enumerate((self.sigmoid1, self.sigmoid2, self.sigmoid3, self.tanh1)):
             mod.in_res.reservoir = self._g[:, i * C:(i + 1) * C]

@@ -258,6 +258,8 @@ class _ConvPlan:
         a.out, a.out_ps, a.out_bits = self.out.data_ptr(), fl.pixel_stride(self.out), self.out_bits.data_ptr()
         self.args = a
         self.mask = TileMask(self.out_bits, n, self.hout, self.wout)
+        self.tail = None            # fields.TailJob: this convolution's dilation, offered to its input's producer
+        self.needs_clear = False    # a carried dilation was never consumed: start from a cleared output
 
 
 class nnConvIncr(nn.Conv2d):
@@ -397,15 +399,26 @@ class nnConvIncr(nn.Conv2d):
             ad, am = fl.resolve(addend, sc, "addend")
             if ad.shape != plan.out.shape:
                 raise RuntimeError("residual delta must have the convolution's output shape")
-            union = am.bits.data_ptr()
+            union = am.bits
             a.addend, a.addend_ps = ad.data_ptr(), fl.pixel_stride(ad)
         else:
             a.addend, a.addend_ps = None, 0
         st = nat.stream_ptr(d.device)
-        nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), n, hin, win, plan.hout, plan.wout, self._k, self._s,
-                                           self._p, union, plan.out_bits.data_ptr(), plan.list.data_ptr(),
-                                           plan.stale.data_ptr(), plan.counts.data_ptr(), plan.flags.data_ptr(), st),
-                  "tiles_dilate")
+        # The tile dilation: carried by the kernel that wrote the input mask when that pairing has been established
+        # (fields.TailJob), else launched here and offered to that kernel for the steps to come.
+        job = plan.tail
+        if job is None or not job.matches(m.bits, union):
+            fl.withdraw_tail(job)
+            job = plan.tail = fl.TailJob(plan, m.bits, union, n, hin, win, self._k, self._s, self._p)
+        if plan.needs_clear:
+            plan.out.zero_(), plan.out_bits.zero_(), plan.counts[:3].zero_()
+            plan.needs_clear = False
+        if not fl.tail_carried(job):
+            nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), n, hin, win, plan.hout, plan.wout, self._k, self._s,
+                                               self._p, union.data_ptr() if union is not None else None,
+                                               plan.out_bits.data_ptr(), plan.list.data_ptr(), plan.stale.data_ptr(),
+                                               plan.counts.data_ptr(), plan.flags.data_ptr(), st), "tiles_dilate")
+            fl.offer_tail(job)
         a.in_, a.in_ps, a.cin = d.data_ptr(), fl.pixel_stride(d), cin
         a.wpacked, a.cin_pad, a.cout, a.cout_pad = wbuf.data_ptr(), cp, self.out_channels, op
         a.wpacked_tc = wtc.data_ptr() if (wtc is not None and config.tensor_cores == "auto" and not refresh) else None
@@ -433,6 +446,7 @@ class nnConvIncr(nn.Conv2d):
         if split and not self.last_used_tensor_cores:
             raise RuntimeError("a split-precision convolution did not qualify for the tensor cores (its three channel "
                                "blocks only add up to the fp32 result there); set precision=None on this layer")
+        a.tail = fl.take_tail(plan.out_bits)
         nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
         if refresh and activation is not None and activation.emitted is not None:
             if activation.emitted.shape == plan.out.shape and activation.thr() > 0.0 and config.carry:

@@ -29,14 +29,15 @@ def test_activation_golden(golden, op, tag):
     k = lambda s: T(g[f"{op}_{tag}_{s}"])
     o1, r1 = R.act_incr(k("x"), k("d1"), op)
     # the reference's own test pins this identity exactly (tests/test_pointops.py:11-22)
-    # (exact for relu and the reservoir; sigmoid/tanh vectorise differently per memory layout on CPU: 1 ulp)
+    # (exact for relu and the reservoir; the CPU sigmoid/tanh take a vector or a scalar path depending on memory layout
+    # and on how the threads partition the tensor, a difference of up to two ulp per call: 5e-7 covers both calls)
     o2, r2 = R.act_incr(r1, k("d2"), op)
     assert torch.equal(r1, k("r1")) and torch.equal(r2, k("r2"))
     if op == "relu":
         assert torch.equal(o1, k("o1")) and torch.equal(o2, k("o2"))
     else:
-        close(o1, k("o1"), 2.5e-7)
-        close(o2, k("o2"), 2.5e-7)
+        close(o1, k("o1"), 5e-7)
+        close(o2, k("o2"), 5e-7)
 
 
 def test_product_golden(golden):
