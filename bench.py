@@ -515,6 +515,8 @@ def run_ours(args):
     mie.config.tensor_cores = args.tensor_cores
     mie.config.tc_thresholded = bool(args.tc_thresholded)
     mie.config.tail_dilation = bool(args.tail_dilation)
+    from maskedincrementeval_b200 import _native as _nat
+    _nat.set_option(_nat.OPT_TC_KSPLIT, 1 if args.ksplit else 0)
     streams = args.streams
     K, Wm = args.steps, args.warmup
     flow = args.net != "e2depth"
@@ -904,6 +906,9 @@ def main():
                          "per window); the headline is e2depth")
     ap.add_argument("--tensor-cores", default="auto", choices=["auto", "off"],
                     help="off keeps every convolution on the FP32 path (secondary measurements)")
+    ap.add_argument("--ksplit", action=argparse.BooleanOptionalAction, default=True,
+                    help="small-image tensor-core layers run as clusters that split the input channels (default); "
+                         "--no-ksplit keeps one thread block per work item")
     ap.add_argument("--tail-dilation", action=argparse.BooleanOptionalAction, default=False,
                     help="tile dilations ride in the tail of the kernel that produces their input mask instead of running "
                          "as separate launches (fewer launches, measured slower)")

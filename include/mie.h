@@ -59,7 +59,11 @@ enum {
   /* counter of the kernels this library has enqueued for the step path (every launch of the kernels behind the entry
    * points below except the one-off packing kernels); mie_set_option stores a value (0 resets), mie_get_option reads
    * it modulo 2^31 */
-  MIE_OPT_LAUNCH_COUNT = 4
+  MIE_OPT_LAUNCH_COUNT = 4,
+  /* 1 (default): small-image layers with long reductions run the tensor-core kernel as clusters of 2 or 4 thread
+   * blocks that split the input channels of a work item and exchange partial sums through distributed shared
+   * memory; 0: one thread block per work item */
+  MIE_OPT_TC_KSPLIT = 5
 };
 int mie_set_option(int option, int value);
 int mie_get_option(int option, int *value /* host */);
@@ -197,6 +201,11 @@ int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);
 
 /* Host only, no device work: 1 if mie_conv_tiles would run these arguments on the tensor cores, else 0. */
 int mie_conv_uses_tensor_cores(const mie_conv_args *args /* host */);
+
+/* Host only, no device work: the number of thread blocks per cluster mie_conv_tiles would use for these arguments on the
+ * tensor cores (2 or 4: the blocks of a cluster split a work item's input channels, see MIE_OPT_TC_KSPLIT; 1: no
+ * cluster), 0 when the layer does not run on the tensor cores.  No counterpart in the reference. */
+int mie_conv_cluster_size(const mie_conv_args *args /* host */);
 
 /* Host helper (no device work): floats needed for the packed copy of a [cout,cin,k,k] filter, and
  * the padded extents the kernels assume. */

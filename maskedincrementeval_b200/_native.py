@@ -18,7 +18,7 @@ OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ETOOBIG = 0, -1, -2, -3, -4, -5
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 UP_BILINEAR, UP_NEAREST = 0, 1
 ERR_BAD_TILE, ERR_WAIT_EXPIRED = 1, 2
-OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS, OPT_LAUNCH_COUNT = 1, 2, 3, 4
+OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS, OPT_LAUNCH_COUNT, OPT_TC_KSPLIT = 1, 2, 3, 4, 5
 TAIL_MAX_TILES = 2048     # MIE_TAIL_MAX_TILES
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -65,6 +65,7 @@ SIGNATURES = {
     "mie_tiles_dilate_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mie_conv_tiles": (_i, [C.POINTER(ConvArgs), _vp]),
     "mie_conv_uses_tensor_cores": (_i, [C.POINTER(ConvArgs)]),
+    "mie_conv_cluster_size": (_i, [C.POINTER(ConvArgs)]),
     "mie_conv_pack_dims": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "mie_pack_conv_weights": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mie_conv_pack_dims_tc": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),

@@ -58,6 +58,28 @@ static inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   // a failure is picked up by check_launch() through cudaGetLastError()
 }
 
+// The same for a kernel that runs as thread-block clusters of `cluster_x` CTAs (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline void launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                          unsigned cluster_x, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  if (e == cudaSuccess) __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+}
+
 static inline int divup(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t divup64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

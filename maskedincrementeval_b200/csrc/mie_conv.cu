@@ -471,11 +471,15 @@ int launch_conv(const ConvParams &p, int max_items, cudaStream_t st) {
   constexpr int NT = 32 * WT * WN;
   constexpr int NB = 4 * CPT * WN;
   const size_t smem = (size_t)WT * G::A_TILE_F4 * 16 + (size_t)2 * K * CC * NB * 4;
-  static bool attr_set = false;  // per instantiation; benign if two threads race (same value)
-  if (!attr_set) {
+  // the attribute belongs to (kernel, device): remembered per instantiation and per device (a race between two host
+  // threads sets the same value twice)
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MIE_ECUDA;
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(conv_tiles_kernel<K, S, WT, WN, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return MIE_ECUDA; }
-    attr_set = true;
+    attr_set[dev] = true;
   }
   // persistent grid: enough blocks to fill the machine, never more than the work that can exist
   int per_sm = (int)((200 * 1024) / (smem + 1024));

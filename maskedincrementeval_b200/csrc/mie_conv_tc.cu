@@ -48,6 +48,8 @@ struct TcParams {
   unsigned spin_limit;   // iterations after which a barrier wait gives up (MIE_OPT_TC_SPIN_LIMIT)
   int withhold_loads;    // self-test: the producers issue nothing, so the first wait runs out (MIE_OPT_TC_WITHHOLD_LOADS)
   mie_tail_job tail;     // the next convolution's tile dilation, run by the last block (list == nullptr: none)
+  int ksplit;            // halo kernel: CTAs of a cluster that share one work item, each reducing 1/ksplit of the
+                         // input-channel chunks (1: no cluster)
 };
 
 namespace {
@@ -188,6 +190,47 @@ __device__ __forceinline__ void umma_commit(unsigned long long *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
+// ---- thread-block cluster helpers (K-split variant of the halo kernel) ----
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address, in the cluster's shared window, of this CTA's shared-memory location `addr` inside CTA `rank`
+__device__ __forceinline__ unsigned mapa_shared(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// every thread of every CTA of the cluster (whole warps: .aligned)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// mbar_wait whose acquire covers writes made by other CTAs of the cluster before their (release.cluster) arrivals
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned long long *bar, unsigned parity, volatile int *abort_flag, unsigned limit) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned it = 0; it < limit; ++it) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -462,6 +505,8 @@ __device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_tota
 constexpr int HALO_THREADS = 384;
 constexpr int HALO_MAX_STAGES = 12;
 
+// KSPLIT: the cluster variant is a separate instantiation, so that the plain one carries neither its code nor its registers.
+template <bool KSPLIT>
 __global__ void __launch_bounds__(HALO_THREADS, 1)
 conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -472,11 +517,21 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const int Wh = 8 + p.k - 1, Hh = 8 + p.k - 1;
   const unsigned row_bytes = 8u * (unsigned)Wh * 16u;           // one halo row of one tile, all 8 channel groups
   const unsigned a_buf_bytes = (unsigned)Hh * 2u * row_bytes;   // both tiles
-  __shared__ unsigned long long b_full[HALO_MAX_STAGES], b_empty[HALO_MAX_STAGES], a_full[2], a_empty[2], acc_full[2], acc_empty[2];
+  // b_full[i][s]: slot s holds a stage for MMA issuer i.  One barrier per (issuer, slot): an issuer then observes every
+  // phase of every barrier it waits on, whatever the ring depth.  (With one barrier per slot and an odd ring a slot
+  // changes hands every lap; the issuer would wait for lap L without having seen lap L-1 complete, and a parity wait
+  // cannot tell "lap L done" from "lap L-2 done".)
+  __shared__ unsigned long long b_full[2][HALO_MAX_STAGES], b_empty[HALO_MAX_STAGES], a_full[2], a_empty[2], acc_full[2], acc_empty[2];
+  __shared__ unsigned long long part_full;   // K-split: every other CTA of the cluster has delivered its partial sums
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // K-split: the CS CTAs of a cluster work on the same item, CTA `crank` reducing chunks [ch_lo, ch_hi); a cluster has
+  // at most one item (the host sizes the grid so), hence `bid` / `nblk` below index clusters, not CTAs.
+  const unsigned CS = KSPLIT ? (unsigned)p.ksplit : 1u;
+  const unsigned crank = CS > 1u ? cluster_ctarank() : 0u;
+  const int bid = (int)(blockIdx.x / CS), nblk = (int)(gridDim.x / CS);
   if (tid == 0) { TC_TRACE(0); TC_TRACE_G(14); }
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&map_in)) : "memory");
@@ -490,8 +545,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const unsigned tmem_cols = 2 * NI * acc_cols;   // per item buffer: one accumulator per issuer
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&b_full[0][s], 1); mbar_init(&b_full[1][s], 1); mbar_init(&b_empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&a_full[b], 1); mbar_init(&a_empty[b], NI); mbar_init(&acc_full[b], NI); mbar_init(&acc_empty[b], 8); }
+    mbar_init(&part_full, CS > 1u ? (CS - 1u) * 8u : 1u);   // one arrival per epilogue warp of every other CTA
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -505,6 +561,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
+  if (CS > 1u) cluster_sync_all();   // no CTA may receive a remote arrival before its barriers exist
 
   // everything above touched no global memory: it may overlap the tail of the previous kernel in the stream
   if (tid == 0) TC_TRACE(1);
@@ -514,7 +571,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const int n_cblk = p.cout_pad / NB;
   int pre0 = -1, pre1 = -1;
   if (warp == 0) {
-    const int e = 2 * ((int)blockIdx.x / n_cblk);
+    const int e = 2 * (bid / n_cblk);
     if (e < p.max_tiles) pre0 = p.list[e];
     if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
   }
@@ -526,17 +583,19 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const int n_pairs = (n_active + 1) >> 1;
   const int n_items = n_pairs * n_cblk;
   const int n_chunks = p.cin_pad >> 5;
+  const int ch_lo = (int)crank * (n_chunks / (int)CS), ch_hi = ch_lo + n_chunks / (int)CS;
   const int taps = p.k * p.k;
   const unsigned b_base = smem_u32(smem);
   const unsigned a_base = b_base + (unsigned)p.stages * st_bytes;
+  const unsigned part_base = a_base + 2u * a_buf_bytes;   // K-split: [source CTA][16-column group][128 rows][16 floats]
 
   if (warp == 0) {
     // =========================== halo producer: lane = 2 * halo row + tile ===========================
     const int hy = lane >> 1, slot = lane & 1;
     unsigned uses = 0;
-    for (int item = blockIdx.x; item < n_items && !p.withhold_loads; item += gridDim.x) {
+    for (int item = bid; item < n_items && !p.withhold_loads; item += nblk) {
       const int pair = item / n_cblk;
-      const bool first = item == (int)blockIdx.x;
+      const bool first = item == bid;
       int t0 = first ? pre0 : p.list[2 * pair];
       int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
       // An entry outside the field is reported and skipped: the epilogue ignores it too, its half of the operand is
@@ -549,8 +608,8 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
       const unsigned tx_bytes = (t1 >= 0 ? 2u : 1u) * (unsigned)Hh * row_bytes;
       bool ok = true;
-      if (lane == 0 && item == (int)blockIdx.x) TC_TRACE_V(4, clock64() + (t0 & 0));
-      for (int chunk = 0; chunk < n_chunks; ++chunk, ++uses) {
+      if (lane == 0 && item == bid) TC_TRACE_V(4, clock64() + (t0 & 0));
+      for (int chunk = ch_lo; chunk < ch_hi; ++chunk, ++uses) {
         const unsigned buf = uses & 1u;
         if (lane == 0) {
           if (uses >= 2) ok = mbar_wait(&a_empty[buf], ((uses >> 1) - 1) & 1u, &s_abort, p.spin_limit);
@@ -567,18 +626,19 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   } else if (warp == 1) {
     // =========================== filter producer ===========================
     if (lane == 0) {
-      unsigned s = 0, wait_parity = 0, stage_addr = b_base;
+      unsigned s = 0, wait_parity = 0, stage_addr = b_base, gs = 0;   // gs: running stage number; issuer gs % NI takes it
       bool first_pass = true, ok = true;
-      for (int item = blockIdx.x; item < n_items && ok && !s_abort && !p.withhold_loads; item += gridDim.x) {
+      for (int item = bid; item < n_items && ok && !s_abort && !p.withhold_loads; item += nblk) {
         const int cbn = (item % n_cblk) * NB;
-        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+        for (int chunk = ch_lo; chunk < ch_hi && ok; ++chunk) {
           for (int tap = 0; tap < taps; tap += p.tps) {
             if (!first_pass && !mbar_wait(&b_empty[s], wait_parity, &s_abort, p.spin_limit)) { ok = false; break; }
-            const unsigned bar = smem_u32(&b_full[s]);
+            const unsigned bar = smem_u32(&b_full[NI == 2u ? (gs & 1u) : 0u][s]);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(st_bytes) : "memory");
             tma_load_4d_raw(stage_addr, &map_w, bar, 0, cbn, chunk, tap);
             if (first_pass && s == 0) TC_TRACE(6);
             stage_addr += st_bytes;
+            ++gs;
             if (++s == (unsigned)p.stages) { s = 0; stage_addr = b_base; if (!first_pass) wait_parity ^= 1u; first_pass = false; }
           }
         }
@@ -597,16 +657,17 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const unsigned long long a_step = 2ull * (unsigned)Wh;     // two channel groups (K = 8) in 16-byte units
       const unsigned spc = (unsigned)(taps / p.tps);              // stages per channel chunk
       const unsigned nst = (unsigned)p.stages;
+      const unsigned period = (NI == 2u && (nst & 1u)) ? 2u * nst : nst;
       unsigned g = 0;                                             // running stage number (all items of this block)
       unsigned item_idx = 0, uses = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok && !s_abort; item += gridDim.x, ++item_idx) {
+      for (int item = bid; item < n_items && ok && !s_abort; item += nblk, ++item_idx) {
         const unsigned buf = item_idx & 1u;
         if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
         tc_fence_after();
         const unsigned tmem_d = tmem_base + (buf * NI + me) * acc_cols;
         unsigned accumulate = 0;
-        for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++uses, g += spc) {
+        for (int chunk = ch_lo; chunk < ch_hi && ok; ++chunk, ++uses, g += spc) {
           const unsigned abuf = uses & 1u;
           if (!mbar_wait(&a_full[abuf], (uses >> 1) & 1u, &s_abort, p.spin_limit)) { ok = false; break; }
           if (me == 0 && uses == 0) TC_TRACE(7);
@@ -615,7 +676,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
           bool issued = false;
           for (unsigned st = (NI == 2u) ? ((me - g) & 1u) : 0u; st < spc; st += NI) {
             const unsigned gs = g + st, lap = gs / nst, slot = gs - lap * nst;
-            if (!mbar_wait(&b_full[slot], lap & 1u, &s_abort, p.spin_limit)) { ok = false; break; }
+            // the u-th stage this issuer takes from this slot: the pair (issuer, slot) recurs every lcm(ring, issuers) stages
+            const unsigned use = gs / period;
+            if (!mbar_wait(&b_full[me][slot], use & 1u, &s_abort, p.spin_limit)) { ok = false; break; }
             if (me == 0 && gs == 0) TC_TRACE(8);
             tc_fence_after();
             const unsigned t0 = st * (unsigned)p.tps;
@@ -656,7 +719,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
     tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
     unsigned item_idx = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
+    for (int item = bid; item < n_items; item += nblk, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
       int t = (li < n_active) ? p.list[li] : -1;
@@ -666,14 +729,71 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
+      const unsigned taddr = tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16);
+      const unsigned acc2 = NI == 2u ? acc_cols : 0u;
+      bool sent;
+      if (KSPLIT) {
+        // ---- K-split: this CTA holds the sums over its share of the input channels for all NB columns.  It sends
+        // every other CTA the partial sums of that CTA's column slice (remote shared-memory stores), receives the
+        // partial sums of its own slice, adds them in a fixed order and finishes only that slice.
+        const int SW = NB / (int)CS, ng = SW >> 4;     // slice width, 16-column groups per slice
+        const int slice0 = (int)crank * SW;
+        if (valid) tc_epilogue_prefetch(p, pix, cb * NB + slice0, 0, SW);
+        if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
+        tc_fence_after();
+        for (unsigned j = 0; j < CS; ++j) {
+          if (j == crank) continue;
+          const unsigned src = crank < j ? crank : crank - 1u;   // this CTA's index among the sources of CTA j
+          for (int gi = half; gi < ng; gi += 2) {
+            float v[16];
+            tmem_ld16_sum(taddr + (unsigned)((int)j * SW + gi * 16), acc2, v);
+            const unsigned dst = mapa_shared(part_base + (((src * (unsigned)ng + (unsigned)gi) * 128u + (unsigned)m) << 6), j);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) st_cluster_f4(dst + 16u * h, v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+          }
+          asm volatile("fence.acq_rel.cluster;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&part_full), j));
+        }
+        if (!mbar_wait_cluster(&part_full, item_idx & 1u, &s_abort, p.spin_limit)) break;
+        bool flag = false;
+        for (int gi = half; gi < ng; gi += 2) {
+          float v[16];
+          tmem_ld16_sum(taddr + (unsigned)(slice0 + gi * 16), acc2, v);
+          for (unsigned sidx = 0; sidx + 1u < CS; ++sidx) {
+            const float4 *sp = reinterpret_cast<const float4 *>(smem + (size_t)p.stages * st_bytes + 2u * a_buf_bytes +
+                                                                 ((((size_t)sidx * ng + gi) * 128u + (unsigned)m) << 6));
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float4 w = sp[h];
+              v[4 * h] += w.x; v[4 * h + 1] += w.y; v[4 * h + 2] += w.z; v[4 * h + 3] += w.w;
+            }
+          }
+          const int co = cb * NB + slice0 + gi * 16;
+          if (valid && co < p.cout) {
+            // a group whose change is exactly zero skips the reservoir (x + 0 = x and f(x) - f(x) = 0: same result)
+            bool any_d = true;
+            if (p.act != MIE_ACT_NONE && !p.emitted && !p.addend) {
+              any_d = false;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) any_d |= (v[i] != 0.0f);
+            }
+            flag |= tc_epilogue_group(p, v, pix, co, any_d);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        sent = valid && flag;
+      } else {
       if (valid) tc_epilogue_prefetch(p, pix, cb * NB, c_lo, c_hi);
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
       if (tid == 128 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       // (the coalesced epilogue of the per-tap kernel measured slower here: with eight epilogue warps and the MMAs of
       // the next item running, the staging round trip costs more than the scattered accesses)
-      const bool sent = tc_epilogue_pixel(p, NB, tmem_base + buf * NI * acc_cols + ((unsigned)(q * 32) << 16), valid, pix,
-                                          cb * NB, &acc_empty[buf], lane, NI == 2u ? acc_cols : 0u, c_lo, c_hi);
+      sent = tc_epilogue_pixel(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, acc2, c_lo, c_hi);
+      }
       if (tid == 128 && item_idx == 0) TC_TRACE(11);
       // ballot bytes: [tile 0 row 2q][tile 1 row 2q][tile 0 row 2q+1][tile 1 row 2q+1]
       const unsigned bal = __ballot_sync(0xffffffffu, sent);
@@ -691,6 +811,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  // K-split: no CTA leaves while another one of its cluster may still store into its shared memory or arrive on its
+  // barrier (every wait above is bounded, so every CTA gets here)
+  if (CS > 1u) cluster_sync_all();
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
@@ -932,19 +1055,53 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Tensor maps are a pure function of their arguments, and a layer asks for the same ones every step: the encoded
+// descriptors are remembered (per host thread, direct-mapped, 256 entries), so only the first launch of a layer at a
+// given geometry and buffer set pays the driver's encoding call.
+struct MapKey {
+  const void *base;
+  int rank, swizzle;
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5];
+};
+struct MapSlot {
+  bool used;
+  MapKey key;
+  CUtensorMap map;
+};
+
 bool encode(EncodeTiledFn fn, CUtensorMap *m, int rank, const void *base, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
             const cuuint32_t *box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  static thread_local MapSlot cache[256];
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.base = base; k.rank = rank; k.swizzle = (int)swizzle;
+  for (int i = 0; i < rank; ++i) { k.dims[i] = dims[i]; k.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) k.strides[i] = strides_bytes[i];
+  unsigned long long h = 1469598103934665603ull;
+  const unsigned char *kb = reinterpret_cast<const unsigned char *>(&k);
+  for (size_t i = 0; i < sizeof(k); ++i) h = (h ^ kb[i]) * 1099511628211ull;
+  MapSlot &slot = cache[(h ^ (h >> 32)) & 255u];
+  if (slot.used && memcmp(&slot.key, &k, sizeof(k)) == 0) {
+    *m = slot.map;
+    return true;
+  }
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims, strides_bytes, box, es,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  slot.used = true;
+  slot.key = k;
+  slot.map = *m;
+  return true;
 }
 
 // Process-wide options of the tensor-core path (mie_set_option / mie_get_option).
 int g_opt_tc_thresholded = 1;               // MIE_OPT_TC_THRESHOLDED
 unsigned g_opt_spin_limit = SPIN_LIMIT;     // MIE_OPT_TC_SPIN_LIMIT
 int g_opt_withhold_loads = 0;               // MIE_OPT_TC_WITHHOLD_LOADS
+int g_opt_ksplit = 1;                       // MIE_OPT_TC_KSPLIT
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: the largest value set so far is
 // remembered per device, so a process that drives several GPUs raises the limit on each of them.
@@ -1001,6 +1158,44 @@ bool tc_eligible(const mie_conv_args *a) {
   return true;
 }
 
+// Channels per block and cluster size of a tensor-core convolution (host-side rules only).
+static void tc_block_shape(const mie_conv_args *a, int *nb_out, int *ksplit_out) {
+  const int cin_pad32 = (a->cin + 31) / 32 * 32;
+  // channels per block: as wide as fits 256 accumulator columns; narrowed (down to 32) only while the layer
+  // could not keep about half of the SMs busy even at full activity -- the small-image layers of a UNet have
+  // a few dozen tiles but thousands of reduction steps.  Measured on B200: a pipeline stage costs about
+  // 0.6 us whatever its width, so narrowing pays only until the work items cover the machine once.
+  int nb = 256;
+  while (nb > 16 && a->cout_pad % nb) nb >>= 1;
+  const int64_t pairs = (a->max_tiles + 1) / 2;
+  while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
+  // K-split (halo kernel only): a layer with so few tile pairs that even 32-channel blocks leave each block a chain of
+  // hundreds of dependent MMA stages takes wide blocks instead and spreads the input-channel chunks of every block over
+  // a cluster of 2 or 4 CTAs, which exchange their partial sums through distributed shared memory.  Conditions: every
+  // cluster gets at most one work item (grid = items x cluster size <= one wave), the chunks divide evenly, and a
+  // CTA's slice of the block's columns is a whole number of 16-channel groups.
+  int ksplit = 1;
+  if (g_opt_ksplit && a->stride == 1 && a->k >= 3 && a->k <= 7 && halo_enabled()) {
+    int nbw = 128;
+    while (nbw > 32 && a->cout_pad % nbw) nbw >>= 1;
+    const int n_chunks = cin_pad32 / 32;
+    const int64_t items_w = pairs * (a->cout_pad / nbw);
+    const int Wh = 8 + a->k - 1;
+    const int a_bytes = 2 * (Wh * 2 * 8 * Wh * 16);
+    for (int cs = 4; cs >= 2 && ksplit == 1; cs >>= 1) {
+      // the received partial sums take shared memory from the filter ring: split only while two ring slots of a whole
+      // filter row each still fit (with single-tap stages the wide block measured no faster than the narrow ones)
+      const int ring = 200 * 1024 - a_bytes - (cs - 1) * (nbw / cs) * 512;
+      if (a->cout_pad % nbw == 0 && n_chunks % cs == 0 && n_chunks / cs >= 1 && items_w * cs <= MIE_SM_COUNT &&
+          (nbw / cs) % 16 == 0 && n_chunks * a->k * a->k >= 72 && 2 * a->k * nbw * 128 <= ring)
+        ksplit = cs;
+    }
+    if (ksplit > 1) nb = nbw;
+  }
+  *nb_out = nb;
+  *ksplit_out = ksplit;
+}
+
 int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   EncodeTiledFn fn = get_encode();
   if (!fn) return MIE_ECUDA;
@@ -1017,14 +1212,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
   p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
   p.tail = tail_for_kernel(a->tail);
-  // channels per block: as wide as fits 256 accumulator columns; narrowed (down to 32) only while the layer
-  // could not keep about half of the SMs busy even at full activity -- the small-image layers of a UNet have
-  // a few dozen tiles but thousands of reduction steps.  Measured on B200: a pipeline stage costs about
-  // 0.6 us whatever its width, so narrowing pays only until the work items cover the machine once.
-  int nb = 256;
-  while (nb > 16 && a->cout_pad % nb) nb >>= 1;
+  p.ksplit = 1;
+  int nb, ksplit;
+  tc_block_shape(a, &nb, &ksplit);
   const int64_t pairs = (a->max_tiles + 1) / 2;
-  while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
   p.nb = nb;
   int acc_cols = 32;
   while (acc_cols < nb) acc_cols <<= 1;
@@ -1041,23 +1232,19 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     // fence / commit once per stage, so stages are made as fat as shared memory allows -- a whole filter (k*k
     // taps), else one filter row (k taps), else a single tap -- even if only two ring slots remain (measured:
     // 5-tap stages x 2 slots beat 1-tap stages x 4 slots by 25 % on a 5x5 256->128 layer).
-    const int budget = 200 * 1024 - a_bytes;
+    const int part_bytes = ksplit > 1 ? (ksplit - 1) * (nb / ksplit) * 512 : 0;   // partial sums received from the cluster
+    const int budget = 200 * 1024 - a_bytes - part_bytes;
     int tps = 0, stages = 0;
     const int cand[3] = {a->k * a->k, a->k, 1};
     for (int i = 0; i < 3 && !tps; ++i)
       if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = budget / (cand[i] * nb * 128); if (stages > 4) stages = 4; }
     p.tps = tps ? tps : 1;
     const int b_bytes = p.tps * nb * 128;
-    p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;
-    // Two issuers take alternate stages.  With an even ring every slot belongs to one issuer, which therefore sees
-    // each of its phases in turn.  With an odd ring a slot changes hands every lap: an issuer would wait for lap L of
-    // a slot whose lap L-1 it never observed, and if that earlier fill had not landed yet the parity wait would pass at
-    // once on the phase before (bulk copies may complete out of order) -- MMAs on a half-written slot and a second
-    // arrival on its "empty" barrier.  So the ring is made even.
-    if (p.issuers == 2 && (stages & 1)) stages -= 1;
+    p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32 / ksplit) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;   // stages per CTA
+    // (Two issuers take alternate stages; each waits on its own "full" barrier per slot, so the ring may be odd.)
     if (stages >= 2) {
       p.stages = stages;
-      const size_t smem = (size_t)stages * b_bytes + a_bytes + 1024;
+      const size_t smem = (size_t)stages * b_bytes + a_bytes + part_bytes + 1024;
       int blocks_per_sm = (int)((220 * 1024) / (smem + 2048));
       const int by_tmem = 512 / (2 * p.issuers * acc_cols);
       if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem;
@@ -1076,8 +1263,16 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
         int grid = max_items < cap ? (int)max_items : (int)cap;
         if (grid < 1) grid = 1;
         static int halo_smem_set[MAX_DEVICES] = {0};
-        { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel, halo_smem_set, smem); if (s_ != MIE_OK) return s_; }
-        launch_chained(conv_tc_halo_kernel, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
+        if (ksplit > 1) {
+          static int halo_ks_smem_set[MAX_DEVICES] = {0};
+          { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<true>, halo_ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+          p.ksplit = ksplit;
+          launch_chained_cluster(conv_tc_halo_kernel<true>, dim3((unsigned)(max_items * ksplit)), dim3(HALO_THREADS), smem, st,
+                                 (unsigned)ksplit, p, map_in, map_w);
+          return check_launch();
+        }
+        { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<false>, halo_smem_set, smem); if (s_ != MIE_OK) return s_; }
+        launch_chained(conv_tc_halo_kernel<false>, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
         return check_launch();
       }
       // a tensor map the driver refuses (unusual strides): the per-tap kernel below takes the layer
@@ -1175,6 +1370,18 @@ extern "C" int mie_debug_trace(long long *host, int n) {
 }
 #endif
 
+extern "C" int mie_conv_cluster_size(const mie_conv_args *a) {
+  if (!a || !tc_eligible(a)) return 0;
+  int nb, ksplit;
+  tc_block_shape(a, &nb, &ksplit);
+  // the cluster variant belongs to the halo kernel: same conditions as in launch_conv_tc
+  const int cin_pad32 = (a->cin + 31) / 32 * 32;
+  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
+  const bool halo = a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) &&
+                    (cin_pad32 > 32 || a->k >= 5) && halo_enabled();
+  return halo ? ksplit : 1;
+}
+
 extern "C" int mie_set_option(int option, int value) {
   switch (option) {
     case MIE_OPT_TC_THRESHOLDED: g_opt_tc_thresholded = value ? 1 : 0; return MIE_OK;
@@ -1183,6 +1390,7 @@ extern "C" int mie_set_option(int option, int value) {
       g_opt_spin_limit = value == 0 ? SPIN_LIMIT : (unsigned)value;
       return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: g_opt_withhold_loads = value ? 1 : 0; return MIE_OK;
+    case MIE_OPT_TC_KSPLIT: g_opt_ksplit = value ? 1 : 0; return MIE_OK;
     case MIE_OPT_LAUNCH_COUNT: __atomic_store_n(&g_launch_count, (unsigned long long)(value < 0 ? 0 : value), __ATOMIC_RELAXED); return MIE_OK;
     default: return MIE_EINVAL;
   }
@@ -1194,6 +1402,7 @@ extern "C" int mie_get_option(int option, int *value) {
     case MIE_OPT_TC_THRESHOLDED: *value = g_opt_tc_thresholded; return MIE_OK;
     case MIE_OPT_TC_SPIN_LIMIT: *value = (int)g_opt_spin_limit; return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: *value = g_opt_withhold_loads; return MIE_OK;
+    case MIE_OPT_TC_KSPLIT: *value = g_opt_ksplit; return MIE_OK;
     case MIE_OPT_LAUNCH_COUNT: *value = (int)(__atomic_load_n(&g_launch_count, __ATOMIC_RELAXED) & 0x7FFFFFFFull); return MIE_OK;
     default: return MIE_EINVAL;
   }

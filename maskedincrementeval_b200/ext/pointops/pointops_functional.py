@@ -70,7 +70,7 @@ def _conv_increment(k, x_incr, mask, filter, out_incr, stride):
     off = (-base) % 256
     nat.check(nat.lib.mie_conv_increment_ext(x_incr.data_ptr(), mptr, msz, filter.data_ptr(), out_incr.data_ptr(),
                                              n, cin, h, w, cout, k, stride, base + off, ws.numel() - off,
-                                             _stream(x_incr)), f"conv{k}x{k}_increment_ext", 4)
+                                             _stream(x_incr)), f"conv{k}x{k}_increment_ext")
 
 
 def conv1x1_increment_ext(x_incr, mask, filter, out_incr, stride):

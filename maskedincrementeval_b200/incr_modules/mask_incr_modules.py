@@ -443,6 +443,7 @@ class nnConvIncr(nn.Conv2d):
         if a.thr > 0.0 or a.emitted:
             nat.set_option(nat.OPT_TC_THRESHOLDED, 1 if config.tc_thresholded else 0)
         self.last_used_tensor_cores = bool(nat.lib.mie_conv_uses_tensor_cores(C.byref(a)))
+        self.last_cluster_size = int(nat.lib.mie_conv_cluster_size(C.byref(a)))
         if split and not self.last_used_tensor_cores:
             raise RuntimeError("a split-precision convolution did not qualify for the tensor cores (its three channel "
                                "blocks only add up to the fp32 result there); set precision=None on this layer")
