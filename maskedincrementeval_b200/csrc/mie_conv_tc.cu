@@ -208,9 +208,11 @@ __device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float a, fl
 __device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// every thread of every CTA of the cluster (whole warps: .aligned)
+// Every thread of every CTA of the cluster (whole warps: .aligned).  An execution barrier only: what it orders here is
+// "barriers initialised (and made visible by fence.mbarrier_init) before any remote arrival" and "no CTA exits before
+// the others are done with its shared memory" -- data is handed over through part_full, with its own release / acquire.
 __device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
 }
 // mbar_wait whose acquire covers writes made by other CTAs of the cluster before their (release.cluster) arrivals
 __device__ __forceinline__ bool mbar_wait_cluster(unsigned long long *bar, unsigned parity, volatile int *abort_flag, unsigned limit) {
@@ -587,7 +589,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   const int taps = p.k * p.k;
   const unsigned b_base = smem_u32(smem);
   const unsigned a_base = b_base + (unsigned)p.stages * st_bytes;
-  const unsigned part_base = a_base + 2u * a_buf_bytes;   // K-split: [source CTA][16-column group][128 rows][16 floats]
+  const unsigned part_base = a_base + 2u * a_buf_bytes;   // K-split: [source CTA][16-column group][4 channel quads][128 rows] float4
 
   if (warp == 0) {
     // =========================== halo producer: lane = 2 * halo row + tile ===========================
@@ -740,6 +742,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
         const int slice0 = (int)crank * SW;
         if (valid) tc_epilogue_prefetch(p, pix, cb * NB + slice0, 0, SW);
         if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
+        if (tid == 128 && item_idx == 0) TC_TRACE(10);
         tc_fence_after();
         for (unsigned j = 0; j < CS; ++j) {
           if (j == crank) continue;
@@ -747,25 +750,28 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
           for (int gi = half; gi < ng; gi += 2) {
             float v[16];
             tmem_ld16_sum(taddr + (unsigned)((int)j * SW + gi * 16), acc2, v);
-            const unsigned dst = mapa_shared(part_base + (((src * (unsigned)ng + (unsigned)gi) * 128u + (unsigned)m) << 6), j);
+            // layout [source][group][channel quad h][row]: the 32 lanes of a warp store 512 contiguous bytes per quad
+            const unsigned dst = mapa_shared(part_base + ((((src * (unsigned)ng + (unsigned)gi) * 4u) * 128u + (unsigned)m) << 4), j);
 #pragma unroll
-            for (int h = 0; h < 4; ++h) st_cluster_f4(dst + 16u * h, v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+            for (int h = 0; h < 4; ++h) st_cluster_f4(dst + 2048u * h, v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
           }
-          asm volatile("fence.acq_rel.cluster;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&part_full), j));
         }
+        // one fence for all the stores above, then lane j tells CTA j (its release is cumulative over the warp's stores)
+        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        __syncwarp();
+        if ((unsigned)lane < CS && (unsigned)lane != crank) mbar_arrive_cluster(mapa_shared(smem_u32(&part_full), (unsigned)lane));
         if (!mbar_wait_cluster(&part_full, item_idx & 1u, &s_abort, p.spin_limit)) break;
+        if (tid == 128 && item_idx == 0) TC_TRACE(3);
         bool flag = false;
         for (int gi = half; gi < ng; gi += 2) {
           float v[16];
           tmem_ld16_sum(taddr + (unsigned)(slice0 + gi * 16), acc2, v);
           for (unsigned sidx = 0; sidx + 1u < CS; ++sidx) {
             const float4 *sp = reinterpret_cast<const float4 *>(smem + (size_t)p.stages * st_bytes + 2u * a_buf_bytes +
-                                                                 ((((size_t)sidx * ng + gi) * 128u + (unsigned)m) << 6));
+                                                                 (((((size_t)sidx * ng + gi) * 4u) * 128u + (unsigned)m) << 4));
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              const float4 w = sp[h];
+              const float4 w = sp[h * 128];
               v[4 * h] += w.x; v[4 * h + 1] += w.y; v[4 * h + 2] += w.z; v[4 * h + 3] += w.w;
             }
           }
