@@ -487,6 +487,66 @@ __device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_tota
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// K-split (cluster variants of both kernels): the CS thread blocks of a cluster work on the same item, each reducing
+// 1/CS of the input-channel chunks, so each holds partial sums for all NB columns.  A block sends every other block
+// the partial sums of that block's column slice (remote shared-memory stores, layout [source][16-column group]
+// [channel quad][128 rows] float4: a warp stores 512 contiguous bytes per quad), receives the partial sums of its own
+// slice, adds them in a fixed order and finishes only that slice with the usual fused epilogue.
+// Called by whole epilogue warps after the accumulator is complete; lane = accumulator row m.  This warp takes the
+// groups g0, g0 + gstep, ... of every slice.  part_full must have been initialised with (CS - 1) x (epilogue warps)
+// arrivals.  Returns false when a wait ran out; *sent tells whether this row's pixel emitted anything.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool ksplit_finish(const TcParams &p, int NB, unsigned CS, unsigned crank, unsigned taddr, unsigned acc2,
+                                              unsigned part_base, const unsigned char *part_ptr, unsigned long long *part_full,
+                                              unsigned parity, int m, int lane, int g0, int gstep, bool valid, int64_t pix,
+                                              int co0, volatile int *abort_flag, unsigned limit, bool *sent) {
+  const int SW = NB / (int)CS, ng = SW >> 4;     // slice width, 16-column groups per slice
+  const int slice0 = (int)crank * SW;
+  for (unsigned j = 0; j < CS; ++j) {
+    if (j == crank) continue;
+    const unsigned src = crank < j ? crank : crank - 1u;   // this block's index among the sources of block j
+    for (int gi = g0; gi < ng; gi += gstep) {
+      float v[16];
+      tmem_ld16_sum(taddr + (unsigned)((int)j * SW + gi * 16), acc2, v);
+      const unsigned dst = mapa_shared(part_base + ((((src * (unsigned)ng + (unsigned)gi) * 4u) * 128u + (unsigned)m) << 4), j);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) st_cluster_f4(dst + 2048u * h, v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+    }
+  }
+  // one fence for all the stores above, then lane j tells block j (its release is cumulative over the warp's stores)
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+  __syncwarp();
+  if ((unsigned)lane < CS && (unsigned)lane != crank) mbar_arrive_cluster(mapa_shared(smem_u32(part_full), (unsigned)lane));
+  if (!mbar_wait_cluster(part_full, parity, abort_flag, limit)) return false;
+  bool flag = false;
+  for (int gi = g0; gi < ng; gi += gstep) {
+    float v[16];
+    tmem_ld16_sum(taddr + (unsigned)(slice0 + gi * 16), acc2, v);
+    for (unsigned sidx = 0; sidx + 1u < CS; ++sidx) {
+      const float4 *sp = reinterpret_cast<const float4 *>(part_ptr + (((((size_t)sidx * ng + gi) * 4u) * 128u + (unsigned)m) << 4));
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float4 w = sp[h * 128];
+        v[4 * h] += w.x; v[4 * h + 1] += w.y; v[4 * h + 2] += w.z; v[4 * h + 3] += w.w;
+      }
+    }
+    const int co = co0 + slice0 + gi * 16;
+    if (valid && co < p.cout) {
+      // a group whose change is exactly zero skips the reservoir (x + 0 = x and f(x) - f(x) = 0: same result)
+      bool any_d = true;
+      if (p.act != MIE_ACT_NONE && !p.emitted && !p.addend) {
+        any_d = false;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) any_d |= (v[i] != 0.0f);
+      }
+      flag |= tc_epilogue_group(p, v, pix, co, any_d);
+    }
+  }
+  *sent = valid && flag;
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // Halo-resident variant for stride-1 layers with k >= 3.
 //
 // The per-tap kernel below fetches the shifted 8x8x32 input box of every filter tap again (9 or 25 times the same
@@ -735,62 +795,18 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const unsigned acc2 = NI == 2u ? acc_cols : 0u;
       bool sent;
       if (KSPLIT) {
-        // ---- K-split: this CTA holds the sums over its share of the input channels for all NB columns.  It sends
-        // every other CTA the partial sums of that CTA's column slice (remote shared-memory stores), receives the
-        // partial sums of its own slice, adds them in a fixed order and finishes only that slice.
-        const int SW = NB / (int)CS, ng = SW >> 4;     // slice width, 16-column groups per slice
-        const int slice0 = (int)crank * SW;
-        if (valid) tc_epilogue_prefetch(p, pix, cb * NB + slice0, 0, SW);
+        // ---- K-split: exchange partial sums with the other blocks of the cluster, finish this block's column slice
+        if (valid) tc_epilogue_prefetch(p, pix, cb * NB + (int)crank * (NB / (int)CS), 0, NB / (int)CS);
         if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
         if (tid == 128 && item_idx == 0) TC_TRACE(10);
         tc_fence_after();
-        for (unsigned j = 0; j < CS; ++j) {
-          if (j == crank) continue;
-          const unsigned src = crank < j ? crank : crank - 1u;   // this CTA's index among the sources of CTA j
-          for (int gi = half; gi < ng; gi += 2) {
-            float v[16];
-            tmem_ld16_sum(taddr + (unsigned)((int)j * SW + gi * 16), acc2, v);
-            // layout [source][group][channel quad h][row]: the 32 lanes of a warp store 512 contiguous bytes per quad
-            const unsigned dst = mapa_shared(part_base + ((((src * (unsigned)ng + (unsigned)gi) * 4u) * 128u + (unsigned)m) << 4), j);
-#pragma unroll
-            for (int h = 0; h < 4; ++h) st_cluster_f4(dst + 2048u * h, v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
-          }
-        }
-        // one fence for all the stores above, then lane j tells CTA j (its release is cumulative over the warp's stores)
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-        __syncwarp();
-        if ((unsigned)lane < CS && (unsigned)lane != crank) mbar_arrive_cluster(mapa_shared(smem_u32(&part_full), (unsigned)lane));
-        if (!mbar_wait_cluster(&part_full, item_idx & 1u, &s_abort, p.spin_limit)) break;
+        if (!ksplit_finish(p, NB, CS, crank, taddr, acc2, part_base, smem + (size_t)p.stages * st_bytes + 2u * a_buf_bytes,
+                           &part_full, item_idx & 1u, m, lane, half, 2, valid, pix, cb * NB, &s_abort, p.spin_limit, &sent))
+          break;
         if (tid == 128 && item_idx == 0) TC_TRACE(3);
-        bool flag = false;
-        for (int gi = half; gi < ng; gi += 2) {
-          float v[16];
-          tmem_ld16_sum(taddr + (unsigned)(slice0 + gi * 16), acc2, v);
-          for (unsigned sidx = 0; sidx + 1u < CS; ++sidx) {
-            const float4 *sp = reinterpret_cast<const float4 *>(smem + (size_t)p.stages * st_bytes + 2u * a_buf_bytes +
-                                                                 (((((size_t)sidx * ng + gi) * 4u) * 128u + (unsigned)m) << 4));
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float4 w = sp[h * 128];
-              v[4 * h] += w.x; v[4 * h + 1] += w.y; v[4 * h + 2] += w.z; v[4 * h + 3] += w.w;
-            }
-          }
-          const int co = cb * NB + slice0 + gi * 16;
-          if (valid && co < p.cout) {
-            // a group whose change is exactly zero skips the reservoir (x + 0 = x and f(x) - f(x) = 0: same result)
-            bool any_d = true;
-            if (p.act != MIE_ACT_NONE && !p.emitted && !p.addend) {
-              any_d = false;
-#pragma unroll
-              for (int i = 0; i < 16; ++i) any_d |= (v[i] != 0.0f);
-            }
-            flag |= tc_epilogue_group(p, v, pix, co, any_d);
-          }
-        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        sent = valid && flag;
       } else {
       if (valid) tc_epilogue_prefetch(p, pix, cb * NB, c_lo, c_hi);
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
@@ -835,20 +851,27 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
 
 // COALESCED: the epilogue variant (and its 8 KB of staging buffers) is a compile-time choice, so that the wide-block
 // instantiation carries neither the code nor the shared memory of the other.
-template <bool COALESCED>
+// KSPLIT: cluster variant (see ksplit_finish), a separate instantiation of the direct-epilogue kernel.
+template <bool COALESCED, bool KSPLIT = false>
 __global__ void __launch_bounds__(TC_THREADS, COALESCED ? 3 : 2)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
+  static_assert(!(COALESCED && KSPLIT), "the cluster variant uses the direct epilogue");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment of every stage is what the 128-byte swizzle of TMA and of the MMA descriptors assume
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int NB = p.nb;
   const int stage_bytes = A_STAGE_BYTES + NB * 128;
   __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+  __shared__ unsigned long long part_full;   // K-split: every other block of the cluster has delivered its partial sums
   __shared__ float4 s_epi[COALESCED ? 4 : 1][COALESCED ? 128 : 1];   // staging buffers of the coalesced epilogue, one per epilogue warp
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // K-split: `bid` / `nblk` index clusters; a cluster has at most one item (the host sizes the grid so)
+  const unsigned CS = KSPLIT ? (unsigned)p.ksplit : 1u;
+  const unsigned crank = CS > 1u ? cluster_ctarank() : 0u;
+  const int bid = (int)(blockIdx.x / CS), nblk = (int)(gridDim.x / CS);
   if (tid == 0) { TC_TRACE(0); TC_TRACE_G(14); }
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&maps.in[0])) : "memory");
@@ -863,6 +886,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    mbar_init(&part_full, CS > 1u ? (CS - 1u) * 4u : 1u);   // one arrival per epilogue warp of every other block
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -876,6 +900,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
+  if (CS > 1u) cluster_sync_all();   // no block may receive a remote arrival before its barriers exist
 
   // everything above touched no global memory: it may overlap the tail of the previous kernel in the stream
   if (tid == 0) TC_TRACE(1);
@@ -886,7 +911,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int n_cblk = p.cout_pad / NB;
   int pre0 = -1, pre1 = -1;
   if (warp == 0) {
-    const int e = 2 * ((int)blockIdx.x / n_cblk);
+    const int e = 2 * (bid / n_cblk);
     if (e < p.max_tiles) pre0 = p.list[e];
     if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
   }
@@ -898,6 +923,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int n_pairs = (n_active + 1) >> 1;
   const int n_items = n_pairs * n_cblk;
   const int n_chunks = p.cin_pad >> 5;
+  const int ch_lo = (int)crank * (n_chunks / (int)CS), ch_hi = ch_lo + n_chunks / (int)CS;   // this block's chunks
   const int taps = p.k * p.k;
 
   if (warp == 0) {
@@ -910,9 +936,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned smem_base = smem_u32(smem);
       unsigned stage_addr = smem_base;
       const unsigned b_bytes = (unsigned)NB * 128u;
-      for (int item = blockIdx.x; item < n_items && !s_abort && !p.withhold_loads; item += gridDim.x) {
+      for (int item = bid; item < n_items && !s_abort && !p.withhold_loads; item += nblk) {
         const int pair = item / n_cblk, cb = item - pair * n_cblk;
-        const bool first = item == (int)blockIdx.x;
+        const bool first = item == bid;
         int t0 = first ? pre0 : p.list[2 * pair];
         int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
         // an entry outside the field is reported and skipped (see the halo kernel's producer)
@@ -924,9 +950,9 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
         const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + b_bytes;
         const int cbn = cb * NB;
-        if (item == (int)blockIdx.x) { TC_TRACE_V(4, clock64() + (t0 & 0)); }
+        if (item == bid) { TC_TRACE_V(4, clock64() + (t0 & 0)); }
         bool ok = true;
-        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+        for (int chunk = ch_lo; chunk < ch_hi && ok; ++chunk) {
           const int c0 = chunk * 32;
           int tap = 0;
           for (int ky = 0; ky < p.k && ok; ++ky) {
@@ -946,7 +972,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
             }
           }
         }
-        if (item == (int)blockIdx.x) TC_TRACE(6);
+        if (item == bid) TC_TRACE(6);
         if (!ok) break;
       }
     }
@@ -960,8 +986,8 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned long long desc_hi = make_smem_desc(0) & 0xFFFFFFFF00000000ull;   // stride, version, swizzle
       const unsigned desc_lo_flags = (unsigned)(make_smem_desc(0) & 0xFFFF0000ull);     // leading-offset field
       unsigned s = 0, parity = 0, stage_addr = smem_base, item_idx = 0;
-      const int k_iters = n_chunks * taps;
-      for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++item_idx) {
+      const int k_iters = (ch_hi - ch_lo) * taps;
+      for (int item = bid; item < n_items && !s_abort; item += nblk, ++item_idx) {
         // the epilogue must have drained this accumulator (used two items ago)
         const unsigned buf = item_idx & 1u;
         if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
@@ -996,7 +1022,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     const int slot = m >> 6, pxi = m & 63;
     tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
     unsigned item_idx = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_idx) {
+    for (int item = bid; item < n_items; item += nblk, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
       int t = (li < n_active) ? p.list[li] : -1;
@@ -1006,14 +1032,28 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const int oy = ty * 8 + (pxi >> 3), ox = tx * 8 + (pxi & 7);
       const bool valid = (t >= 0) && oy < p.hout && ox < p.wout;
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;
-      if (valid) tc_epilogue_prefetch(p, pix, cb * NB, 0, NB);
+      if (valid) {
+        if (KSPLIT) tc_epilogue_prefetch(p, pix, cb * NB + (int)crank * (NB / (int)CS), 0, NB / (int)CS);
+        else tc_epilogue_prefetch(p, pix, cb * NB, 0, NB);
+      }
       if (tid == 64 && item_idx == 0) TC_TRACE_V(9, clock64() + (t & 0));
       if (!mbar_wait(&acc_full[buf], (item_idx >> 1) & 1u, &s_abort, p.spin_limit)) break;
       if (tid == 64 && item_idx == 0) TC_TRACE(10);
       tc_fence_after();
       const unsigned taddr = tmem_base + buf * acc_cols + ((unsigned)(q * 32) << 16);
-      const bool sent = COALESCED ? tc_epilogue_pixel_coalesced(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, s_epi[COALESCED ? warp - 2 : 0], 0u, 0, NB)
-                                  : tc_epilogue_pixel(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane);
+      bool sent;
+      if (KSPLIT) {
+        if (!ksplit_finish(p, NB, CS, crank, taddr, 0u, smem_u32(smem) + (unsigned)(p.stages * stage_bytes),
+                           smem + (size_t)p.stages * stage_bytes, &part_full, item_idx & 1u, m, lane, 0, 1, valid, pix, cb * NB,
+                           &s_abort, p.spin_limit, &sent))
+          break;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      } else {
+        sent = COALESCED ? tc_epilogue_pixel_coalesced(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane, s_epi[COALESCED ? warp - 2 : 0], 0u, 0, NB)
+                         : tc_epilogue_pixel(p, NB, taddr, valid, pix, cb * NB, &acc_empty[buf], lane);
+      }
       if (tid == 64 && item_idx == 0) TC_TRACE(11);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
       if (lane == 0 && t >= 0 && sent_bits) {
@@ -1027,6 +1067,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __syncwarp();  // single-lane roles: the whole warp reaches the block-wide barrier together
   tc_fence_before();
   __syncthreads();
+  if (CS > 1u) cluster_sync_all();   // K-split: no block leaves while another may still store into its shared memory
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     // give copies that may still be in flight time to land before shared memory is released
@@ -1175,25 +1216,30 @@ static void tc_block_shape(const mie_conv_args *a, int *nb_out, int *ksplit_out)
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
   while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
-  // K-split (halo kernel only): a layer with so few tile pairs that even 32-channel blocks leave each block a chain of
-  // hundreds of dependent MMA stages takes wide blocks instead and spreads the input-channel chunks of every block over
-  // a cluster of 2 or 4 CTAs, which exchange their partial sums through distributed shared memory.  Conditions: every
-  // cluster gets at most one work item (grid = items x cluster size <= one wave), the chunks divide evenly, and a
-  // CTA's slice of the block's columns is a whole number of 16-channel groups.
+  // K-split: a layer with so few tile pairs that even 32-channel blocks leave each block a chain of hundreds of
+  // dependent MMA stages takes wide blocks instead and spreads the input-channel chunks of every block over a cluster of
+  // 2 or 4 thread blocks, which exchange their partial sums through distributed shared memory (ksplit_finish).
+  // Conditions: every cluster gets at most one work item (grid = items x cluster size <= one wave), the chunks divide
+  // evenly, and a block's slice of the columns is a whole number of 16-channel groups.
   int ksplit = 1;
-  if (g_opt_ksplit && a->stride == 1 && a->k >= 3 && a->k <= 7 && halo_enabled()) {
+  if (g_opt_ksplit && a->k >= 3 && a->k <= 7) {
     int nbw = 128;
     while (nbw > 32 && a->cout_pad % nbw) nbw >>= 1;
     const int n_chunks = cin_pad32 / 32;
     const int64_t items_w = pairs * (a->cout_pad / nbw);
+    const bool halo = a->stride == 1 && (cin_pad32 > 32 || a->k >= 5) && halo_enabled();   // which kernel takes the layer
     const int Wh = 8 + a->k - 1;
     const int a_bytes = 2 * (Wh * 2 * 8 * Wh * 16);
     for (int cs = 4; cs >= 2 && ksplit == 1; cs >>= 1) {
-      // the received partial sums take shared memory from the filter ring: split only while two ring slots of a whole
-      // filter row each still fit (with single-tap stages the wide block measured no faster than the narrow ones)
-      const int ring = 200 * 1024 - a_bytes - (cs - 1) * (nbw / cs) * 512;
+      const int part_bytes = (cs - 1) * (nbw / cs) * 512;
+      // the received partial sums take shared memory from the operand ring.  Halo kernel: split only while two ring
+      // slots of a whole filter row each still fit (with single-tap stages the wide block measured no faster than the
+      // narrow ones); per-tap kernel: three stages must fit.
+      const bool fits = halo ? 2 * a->k * nbw * 128 <= 200 * 1024 - a_bytes - part_bytes
+                             : 3 * (A_STAGE_BYTES + nbw * 128) + part_bytes <= 200 * 1024;
+      // worth it from about 70 operand stages per item on (the per-tap kernel's stages are single taps: from 50)
       if (a->cout_pad % nbw == 0 && n_chunks % cs == 0 && n_chunks / cs >= 1 && items_w * cs <= MIE_SM_COUNT &&
-          (nbw / cs) % 16 == 0 && n_chunks * a->k * a->k >= 72 && 2 * a->k * nbw * 128 <= ring)
+          (nbw / cs) % 16 == 0 && n_chunks * a->k * a->k >= (halo ? 72 : 50) && fits)
         ksplit = cs;
     }
     if (ksplit > 1) nb = nbw;
@@ -1288,7 +1334,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int stage_bytes = A_STAGE_BYTES + nb * 128;
   // Narrow blocks (few MMAs per item: the epilogue is exposed) take the coalesced epilogue; wide blocks, whose epilogue
   // hides behind the next item's MMAs, measured faster on the direct one.
-  const bool coalesced = nb <= 32 && a->thr == 0.0f && !a->emitted && (a->cout & 3) == 0;
+  const bool coalesced = nb <= 32 && a->thr == 0.0f && !a->emitted && (a->cout & 3) == 0 && ksplit == 1;
   const int epi_bytes = coalesced ? 8192 : 0;   // static staging buffers of the coalesced epilogue
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 8) stages = 8;
@@ -1301,9 +1347,14 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     const int deep = ((220 * 1024) / 3 - 3072 - epi_bytes) / stage_bytes;
     stages = deep > 3 ? (deep < stages ? deep : stages) : 3;
   }
+  const int part_bytes = ksplit > 1 ? (ksplit - 1) * (nb / ksplit) * 512 : 0;   // partial sums received from the cluster
+  if (ksplit > 1) {
+    stages = (200 * 1024 - part_bytes) / stage_bytes;
+    if (stages > 4) stages = 4;
+  }
   if (stages < 2) return MIE_EUNSUPPORTED;
   p.stages = stages;
-  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  const size_t smem = (size_t)stages * stage_bytes + part_bytes + 1024;
   int blocks_per_sm = (int)((220 * 1024) / (smem + 2048 + epi_bytes));
   { const int by_tmem = 512 / (2 * acc_cols); if (blocks_per_sm > by_tmem) blocks_per_sm = by_tmem; }
   // registers: the coalesced instantiation (79) fits three blocks of 192 threads, the direct one (142) two
@@ -1337,14 +1388,22 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
   int grid = max_items < cap ? (int)max_items : (int)cap;
   if (grid < 1) grid = 1;
+  if (ksplit > 1) {
+    static int ks_smem_set[MAX_DEVICES] = {0};
+    { const int s_ = ensure_dynamic_smem(conv_tc_kernel<false, true>, ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+    p.ksplit = ksplit;
+    launch_chained_cluster(conv_tc_kernel<false, true>, dim3((unsigned)(max_items * ksplit)), dim3(TC_THREADS), smem, st,
+                           (unsigned)ksplit, p, maps);
+    return check_launch();
+  }
   static int smem_set[2][MAX_DEVICES] = {{0}};
   {
-    const int s_ = coalesced ? ensure_dynamic_smem(conv_tc_kernel<true>, smem_set[1], smem)
-                             : ensure_dynamic_smem(conv_tc_kernel<false>, smem_set[0], smem);
+    const int s_ = coalesced ? ensure_dynamic_smem(conv_tc_kernel<true, false>, smem_set[1], smem)
+                             : ensure_dynamic_smem(conv_tc_kernel<false, false>, smem_set[0], smem);
     if (s_ != MIE_OK) return s_;
   }
-  if (coalesced) launch_chained(conv_tc_kernel<true>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
-  else launch_chained(conv_tc_kernel<false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  if (coalesced) launch_chained(conv_tc_kernel<true, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  else launch_chained(conv_tc_kernel<false, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
   return check_launch();
 }
 
@@ -1380,12 +1439,7 @@ extern "C" int mie_conv_cluster_size(const mie_conv_args *a) {
   if (!a || !tc_eligible(a)) return 0;
   int nb, ksplit;
   tc_block_shape(a, &nb, &ksplit);
-  // the cluster variant belongs to the halo kernel: same conditions as in launch_conv_tc
-  const int cin_pad32 = (a->cin + 31) / 32 * 32;
-  const int64_t max_items = (int64_t)((a->max_tiles + 1) / 2) * (a->cout_pad / nb);
-  const bool halo = a->stride == 1 && a->k >= 3 && a->k <= 7 && !(nb == 256 && max_items > MIE_SM_COUNT) &&
-                    (cin_pad32 > 32 || a->k >= 5) && halo_enabled();
-  return halo ? ksplit : 1;
+  return ksplit;
 }
 
 extern "C" int mie_set_option(int option, int value) {
