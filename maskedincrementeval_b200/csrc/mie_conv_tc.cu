@@ -8,7 +8,7 @@
 // Two kernels share the epilogue (tcgen05.ld, fused incremental activation, tile words):
 //
 // conv_tc_kernel (per-tap): one pipeline stage per (chunk, tap), both operands moved by TMA (tiled mode,
-// 128-byte swizzle, no cluster, no multicast):
+// 128-byte swizzle; every copy is issued by one thread block for its own shared memory, also in the cluster variants):
 //   A: for each of the two tiles a box [1 image][8 rows][8 cols][32 channels] of the input field, shifted by
 //      the tap; out-of-image elements are zero-filled by the TMA unit, which is the convolution padding.
 //      The box lands as 64 rows of 128 bytes in pixel order = the K-major operand layout tcgen05.mma reads.
