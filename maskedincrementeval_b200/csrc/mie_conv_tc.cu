@@ -1167,6 +1167,17 @@ int ensure_dynamic_smem(Kernel kernel, int *set_per_device, size_t smem) {
   return MIE_OK;
 }
 
+// Shared memory the halo kernel's operands may take (KB) and the largest filter ring (slots); MIE_TC_RING_KB /
+// MIE_TC_RING_CAP in the environment override them for A/B measurements.
+int halo_ring_kb() {
+  static const int v = []() { const char *e = getenv("MIE_TC_RING_KB"); const int x = e ? atoi(e) : 0; return (x >= 128 && x <= 224) ? x : 200; }();
+  return v;
+}
+int halo_ring_cap() {
+  static const int v = []() { const char *e = getenv("MIE_TC_RING_CAP"); const int x = e ? atoi(e) : 0; return (x >= 2 && x <= HALO_MAX_STAGES) ? x : 4; }();
+  return v;
+}
+
 // MIE_TC_HALO=0 in the environment keeps every layer on the per-tap kernel (for A/B measurements).
 bool halo_enabled() {
   static const bool on = []() { const char *e = getenv("MIE_TC_HALO"); return !(e && e[0] == '0'); }();
@@ -1285,11 +1296,11 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     // taps), else one filter row (k taps), else a single tap -- even if only two ring slots remain (measured:
     // 5-tap stages x 2 slots beat 1-tap stages x 4 slots by 25 % on a 5x5 256->128 layer).
     const int part_bytes = ksplit > 1 ? (ksplit - 1) * (nb / ksplit) * 512 : 0;   // partial sums received from the cluster
-    const int budget = 200 * 1024 - a_bytes - part_bytes;
+    const int budget = halo_ring_kb() * 1024 - a_bytes - part_bytes;
     int tps = 0, stages = 0;
     const int cand[3] = {a->k * a->k, a->k, 1};
     for (int i = 0; i < 3 && !tps; ++i)
-      if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = budget / (cand[i] * nb * 128); if (stages > 4) stages = 4; }
+      if (2 * cand[i] * nb * 128 <= budget) { tps = cand[i]; stages = budget / (cand[i] * nb * 128); if (stages > halo_ring_cap()) stages = halo_ring_cap(); }
     p.tps = tps ? tps : 1;
     const int b_bytes = p.tps * nb * 128;
     p.issuers = (2 * 2 * acc_cols <= 512 && (p.cin_pad / 32 / ksplit) * (a->k * a->k / p.tps) >= 2) ? 2 : 1;   // stages per CTA
