@@ -1358,6 +1358,10 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
     const int deep = ((220 * 1024) / 3 - 3072 - epi_bytes) / stage_bytes;
     stages = deep > 3 ? (deep < stages ? deep : stages) : 3;
   }
+  { // MIE_TC_TAP_STAGES in the environment forces the per-tap ring depth (A/B measurements)
+    static const int forced = []() { const char *e = getenv("MIE_TC_TAP_STAGES"); const int x = e ? atoi(e) : 0; return (x >= 2 && x <= 8) ? x : 0; }();
+    if (forced && forced * stage_bytes <= 200 * 1024) stages = forced;
+  }
   const int part_bytes = ksplit > 1 ? (ksplit - 1) * (nb / ksplit) * 512 : 0;   // partial sums received from the cluster
   if (ksplit > 1) {
     stages = (200 * 1024 - part_bytes) / stage_bytes;
