@@ -195,6 +195,14 @@ typedef struct mie_conv_args {
   int refresh;
   /* optional tile dilation of the next convolution, run in this kernel's tail (in_bits == out_bits of this call) */
   const mie_tail_job *tail;
+  /* 1x1 prediction heads only (k == 1, stride 1, pad 0, cout <= 4; MIE_EUNSUPPORTED elsewhere):
+   * `in2` -- a second input field of the same shape, added to `in` as it is read (the skip sum in front of the
+   *          prediction layer, incr_modules/e2depth_incr.py:430-434, without materialising it); its tile words go to
+   *          mie_tiles_dilate as `union_bits`, which for a 1x1 convolution has the input's geometry;
+   * `accum` -- a [N,cout,H,W] field that receives `accum += out` at the pixels this call sends (the driver's
+   *          `c += c_incr[0]`, run_e2depth_continuous_dataset.py:74, without a separate pass); not in dense evaluation. */
+  const float *in2; int64_t in2_ps;
+  float *accum; int64_t accum_ps;
 } mie_conv_args;
 
 int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);

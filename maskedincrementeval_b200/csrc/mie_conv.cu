@@ -37,6 +37,8 @@ struct ConvParams {
   const float *bias;   // per output channel, added before the activation (dense evaluation only)
   int refresh;         // dense evaluation: the reservoir is set instead of advanced, the output is f(conv + bias)
   mie_tail_job tail;   // the next convolution's tile dilation, run by the last block (list == nullptr: none)
+  const float *in2; int64_t in2_ps;   // 1x1 head: second input, added on the fly
+  float *accum; int64_t accum_ps;     // 1x1 head: accum += out at the sent pixels
 };
 
 constexpr int CC = 8;  // input channels per chunk
@@ -407,21 +409,28 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
     if (valid) {
       const int64_t pix = (int64_t)(n * p.hout + oy) * p.wout + ox;  // 1x1, stride 1: input pixel == output pixel
       const float *ip = p.in + pix * p.in_ps;
+      const float *ip2 = p.in2 ? p.in2 + pix * p.in2_ps : nullptr;
       float acc[SMALL_COUT] = {0.f, 0.f, 0.f, 0.f};
       if (p.in_vec) {
         for (int c = 0; c + 3 < p.cin; c += 4) {
-          const float4 v = *reinterpret_cast<const float4 *>(ip + c);
+          float4 v = *reinterpret_cast<const float4 *>(ip + c);
+          if (ip2) {
+            const float4 u = *reinterpret_cast<const float4 *>(ip2 + c);
+            v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+          }
           const float *w = s_w + c * SMALL_COUT;
 #pragma unroll
           for (int j = 0; j < SMALL_COUT; ++j)
             acc[j] += v.x * w[j] + v.y * w[SMALL_COUT + j] + v.z * w[2 * SMALL_COUT + j] + v.w * w[3 * SMALL_COUT + j];
         }
-        for (int c = p.cin & ~3; c < p.cin; ++c)
+        for (int c = p.cin & ~3; c < p.cin; ++c) {
+          const float v = ip[c] + (ip2 ? ip2[c] : 0.0f);
 #pragma unroll
-          for (int j = 0; j < SMALL_COUT; ++j) acc[j] += ip[c] * s_w[c * SMALL_COUT + j];
+          for (int j = 0; j < SMALL_COUT; ++j) acc[j] += v * s_w[c * SMALL_COUT + j];
+        }
       } else {
         for (int c = 0; c < p.cin; ++c) {
-          const float v = ip[c];
+          const float v = ip[c] + (ip2 ? ip2[c] : 0.0f);
 #pragma unroll
           for (int j = 0; j < SMALL_COUT; ++j) acc[j] += v * s_w[c * SMALL_COUT + j];
         }
@@ -457,6 +466,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
           const float v = flag ? dy[j] : 0.0f;
           p.out[pix * p.out_ps + j] = v;
           if (p.emitted && flag) p.emitted[pix * p.emitted_ps + j] += v;
+          if (p.accum && flag) p.accum[pix * p.accum_ps + j] += v;
         }
     }
     const unsigned half = __ballot_sync(0xffffffffu, flag);
@@ -567,6 +577,9 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   p.addend = a->addend; p.addend_ps = a->addend_ps;
   p.bias = a->bias; p.refresh = a->refresh ? 1 : 0;
   p.tail = tail_for_kernel(a->tail);
+  p.in2 = a->in2; p.in2_ps = a->in2_ps; p.accum = a->accum; p.accum_ps = a->accum_ps;
+  if (a->in2 && a->in2_ps < a->cin) return MIE_EINVAL;
+  if (a->accum && (a->accum_ps < a->cout || a->refresh)) return MIE_EINVAL;
   // 16-byte staging reads whole channel quads: with cin % 4 != 0 the last quad reaches into the pixel's
   // padding channels (in_ps >= cin rounded up to 4), which meet zero filter rows and must be finite
   p.in_vec = (a->in_ps % 4 == 0) && aligned16(a->in) && (a->in_ps >= (a->cin + 3) / 4 * 4);
@@ -577,11 +590,13 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (a->k == 1 && a->stride == 1 && a->pad == 0 && a->cout <= SMALL_COUT && a->cin <= 2048) {
     int blocks = divup(a->max_tiles, 4);
     if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
-    p.in_vec = p.in_vec && (a->cin % 4 == 0 || a->in_ps >= (a->cin + 3) / 4 * 4);
+    p.in_vec = p.in_vec && (a->cin % 4 == 0 || a->in_ps >= (a->cin + 3) / 4 * 4) &&
+               (!a->in2 || (a->in2_ps % 4 == 0 && aligned16(a->in2) && a->in2_ps >= (a->cin + 3) / 4 * 4));
     launch_chained(conv1x1_small_kernel, dim3(blocks), dim3(256), (size_t)a->cin * SMALL_COUT * sizeof(float), (cudaStream_t)stream, p);
     return tail_after_launch(check_launch(), a->tail, true, stream);
   }
 
+  if (a->in2 || a->accum) return MIE_EUNSUPPORTED;   // only the 1x1 head kernel above takes them
   // block shape: 32 channels -> 4 tiles x 1; otherwise 4 tiles x 64 channels.  (A thresholded fused activation
   // decides per 16-channel group, which both shapes hold inside one warp.)
   int wt = 4, wn = 2;

@@ -1188,6 +1188,7 @@ bool halo_enabled() {
 
 // Whether the tensor-core path can take this convolution (host-side rules only).
 bool tc_eligible(const mie_conv_args *a) {
+  if (a->in2 || a->accum) return false;   // the 1x1 head kernel's extras
   if (!a->wpacked_tc) return false;
   if (a->refresh || a->bias) return false;   // dense evaluation (full fp32, bias, reservoir set) is the FP32 kernel's
   if (!(a->stride == 1 || a->stride == 2)) return false;

@@ -49,6 +49,8 @@ class IncrConfig:
     tail_dilation    True: a convolution's tile dilation rides in the tail of the kernel that produces its input mask
                      (one launch less per convolution; measured slower than the separate launch when launches overlap
                      through programmatic dependent launch, so it is off by default); False: separate launch
+    fuse_accumulate  True (default): IncrementalRunner lets a 1x1 prediction head add its output into the accumulated
+                     prediction inside its own kernel instead of launching mie_accumulate afterwards
     tc_thresholded   True (default): thresholded convolutions (threshold > 0, with or without carry) use the tensor
                      cores like lossless ones; False routes them to the FP32 kernel
     """
@@ -59,6 +61,7 @@ class IncrConfig:
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
     tc_thresholded: bool = True
     tail_dilation: bool = False
+    fuse_accumulate: bool = True
     kfenced_step: Optional[float] = None
     refresh: str = "native"
 

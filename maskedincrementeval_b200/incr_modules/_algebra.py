@@ -52,8 +52,8 @@ class DenseOps:
     def gru(self, cell, x, prev_state):
         return cell.forward_refresh_reservoirs(x, prev_state)
 
-    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
-        y = conv.forward_refresh_reservoirs(x)
+    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None, second=None):
+        y = conv.forward_refresh_reservoirs(x if second is None else x + second)
         if norm is not None:
             y = norm.forward_refresh_reservoirs(y)
         if addend is not None:
@@ -95,11 +95,14 @@ class IncrOps:
     def gru(self, cell, x, prev_state):
         return cell(x, prev_state)
 
-    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
+    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None, second=None):
+        if second is not None and not (norm is None and addend is None and cin_limit is None and conv.takes_second_input()
+                                       and not fl.config.kfenced_step and x[0].shape == second[0].shape):
+            x, second = self.add(x, second, conv._scratch, "second.sum"), None      # no fused form: add first
         if norm is not None:      # batch-norm between convolution and activation: not fused
             y = norm(conv.forward_fused(x, None, addend, cin_limit=cin_limit))
             return y if act is None else act(y)
-        return conv.forward_fused(x, act, addend, cin_limit=cin_limit)
+        return conv.forward_fused(x, act, addend, cin_limit=cin_limit, second=second)
 
     def act(self, act, x):
         return act(x)
@@ -158,10 +161,13 @@ class NativeDenseOps(IncrOps):
     def lower(self, v):
         return v[0].clone()
 
-    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None):
+    def conv(self, conv, x, act=None, addend=None, norm=None, cin_limit: Optional[int] = None, second=None):
         if norm is not None:
             raise NotImplementedError("batch-norm layers take the library dense pass (config.refresh = 'library')")
-        return conv.forward_fused(x, act, addend, cin_limit=cin_limit, refresh=True)
+        if second is not None and not (addend is None and cin_limit is None and conv.takes_second_input()
+                                       and x[0].shape == second[0].shape):
+            x, second = self.add(x, second, conv._scratch, "second.sum"), None
+        return conv.forward_fused(x, act, addend, cin_limit=cin_limit, refresh=True, second=second)
 
     def act(self, act, x):
         return [act.forward_refresh_reservoirs(x[0]), x[1]]

@@ -374,11 +374,10 @@ class UNetRecurrentIncr(BaseUNetIncr):
                 x = dec._run(ops, x, skip if skips else None)      # the sum happens inside the upsample kernel
             else:
                 x = dec._run(ops, x + skip)
-        if skips:
-            x = ops.add(x, head, self._scratch, "tail")
-        # 1x1 prediction and the final activation (one launch incrementally)
+        # 1x1 prediction and the final activation, with the head's skip added as the kernel reads its input (one launch
+        # incrementally; the reference sums first, ``:430-434``)
         norm = self.pred.norm_layer if (self.norm == 'BN' and not ops.incremental) else None
-        return ops.conv(self.pred.conv2d, x, self.activation, norm=norm), states
+        return ops.conv(self.pred.conv2d, x, self.activation, norm=norm, second=head if skips else None), states
 
     def forward(self, x_incr: Masked, prev_states_incr):
         return self._run(INCR, x_incr, prev_states_incr)

@@ -260,6 +260,8 @@ class _ConvPlan:
         self.mask = TileMask(self.out_bits, n, self.hout, self.wout)
         self.tail = None            # fields.TailJob: this convolution's dilation, offered to its input's producer
         self.needs_clear = False    # a carried dilation was never consumed: start from a cleared output
+        self.accum_target = None    # set by a driver for the duration of one call: the kernel adds its output in
+        self.accumulated = False    # ... and reports here that it did
 
 
 class nnConvIncr(nn.Conv2d):
@@ -361,9 +363,14 @@ class nnConvIncr(nn.Conv2d):
             p = self._plans[key] = _ConvPlan(self, n, hin, win, device)
         return p
 
+    def takes_second_input(self) -> bool:
+        """True for the 1x1 prediction heads whose kernel can add a second input field as it reads the first."""
+        return self._k == 1 and self._s == 1 and self._p == 0 and self.out_channels <= 4 and self.in_channels <= 2048
+
     def forward_fused(self, x_incr: Masked, activation: "Optional[nnReservedActivation]" = None,
                       addend: Optional[Masked] = None, cin_limit: Optional[int] = None,
-                      bn: "Optional[nn.BatchNorm2d]" = None, refresh: bool = False) -> Masked:
+                      bn: "Optional[nn.BatchNorm2d]" = None, refresh: bool = False,
+                      second: Optional[Masked] = None) -> Masked:
         """conv(dx) [* batch-norm scale] [+ addend] [-> incremental activation], one dilation launch and one
         convolution launch.
 
@@ -395,6 +402,17 @@ class nnConvIncr(nn.Conv2d):
             d, cin = d3, c3
         a = plan.args
         union = None
+        a.in2, a.in2_ps = None, 0
+        if second is not None:
+            # the sum x + second is formed as the 1x1 head kernel reads its input; the second mask joins the tile set
+            # as the dilation's union mask (output geometry = input geometry for a 1x1 convolution)
+            if not self.takes_second_input() or addend is not None or split or config.kfenced_step:
+                raise RuntimeError("a second input needs a plain 1x1 prediction head")
+            d2, m2 = fl.resolve(second, sc, "in2")
+            if d2.shape != d.shape:
+                raise RuntimeError("the second input must have the first one's shape")
+            union = m2.bits
+            a.in2, a.in2_ps = d2.data_ptr(), fl.pixel_stride(d2)
         if addend is not None:
             ad, am = fl.resolve(addend, sc, "addend")
             if ad.shape != plan.out.shape:
@@ -448,6 +466,10 @@ class nnConvIncr(nn.Conv2d):
             raise RuntimeError("a split-precision convolution did not qualify for the tensor cores (its three channel "
                                "blocks only add up to the fp32 result there); set precision=None on this layer")
         a.tail = fl.take_tail(plan.out_bits)
+        a.accum, a.accum_ps, plan.accumulated = None, 0, False
+        tgt = plan.accum_target
+        if tgt is not None and not refresh and self.takes_second_input() and tgt.shape == plan.out.shape:
+            a.accum, a.accum_ps, plan.accumulated = tgt.data_ptr(), fl.pixel_stride(tgt), True
         nat.check(nat.lib.mie_conv_tiles(C.byref(a), st), "conv_tiles")
         if refresh and activation is not None and activation.emitted is not None:
             if activation.emitted.shape == plan.out.shape and activation.thr() > 0.0 and config.carry:

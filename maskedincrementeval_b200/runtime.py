@@ -72,6 +72,7 @@ class IncrementalRunner:
         if feedback and not self.takes_states:
             raise ValueError("feedback=True needs a network that takes recurrent states (E2Depth)")
         self.feedback = feedback
+        self._heads, self._head_of, self._heads_known = [], {}, False   # prediction heads that accumulate in their kernel
         self._states = None        # accumulated dense (h, c) per encoder
         self._prev_incr = None     # state deltas handed to the next incremental step: [(dh, mask_h, dc, mask_c)]
         self._x_prev = self._x_in = self._dx = None
@@ -121,6 +122,7 @@ class IncrementalRunner:
             self._graph = None
             self._pipe = None
             self._eager_steps = 0
+            self._heads, self._head_of, self._heads_known = [], {}, False
         else:
             self._x_prev.copy_(x)
             for dst, src in zip(self._y, ys):
@@ -168,19 +170,47 @@ class IncrementalRunner:
         # input delta, previous-frame update and input mask in one kernel
         m_in = fl.delta_mask(self._x_in, self._x_prev, self._dx, self._dx_bits, fl.config.input_threshold)
         x_incr = (self._dx, m_in)
-        if self.feedback:
-            prev = [([dh, TileMask(bh, *dh.shape[:1], *dh.shape[2:])], [dc, TileMask(bc, *dc.shape[:1], *dc.shape[2:])])
-                    for dh, bh, dc, bc in self._prev_incr]
-            out = self.model(x_incr, prev)
-            self._feed_back(out[1])
-        else:
-            out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
-        for y, d in zip(self._y, _deltas_of(out)):
+        # A prediction head whose kernel can add its output into the accumulated prediction does so (one launch less);
+        # which convolution writes which output buffer is learnt from the first step.  The target is lent for the
+        # duration of this call only: the model behaves as usual when it is run outside the runner.
+        for plan, y in self._heads:
+            plan.accum_target = y
+        try:
+            if self.feedback:
+                prev = [([dh, TileMask(bh, *dh.shape[:1], *dh.shape[2:])], [dc, TileMask(bc, *dc.shape[:1], *dc.shape[2:])])
+                        for dh, bh, dc, bc in self._prev_incr]
+                out = self.model(x_incr, prev)
+                self._feed_back(out[1])
+            else:
+                out = self.model(x_incr, None) if self.takes_states else self.model(x_incr)
+        finally:
+            for plan, _ in self._heads:
+                plan.accum_target = None
+        deltas = list(_deltas_of(out))
+        for y, d in zip(self._y, deltas):
             m = d[1]
-            if isinstance(m, TileMask):
+            plan = self._head_of.get(d[0].data_ptr())
+            if plan is not None and plan.accumulated:
+                plan.accumulated = False          # the head's kernel has added this delta already
+            elif isinstance(m, TileMask):
                 fl.accumulate(y, d[0], m)
             else:
                 y.add_(d[0])
+        if not self._heads_known:
+            self._learn_heads(deltas)
+
+    def _learn_heads(self, deltas) -> None:
+        """Find, for every output delta, the 1x1 prediction head whose plan owns that buffer."""
+        from .incr_modules.mask_incr_modules import nnConvIncr
+        self._heads_known = True
+        plans = {p.out.data_ptr(): p for m in self.model.modules() if isinstance(m, nnConvIncr) and m.takes_second_input()
+                 for p in m._plans.values()}
+        self._heads, self._head_of = [], {}
+        for y, d in zip(self._y, deltas):
+            plan = plans.get(d[0].data_ptr())
+            if plan is not None and plan.out.shape == y.shape and fl.config.fuse_accumulate:
+                self._heads.append((plan, y))
+                self._head_of[d[0].data_ptr()] = plan
 
     def step(self, x: torch.Tensor):
         if self._x_prev is None:
