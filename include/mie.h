@@ -335,9 +335,13 @@ int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_ps, const u
 
 /* dx = x - x_prev; x_prev = x; bits = per-pixel any_c(|dx| > thr), one pass.  Withheld pixels (all |dx| <= thr)
  * are written as 0 and keep their x_prev, so nothing is lost, only deferred.
- * The driver's `x = event_tensor - event_tensor_prev` (run_e2depth_continuous_dataset.py:66) plus the mask. */
+ * The driver's `x = event_tensor - event_tensor_prev` (run_e2depth_continuous_dataset.py:66) plus the mask.
+ * `split` (may be null): also write what mie_split_tf32 would make of dx -- [dx, dx - tf32(dx), dx] as three blocks of
+ * C rounded up to 8 channels, pixel stride split_ps, tile words split_bits (which must describe the copy's previous
+ * contents: half tiles that are and were inactive are skipped) -- for a first layer that runs in split precision. */
 int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
                    uint64_t *bits, int N, int C, int H, int W, float thr,
+                   float *split /* may be null */, int64_t split_ps, uint64_t *split_bits,
                    const mie_tail_job *tail /* reads bits; may be null */, void *stream);
 
 /* Voxel grid of one window of events: temporal-bilinear, spatial-nearest accumulation, as

@@ -84,7 +84,7 @@ SIGNATURES = {
     "mie_add": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _vp, _vp]),
     "mie_cat2": (_i, [_vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i, _i, _vp, _vp]),
     "mie_accumulate": (_i, [_vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _vp]),
-    "mie_delta_mask": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
+    "mie_delta_mask": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _f, _vp, _i64, _vp, _vp, _vp]),
     "mie_events_to_voxel": (_i, [_vp, _i, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mie_events_to_count_image": (_i, [_vp, _i, _i, _i, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mie_maxpool_incr": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),

@@ -1112,7 +1112,11 @@ int launch_act_dense(float *X, const float *in, float *out, int64_t n, cudaStrea
 __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict__ x, int64_t x_ps, float *__restrict__ xp,
                                                          int64_t xp_ps, float *__restrict__ dx, int64_t dx_ps,
                                                          unsigned *__restrict__ bits32, int N, int C, int H, int W, float thr,
-                                                         const mie_tail_job tail) {
+                                                         float *__restrict__ split, int64_t split_ps, int shalf,
+                                                         unsigned *__restrict__ split_bits32, const mie_tail_job tail) {
+  // `split` (optional): the split-precision copy [d, d - tf32(d), d] of the delta (what mie_split_tf32 would make of it),
+  // written in the same pass; a half tile (32 pixels = one warp) that is inactive now and was inactive in the copy's
+  // last state is skipped, so the copy keeps the zero invariant at the cost of the active half tiles only.
   grid_dependency_wait();
   grid_dependency_trigger();
   const int TH = (H + 7) >> 3, TW = (W + 7) >> 3;
@@ -1122,19 +1126,33 @@ __global__ void __launch_bounds__(256) delta_mask_kernel(const float *__restrict
     const int p = threadIdx.x & 63;
     const int tx = t % TW, ty = (t / TW) % TH, n = t / (TW * TH);
     const int y = ty * 8 + (p >> 3), xx = tx * 8 + (p & 7);
+    const bool inside = y < H && xx < W;
+    const int64_t pix = inside ? (int64_t)(n * H + y) * W + xx : 0;
     bool a = false;
-    if (y < H && xx < W) {
-      const int64_t pix = (int64_t)(n * H + y) * W + xx;
+    if (inside)
       for (int c = 0; c < C; ++c) a |= fabsf(x[pix * x_ps + c] - xp[pix * xp_ps + c]) > thr;
+    const unsigned half = __ballot_sync(0xffffffffu, a);
+    const size_t wi = 2 * (size_t)t + ((p >> 5) & 1);
+    const bool copy = split && (half | split_bits32[wi]) != 0u;
+    if (inside) {
       for (int c = 0; c < C; ++c) {
         const float v = x[pix * x_ps + c];
         const float d = a ? v - xp[pix * xp_ps + c] : 0.0f;
         dx[pix * dx_ps + c] = d;
         if (a) xp[pix * xp_ps + c] = v;
+        if (copy) {
+          float *o = split + pix * split_ps + c;
+          o[0] = d;
+          o[shalf] = d - __uint_as_float(__float_as_uint(d) & 0xFFFFE000u);
+          o[2 * shalf] = d;
+        }
       }
     }
-    const unsigned half = __ballot_sync(0xffffffffu, a);
-    if (lane == 0) bits32[2 * (size_t)t + ((p >> 5) & 1)] = half;
+    __syncwarp();      // every lane has read the copy's old word before lane 0 replaces it
+    if (lane == 0) {
+      bits32[wi] = half;
+      if (split) split_bits32[wi] = half;
+    }
   }
   run_tail_job(tail);
 }
@@ -1501,16 +1519,19 @@ extern "C" int mie_accumulate(float *y, int64_t y_ps, const float *d, int64_t d_
 }
 
 extern "C" int mie_delta_mask(const float *x, int64_t x_ps, float *x_prev, int64_t xp_ps, float *dx, int64_t dx_ps,
-                              uint64_t *bits, int N, int C, int H, int W, float thr, const mie_tail_job *tail, void *stream) {
+                              uint64_t *bits, int N, int C, int H, int W, float thr, float *split, int64_t split_ps,
+                              uint64_t *split_bits, const mie_tail_job *tail, void *stream) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || !bits || !(thr >= 0.0f)) return MIE_EINVAL;
   if (tail_check(tail, bits) != MIE_OK) return MIE_EINVAL;
+  const int shalf = divup(C, 8) * 8;
+  if (split && (!split_bits || split_ps < 3 * shalf)) return MIE_EINVAL;
   MIE_CHECK_FIELD(x, x_ps, C); MIE_CHECK_FIELD(x_prev, xp_ps, C); MIE_CHECK_FIELD(dx, dx_ps, C);
   const int ntiles = N * divup(H, 8) * divup(W, 8);
   int blocks = divup(ntiles, 4);
   if (blocks > MIE_SM_COUNT * 8) blocks = MIE_SM_COUNT * 8;
   launch_chained(delta_mask_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, x_ps, x_prev, xp_ps, dx, dx_ps,
-                                                              reinterpret_cast<unsigned *>(bits), N, C, H, W, thr,
-                                                              tail_for_kernel(tail));
+                                                              reinterpret_cast<unsigned *>(bits), N, C, H, W, thr, split, split_ps,
+                                                              shalf, reinterpret_cast<unsigned *>(split_bits), tail_for_kernel(tail));
   return tail_after_launch(check_launch(), tail, true, stream);
 }
 

@@ -229,9 +229,10 @@ def withdraw_tail(job: Optional[TailJob]) -> None:
 
 
 def forget_tails() -> None:
-    """Drop every offered job (the buffers they point to are about to be released)."""
+    """Drop every offered job and split request (the buffers they point to are about to be released)."""
     _tail_jobs.clear()
     _produced_at.clear()
+    _split_requests.clear()
 
 
 def mask_from_delta(x: torch.Tensor, thr: float = 0.0, bits: Optional[torch.Tensor] = None) -> TileMask:
@@ -442,12 +443,38 @@ def pack_conv_weights_tc(weight: torch.Tensor) -> torch.Tensor:
     return buf
 
 
+# A first layer that runs in split precision asks the producer of its input delta for the split copy: the request is
+# filed under the delta's address after the layer made the copy itself once; `delta_mask` honours it from then on.
+_split_requests: Dict[int, list] = {}     # delta address -> [copy tensor, copy tile words, made-by-producer flag]
+
+
+def request_split(d: torch.Tensor, copy: torch.Tensor, copy_bits: torch.Tensor) -> None:
+    _split_requests[d.data_ptr()] = [copy, copy_bits, False]
+
+
+def split_made(d: torch.Tensor, copy: torch.Tensor) -> bool:
+    """Consumer side: True when the producer of ``d`` wrote ``copy`` since the last call."""
+    r = _split_requests.get(d.data_ptr())
+    if r is not None and r[0] is copy and r[2]:
+        r[2] = False
+        return True
+    return False
+
+
 def delta_mask(x: torch.Tensor, x_prev: torch.Tensor, dx: torch.Tensor, bits: torch.Tensor, thr: float = 0.0) -> TileMask:
-    """dx = x - x_prev, x_prev = x and the mask of dx in one kernel (pixels with every |dx| <= thr are deferred)."""
+    """dx = x - x_prev, x_prev = x and the mask of dx in one kernel (pixels with every |dx| <= thr are deferred);
+    also the split-precision copy of dx when the layer that consumes it has asked for one."""
     n, c, h, w = x.shape
+    r = _split_requests.get(dx.data_ptr())
+    sp = sps = sb = None
+    if r is not None:
+        if r[2] or r[0].shape[0] != n or r[0].shape[2:] != (h, w):      # the consumer did not pick the last copy up
+            del _split_requests[dx.data_ptr()]
+        else:
+            sp, sps, sb, r[2] = r[0].data_ptr(), pixel_stride(r[0]), r[1].data_ptr(), True
     nat.check(nat.lib.mie_delta_mask(x.data_ptr(), pixel_stride(x), x_prev.data_ptr(), pixel_stride(x_prev), dx.data_ptr(),
-                                     pixel_stride(dx), bits.data_ptr(), n, c, h, w, float(thr), take_tail(bits),
-                                     nat.stream_ptr(x.device)), "delta_mask")
+                                     pixel_stride(dx), bits.data_ptr(), n, c, h, w, float(thr), sp, sps or 0, sb,
+                                     take_tail(bits), nat.stream_ptr(x.device)), "delta_mask")
     return TileMask(bits, n, h, w)
 
 

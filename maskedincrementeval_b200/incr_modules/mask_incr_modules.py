@@ -398,7 +398,11 @@ class nnConvIncr(nn.Conv2d):
             c3 = 3 * ((cin + 7) // 8 * 8)
             d3 = sc.get("split", (n, c3, hin, win), torch.float32, d.device, channels_last=True)
             sb = sc.get("split.bits", (fl.n_tiles(n, hin, win),), torch.int64, d.device)
-            fl.split_tf32(d, m, d3, sb)
+            # the producer of the delta (the driver's input-delta kernel) writes the copy itself once asked to
+            if not fl.split_made(d, d3):
+                fl.split_tf32(d, m, d3, sb)
+                if x_incr[1] is m and cin_limit is None:
+                    fl.request_split(d, d3, sb)
             d, cin = d3, c3
         a = plan.args
         union = None

@@ -98,3 +98,31 @@ def test_runner_accumulates_in_the_head_kernel(dev):
     for a, b in zip(*results):
         assert torch.equal(a, b)
     assert launches[0] == launches[1] - 1, launches      # the separate accumulation launch is gone
+
+
+def test_input_delta_kernel_writes_the_split_copy(dev):
+    """mie_delta_mask with a split target == mie_delta_mask followed by mie_split_tf32, over steps in which tiles come
+    and go (the copy must return to zero where the delta does)."""
+    from maskedincrementeval_b200 import _native as nat, fields as fl
+    g = torch.Generator().manual_seed(2)
+    n, c, h, w = 1, 5, 45, 70
+    half = 8
+    st = nat.stream_ptr(dev)
+    x = cl(torch.randn(n, c, h, w, generator=g), dev)
+    prev = [x.clone(), x.clone()]
+    dxs = [torch.zeros_like(x), torch.zeros_like(x)]
+    bits = [fl.new_bits(n, h, w, dev), fl.new_bits(n, h, w, dev)]
+    copies = [fl.new_field(n, 3 * half, h, w, dev), fl.new_field(n, 3 * half, h, w, dev)]
+    cbits = [fl.new_bits(n, h, w, dev), fl.new_bits(n, h, w, dev)]
+    for step in range(5):
+        x = x + cl(sparse(g, (n, c, h, w), [0.02, 0.0, 0.3, 0.01, 0.0][step]), dev)
+        # fused
+        nat.check(nat.lib.mie_delta_mask(x.data_ptr(), fl.pixel_stride(x), prev[0].data_ptr(), fl.pixel_stride(prev[0]),
+                                         dxs[0].data_ptr(), fl.pixel_stride(dxs[0]), bits[0].data_ptr(), n, c, h, w, 0.0,
+                                         copies[0].data_ptr(), 3 * half, cbits[0].data_ptr(), None, st), "delta_mask")
+        # two launches
+        m = fl.delta_mask(x, prev[1], dxs[1], bits[1])
+        fl.split_tf32(dxs[1], m, copies[1], cbits[1])
+        assert torch.equal(dxs[0], dxs[1]) and torch.equal(bits[0], bits[1])
+        assert torch.equal(copies[0], copies[1]) and torch.equal(cbits[0], cbits[1])
+    assert float(copies[0].abs().max()) == 0.0     # the last step had no change anywhere

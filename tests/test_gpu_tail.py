@@ -141,7 +141,7 @@ def test_point_kernels_carry_the_dilation(dev, k, s, p):
         bits = fl.new_bits(n, h, w, dev)
         job = _Job(dev, bits, n, h, w, k, s, p)
         nat.check(nat.lib.mie_delta_mask(x1.data_ptr(), fl.pixel_stride(x1), prev.data_ptr(), fl.pixel_stride(prev),
-                                         dx.data_ptr(), fl.pixel_stride(dx), bits.data_ptr(), n, 5, h, w, 0.0,
+                                         dx.data_ptr(), fl.pixel_stride(dx), bits.data_ptr(), n, 5, h, w, 0.0, None, 0, None,
                                          job.ptr() if carried else None, st), "delta_mask")
         if not carried:
             job.separate(dev)
