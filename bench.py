@@ -515,6 +515,7 @@ def run_ours(args):
     mie.config.tensor_cores = args.tensor_cores
     mie.config.tc_thresholded = bool(args.tc_thresholded)
     mie.config.tail_dilation = bool(args.tail_dilation)
+    mie.config.head_dilation = int(args.head_dilation)
     from maskedincrementeval_b200 import _native as _nat
     _nat.set_option(_nat.OPT_TC_KSPLIT, 1 if args.ksplit else 0)
     streams = args.streams
@@ -909,6 +910,9 @@ def main():
     ap.add_argument("--ksplit", action=argparse.BooleanOptionalAction, default=True,
                     help="small-image tensor-core layers run as clusters that split the input channels (default); "
                          "--no-ksplit keeps one thread block per work item")
+    ap.add_argument("--head-dilation", type=int, default=0,
+                    help="largest number of output tiles up to which a convolution runs its own tile dilation inside its "
+                         "kernel (first block makes the lists, the others wait); 0 = separate launches (default)")
     ap.add_argument("--tail-dilation", action=argparse.BooleanOptionalAction, default=False,
                     help="tile dilations ride in the tail of the kernel that produces their input mask instead of running "
                          "as separate launches (fewer launches, measured slower)")

@@ -195,6 +195,11 @@ typedef struct mie_conv_args {
   int refresh;
   /* optional tile dilation of the next convolution, run in this kernel's tail (in_bits == out_bits of this call) */
   const mie_tail_job *tail;
+  /* optional: THIS convolution's own tile dilation (the mie_tiles_dilate call that would precede it: same geometry,
+   * list / stale / counts / out_bits of this call), run by the first thread block of the convolution kernel while the
+   * others wait for its lists -- one launch instead of two.  counts[2] must be 0 on entry and is 0 on exit.  More than
+   * MIE_TAIL_MAX_TILES output tiles: the entry point enqueues the separate launch itself. */
+  const mie_tail_job *head;
   /* 1x1 prediction heads only (k == 1, stride 1, pad 0, cout <= 4; MIE_EUNSUPPORTED elsewhere):
    * `in2` -- a second input field of the same shape, added to `in` as it is read (the skip sum in front of the
    *          prediction layer, incr_modules/e2depth_incr.py:430-434, without materialising it); its tile words go to

@@ -47,6 +47,7 @@ class ConvArgs(C.Structure):
         ("wpacked_tc", _vp),
         ("bias", _vp), ("refresh", _i),
         ("tail", _vp),
+        ("head", _vp),
         ("in2", _vp), ("in2_ps", _i64),
         ("accum", _vp), ("accum_ps", _i64),
     ]

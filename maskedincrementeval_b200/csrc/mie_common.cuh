@@ -275,7 +275,7 @@ constexpr int TAIL_MAX_TILES = MIE_TAIL_MAX_TILES;   // larger fields keep the s
 static __device__ __noinline__ void run_tail_job_last(const uint64_t *in_bits, int N, int Hin, int Win, int Hout, int Wout,
                                                       int k, int stride, int pad, const uint64_t *union_bits,
                                                       uint64_t *out_bits, int32_t *list, int32_t *stale, int32_t *counts,
-                                                      uint8_t *flags) {
+                                                      uint8_t *flags, bool clear_ticket) {
   const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
   for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
     flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
@@ -285,7 +285,55 @@ static __device__ __noinline__ void run_tail_job_last(const uint64_t *in_bits, i
   if (threadIdx.x == 0) {
     counts[0] = na;
     counts[1] = ns;
-    counts[2] = 0;
+    if (clear_ticket) counts[2] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Head job: a convolution's OWN tile dilation, run by block 0 of the convolution kernel while the other blocks of the
+// launch wait for it (mie_conv_args.head).  One launch instead of two, and no race: no block reads the lists, clears or
+// sets a tile word before block 0 has published them.  counts[2] carries the hand-over: bit 30 = "lists ready", the low
+// bits count the blocks that have left; the last one to leave puts the word back to 0 for the next launch.
+// All blocks of one launch are resident together or are dispatched in index order, so block 0 runs while the others
+// poll; the poll is bounded all the same (MIE_ERR_WAIT_EXPIRED, the layer is then treated as empty).
+// run_head_job(): every thread of every block, right after grid_dependency_wait() and before the first read of the
+// lists; returns false when the wait ran out.  finish_head_job(): every thread of every block, as the kernel's last
+// action before an optional tail job.
+// ---------------------------------------------------------------------------------------------
+constexpr int HEAD_READY = 1 << 30;
+
+__device__ __forceinline__ bool run_head_job(const mie_tail_job &j, unsigned spin_limit) {
+  if (j.list == nullptr) return true;     // uniform over the grid
+  if (blockIdx.x == 0) {
+    run_tail_job_last(j.in_bits, j.N, j.Hin, j.Win, j.Hout, j.Wout, j.k, j.stride, j.pad, j.union_bits, j.out_bits, j.list,
+                      j.stale, j.counts, j.flags, false);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicOr(&j.counts[2], HEAD_READY);
+    return true;
+  }
+  __shared__ int s_head_ok;
+  if (threadIdx.x == 0) {
+    int ok = 0;
+    for (unsigned it = 0; it < spin_limit && !ok; ++it) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(j.counts + 2) : "memory");
+      ok = (v & HEAD_READY) != 0;
+      if (!ok) __nanosleep(32);
+    }
+    if (!ok) atomicOr(&j.counts[3], MIE_ERR_WAIT_EXPIRED);
+    s_head_ok = ok;
+  }
+  __syncthreads();
+  return s_head_ok != 0;
+}
+
+__device__ __forceinline__ void finish_head_job(const mie_tail_job &j) {
+  if (j.list == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&j.counts[2], 1);
+    if ((old & (HEAD_READY - 1)) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) j.counts[2] = 0;   // every block has passed the wait
   }
 }
 
@@ -300,7 +348,7 @@ __device__ __forceinline__ void run_tail_job(const mie_tail_job &j) {
   if (!s_tail_last) return;
   __threadfence();
   run_tail_job_last(j.in_bits, j.N, j.Hin, j.Win, j.Hout, j.Wout, j.k, j.stride, j.pad, j.union_bits, j.out_bits, j.list,
-                    j.stale, j.counts, j.flags);
+                    j.stale, j.counts, j.flags, true);
 }
 
 // ---- host side of the tail job -----------------------------------------------------------------------------------
@@ -318,6 +366,16 @@ static inline int tail_check(const mie_tail_job *t, const void *produced_bits) {
   if (t->k < 1 || t->k > 7 || t->stride < 1 || t->stride > 2 || t->pad < 0 || t->pad > t->k) return MIE_EINVAL;
   if (t->out_bits && !t->stale) return MIE_EINVAL;
   if (static_cast<const void *>(t->in_bits) != produced_bits) return MIE_EINVAL;
+  return MIE_OK;
+}
+// A head job must fill exactly the lists the convolution call reads.
+static inline int head_check(const mie_tail_job *t, const mie_conv_args *a) {
+  if (!t) return MIE_OK;
+  if (tail_check(t, t->in_bits) != MIE_OK) return MIE_EINVAL;
+  if (t->list != a->list || t->counts != a->counts || t->stale != a->stale || t->out_bits != a->out_bits) return MIE_EINVAL;
+  if (t->N != a->n || t->Hin != a->hin || t->Win != a->win || t->Hout != a->hout || t->Wout != a->wout || t->k != a->k ||
+      t->stride != a->stride || t->pad != a->pad)
+    return MIE_EINVAL;
   return MIE_OK;
 }
 static inline mie_tail_job tail_for_kernel(const mie_tail_job *t) {

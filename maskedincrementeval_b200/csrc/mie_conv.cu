@@ -37,11 +37,13 @@ struct ConvParams {
   const float *bias;   // per output channel, added before the activation (dense evaluation only)
   int refresh;         // dense evaluation: the reservoir is set instead of advanced, the output is f(conv + bias)
   mie_tail_job tail;   // the next convolution's tile dilation, run by the last block (list == nullptr: none)
+  mie_tail_job head;   // this convolution's own tile dilation, run by block 0 while the others wait (list == nullptr: none)
   const float *in2; int64_t in2_ps;   // 1x1 head: second input, added on the fly
   float *accum; int64_t accum_ps;     // 1x1 head: accum += out at the sent pixels
 };
 
 constexpr int CC = 8;  // input channels per chunk
+constexpr unsigned HEAD_SPIN_LIMIT = 1u << 22;   // polls (32 ns apart) a block waits for block 0's tile lists
 
 template <int K, int S>
 struct Geo {
@@ -66,6 +68,7 @@ template <int K, int S, int WT, int WN, int CPT>
 __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles_kernel(const ConvParams p) {
   grid_dependency_wait();
   grid_dependency_trigger();
+  const bool head_ok = run_head_job(p.head, HEAD_SPIN_LIMIT);
   using G = Geo<K, S>;
   constexpr int NT = 32 * WT * WN;
   constexpr int NBW = 4 * CPT;          // channels per warp
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
 
   // ---- zero the tiles that held data last step and are inactive now ----------------------------
   {
-    const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
+    const int n_stale = (p.stale && head_ok) ? min(p.counts[1], p.max_tiles) : 0;
     for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
       const int t = p.stale[s];
       if (t < 0 || t >= ntiles_total) { if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
@@ -99,7 +102,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
     }
   }
 
-  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
   const int n_groups = (n_active + WT - 1) / WT;
   const int n_cblk = p.cout_pad / NB;
   const int n_items = n_groups * n_cblk;
@@ -366,6 +369,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
   }
+  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -389,7 +393,8 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
   const int THo = (p.hout + 7) >> 3, TWo = (p.wout + 7) >> 3;
   const int ntiles_total = p.n * THo * TWo;
   unsigned *bits32 = reinterpret_cast<unsigned *>(p.out_bits);
-  const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
+  const bool head_ok = run_head_job(p.head, HEAD_SPIN_LIMIT);
+  const int n_stale = (p.stale && head_ok) ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x * 4 + grp; s < n_stale; s += gridDim.x * 4) {
     const int t = p.stale[s];
     if (t < 0 || t >= ntiles_total) { if (px == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
@@ -398,7 +403,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
     if (oy < p.hout && ox < p.wout)
       for (int c = 0; c < p.cout; ++c) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
   }
-  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
   for (int li = blockIdx.x * 4 + grp; li < n_active; li += gridDim.x * 4) {
     const int t = p.list[li];
     if (t < 0 || t >= ntiles_total) { if (px == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
@@ -472,6 +477,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
     const unsigned half = __ballot_sync(0xffffffffu, flag);
     if (lane == 0 && half) bits32[2 * (size_t)t + ((px >> 5) & 1)] = half;
   }
+  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -563,7 +569,16 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (a->stride < 1 || a->stride > 2) return MIE_EUNSUPPORTED;
   if (!aligned16(a->wpacked)) return MIE_EALIGN;
   if (a->wpacked_tc && !aligned16(a->wpacked_tc)) return MIE_EALIGN;
-  if (tail_check(a->tail, a->out_bits) != MIE_OK) return MIE_EINVAL;
+  if (tail_check(a->tail, a->out_bits) != MIE_OK || head_check(a->head, a) != MIE_OK) return MIE_EINVAL;
+  if (a->head && !tail_fits(a->head)) {   // too many tiles for one block: the separate launch, then a plain convolution
+    const mie_tail_job *h = a->head;
+    const int s = mie_tiles_dilate(h->in_bits, h->N, h->Hin, h->Win, h->Hout, h->Wout, h->k, h->stride, h->pad, h->union_bits,
+                                   h->out_bits, h->list, h->stale, h->counts, h->flags, stream);
+    if (s != MIE_OK) return s;
+    mie_conv_args b = *a;
+    b.head = nullptr;
+    return mie_conv_tiles(&b, stream);
+  }
   if (tc_eligible(a)) return tail_after_launch(launch_conv_tc(a, (cudaStream_t)stream), a->tail, true, stream);
 
   ConvParams p;
@@ -577,6 +592,7 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   p.addend = a->addend; p.addend_ps = a->addend_ps;
   p.bias = a->bias; p.refresh = a->refresh ? 1 : 0;
   p.tail = tail_for_kernel(a->tail);
+  p.head = tail_for_kernel(a->head);
   p.in2 = a->in2; p.in2_ps = a->in2_ps; p.accum = a->accum; p.accum_ps = a->accum_ps;
   if (a->in2 && a->in2_ps < a->cin) return MIE_EINVAL;
   if (a->accum && (a->accum_ps < a->cout || a->refresh)) return MIE_EINVAL;

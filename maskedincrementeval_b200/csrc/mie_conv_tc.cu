@@ -48,6 +48,7 @@ struct TcParams {
   unsigned spin_limit;   // iterations after which a barrier wait gives up (MIE_OPT_TC_SPIN_LIMIT)
   int withhold_loads;    // self-test: the producers issue nothing, so the first wait runs out (MIE_OPT_TC_WITHHOLD_LOADS)
   mie_tail_job tail;     // the next convolution's tile dilation, run by the last block (list == nullptr: none)
+  mie_tail_job head;     // this convolution's own tile dilation, run by block 0 while the others wait (list == nullptr: none)
   int ksplit;            // halo kernel: CTAs of a cluster that share one work item, each reducing 1/ksplit of the
                          // input-channel chunks (1: no cluster)
 };
@@ -629,6 +630,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
+  const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
   // the halo producer asks for the tile-list entries of its first item together with the device-side count
   const int n_cblk = p.cout_pad / NB;
   int pre0 = -1, pre1 = -1;
@@ -637,7 +639,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     if (e < p.max_tiles) pre0 = p.list[e];
     if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
   }
-  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
   if (tid == 0) TC_TRACE(2);
 
   if (tid == 0) TC_TRACE(3);
@@ -779,7 +781,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
     const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
-    tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
+    if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
     unsigned item_idx = 0;
     for (int item = bid; item < n_items; item += nblk, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
@@ -846,6 +848,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
+  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -906,6 +909,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
+  const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
   // The producer asks for the tile-list entries of its first item together with the device-side count, before the count
   // is known: one round trip to memory instead of two on the path count -> list -> first operand load.
   const int n_cblk = p.cout_pad / NB;
@@ -915,7 +919,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     if (e < p.max_tiles) pre0 = p.list[e];
     if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
   }
-  const int n_active = min(p.counts[0], p.max_tiles);
+  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
   if (tid == 0) TC_TRACE(2);
 
   if (tid == 0) TC_TRACE(3);
@@ -1020,7 +1024,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
-    tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
+    if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
     unsigned item_idx = 0;
     for (int item = bid; item < n_items; item += nblk, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
@@ -1079,6 +1083,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
+  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -1276,6 +1281,7 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.act = a->act; p.thr = a->thr; p.res = a->res; p.res_ps = a->res_ps;
   p.emitted = a->emitted; p.emitted_ps = a->emitted_ps; p.addend = a->addend; p.addend_ps = a->addend_ps;
   p.tail = tail_for_kernel(a->tail);
+  p.head = tail_for_kernel(a->head);
   p.ksplit = 1;
   int nb, ksplit;
   tc_block_shape(a, &nb, &ksplit);

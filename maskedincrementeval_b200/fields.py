@@ -49,6 +49,10 @@ class IncrConfig:
     tail_dilation    True: a convolution's tile dilation rides in the tail of the kernel that produces its input mask
                      (one launch less per convolution; measured slower than the separate launch when launches overlap
                      through programmatic dependent launch, so it is off by default); False: separate launch
+    head_dilation    largest number of output tiles (at most 2048, the library's limit; default 0: never) up to which a
+                     convolution's tile dilation runs inside the convolution kernel itself -- its first thread block
+                     makes the lists while the others wait -- instead of as a launch of its own (22 launches per E2Depth
+                     step instead of 37, measured slower: the hand-over costs more than the launch it saves)
     fuse_accumulate  True (default): IncrementalRunner lets a 1x1 prediction head add its output into the accumulated
                      prediction inside its own kernel instead of launching mie_accumulate afterwards
     tc_thresholded   True (default): thresholded convolutions (threshold > 0, with or without carry) use the tensor
@@ -61,6 +65,7 @@ class IncrConfig:
     tensor_cores: str = "auto"   # "auto": tcgen05/TF32 for convolutions with Cin*k*k >= 256; "off": FP32 everywhere
     tc_thresholded: bool = True
     tail_dilation: bool = False
+    head_dilation: int = 0
     fuse_accumulate: bool = True
     kfenced_step: Optional[float] = None
     refresh: str = "native"

@@ -435,7 +435,10 @@ class nnConvIncr(nn.Conv2d):
         if plan.needs_clear:
             plan.out.zero_(), plan.out_bits.zero_(), plan.counts[:3].zero_()
             plan.needs_clear = False
-        if not fl.tail_carried(job):
+        a.head = None
+        if config.head_dilation and plan.ntiles <= min(config.head_dilation, nat.TAIL_MAX_TILES) and not config.tail_dilation:
+            a.head = C.addressof(job.c)     # the convolution kernel's first block makes the lists itself
+        elif not fl.tail_carried(job):
             nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), n, hin, win, plan.hout, plan.wout, self._k, self._s,
                                                self._p, union.data_ptr() if union is not None else None,
                                                plan.out_bits.data_ptr(), plan.list.data_ptr(), plan.stale.data_ptr(),

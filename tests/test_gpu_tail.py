@@ -27,7 +27,7 @@ def dev():
 @pytest.fixture(autouse=True)
 def restore_config():
     from maskedincrementeval_b200 import fields as fl
-    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tail_dilation", "compat")}
+    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tail_dilation", "head_dilation", "compat")}
     yield
     for k, v in saved.items():
         setattr(fl.config, k, v)
@@ -208,6 +208,7 @@ def test_convolution_kernels_carry_the_dilation(dev, cfg):
     g = torch.Generator().manual_seed(11)
     n, h, w = 1, 48, 72
     outs, counts = [], []
+    fl.config.head_dilation = 0          # compare with the separate launch, not with the in-kernel dilation
     for tails in (True, False):
         fl.config.tail_dilation = tails
         torch.manual_seed(0)
@@ -242,6 +243,7 @@ def test_network_step_is_bit_identical_and_shorter(dev):
            "num_residual_blocks": 2, "use_upsample_conv": True, "norm": "none"}
     frames = [f.to(dev) for f in voxel_sequence(1, 128, 160, 8, 4000, 6, seed=3)]
     fl.config.compat = "exact"
+    fl.config.head_dilation = 0
     results, launches = [], []
     for tails in (True, False):
         fl.config.tail_dilation = tails
@@ -321,3 +323,96 @@ def test_feedback_runner_with_changing_inputs_is_bit_identical(dev):
         outs.append(ys)
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------------------------------------
+# head jobs: the convolution kernel's first block runs the convolution's own dilation
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cfg", [("off", 16, 32, 3, 1), ("auto", 32, 32, 3, 1), ("auto", 64, 64, 3, 1), ("auto", 32, 64, 5, 2),
+                                 ("off", 32, 1, 1, 1), ("auto", 256, 256, 3, 1), ("auto", 128, 256, 5, 2)])
+def test_convolution_kernels_run_their_own_dilation(dev, cfg):
+    """FP32, 1x1, per-tap, halo and both cluster kernels: identical output bits with the dilation inside the kernel and
+    as a launch of its own, over steps in which tiles go stale; one launch less per layer."""
+    from maskedincrementeval_b200 import _native as nat, fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    from maskedincrementeval_b200.incr_modules.mask_incr_modules import check_device_errors
+    mode, cin, cout, k, s = cfg
+    fl.config.tensor_cores = mode
+    n, h, w = 1, 34, 44
+    outs, counts = [], []
+    for head in (2048, 0):
+        fl.config.head_dilation = head
+        torch.manual_seed(0)
+        layer = ConvLayerIncr(cin, cout, k, s, k // 2, activation="relu").to(dev).eval()
+        gg = torch.Generator().manual_seed(5)
+        x0 = cl(torch.randn(n, cin, h, w, generator=gg), dev)
+        res = []
+        with torch.no_grad():
+            layer.forward_refresh_reservoirs(x0)
+            for step in range(5):
+                d = cl(sparse(gg, (n, cin, h, w), [0.02, 0.3, 0.0, 0.01, 1.0][step]), dev)
+                m = fl.mask_from_delta(d)
+                nat.reset_launch_count()
+                y = layer([d, m])
+                counts.append(nat.launch_count())
+                res.append((y[0].clone(), y[1].bits.clone()))
+            check_device_errors(layer)
+        outs.append(res)
+    for (ya, ba), (yb, bb) in zip(*outs):
+        assert torch.equal(ya, yb) and torch.equal(ba, bb)
+    assert counts[:5] == [1] * 5 and counts[5:] == [2] * 5, counts
+
+
+def test_head_job_must_describe_the_call(dev):
+    """A head job whose lists or geometry are not the convolution's own is refused before anything is launched."""
+    import ctypes as C
+    from maskedincrementeval_b200 import _native as nat, fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import ConvLayerIncr
+    fl.config.tensor_cores = "off"
+    torch.manual_seed(0)
+    layer = ConvLayerIncr(16, 32, 3, 1, 1, activation=None).to(dev).eval()
+    g = torch.Generator().manual_seed(1)
+    d = cl(sparse(g, (1, 16, 24, 32), 0.05), dev)
+    with torch.no_grad():
+        layer.forward_refresh_reservoirs(cl(torch.randn(1, 16, 24, 32, generator=g), dev))
+        layer([d, None])
+    plan = next(iter(layer.conv2d._plans.values()))
+    a = plan.args
+    other = torch.zeros_like(plan.list)
+    bad = nat.TailJob(plan.tail.c.in_bits, 1, 24, 32, 24, 32, 3, 1, 1, None, plan.out_bits.data_ptr(), other.data_ptr(),
+                      plan.stale.data_ptr(), plan.counts.data_ptr(), plan.flags.data_ptr())
+    a.head = C.addressof(bad)
+    assert nat.lib.mie_conv_tiles(C.byref(a), nat.stream_ptr(dev)) == nat.EINVAL
+    a.head = None
+    torch.cuda.synchronize()
+
+
+def test_network_step_with_in_kernel_dilation(dev):
+    """E2Depth at 128x160 through the runner: the same accumulated output to the bit, 15 launches fewer per step."""
+    from maskedincrementeval_b200 import _native as nat, fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+    cfg = {"num_bins": 5, "skip_type": "sum", "recurrent_block_type": "convlstm", "num_encoders": 3, "base_num_channels": 32,
+           "num_residual_blocks": 2, "use_upsample_conv": True, "norm": "none"}
+    frames = [f.to(dev) for f in voxel_sequence(1, 128, 160, 10, 4000, 6, seed=3)]
+    fl.config.compat = "exact"
+    results, launches = [], []
+    for head in (2048, 0):
+        fl.config.head_dilation = head
+        net = E2VIDRecurrentIncr(dict(cfg)).to(dev).eval()
+        shapes = {k_: tuple(v.shape) for k_, v in net.state_dict().items()}
+        net.load_state_dict(seeded_state_dict(shapes, seed=1))
+        run = IncrementalRunner(net, use_graph=True, refresh_every=7)
+        with torch.no_grad():
+            run.refresh(frames[0])
+            run.step(frames[1])
+            nat.reset_launch_count()
+            run.step(frames[2])
+            launches.append(nat.launch_count())
+            ys = [run.step(f).clone() for f in frames[3:]]
+            run.check()
+        results.append(ys)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert launches[0] == launches[1] - 15, launches
