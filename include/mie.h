@@ -6,8 +6,10 @@
  * reference runs around it (incr_modules/mask_incr_functional.py, incr_modules/mask_incr_modules.py).
  *
  * Conventions shared by every entry point
- *  - every pointer is a DEVICE pointer unless its comment says "host"; the library allocates
- *    nothing, owns nothing and keeps no state between calls (one exception is declared as such);
+ *  - every pointer is a DEVICE pointer unless its comment says "host"; the library allocates no device
+ *    memory and owns none (one exception is declared as such); what it keeps between calls never shows in a
+ *    result: the process-wide options of mie_set_option, a launch counter, a per-thread cache of encoded tensor
+ *    maps, and which devices have had a kernel's shared-memory limit raised;
  *  - tensors are fp32, NCHW-logical and channels-last in memory: element (n,y,x,c) of a field lives
  *    at base[((n*H + y)*W + x)*ps + c]; `ps` (pixel stride, in floats) >= C lets a field be a channel
  *    slice of a wider buffer;
