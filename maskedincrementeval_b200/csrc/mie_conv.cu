@@ -570,7 +570,10 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   if (!aligned16(a->wpacked)) return MIE_EALIGN;
   if (a->wpacked_tc && !aligned16(a->wpacked_tc)) return MIE_EALIGN;
   if (tail_check(a->tail, a->out_bits) != MIE_OK || head_check(a->head, a) != MIE_OK) return MIE_EINVAL;
-  if (a->head && !tail_fits(a->head)) {   // too many tiles for one block: the separate launch, then a plain convolution
+  // Too many tiles for one block, or a cluster kernel (its blocks decide together, from the item count, whether to meet
+  // at the closing cluster barrier: a block whose wait for the lists ran out would count differently): the separate
+  // launch, then a plain convolution.
+  if (a->head && (!tail_fits(a->head) || mie_conv_cluster_size(a) > 1)) {
     const mie_tail_job *h = a->head;
     const int s = mie_tiles_dilate(h->in_bits, h->N, h->Hin, h->Win, h->Hout, h->Wout, h->k, h->stride, h->pad, h->union_bits,
                                    h->out_bits, h->list, h->stale, h->counts, h->flags, stream);

@@ -836,8 +836,9 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   tc_fence_before();
   __syncthreads();
   // K-split: no CTA leaves while another one of its cluster may still store into its shared memory or arrive on its
-  // barrier (every wait above is bounded, so every CTA gets here)
-  if (CS > 1u) cluster_sync_all();
+  // barrier (every wait above is bounded, so every CTA gets here).  A cluster without an item exchanges nothing; all
+  // of its CTAs see the same item count, so they skip the barrier together.
+  if (CS > 1u && bid < n_items) cluster_sync_all();
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
@@ -1071,7 +1072,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __syncwarp();  // single-lane roles: the whole warp reaches the block-wide barrier together
   tc_fence_before();
   __syncthreads();
-  if (CS > 1u) cluster_sync_all();   // K-split: no block leaves while another may still store into its shared memory
+  if (CS > 1u && bid < n_items) cluster_sync_all();   // K-split: no block leaves while another may still store into its shared memory
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     // give copies that may still be in flight time to land before shared memory is released
