@@ -274,6 +274,15 @@ __device__ __forceinline__ bool bit_at(const uint64_t *bits, int n, int y, int x
 // the index arithmetic of torch's bilinear interpolation with align_corners=False
 __device__ __forceinline__ void up_src(int o, int L, int mode, int scale, float rs, int &i0, int &i1, float &w1) {
   if (mode == MIE_UP_NEAREST) { i0 = i1 = o / scale; w1 = 0.0f; return; }
+  if (scale == 2) {
+    // closed form of the lines below for scale 2 (0.5 * (o + 0.5) - 0.5 = o / 2 - 0.25 is exact in fp32): the same
+    // indices and the same weights 0.75 / 0.25, without the conversions
+    const int i = o >> 1;
+    if (o & 1) { i0 = i; i1 = min(i + 1, L - 1); w1 = 0.25f; }
+    else if (i == 0) { i0 = i1 = 0; w1 = 0.0f; }
+    else { i0 = i - 1; i1 = i; w1 = 0.75f; }
+    return;
+  }
   float s = rs * (o + 0.5f) - 0.5f;
   if (s < 0.0f) s = 0.0f;
   i0 = (int)s;
@@ -908,7 +917,7 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_tile_kernel(
     }
     __syncthreads();
     for (int e = tid; e < 64 * q4; e += blockDim.x) {
-      const int p = e / q4, q = e - p * q4;
+      const int p = (q4 == 8) ? (e >> 3) : e / q4, q = e - p * q4;   // full 32-channel blocks: no division
       if (!pix_valid(g, p)) continue;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if ((wout >> p) & 1ull) {
