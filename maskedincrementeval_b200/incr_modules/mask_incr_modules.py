@@ -410,7 +410,7 @@ class nnConvIncr(nn.Conv2d):
         if second is not None:
             # the sum x + second is formed as the 1x1 head kernel reads its input; the second mask joins the tile set
             # as the dilation's union mask (output geometry = input geometry for a 1x1 convolution)
-            if not self.takes_second_input() or addend is not None or split or config.kfenced_step:
+            if not self.takes_second_input() or addend is not None or split or (config.kfenced_step and not refresh):
                 raise RuntimeError("a second input needs a plain 1x1 prediction head")
             d2, m2 = fl.resolve(second, sc, "in2")
             if d2.shape != d.shape:

@@ -126,3 +126,33 @@ def test_input_delta_kernel_writes_the_split_copy(dev):
         assert torch.equal(dxs[0], dxs[1]) and torch.equal(bits[0], bits[1])
         assert torch.equal(copies[0], copies[1]) and torch.equal(cbits[0], cbits[1])
     assert float(copies[0].abs().max()) == 0.0     # the last step had no change anywhere
+
+
+def test_quantiser_in_front_of_the_head_falls_back_to_the_sum(dev):
+    """With the k-fenced quantiser switched on the prediction head takes the explicit sum (the quantiser acts on one
+    input delta), the dense pass on the kernels still adds the second input on the fly; the network runs and tracks."""
+    from maskedincrementeval_b200 import fields as fl
+    from maskedincrementeval_b200.incr_modules.e2depth_incr import E2VIDRecurrentIncr
+    from maskedincrementeval_b200.runtime import IncrementalRunner
+    from maskedincrementeval_b200.synthetic import seeded_state_dict, voxel_sequence
+    cfg = {"num_bins": 5, "skip_type": "sum", "recurrent_block_type": "convlstm", "num_encoders": 3, "base_num_channels": 8,
+           "num_residual_blocks": 2, "use_upsample_conv": True, "norm": "none"}
+    frames = [f.to(dev) for f in voxel_sequence(1, 64, 96, 5, 2000, 4, seed=3)]
+    fl.config.compat = "exact"
+    old = fl.config.kfenced_step
+    fl.config.kfenced_step = 1e-4
+    try:
+        net = E2VIDRecurrentIncr(dict(cfg)).to(dev).eval()
+        shapes = {k_: tuple(v.shape) for k_, v in net.state_dict().items()}
+        net.load_state_dict(seeded_state_dict(shapes, seed=1))
+        run = IncrementalRunner(net, use_graph=False)
+        with torch.no_grad():
+            run.refresh(frames[0])
+            for f in frames[1:]:
+                y = run.step(f)
+            fl.config.kfenced_step = None
+            yd = net.forward_refresh_reservoirs(frames[-1], None)[0]
+        rng = float(yd.max() - yd.min())
+        assert float((y - yd).abs().max()) <= 2e-2 * rng
+    finally:
+        fl.config.kfenced_step = old
