@@ -1230,7 +1230,9 @@ static void tc_block_shape(const mie_conv_args *a, int *nb_out, int *ksplit_out)
   // could not keep about half of the SMs busy even at full activity -- the small-image layers of a UNet have
   // a few dozen tiles but thousands of reduction steps.  Measured on B200: a pipeline stage costs about
   // 0.6 us whatever its width, so narrowing pays only until the work items cover the machine once.
-  int nb = 256;
+  // MIE_TC_NB_MAX in the environment caps the block width (A/B measurements)
+  static const int nb_max = []() { const char *e = getenv("MIE_TC_NB_MAX"); const int x = e ? atoi(e) : 0; return (x == 32 || x == 64 || x == 128) ? x : 256; }();
+  int nb = nb_max;
   while (nb > 16 && a->cout_pad % nb) nb >>= 1;
   const int64_t pairs = (a->max_tiles + 1) / 2;
   while (nb > 32 && a->cout_pad % (nb / 2) == 0 && pairs * (a->cout_pad / nb) < 64) nb >>= 1;
