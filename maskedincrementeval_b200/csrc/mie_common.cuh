@@ -276,12 +276,16 @@ static __device__ __noinline__ void run_tail_job_last(const uint64_t *in_bits, i
                                                       int k, int stride, int pad, const uint64_t *union_bits,
                                                       uint64_t *out_bits, int32_t *list, int32_t *stale, int32_t *counts,
                                                       uint8_t *flags, bool clear_ticket) {
+  // the per-tile flags stay in shared memory (at most TAIL_MAX_TILES of them: the host sends larger fields to the
+  // separate launch); `flags` is the global scratch of that launch and is not touched here
+  (void)flags;
+  __shared__ uint8_t s_tile_flags[TAIL_MAX_TILES];
   const int ntiles = N * ((Hout + 7) >> 3) * ((Wout + 7) >> 3);
   for (int t = threadIdx.x; t < ntiles; t += blockDim.x)
-    flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
+    s_tile_flags[t] = dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits);
   __syncthreads();
   int na, ns;
-  block_ordered_compact2([&](int i) { return (int)__ldcg(flags + i); }, ntiles, list, stale, &na, &ns);
+  block_ordered_compact2([&](int i) { return (int)s_tile_flags[i]; }, ntiles, list, stale, &na, &ns);
   if (threadIdx.x == 0) {
     counts[0] = na;
     counts[1] = ns;
@@ -297,8 +301,7 @@ static __device__ __noinline__ void run_tail_job_last(const uint64_t *in_bits, i
 // All blocks of one launch are resident together or are dispatched in index order, so block 0 runs while the others
 // poll; the poll is bounded all the same (MIE_ERR_WAIT_EXPIRED, the layer is then treated as empty).
 // run_head_job(): every thread of every block, right after grid_dependency_wait() and before the first read of the
-// lists; returns false when the wait ran out.  finish_head_job(): every thread of every block, as the kernel's last
-// action before an optional tail job.
+// lists; returns false when the wait ran out.  count_head_job_passed(): one thread of every block, any time after.
 // ---------------------------------------------------------------------------------------------
 constexpr int HEAD_READY = 1 << 30;
 
@@ -307,9 +310,13 @@ __device__ __forceinline__ bool run_head_job(const mie_tail_job &j, unsigned spi
   if (blockIdx.x == 0) {
     run_tail_job_last(j.in_bits, j.N, j.Hin, j.Win, j.Hout, j.Wout, j.k, j.stride, j.pad, j.union_bits, j.out_bits, j.list,
                       j.stale, j.counts, j.flags, false);
-    __threadfence();
+    // block barrier, then one fence and the flag by one thread: the fence is cumulative over what the barrier ordered
+    // before it (the hand-over a grid-wide barrier uses)
     __syncthreads();
-    if (threadIdx.x == 0) atomicOr(&j.counts[2], HEAD_READY);
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicOr(&j.counts[2], HEAD_READY);
+    }
     return true;
   }
   __shared__ int s_head_ok;
@@ -319,7 +326,7 @@ __device__ __forceinline__ bool run_head_job(const mie_tail_job &j, unsigned spi
       int v;
       asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(j.counts + 2) : "memory");
       ok = (v & HEAD_READY) != 0;
-      if (!ok) __nanosleep(32);
+      if (!ok) __nanosleep(128);   // a hundred-odd blocks poll one word that shares its line with the counts block 0 writes
     }
     if (!ok) atomicOr(&j.counts[3], MIE_ERR_WAIT_EXPIRED);
     s_head_ok = ok;
@@ -328,13 +335,13 @@ __device__ __forceinline__ bool run_head_job(const mie_tail_job &j, unsigned spi
   return s_head_ok != 0;
 }
 
-__device__ __forceinline__ void finish_head_job(const mie_tail_job &j) {
+// Counts this block among those that have passed the wait; the last one puts the word back to 0 for the next launch
+// (nobody polls it any more).  Called once per block by ONE thread that is off the block's critical path -- the
+// atomic's round trip then overlaps the block's work instead of delaying its exit.
+__device__ __forceinline__ void count_head_job_passed(const mie_tail_job &j) {
   if (j.list == nullptr) return;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int old = atomicAdd(&j.counts[2], 1);
-    if ((old & (HEAD_READY - 1)) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) j.counts[2] = 0;   // every block has passed the wait
-  }
+  const int old = atomicAdd(&j.counts[2], 1);
+  if ((old & (HEAD_READY - 1)) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) j.counts[2] = 0;
 }
 
 __device__ __forceinline__ void run_tail_job(const mie_tail_job &j) {

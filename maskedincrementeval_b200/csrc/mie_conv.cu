@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
   grid_dependency_wait();
   grid_dependency_trigger();
   const bool head_ok = run_head_job(p.head, HEAD_SPIN_LIMIT);
+  if (threadIdx.x == blockDim.x - 1) count_head_job_passed(p.head);
   using G = Geo<K, S>;
   constexpr int NT = 32 * WT * WN;
   constexpr int NBW = 4 * CPT;          // channels per warp
@@ -369,7 +370,6 @@ __global__ void __launch_bounds__(32 * WT * WN, 512 / (32 * WT * WN)) conv_tiles
       }
     }
   }
-  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -394,6 +394,7 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
   const int ntiles_total = p.n * THo * TWo;
   unsigned *bits32 = reinterpret_cast<unsigned *>(p.out_bits);
   const bool head_ok = run_head_job(p.head, HEAD_SPIN_LIMIT);
+  if (threadIdx.x == blockDim.x - 1) count_head_job_passed(p.head);
   const int n_stale = (p.stale && head_ok) ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x * 4 + grp; s < n_stale; s += gridDim.x * 4) {
     const int t = p.stale[s];
@@ -477,7 +478,6 @@ __global__ void __launch_bounds__(256) conv1x1_small_kernel(const ConvParams p) 
     const unsigned half = __ballot_sync(0xffffffffu, flag);
     if (lane == 0 && half) bits32[2 * (size_t)t + ((px >> 5) & 1)] = half;
   }
-  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 

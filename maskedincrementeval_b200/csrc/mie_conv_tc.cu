@@ -631,6 +631,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   grid_dependency_wait();
   grid_dependency_trigger();
   const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
+  if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
   // the halo producer asks for the tile-list entries of its first item together with the device-side count
   const int n_cblk = p.cout_pad / NB;
   int pre0 = -1, pre1 = -1;
@@ -849,7 +850,6 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
-  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 
@@ -911,6 +911,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   grid_dependency_wait();
   grid_dependency_trigger();
   const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
+  if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
   // The producer asks for the tile-list entries of its first item together with the device-side count, before the count
   // is known: one round trip to memory instead of two on the path count -> list -> first operand load.
   const int n_cblk = p.cout_pad / NB;
@@ -1084,7 +1085,6 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
   if (tid == 0) { TC_TRACE(12); TC_TRACE_G(15); TC_TRACE_V(13, (long long)n_items); }
-  finish_head_job(p.head);
   run_tail_job(p.tail);
 }
 

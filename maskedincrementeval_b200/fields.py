@@ -51,7 +51,7 @@ class IncrConfig:
                      through programmatic dependent launch, so it is off by default); False: separate launch
     head_dilation    largest number of output tiles (at most 2048, the library's limit; default 0: never) up to which a
                      convolution's tile dilation runs inside the convolution kernel itself -- its first thread block
-                     makes the lists while the others wait -- instead of as a launch of its own (22 launches per E2Depth
+                     makes the lists while the others wait -- instead of as a launch of its own (28 launches per E2Depth
                      step instead of 37, measured slower: the hand-over costs more than the launch it saves)
     fuse_accumulate  True (default): IncrementalRunner lets a 1x1 prediction head add its output into the accumulated
                      prediction inside its own kernel instead of launching mie_accumulate afterwards
