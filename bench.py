@@ -516,6 +516,8 @@ def run_ours(args):
     mie.config.tc_thresholded = bool(args.tc_thresholded)
     mie.config.tail_dilation = bool(args.tail_dilation)
     mie.config.head_dilation = int(args.head_dilation)
+    if args.own_tiles is not None:
+        mie.config.own_tiles = bool(args.own_tiles)
     from maskedincrementeval_b200 import _native as _nat
     _nat.set_option(_nat.OPT_TC_KSPLIT, 1 if args.ksplit else 0)
     streams = args.streams
@@ -910,6 +912,9 @@ def main():
     ap.add_argument("--ksplit", action=argparse.BooleanOptionalAction, default=True,
                     help="small-image tensor-core layers run as clusters that split the input channels (default); "
                          "--no-ksplit keeps one thread block per work item")
+    ap.add_argument("--own-tiles", action=argparse.BooleanOptionalAction, default=None,
+                    help="tensor-core convolutions find their active tiles themselves instead of reading a list made by "
+                         "a dilation launch in front of them (default: the library's setting)")
     ap.add_argument("--head-dilation", type=int, default=0,
                     help="largest number of output tiles up to which a convolution runs its own tile dilation inside its "
                          "kernel (first block makes the lists, the others wait); 0 = separate launches (default)")

@@ -65,7 +65,11 @@ enum {
   /* 1 (default): small-image layers with long reductions run the tensor-core kernel as clusters of 2 or 4 thread
    * blocks that split the input channels of a work item and exchange partial sums through distributed shared
    * memory; 0: one thread block per work item */
-  MIE_OPT_TC_KSPLIT = 5
+  MIE_OPT_TC_KSPLIT = 5,
+  /* which tensor-core kernels honour mie_conv_args.own_tiles, as a bit mask: 1 the per-tap kernel, 2 the per-tap kernel as
+   * clusters, 4 the halo kernel, 8 the halo kernel as clusters; the others get the separate dilation launch from the
+   * entry point.  Default 7: the clustered halo kernel measured slower with the mode than without */
+  MIE_OPT_TC_OWN_KERNELS = 6
 };
 int mie_set_option(int option, int value);
 int mie_get_option(int option, int *value /* host */);
@@ -210,6 +214,19 @@ typedef struct mie_conv_args {
    *          `c += c_incr[0]`, run_e2depth_continuous_dataset.py:74, without a separate pass); not in dense evaluation. */
   const float *in2; int64_t in2_ps;
   float *accum; int64_t accum_ps;
+  /* `own_tiles` non-zero, together with `head`: no global tile list is made at all.  The thread blocks of the
+   * convolution kernel share out the output tiles statically (tile pairs dealt round-robin); each block tests the
+   * tiles it owns against the input words itself (the same test as mie_tiles_dilate), compacts the active ones into a
+   * list in its shared memory and works through that; the block that owns a tile zeroes it when it is stale.  One
+   * launch instead of two and no hand-over between blocks; at full activity the work is spread exactly as with the
+   * global list.  `list`, `stale` and counts[0..2] are neither read nor written (counts[3] still collects errors).
+   * A tile that several blocks work on (column blocks, clusters) gets its word through `own_scratch`: 12 bytes per output
+   * tile, 8-byte aligned, zero on entry and zero again on exit (8 bytes in which the blocks OR their pixels + a ticket;
+   * the last block to contribute stores the word).  Convolutions that run on the FP32 kernels or on a kernel that
+   * MIE_OPT_TC_OWN_KERNELS leaves out, and fields with more than 256 tiles per thread block, get the separate
+   * mie_tiles_dilate launch from the entry point instead. */
+  int own_tiles;
+  void *own_scratch;
 } mie_conv_args;
 
 int mie_conv_tiles(const mie_conv_args *args /* host */, void *stream);

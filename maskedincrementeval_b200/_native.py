@@ -18,7 +18,7 @@ OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ETOOBIG = 0, -1, -2, -3, -4, -5
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 UP_BILINEAR, UP_NEAREST = 0, 1
 ERR_BAD_TILE, ERR_WAIT_EXPIRED = 1, 2
-OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS, OPT_LAUNCH_COUNT, OPT_TC_KSPLIT = 1, 2, 3, 4, 5
+OPT_TC_THRESHOLDED, OPT_TC_SPIN_LIMIT, OPT_TC_WITHHOLD_LOADS, OPT_LAUNCH_COUNT, OPT_TC_KSPLIT, OPT_TC_OWN_KERNELS = 1, 2, 3, 4, 5, 6
 TAIL_MAX_TILES = 2048     # MIE_TAIL_MAX_TILES
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -50,6 +50,7 @@ class ConvArgs(C.Structure):
         ("head", _vp),
         ("in2", _vp), ("in2_ps", _i64),
         ("accum", _vp), ("accum_ps", _i64),
+        ("own_tiles", _i), ("own_scratch", _vp),
     ]
 
 

@@ -200,10 +200,11 @@ __device__ __forceinline__ unsigned feed_set(int o0, int cnt, int k, int stride,
 }
 
 // 0: inactive, 1: active, 2: inactive now but the output tile holds data from the previous step (stale).
-// Also clears the output word.
+// Also clears the output word (clear_active = false: only that of a stale tile; the word of an active tile is then
+// stored, not ORed into, by whoever finishes the tile).
 __device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *in_bits, int Hin, int Win, int Hout,
                                                int Wout, int k, int stride, int pad,
-                                               const uint64_t *union_bits, uint64_t *out_bits) {
+                                               const uint64_t *union_bits, uint64_t *out_bits, bool clear_active = true) {
   const int THi = (Hin + 7) >> 3, TWi = (Win + 7) >> 3;
   const int THo = (Hout + 7) >> 3, TWo = (Wout + 7) >> 3;
   const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
@@ -255,7 +256,7 @@ __device__ __forceinline__ uint8_t dilate_flag(int t, const uint64_t *in_bits, i
   uint8_t f = active ? 1 : 0;
   if (out_bits) {
     if (!active && prev != 0ull) f = 2;
-    if (prev != 0ull) out_bits[t] = 0ull;
+    if (prev != 0ull && (clear_active || !active)) out_bits[t] = 0ull;
   }
   return f;
 }

@@ -573,13 +573,16 @@ extern "C" int mie_conv_tiles(const mie_conv_args *a, void *stream) {
   // Too many tiles for one block, or a cluster kernel (its blocks decide together, from the item count, whether to meet
   // at the closing cluster barrier: a block whose wait for the lists ran out would count differently): the separate
   // launch, then a plain convolution.
-  if (a->head && (!tail_fits(a->head) || mie_conv_cluster_size(a) > 1)) {
+  if (a->own_tiles && (!a->head || !a->own_scratch || (reinterpret_cast<uintptr_t>(a->own_scratch) & 7))) return MIE_EINVAL;
+  // own-tiles mode exists in the tensor-core kernels only; elsewhere it is the separate launch and a plain convolution
+  if (a->head && (a->own_tiles ? !tc_eligible(a) : (!tail_fits(a->head) || mie_conv_cluster_size(a) > 1))) {
     const mie_tail_job *h = a->head;
     const int s = mie_tiles_dilate(h->in_bits, h->N, h->Hin, h->Win, h->Hout, h->Wout, h->k, h->stride, h->pad, h->union_bits,
                                    h->out_bits, h->list, h->stale, h->counts, h->flags, stream);
     if (s != MIE_OK) return s;
     mie_conv_args b = *a;
     b.head = nullptr;
+    b.own_tiles = 0;
     return mie_conv_tiles(&b, stream);
   }
   if (tc_eligible(a)) return tail_after_launch(launch_conv_tc(a, (cudaStream_t)stream), a->tail, true, stream);

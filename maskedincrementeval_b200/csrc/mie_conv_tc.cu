@@ -51,6 +51,10 @@ struct TcParams {
   mie_tail_job head;     // this convolution's own tile dilation, run by block 0 while the others wait (list == nullptr: none)
   int ksplit;            // halo kernel: CTAs of a cluster that share one work item, each reducing 1/ksplit of the
                          // input-channel chunks (1: no cluster)
+  int own;               // every block finds the active tiles among those it owns itself (`head` describes the test);
+                         // no global list is read
+  unsigned long long *own_words;   // own mode, tiles that several blocks finish: the word under construction ...
+  int *own_tickets;                // ... and how many epilogue warps have contributed to it (both zero between launches)
 };
 
 namespace {
@@ -473,17 +477,90 @@ struct TcMaps {
 
 // Zeroes the stale tiles of the output field.  Run by the epilogue warps (`tid` = index within them, `nthreads` = how
 // many they are) before their first accumulator arrives: the producer and the MMA issuer do not wait for it.
+__device__ __forceinline__ void tc_zero_tile(const TcParams &p, int t, int THo, int TWo, int tid, int nthreads) {
+  const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
+  for (int i = tid; i < 64 * p.cout; i += nthreads) {
+    const int px = i / p.cout, c = i - px * p.cout;
+    const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
+    if (oy < p.hout && ox < p.wout) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
+  }
+}
 __device__ __forceinline__ void tc_zero_stale(const TcParams &p, int ntiles_total, int THo, int TWo, int tid, int nthreads) {
   const int n_stale = p.stale ? min(p.counts[1], p.max_tiles) : 0;
   for (int s = blockIdx.x; s < n_stale; s += gridDim.x) {
     const int t = p.stale[s];
     if (t < 0 || t >= ntiles_total) { if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE); continue; }
-    const int tx = t % TWo, ty = (t / TWo) % THo, n = t / (TWo * THo);
-    for (int i = tid; i < 64 * p.cout; i += nthreads) {
-      const int px = i / p.cout, c = i - px * p.cout;
-      const int oy = ty * 8 + (px >> 3), ox = tx * 8 + (px & 7);
-      if (oy < p.hout && ox < p.wout) p.out[((int64_t)(n * p.hout + oy) * p.wout + ox) * p.out_ps + c] = 0.0f;
+    tc_zero_tile(p, t, THo, TWo, tid, nthreads);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// "Own tiles" mode (mie_conv_args.own_tiles): the convolution needs no tile list from a launch before it.  The output
+// tiles are dealt to the thread blocks in static pairs (2P, 2P+1), pair P to group P mod G, a group being the n_cblk
+// blocks (or clusters) that finish the column blocks of the same pixels.  After the grid dependency wait every block
+// tests the tiles of its group against the input words (dilate_flag: one round trip to L2, all loads in flight at once),
+// compacts the active ones in ascending order into shared memory and pairs them up as work items; all blocks of a group
+// arrive at the same list.  At full activity this spreads the work exactly as the global list does; at partial activity a
+// block's share is what is active among its own tiles.  Stale tiles are zeroed by the one block of the group that also
+// reads the previous word (column block 0, cluster rank 0).
+// Tile words: a tile that a single block finishes is cleared by that block before its epilogue ORs the sent pixels in, as
+// after a separate dilation.  A tile that several blocks finish cannot be cleared by one of them without racing the
+// others' ORs; there the epilogue warps OR into a scratch word and draw a ticket, and the warp that draws the last ticket
+// stores the finished word and leaves both scratch entries zero.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int OWN_MAX = 256;   // tiles one group can own; the host sends larger shares to the separate dilation launch
+
+struct OwnShared {
+  int list[OWN_MAX];           // active tiles from the front (ascending), stale tiles from the back
+  int n_active, n_stale;
+  uint8_t flags[OWN_MAX];
+};
+template <bool OWN> struct OwnSharedT : OwnShared {};
+template <> struct OwnSharedT<false> { int list[1]; int n_active, n_stale; };
+
+// Every thread of the block.  (Inlined: as a function of its own, called by all kernels, it made an E2Depth step 3 % slower.)
+__device__ __forceinline__ void own_scan(const uint64_t *in_bits, int Hin, int Win, int Hout, int Wout, int k, int stride, int pad,
+                                             const uint64_t *union_bits, uint64_t *out_bits /* null unless this block reads and
+                                             clears the previous words */, OwnShared &sh, int g, int G, int ntiles_total, bool single) {
+  const int SP = (ntiles_total + 1) >> 1;
+  const int n_own = g < SP ? 2 * ((SP - g + G - 1) / G) : 0;
+  for (int idx = threadIdx.x; idx < n_own; idx += blockDim.x) {
+    const int t = 2 * (g + (idx >> 1) * G) + (idx & 1);
+    sh.flags[idx] = t < ntiles_total ? dilate_flag(t, in_bits, Hin, Win, Hout, Wout, k, stride, pad, union_bits, out_bits, single)
+                                     : (uint8_t)0;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int na = 0, ns = 0;
+    const unsigned below = (1u << threadIdx.x) - 1u;
+    for (int base = 0; base < n_own; base += 32) {
+      const int idx = base + (int)threadIdx.x;
+      const int f = idx < n_own ? sh.flags[idx] : 0;
+      const unsigned ba = __ballot_sync(0xffffffffu, f == 1), bs = __ballot_sync(0xffffffffu, f == 2);
+      const int t = 2 * (g + (idx >> 1) * G) + (idx & 1);
+      if (f == 1) sh.list[na + __popc(ba & below)] = t;
+      if (f == 2) sh.list[OWN_MAX - 1 - (ns + __popc(bs & below))] = t;
+      na += __popc(ba);
+      ns += __popc(bs);
     }
+    if (threadIdx.x == 0) { sh.n_active = na; sh.n_stale = ns; }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void tc_zero_stale_own(const TcParams &p, const OwnShared &sh, int THo, int TWo, int tid, int nthreads) {
+  for (int s = 0; s < sh.n_stale; ++s) tc_zero_tile(p, sh.list[OWN_MAX - 1 - s], THo, TWo, tid, nthreads);
+}
+
+// One lane per (epilogue warp, tile): `v` = this warp's sent pixels, already shifted into 32-bit half `half32` of the
+// tile word; `total` = warps that contribute to a tile over all blocks.
+__device__ __forceinline__ void own_contribute(const TcParams &p, int t, int half32, unsigned v, int total) {
+  if (v) atomicOr(reinterpret_cast<unsigned *>(p.own_words + t) + half32, v);
+  __threadfence();
+  if (atomicAdd(p.own_tickets + t, 1) == total - 1) {
+    __threadfence();
+    reinterpret_cast<unsigned long long *>(p.out_bits32)[t] = atomicExch(p.own_words + t, 0ull);
+    p.own_tickets[t] = 0;
   }
 }
 
@@ -569,7 +646,9 @@ constexpr int HALO_THREADS = 384;
 constexpr int HALO_MAX_STAGES = 12;
 
 // KSPLIT: the cluster variant is a separate instantiation, so that the plain one carries neither its code nor its registers.
-template <bool KSPLIT>
+// OWN: the own-tiles mode, again a separate instantiation: the list-mode kernels are compiled exactly as if it did not exist
+// (with the mode as a run-time flag every layer ran 1.5 us longer in list mode, too).
+template <bool KSPLIT, bool OWN>
 __global__ void __launch_bounds__(HALO_THREADS, 1)
 conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -586,6 +665,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   // cannot tell "lap L done" from "lap L-2 done".)
   __shared__ unsigned long long b_full[2][HALO_MAX_STAGES], b_empty[HALO_MAX_STAGES], a_full[2], a_empty[2], acc_full[2], acc_empty[2];
   __shared__ unsigned long long part_full;   // K-split: every other CTA of the cluster has delivered its partial sums
+  __shared__ OwnSharedT<OWN> s_own;          // own-tiles mode: this block's tile list (a stub in the list-mode kernels)
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
 
@@ -630,17 +710,39 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
-  const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
-  if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
-  // the halo producer asks for the tile-list entries of its first item together with the device-side count
-  const int n_cblk = p.cout_pad / NB;
-  int pre0 = -1, pre1 = -1;
-  if (warp == 0) {
-    const int e = 2 * (bid / n_cblk);
-    if (e < p.max_tiles) pre0 = p.list[e];
-    if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+  constexpr bool own = OWN;
+  bool head_ok = true;
+  if constexpr (!OWN) {
+    head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
+    if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
   }
-  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
+  const int n_cblk = p.cout_pad / NB;
+  // work items of this block: item0, item0 + item_step, ... < n_items; item -> (tile pair, column block); tiles from `lst`
+  int item0 = bid, item_step = nblk, n_active;
+  const int32_t *lst = p.list;
+  const bool own_multi = own && n_cblk * (int)CS > 1;   // several blocks finish a tile: its word goes through the scratch
+  int pre0 = -1, pre1 = -1;
+  if constexpr (OWN) {
+    // own-tiles mode: this block's group tests its share of the tiles itself and works through a list in shared memory
+    const int G = nblk / n_cblk, g = bid / n_cblk;
+    own_scan(p.head.in_bits, p.head.Hin, p.head.Win, p.head.Hout, p.head.Wout, p.head.k, p.head.stride, p.head.pad, p.head.union_bits,
+             (bid % n_cblk == 0 && crank == 0u) ? p.head.out_bits : nullptr, s_own, g < G ? g : 0x3fffffff, G, ntiles_total, !own_multi);
+    lst = s_own.list;
+    n_active = s_own.n_active;
+    item0 = bid % n_cblk;
+    item_step = n_cblk;
+    if (n_active > 0) pre0 = lst[0];
+    if (n_active > 1) pre1 = lst[1];
+  } else {
+    // the producer asks for the tile-list entries of its first item together with the device-side count, before the
+    // count is known: one round trip to memory instead of two on the path count -> list -> first operand load
+    if (warp == 0) {
+      const int e = 2 * (bid / n_cblk);
+      if (e < p.max_tiles) pre0 = p.list[e];
+      if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+    }
+    n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
+  }
   if (tid == 0) TC_TRACE(2);
 
   if (tid == 0) TC_TRACE(3);
@@ -658,11 +760,11 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     // =========================== halo producer: lane = 2 * halo row + tile ===========================
     const int hy = lane >> 1, slot = lane & 1;
     unsigned uses = 0;
-    for (int item = bid; item < n_items && !p.withhold_loads; item += nblk) {
+    for (int item = item0; item < n_items && !p.withhold_loads; item += item_step) {
       const int pair = item / n_cblk;
-      const bool first = item == bid;
-      int t0 = first ? pre0 : p.list[2 * pair];
-      int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
+      const bool first = item == item0;
+      int t0 = first ? pre0 : lst[2 * pair];
+      int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : lst[2 * pair + 1]) : -1;
       // An entry outside the field is reported and skipped: the epilogue ignores it too, its half of the operand is
       // filled from tile 0 (any in-range load) or left out, and the partner tile of the pair is computed as usual.
       const bool bad0 = t0 < 0 || t0 >= ntiles_total, bad1 = (2 * pair + 1 < n_active) && (t1 < 0 || t1 >= ntiles_total);
@@ -673,7 +775,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       const int x0 = (t >= 0) ? (t % TWo) * 8 - p.pad : 0, y0 = (t >= 0) ? ((t / TWo) % THo) * 8 - p.pad : 0, n0 = (t >= 0) ? t / (TWo * THo) : 0;
       const unsigned tx_bytes = (t1 >= 0 ? 2u : 1u) * (unsigned)Hh * row_bytes;
       bool ok = true;
-      if (lane == 0 && item == bid) TC_TRACE_V(4, clock64() + (t0 & 0));
+      if (lane == 0 && item == item0) TC_TRACE_V(4, clock64() + (t0 & 0));
       for (int chunk = ch_lo; chunk < ch_hi; ++chunk, ++uses) {
         const unsigned buf = uses & 1u;
         if (lane == 0) {
@@ -693,7 +795,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     if (lane == 0) {
       unsigned s = 0, wait_parity = 0, stage_addr = b_base, gs = 0;   // gs: running stage number; issuer gs % NI takes it
       bool first_pass = true, ok = true;
-      for (int item = bid; item < n_items && ok && !s_abort && !p.withhold_loads; item += nblk) {
+      for (int item = item0; item < n_items && ok && !s_abort && !p.withhold_loads; item += item_step) {
         const int cbn = (item % n_cblk) * NB;
         for (int chunk = ch_lo; chunk < ch_hi && ok; ++chunk) {
           for (int tap = 0; tap < taps; tap += p.tps) {
@@ -726,7 +828,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       unsigned g = 0;                                             // running stage number (all items of this block)
       unsigned item_idx = 0, uses = 0;
       bool ok = true;
-      for (int item = bid; item < n_items && ok && !s_abort; item += nblk, ++item_idx) {
+      for (int item = item0; item < n_items && ok && !s_abort; item += item_step, ++item_idx) {
         const unsigned buf = item_idx & 1u;
         if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
         tc_fence_after();
@@ -782,12 +884,13 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
     const int c_hi = whole ? NB : c_lo + (NB >> 1);
     const int m = q * 32 + lane;                       // accumulator row
     const int slot = (m >> 3) & 1, pxi = ((m >> 4) << 3) | (m & 7);
-    if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
+    if constexpr (OWN) { if (bid % n_cblk == 0 && crank == 0u) tc_zero_stale_own(p, s_own, THo, TWo, tid - 128, HALO_THREADS - 128); }
+    else if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 128, HALO_THREADS - 128);
     unsigned item_idx = 0;
-    for (int item = bid; item < n_items; item += nblk, ++item_idx) {
+    for (int item = item0; item < n_items; item += item_step, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
-      int t = (li < n_active) ? p.list[li] : -1;
+      int t = (li < n_active) ? lst[li] : -1;
       if (t < 0 || t >= ntiles_total) t = -1;
       const unsigned buf = item_idx & 1u;
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
@@ -825,7 +928,8 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
       if ((lane == 0 || lane == 8) && t >= 0) {
         const unsigned sh = lane;                      // 0 for tile 0, 8 for tile 1
         const unsigned rows = ((bal >> sh) & 0xFFu) | (((bal >> (16 + sh)) & 0xFFu) << 8);
-        if (rows) atomicOr(p.out_bits32 + 2 * (size_t)t + (q >> 1), rows << ((q & 1) * 16));
+        if (own_multi) own_contribute(p, t, q >> 1, rows << ((q & 1) * 16), n_cblk * (int)CS * 8);
+        else if (rows) atomicOr(p.out_bits32 + 2 * (size_t)t + (q >> 1), rows << ((q & 1) * 16));
       }
     }
   }
@@ -839,7 +943,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
   // K-split: no CTA leaves while another one of its cluster may still store into its shared memory or arrive on its
   // barrier (every wait above is bounded, so every CTA gets here).  A cluster without an item exchanges nothing; all
   // of its CTAs see the same item count, so they skip the barrier together.
-  if (CS > 1u && bid < n_items) cluster_sync_all();
+  if (CS > 1u && item0 < n_items) cluster_sync_all();
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     if (warp == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
@@ -856,7 +960,7 @@ conv_tc_halo_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_in
 // COALESCED: the epilogue variant (and its 8 KB of staging buffers) is a compile-time choice, so that the wide-block
 // instantiation carries neither the code nor the shared memory of the other.
 // KSPLIT: cluster variant (see ksplit_finish), a separate instantiation of the direct-epilogue kernel.
-template <bool COALESCED, bool KSPLIT = false>
+template <bool COALESCED, bool KSPLIT, bool OWN>
 __global__ void __launch_bounds__(TC_THREADS, COALESCED ? 3 : 2)
 conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   static_assert(!(COALESCED && KSPLIT), "the cluster variant uses the direct epilogue");
@@ -867,6 +971,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   const int stage_bytes = A_STAGE_BYTES + NB * 128;
   __shared__ unsigned long long full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
   __shared__ unsigned long long part_full;   // K-split: every other block of the cluster has delivered its partial sums
+  __shared__ OwnSharedT<OWN> s_own;          // own-tiles mode: this block's tile list (a stub in the list-mode kernels)
   __shared__ float4 s_epi[COALESCED ? 4 : 1][COALESCED ? 128 : 1];   // staging buffers of the coalesced epilogue, one per epilogue warp
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort;
@@ -910,18 +1015,39 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   if (tid == 0) TC_TRACE(1);
   grid_dependency_wait();
   grid_dependency_trigger();
-  const bool head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
-  if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
-  // The producer asks for the tile-list entries of its first item together with the device-side count, before the count
-  // is known: one round trip to memory instead of two on the path count -> list -> first operand load.
-  const int n_cblk = p.cout_pad / NB;
-  int pre0 = -1, pre1 = -1;
-  if (warp == 0) {
-    const int e = 2 * (bid / n_cblk);
-    if (e < p.max_tiles) pre0 = p.list[e];
-    if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+  constexpr bool own = OWN;
+  bool head_ok = true;
+  if constexpr (!OWN) {
+    head_ok = run_head_job(p.head, p.spin_limit);   // block 0 makes the tile lists, the others wait for them
+    if (tid == (int)blockDim.x - 1) count_head_job_passed(p.head);   // a lane of the last epilogue warp: off the critical path
   }
-  const int n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
+  const int n_cblk = p.cout_pad / NB;
+  // work items of this block: item0, item0 + item_step, ... < n_items; item -> (tile pair, column block); tiles from `lst`
+  int item0 = bid, item_step = nblk, n_active;
+  const int32_t *lst = p.list;
+  const bool own_multi = own && n_cblk * (int)CS > 1;   // several blocks finish a tile: its word goes through the scratch
+  int pre0 = -1, pre1 = -1;
+  if constexpr (OWN) {
+    // own-tiles mode: this block's group tests its share of the tiles itself and works through a list in shared memory
+    const int G = nblk / n_cblk, g = bid / n_cblk;
+    own_scan(p.head.in_bits, p.head.Hin, p.head.Win, p.head.Hout, p.head.Wout, p.head.k, p.head.stride, p.head.pad, p.head.union_bits,
+             (bid % n_cblk == 0 && crank == 0u) ? p.head.out_bits : nullptr, s_own, g < G ? g : 0x3fffffff, G, ntiles_total, !own_multi);
+    lst = s_own.list;
+    n_active = s_own.n_active;
+    item0 = bid % n_cblk;
+    item_step = n_cblk;
+    if (n_active > 0) pre0 = lst[0];
+    if (n_active > 1) pre1 = lst[1];
+  } else {
+    // the producer asks for the tile-list entries of its first item together with the device-side count, before the
+    // count is known: one round trip to memory instead of two on the path count -> list -> first operand load
+    if (warp == 0) {
+      const int e = 2 * (bid / n_cblk);
+      if (e < p.max_tiles) pre0 = p.list[e];
+      if (e + 1 < p.max_tiles) pre1 = p.list[e + 1];
+    }
+    n_active = head_ok ? min(p.counts[0], p.max_tiles) : 0;
+  }
   if (tid == 0) TC_TRACE(2);
 
   if (tid == 0) TC_TRACE(3);
@@ -942,11 +1068,11 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned smem_base = smem_u32(smem);
       unsigned stage_addr = smem_base;
       const unsigned b_bytes = (unsigned)NB * 128u;
-      for (int item = bid; item < n_items && !s_abort && !p.withhold_loads; item += nblk) {
+      for (int item = item0; item < n_items && !s_abort && !p.withhold_loads; item += item_step) {
         const int pair = item / n_cblk, cb = item - pair * n_cblk;
-        const bool first = item == bid;
-        int t0 = first ? pre0 : p.list[2 * pair];
-        int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : p.list[2 * pair + 1]) : -1;
+        const bool first = item == item0;
+        int t0 = first ? pre0 : lst[2 * pair];
+        int t1 = (2 * pair + 1 < n_active) ? (first ? pre1 : lst[2 * pair + 1]) : -1;
         // an entry outside the field is reported and skipped (see the halo kernel's producer)
         const bool bad0 = t0 < 0 || t0 >= ntiles_total, bad1 = (2 * pair + 1 < n_active) && (t1 < 0 || t1 >= ntiles_total);
         if (bad0 || bad1) atomicOr(&p.counts[3], MIE_ERR_BAD_TILE);
@@ -956,7 +1082,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
         const int x1 = (t1 >= 0) ? (t1 % TWo) * 8 : 0, y1 = (t1 >= 0) ? ((t1 / TWo) % THo) * 8 : 0, n1 = (t1 >= 0) ? t1 / (TWo * THo) : 0;
         const unsigned tx_bytes = (t1 >= 0 ? A_STAGE_BYTES : A_STAGE_BYTES / 2) + b_bytes;
         const int cbn = cb * NB;
-        if (item == bid) { TC_TRACE_V(4, clock64() + (t0 & 0)); }
+        if (item == item0) { TC_TRACE_V(4, clock64() + (t0 & 0)); }
         bool ok = true;
         for (int chunk = ch_lo; chunk < ch_hi && ok; ++chunk) {
           const int c0 = chunk * 32;
@@ -978,7 +1104,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
             }
           }
         }
-        if (item == bid) TC_TRACE(6);
+        if (item == item0) TC_TRACE(6);
         if (!ok) break;
       }
     }
@@ -993,7 +1119,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       const unsigned desc_lo_flags = (unsigned)(make_smem_desc(0) & 0xFFFF0000ull);     // leading-offset field
       unsigned s = 0, parity = 0, stage_addr = smem_base, item_idx = 0;
       const int k_iters = (ch_hi - ch_lo) * taps;
-      for (int item = bid; item < n_items && !s_abort; item += nblk, ++item_idx) {
+      for (int item = item0; item < n_items && !s_abort; item += item_step, ++item_idx) {
         // the epilogue must have drained this accumulator (used two items ago)
         const unsigned buf = item_idx & 1u;
         if (item_idx >= 2 && !mbar_wait(&acc_empty[buf], ((item_idx >> 1) - 1) & 1u, &s_abort, p.spin_limit)) break;
@@ -1026,12 +1152,13 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
     const int q = warp & 3;           // tensor-memory lane group this warp may read: lanes 32q .. 32q+31
     const int m = q * 32 + lane;      // accumulator row = pixel of the pair
     const int slot = m >> 6, pxi = m & 63;
-    if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
+    if constexpr (OWN) { if (bid % n_cblk == 0 && crank == 0u) tc_zero_stale_own(p, s_own, THo, TWo, tid - 64, TC_THREADS - 64); }
+    else if (head_ok) tc_zero_stale(p, ntiles_total, THo, TWo, tid - 64, TC_THREADS - 64);
     unsigned item_idx = 0;
-    for (int item = bid; item < n_items; item += nblk, ++item_idx) {
+    for (int item = item0; item < n_items; item += item_step, ++item_idx) {
       const int pair = item / n_cblk, cb = item - pair * n_cblk;
       const int li = 2 * pair + slot;
-      int t = (li < n_active) ? p.list[li] : -1;
+      int t = (li < n_active) ? lst[li] : -1;
       if (t < 0 || t >= ntiles_total) t = -1;
       const unsigned buf = item_idx & 1u;
       const int tx = (t >= 0) ? t % TWo : 0, ty = (t >= 0) ? (t / TWo) % THo : 0, n = (t >= 0) ? t / (TWo * THo) : 0;
@@ -1062,9 +1189,10 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
       }
       if (tid == 64 && item_idx == 0) TC_TRACE(11);
       const unsigned sent_bits = __ballot_sync(0xffffffffu, sent);
-      if (lane == 0 && t >= 0 && sent_bits) {
-        unsigned int *wp = p.out_bits32 + 2 * (size_t)t + (q & 1);
-        atomicOr(wp, sent_bits);
+      if (lane == 0 && t >= 0) {
+        // two epilogue warps share a tile (32 pixels each)
+        if (own_multi) own_contribute(p, t, q & 1, sent_bits, n_cblk * (int)CS * 2);
+        else if (sent_bits) atomicOr(p.out_bits32 + 2 * (size_t)t + (q & 1), sent_bits);
       }
     }
   }
@@ -1073,7 +1201,7 @@ conv_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   __syncwarp();  // single-lane roles: the whole warp reaches the block-wide barrier together
   tc_fence_before();
   __syncthreads();
-  if (CS > 1u && bid < n_items) cluster_sync_all();   // K-split: no block leaves while another may still store into its shared memory
+  if (CS > 1u && item0 < n_items) cluster_sync_all();   // K-split: no block leaves while another may still store into its shared memory
   if (s_abort) {
     if (tid == 0) atomicOr(&p.counts[3], MIE_ERR_WAIT_EXPIRED);
     // give copies that may still be in flight time to land before shared memory is released
@@ -1155,6 +1283,7 @@ int g_opt_tc_thresholded = 1;               // MIE_OPT_TC_THRESHOLDED
 unsigned g_opt_spin_limit = SPIN_LIMIT;     // MIE_OPT_TC_SPIN_LIMIT
 int g_opt_withhold_loads = 0;               // MIE_OPT_TC_WITHHOLD_LOADS
 int g_opt_ksplit = 1;                       // MIE_OPT_TC_KSPLIT
+int g_opt_own_kernels = 7;                  // MIE_OPT_TC_OWN_KERNELS
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: the largest value set so far is
 // remembered per device, so a process that drives several GPUs raises the limit on each of them.
@@ -1288,7 +1417,29 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   p.ksplit = 1;
   int nb, ksplit;
   tc_block_shape(a, &nb, &ksplit);
-  const int64_t pairs = (a->max_tiles + 1) / 2;
+  // Own-tiles mode: the grid must consist of whole groups of n_cblk blocks (or clusters), and a group's share of the tiles
+  // must fit the list in its shared memory.  own_grid() returns the grid to launch; when the mode was asked for and
+  // cannot be had, it enqueues the separate dilation and the kernel reads the global lists as usual.
+  int own_status = MIE_OK;
+  const int own_mask = g_opt_own_kernels;   // kind: 1 per-tap, 2 per-tap as clusters, 4 halo, 8 halo as clusters
+  auto own_grid = [&](int64_t grid, int kind) -> int64_t {
+    if (!a->own_tiles) return grid;
+    const int n_cblk = a->cout_pad / nb;
+    const int64_t groups = grid / n_cblk, sp = ((int64_t)a->max_tiles + 1) / 2;
+    const int64_t ntiles = (int64_t)a->n * divup(a->hout, 8) * divup(a->wout, 8);
+    if ((own_mask & kind) && groups >= 1 && 2 * ((sp + groups - 1) / groups) <= OWN_MAX && a->max_tiles == ntiles) {
+      p.own = 1;
+      p.head = *a->head;
+      p.own_words = static_cast<unsigned long long *>(a->own_scratch);
+      p.own_tickets = reinterpret_cast<int *>(static_cast<char *>(a->own_scratch) + 8 * ntiles);
+      return groups * n_cblk;
+    }
+    const mie_tail_job *h = a->head;
+    own_status = mie_tiles_dilate(h->in_bits, h->N, h->Hin, h->Win, h->Hout, h->Wout, h->k, h->stride, h->pad, h->union_bits,
+                                  h->out_bits, h->list, h->stale, h->counts, h->flags, st);
+    p.head = mie_tail_job{};
+    return grid;
+  };
   p.nb = nb;
   int acc_cols = 32;
   while (acc_cols < nb) acc_cols <<= 1;
@@ -1335,17 +1486,32 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
         const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
         int grid = max_items < cap ? (int)max_items : (int)cap;
         if (grid < 1) grid = 1;
+        grid = (int)own_grid(ksplit > 1 ? max_items : grid, ksplit > 1 ? 8 : 4);   // clusters: one per possible item, as below
+        if (own_status != MIE_OK) return own_status;
         static int halo_smem_set[MAX_DEVICES] = {0};
         if (ksplit > 1) {
           static int halo_ks_smem_set[MAX_DEVICES] = {0};
-          { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<true>, halo_ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+          static int halo_ks_own_smem_set[MAX_DEVICES] = {0};
           p.ksplit = ksplit;
-          launch_chained_cluster(conv_tc_halo_kernel<true>, dim3((unsigned)(max_items * ksplit)), dim3(HALO_THREADS), smem, st,
+          if (p.own) {
+            { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<true, true>, halo_ks_own_smem_set, smem); if (s_ != MIE_OK) return s_; }
+            launch_chained_cluster(conv_tc_halo_kernel<true, true>, dim3((unsigned)(max_items * ksplit)), dim3(HALO_THREADS), smem, st,
+                                   (unsigned)ksplit, p, map_in, map_w);
+            return check_launch();
+          }
+          { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<true, false>, halo_ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+          launch_chained_cluster(conv_tc_halo_kernel<true, false>, dim3((unsigned)(max_items * ksplit)), dim3(HALO_THREADS), smem, st,
                                  (unsigned)ksplit, p, map_in, map_w);
           return check_launch();
         }
-        { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<false>, halo_smem_set, smem); if (s_ != MIE_OK) return s_; }
-        launch_chained(conv_tc_halo_kernel<false>, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
+        if (p.own) {
+          static int halo_own_smem_set[MAX_DEVICES] = {0};
+          { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<false, true>, halo_own_smem_set, smem); if (s_ != MIE_OK) return s_; }
+          launch_chained(conv_tc_halo_kernel<false, true>, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
+          return check_launch();
+        }
+        { const int s_ = ensure_dynamic_smem(conv_tc_halo_kernel<false, false>, halo_smem_set, smem); if (s_ != MIE_OK) return s_; }
+        launch_chained(conv_tc_halo_kernel<false, false>, dim3(grid), dim3(HALO_THREADS), smem, st, p, map_in, map_w);
         return check_launch();
       }
       // a tensor map the driver refuses (unusual strides): the per-tap kernel below takes the layer
@@ -1413,22 +1579,38 @@ int launch_conv_tc(const mie_conv_args *a, cudaStream_t st) {
   const int64_t cap = (int64_t)MIE_SM_COUNT * blocks_per_sm;
   int grid = max_items < cap ? (int)max_items : (int)cap;
   if (grid < 1) grid = 1;
+  grid = (int)own_grid(ksplit > 1 ? max_items : grid, ksplit > 1 ? 2 : 1);
+  if (own_status != MIE_OK) return own_status;
   if (ksplit > 1) {
     static int ks_smem_set[MAX_DEVICES] = {0};
-    { const int s_ = ensure_dynamic_smem(conv_tc_kernel<false, true>, ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+    static int ks_own_smem_set[MAX_DEVICES] = {0};
     p.ksplit = ksplit;
-    launch_chained_cluster(conv_tc_kernel<false, true>, dim3((unsigned)(max_items * ksplit)), dim3(TC_THREADS), smem, st,
+    if (p.own) {
+      { const int s_ = ensure_dynamic_smem(conv_tc_kernel<false, true, true>, ks_own_smem_set, smem); if (s_ != MIE_OK) return s_; }
+      launch_chained_cluster(conv_tc_kernel<false, true, true>, dim3((unsigned)(max_items * ksplit)), dim3(TC_THREADS), smem, st,
+                             (unsigned)ksplit, p, maps);
+      return check_launch();
+    }
+    { const int s_ = ensure_dynamic_smem(conv_tc_kernel<false, true, false>, ks_smem_set, smem); if (s_ != MIE_OK) return s_; }
+    launch_chained_cluster(conv_tc_kernel<false, true, false>, dim3((unsigned)(max_items * ksplit)), dim3(TC_THREADS), smem, st,
                            (unsigned)ksplit, p, maps);
     return check_launch();
   }
-  static int smem_set[2][MAX_DEVICES] = {{0}};
+  static int smem_set[4][MAX_DEVICES] = {{0}};
   {
-    const int s_ = coalesced ? ensure_dynamic_smem(conv_tc_kernel<true, false>, smem_set[1], smem)
-                             : ensure_dynamic_smem(conv_tc_kernel<false, false>, smem_set[0], smem);
+    const int s_ = coalesced ? (p.own ? ensure_dynamic_smem(conv_tc_kernel<true, false, true>, smem_set[3], smem)
+                                      : ensure_dynamic_smem(conv_tc_kernel<true, false, false>, smem_set[1], smem))
+                             : (p.own ? ensure_dynamic_smem(conv_tc_kernel<false, false, true>, smem_set[2], smem)
+                                      : ensure_dynamic_smem(conv_tc_kernel<false, false, false>, smem_set[0], smem));
     if (s_ != MIE_OK) return s_;
   }
-  if (coalesced) launch_chained(conv_tc_kernel<true, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
-  else launch_chained(conv_tc_kernel<false, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  if (coalesced) {
+    if (p.own) launch_chained(conv_tc_kernel<true, false, true>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+    else launch_chained(conv_tc_kernel<true, false, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  } else {
+    if (p.own) launch_chained(conv_tc_kernel<false, false, true>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+    else launch_chained(conv_tc_kernel<false, false, false>, dim3(grid), dim3(TC_THREADS), smem, st, p, maps);
+  }
   return check_launch();
 }
 
@@ -1476,6 +1658,10 @@ extern "C" int mie_set_option(int option, int value) {
       return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: g_opt_withhold_loads = value ? 1 : 0; return MIE_OK;
     case MIE_OPT_TC_KSPLIT: g_opt_ksplit = value ? 1 : 0; return MIE_OK;
+    case MIE_OPT_TC_OWN_KERNELS:
+      if (value < 0 || value > 15) return MIE_EINVAL;
+      g_opt_own_kernels = value;
+      return MIE_OK;
     case MIE_OPT_LAUNCH_COUNT: __atomic_store_n(&g_launch_count, (unsigned long long)(value < 0 ? 0 : value), __ATOMIC_RELAXED); return MIE_OK;
     default: return MIE_EINVAL;
   }
@@ -1488,6 +1674,7 @@ extern "C" int mie_get_option(int option, int *value) {
     case MIE_OPT_TC_SPIN_LIMIT: *value = (int)g_opt_spin_limit; return MIE_OK;
     case MIE_OPT_TC_WITHHOLD_LOADS: *value = g_opt_withhold_loads; return MIE_OK;
     case MIE_OPT_TC_KSPLIT: *value = g_opt_ksplit; return MIE_OK;
+    case MIE_OPT_TC_OWN_KERNELS: *value = g_opt_own_kernels; return MIE_OK;
     case MIE_OPT_LAUNCH_COUNT: *value = (int)(__atomic_load_n(&g_launch_count, __ATOMIC_RELAXED) & 0x7FFFFFFFull); return MIE_OK;
     default: return MIE_EINVAL;
   }

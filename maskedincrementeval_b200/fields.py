@@ -53,6 +53,12 @@ class IncrConfig:
                      convolution's tile dilation runs inside the convolution kernel itself -- its first thread block
                      makes the lists while the others wait -- instead of as a launch of its own (28 launches per E2Depth
                      step instead of 37, measured slower: the hand-over costs more than the launch it saves)
+    own_tiles        True (default): in a lossless run (threshold 0, no quantiser) a tensor-core convolution needs no tile
+                     list from a launch before it -- its thread blocks share out the output tiles statically and each
+                     tests its own against the input words (one launch per convolution instead of two, no hand-over
+                     between blocks; E2Depth step 37 -> 23 launches).  False, and in thresholded runs: the separate
+                     dilation launch, whose global list spreads sparse activity evenly over the blocks.  "always": in
+                     thresholded runs too
     fuse_accumulate  True (default): IncrementalRunner lets a 1x1 prediction head add its output into the accumulated
                      prediction inside its own kernel instead of launching mie_accumulate afterwards
     tc_thresholded   True (default): thresholded convolutions (threshold > 0, with or without carry) use the tensor
@@ -66,6 +72,7 @@ class IncrConfig:
     tc_thresholded: bool = True
     tail_dilation: bool = False
     head_dilation: int = 0
+    own_tiles: object = True     # True, False or "always"
     fuse_accumulate: bool = True
     kfenced_step: Optional[float] = None
     refresh: str = "native"
@@ -305,6 +312,7 @@ def reset_delta_state(model) -> None:
             plan.out.zero_()
             plan.out_bits.zero_()
             plan.counts[:3].zero_()
+            plan.own_scratch.zero_()
 
 
 class Scratch:

@@ -250,6 +250,8 @@ class _ConvPlan:
         self.stale = torch.zeros(nt, dtype=torch.int32, device=device)
         self.counts = torch.zeros(4, dtype=torch.int32, device=device)
         self.flags = torch.zeros(nt, dtype=torch.uint8, device=device)
+        # own-tiles mode: per tile a 64-bit word under construction, then a 32-bit ticket (zero between launches)
+        self.own_scratch = torch.zeros(3 * nt, dtype=torch.int32, device=device)
         self.geometry = (n, hin, win)
         a = nat.ConvArgs()
         a.hin, a.win, a.n, a.hout, a.wout = hin, win, n, self.hout, self.wout
@@ -433,11 +435,18 @@ class nnConvIncr(nn.Conv2d):
             fl.withdraw_tail(job)
             job = plan.tail = fl.TailJob(plan, m.bits, union, n, hin, win, self._k, self._s, self._p)
         if plan.needs_clear:
-            plan.out.zero_(), plan.out_bits.zero_(), plan.counts[:3].zero_()
+            plan.out.zero_(), plan.out_bits.zero_(), plan.counts[:3].zero_(), plan.own_scratch.zero_()
             plan.needs_clear = False
-        a.head = None
+        a.head, a.own_tiles, a.own_scratch = None, 0, None
         if config.head_dilation and plan.ntiles <= min(config.head_dilation, nat.TAIL_MAX_TILES) and not config.tail_dilation:
             a.head = C.addressof(job.c)     # the convolution kernel's first block makes the lists itself
+        elif (config.own_tiles and not refresh and not config.tail_dilation and not config.head_dilation
+              and (config.own_tiles == "always" or (config.threshold == 0.0 and not config.kfenced_step))):
+            # Every thread block of the convolution kernel finds its own tiles (the library falls back to the separate
+            # launch for the FP32 kernels and for fields too large for that).  Lossless runs only: their fields are
+            # densely active after the first layers, where the static deal of tiles to blocks loses nothing; a
+            # thresholded run keeps the global list, which spreads few active tiles evenly (measured +3 % otherwise).
+            a.head, a.own_tiles, a.own_scratch = C.addressof(job.c), 1, plan.own_scratch.data_ptr()
         elif not fl.tail_carried(job):
             nat.check(nat.lib.mie_tiles_dilate(m.bits.data_ptr(), n, hin, win, plan.hout, plan.wout, self._k, self._s,
                                                self._p, union.data_ptr() if union is not None else None,
@@ -503,6 +512,13 @@ class nnConvIncr(nn.Conv2d):
         raised since it was last cleared (see ``check_device_errors``)."""
         return [(p.geometry, p.counts) for p in self._plans.values()]
 
+    def clear_errors(self):
+        """Clear the error word of every plan, and the tile-word scratch of the own-tiles mode, which an aborted
+        launch may have left half-filled."""
+        for p in self._plans.values():
+            p.counts[3] = 0
+            p.own_scratch.zero_()
+
     def forward_refresh_reservoirs(self, x):
         # The reference also resets its (never applied) quantiser here, which costs a norm and a
         # zero tensor of the input's size per convolution (``:193``); nothing reads either.  When the quantiser is
@@ -526,8 +542,9 @@ def check_device_errors(model: nn.Module, clear: bool = True) -> None:
     if not bad:
         return
     if clear:
-        for _, _, cnt in named:
-            cnt[3] = 0
+        for m in model.modules():
+            if isinstance(m, nnConvIncr):
+                m.clear_errors()
     raise nat.MieError("; ".join(f"{name or '<conv>'} (batch {g[0]}, input {g[1]}x{g[2]}): {nat.describe_error_word(w)}"
                                  for name, g, w in bad))
 

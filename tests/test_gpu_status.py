@@ -27,7 +27,8 @@ def dev():
 def restore_config():
     from maskedincrementeval_b200 import _native as nat
     from maskedincrementeval_b200 import fields as fl
-    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tc_thresholded", "compat")}
+    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tc_thresholded", "compat", "own_tiles")}
+    fl.config.own_tiles = False     # the hand-made tile lists of these tests are only read in list mode
     yield
     for k, v in saved.items():
         setattr(fl.config, k, v)
@@ -107,8 +108,9 @@ def test_bad_tile_entry_is_skipped_and_reported(dev, cfg):
         check_device_errors(layer)                                              # and quiet afterwards
 
 
-@pytest.mark.parametrize("cfg", [(32, 32, 3, 1), (64, 64, 3, 1), (32, 64, 5, 2)])
-def test_bounded_wait_expires_cleanly(dev, cfg):
+@pytest.mark.parametrize("own", [False, True], ids=["list", "own-tiles"])
+@pytest.mark.parametrize("cfg", [(32, 32, 3, 1), (64, 64, 3, 1), (32, 64, 5, 2), (256, 256, 3, 1)])
+def test_bounded_wait_expires_cleanly(dev, cfg, own):
     """With the loads withheld and a limit of 300 polls every tensor-core block with work gives up its first wait:
     the kernel returns, counts[3] carries MIE_ERR_WAIT_EXPIRED, the tensor memory is free again (the next launch of the
     same kernel runs and is correct), and the runner-level check raises."""
@@ -116,7 +118,7 @@ def test_bounded_wait_expires_cleanly(dev, cfg):
     from maskedincrementeval_b200 import fields as fl
     from maskedincrementeval_b200.incr_modules.mask_incr_modules import check_device_errors
     cin, cout, k, s = cfg
-    fl.config.tensor_cores = "auto"
+    fl.config.tensor_cores, fl.config.own_tiles = "auto", own
     n, h, w = 1, 40, 56
     layer = _layer(dev, cin, cout, k, s, "relu")
     wt, b = layer.conv2d.weight.detach().cpu(), layer.conv2d.bias.detach().cpu()

@@ -27,7 +27,9 @@ def dev():
 @pytest.fixture(autouse=True)
 def restore_config():
     from maskedincrementeval_b200 import fields as fl
-    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tail_dilation", "head_dilation", "compat")}
+    saved = {k: getattr(fl.config, k) for k in ("threshold", "carry", "tensor_cores", "tail_dilation", "head_dilation", "compat",
+                                                "own_tiles")}
+    fl.config.own_tiles = False     # these tests compare with the separate dilation launch
     yield
     for k, v in saved.items():
         setattr(fl.config, k, v)
