@@ -847,7 +847,7 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_vec_kernel(
 // loaded at all) and the 64 outputs are blended from shared memory.  Same interpolation arithmetic (up_src).
 constexpr int UP_WIN = 6;
 
-__global__ void __launch_bounds__(PW_THREADS) upsample2x_tile_kernel(
+__global__ void __launch_bounds__(PW_THREADS, 8) upsample2x_tile_kernel(
     const float *__restrict__ a, int64_t a_ps, const uint64_t *__restrict__ a_bits, const float *__restrict__ b,
     int64_t b_ps, const uint64_t *__restrict__ b_bits, float *__restrict__ out, int64_t out_ps, uint64_t *out_bits, int N,
     int C, int H, int W, int mode, const mie_tail_job tail) {
@@ -905,6 +905,63 @@ __global__ void __launch_bounds__(PW_THREADS) upsample2x_tile_kernel(
       continue;
     }
     const int c_lo = cb * CB, q4 = (min(C, c_lo + CB) - c_lo) >> 2;
+    if (q4 == CB / 4) {
+      // ---- whole 32-channel blocks: every index is a shift or a per-thread constant.  (The general loops below spend
+      // more than 200 instructions per 16-byte store on divisions, up_src and 64-bit pixel indices, and the kernel was
+      // bound by instruction issue at a third of the memory bandwidth.)
+      const int q = tid & 7;
+#pragma unroll
+      for (int it = 0; it < 3; ++it) {
+        const int sp = (tid >> 3) + 16 * it;
+        if (sp < UP_WIN * UP_WIN) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if ((on_mask >> sp) & 1ull) {
+            const int sy = min(max(r0 + sp / UP_WIN, 0), H - 1), sx = min(max(c0 + sp % UP_WIN, 0), W - 1);
+            const int64_t pix = (int64_t)(g.n * H + sy) * W + sx;
+            if ((mask_a >> sp) & 1ull) v = ld4(a + pix * a_ps + c_lo + q * 4);
+            if ((mask_b >> sp) & 1ull) v = f4add(v, ld4(b + pix * b_ps + c_lo + q * 4));
+          }
+          s_src[sp][q] = v;
+        }
+      }
+      __syncthreads();
+      // Output pixel (row pr, column pc) of the tile.  Window entries are loaded from clamped coordinates, so a clamped
+      // neighbour is a duplicate of the pixel itself: the even output coordinate 2i always blends window entries
+      // (i', i'+1) with weight 0.75 on the second (0 at the field's first row / column, where up_src gives both sources
+      // as pixel 0), the odd one (i'+1, i'+2) with weight 0.25 -- up_src's sources and weights without its branches.
+      const int pc = (tid >> 3) & 7, prb = tid >> 6;
+      const int ox = g.tx * 8 + pc;
+      const bool nearest = mode == MIE_UP_NEAREST;
+      const int kx = nearest ? (pc >> 1) + 1 : (pc >> 1) + (pc & 1);
+      const float wx = (pc & 1) ? 0.25f : (ox == 0 ? 0.0f : 0.75f), ax = 1.0f - wx;
+      if (ox < Wo) {
+        float *op = out + ((int64_t)(g.n * Ho + g.ty * 8 + prb) * Wo + ox) * out_ps + c_lo + q * 4;
+        const int64_t row_step = 2 * (int64_t)Wo * out_ps;
+#pragma unroll
+        for (int it = 0; it < 4; ++it, op += row_step) {
+          const int pr = prb + 2 * it, oy = g.ty * 8 + pr;
+          if (oy >= Ho) break;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if ((wout >> (pr * 8 + pc)) & 1ull) {
+            if (nearest) {
+              v = s_src[((pr >> 1) + 1) * UP_WIN + kx][q];
+            } else {
+              const int ky = (pr >> 1) + (pr & 1);
+              const float wy = (pr & 1) ? 0.25f : (oy == 0 ? 0.0f : 0.75f), ay = 1.0f - wy;
+              const float4 v00 = s_src[ky * UP_WIN + kx][q], v01 = s_src[ky * UP_WIN + kx + 1][q];
+              const float4 v10 = s_src[(ky + 1) * UP_WIN + kx][q], v11 = s_src[(ky + 1) * UP_WIN + kx + 1][q];
+              v.x = ay * (ax * v00.x + wx * v01.x) + wy * (ax * v10.x + wx * v11.x);
+              v.y = ay * (ax * v00.y + wx * v01.y) + wy * (ax * v10.y + wx * v11.y);
+              v.z = ay * (ax * v00.z + wx * v01.z) + wy * (ax * v10.z + wx * v11.z);
+              v.w = ay * (ax * v00.w + wx * v01.w) + wy * (ax * v10.w + wx * v11.w);
+            }
+          }
+          st4(op, v);
+        }
+      }
+      if (cb == 0 && tid == 0) out_bits[t] = wout;
+      continue;
+    }
     // stage the window: one 16-byte load per (source pixel, channel quad), all independent
     for (int i = tid; i < UP_WIN * UP_WIN * q4; i += blockDim.x) {
       const int sp = i / q4, q = i - sp * q4;
