@@ -247,6 +247,7 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
                 res = layer.activation.in_res.reservoir
                 a.act, a.thr, a.res, a.res_ps = nat.ACT_RELU, 0.0, res.data_ptr(), 32
                 a.emitted, a.emitted_ps, a.addend, a.addend_ps = None, 0, None, 0
+                a.head, a.own_tiles, a.own_scratch, a.tail = None, 0, None, None   # the tile lists come from the call above
                 flush()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(st)
@@ -294,6 +295,7 @@ def roofline_conv3x3(dev, peak_gbs, peak_kind, repeats=3, args_tc=True):
             res = li.activation.in_res.reservoir
             a.act, a.thr, a.res, a.res_ps = nat.ACT_RELU, 0.0, res.data_ptr(), 32
             a.emitted, a.emitted_ps, a.addend, a.addend_ps = None, 0, None, 0
+            a.head, a.own_tiles, a.own_scratch, a.tail = None, 0, None, None       # the tile lists come from the call above
             states.append((li, d, m, plan, a, wbuf, wtc))
         torch.cuda.synchronize(dev)
         counts = [s_[3].counts.cpu().tolist() for s_ in states]
