@@ -191,3 +191,30 @@ def test_default_leaves_the_clustered_halo_kernel_on_the_list(dev):
     with pytest.raises(Exception):
         nat.set_option(nat.OPT_TC_OWN_KERNELS, 16)
     assert nat.get_option(nat.OPT_TC_OWN_KERNELS) == 7
+
+
+def test_random_shapes_equal_the_separate_dilation(dev):
+    """Forty seeded random layers (kernel size, stride, widths, field size, batch, threshold, activation): whatever kernel
+    the library picks for each, own-tiles mode gives the bits of the list path at every step."""
+    import random
+    rnd = random.Random(11)
+    checked = 0
+    for it in range(40):
+        k = rnd.choice([3, 3, 5, 7, 1])
+        s = rnd.choice([1, 1, 2])
+        cin = rnd.choice([32, 48, 64, 96, 128, 256, 320])
+        cout = rnd.choice([16, 32, 48, 64, 96, 128, 256, 512])
+        h = rnd.choice([16, 24, 33, 34, 40, 66, 70, 96])
+        w = rnd.choice([16, 22, 44, 48, 56, 88, 90, 120])
+        if s == 2:
+            h, w = h + (h & 1), w + (w & 1)
+        n = rnd.choice([1, 1, 2, 3])
+        thr = rnd.choice([0.0, 0.0, 0.0, 0.02])
+        case = ("auto", cin, cout, k, s, n, h, w, thr, False, 0, "")
+        own, _, layer = _run(dev, case, True)
+        sep, _, _ = _run(dev, case, False)
+        checked += bool(layer.conv2d.last_used_tensor_cores)
+        for step, ((ya, ba, ra, sa), (yb, bb, rb, _)) in enumerate(zip(own, sep)):
+            assert torch.equal(ba, bb) and torch.equal(ya, yb) and torch.equal(ra, rb), (case, step)
+            assert int(sa.abs().max()) == 0, (case, step)
+    assert checked >= 25      # most of them run on the tensor cores, where the mode exists
